@@ -1,0 +1,105 @@
+/* lg_b200.h -- C ABI of liblg_b200.so, the sm_100a backend of the little-gemma speculative-decode
+ * step.  Plain C types only.  Struct layouts are in lg_abi.h.
+ *
+ * Part 1 is the backend seam of the reference: the very symbols its host C (run.c, mtp.c)
+ * resolves at link time against model-cuda-i8.cu; each declaration cites the reference
+ * interface it replaces.  Part 2 adds entry points the reference does not have.
+ */
+#ifndef LG_B200_H
+#define LG_B200_H
+
+#include "lg_abi.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ===== Part 1: the reference's backend seam ============================================== */
+
+/* 0: cache rows live on the device, so the host draft in mtp.c must call the *_device hooks.
+ * Replaces: include/model.h:190 (set in src/cuda/model-cuda.cuh). */
+extern const int model_kv_host;
+
+/* Allocate the f16 K/V cache on the device: global layers max_seq rows, sliding-window layers
+ * a ring of window + spare rows, row(p) = p % seq; borrowing layers get NULL.  0 / -1.
+ * Replaces: include/model.h:79 (src/cuda/model-cuda.cuh:999-1051). */
+int  kvcache_init(struct kvcache *kv, const struct model *m, int max_seq);
+/* Replaces: include/model.h:80 (src/cuda/model-cuda.cuh:1052-1060). */
+void kvcache_free(struct kvcache *kv);
+/* Save / restore the first min(n, seq) rows of every owning layer (system-prefix reuse).
+ * Replaces: include/model.h:91-92 (src/cuda/model-cuda.cuh:1065-1088). */
+void kvcache_save_prefix(struct kvcache *kv, int n);
+void kvcache_restore_prefix(struct kvcache *kv, int n);
+
+/* One token at position pos; writes n_vocab soft-capped logits to the caller's host buffer
+ * (logits == NULL: cache writes only).  Replaces: include/model.h:98 (model-cuda.cuh:1318-1354). */
+void model_forward(struct model *m, struct kvcache *kv, int token, int pos, float *logits);
+/* Same forward, returns the greedy next token (argmax on the device, lowest index on ties);
+ * with model_pick set, calls it on the logits row instead.
+ * Replaces: include/model.h:103 (model-cuda.cuh:1356-1367). */
+int  model_forward_next(struct model *m, struct kvcache *kv, int token, int pos);
+/* Fill the cache for tokens[0..n) at pos0.., no head.
+ * Replaces: include/model.h:123 (src/cuda/prefill-kernel.cuh:631-675). */
+void model_prefill(struct model *m, struct kvcache *kv, const int *tokens, int n, int pos0);
+/* Media-row prefill forms: outside the speculative-decode path; _embd exits with a message,
+ * _mixed accepts all-text spans.  Replaces: include/model.h:133,143 (prefill-kernel.cuh:678-810). */
+void model_prefill_embd(struct model *m, struct kvcache *kv, const float *rows, int n, int pos0);
+void model_prefill_mixed(struct model *m, struct kvcache *kv, const float *rows, const int *ids, int n, int pos0);
+/* No-op here (buffers are sized at load).  Replaces: include/model.h:149. */
+void model_prefill_reserve(void);
+
+/* Verify LG_MTP_N tokens (toks[0] chosen, toks[1..] drafts) at pos.. in ONE weight pass:
+ * out[j] = greedy successor of toks[j]; returns adv = 1 + the run of out[j-1] == toks[j];
+ * leaves the draft head's h_prev at row adv-1.  LG_MTP_N is compile time and must equal the
+ * caller's.  Replaces: include/model.h:186 (src/cuda/mtp-kernel.cuh:82-120). */
+int  model_forward_spec(struct model *m, struct kvcache *kv, const int *toks, int pos, int *out);
+
+/* Draft the successor of `token` (the token chosen for `pos`) with the head resident on the
+ * device; -1 = drafting unavailable.  Replaces: src/mtp-internal.h:33-34 (mtp-kernel.cuh:329-370). */
+int  mtp_draft_device(struct mtp *t, const struct model *m, const struct kvcache *kv, int token, int pos);
+/* Chained draft on the head's own hidden through the post-projection; -1 = no chaining.
+ * Replaces: src/mtp-internal.h:35-36 (mtp-kernel.cuh:378-402). */
+int  mtp_draft_chain_device(struct mtp *t, const struct model *m, const struct kvcache *kv, int token, int pos);
+/* Replaces: src/mtp-internal.h:37 (mtp-kernel.cuh:404-421). */
+void mtp_free_device(struct mtp *t);
+
+/* ===== Part 2: additions ================================================================= */
+
+/* model_forward_spec with a run-time width n in [1, 8] (n = 1 is plain decode). */
+int  lg_forward_spec_n(struct model *m, struct kvcache *kv, int n, const int *toks, int pos, int *out);
+
+/* Device-resident rounds: [drafts -> verify of width n -> greedy accept -> advance] repeated
+ * n_rounds times with NO host synchronisation in between.  mode 0: no drafts (n must be 1),
+ * 1: drafts from head t, 2: drafts from the table given to lg_set_replay (head t, if given,
+ * still runs and is overridden).  begin sets the chosen token / position / emitted count,
+ * enqueue only launches, collect synchronises once and returns the emitted tokens [from..)
+ * and stats = {pos, n_emitted, n_draft, n_accept}. */
+int  lg_set_replay(struct model *m, const int *replay, int n);
+int  lg_rounds_begin(struct model *m, int first_token, int pos, int n_emitted);
+int  lg_rounds_enqueue(struct model *m, struct kvcache *kv, struct mtp *t, int n, int mode, int n_rounds);
+int  lg_rounds_collect(struct model *m, int *tokens, int from, int cap, int *stats);
+
+/* Introspection for tests and the benchmark. */
+long long lg_weight_bytes(struct model *m);          /* file bytes of all matrices uploaded so far */
+long long lg_round_launches(struct model *m);        /* kernels in one captured round */
+int   lg_last_hidden(struct model *m, float *out);   /* h_prev (n_embd floats) */
+int   lg_kv_row(struct model *m, struct kvcache *kv, int layer, int pos, float *k, float *v);
+void *lg_stream(struct model *m);                    /* the cudaStream_t all work is issued on */
+void  lg_engine_release(void);                       /* free all device state of the loaded model */
+
+/* Kernel-level entry points (host buffers in, host buffers out) used by the parity tests.
+ * Each returns 0 or a negative error. */
+/* Decode n_rows rows of k elements of ggml type (2 = q4_0, 12 = q4_K) on the device. */
+int  lg_dequant_host(int type, const void *blocks, int n_rows, int k, float *out);
+/* y[tok][row] = W x[tok] for tok < M <= 8 through the tile-major repack, the 16-bit activation
+ * panel and the tensor-core kernel; W is m rows of file-format blocks. */
+int  lg_gemv_host(int type, const void *blocks, int m, int k, const float *x, int M, int kslices, float *y);
+/* Split-KV flash-decode of M query rows over an f16 cache given as f32 host arrays
+ * (rounded to f16 on upload): q [M][H][hd], k/v [seq][Hkv*hd], positions pos..pos+M-1. */
+int  lg_flash_decode_host(const float *q, const float *k, const float *v, int M, int H, int Hkv, int hd,
+                          int seq, int window, int pos, float *out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LG_B200_H */

@@ -1,0 +1,235 @@
+"""ctypes binding of liblg_b200.so -- the sm_100a backend of the little-gemma speculative-decode
+step.  The library is the product; this module only loads it and exposes a `Session` whose
+methods map one-to-one onto the C model API (model_forward, model_forward_next, model_prefill,
+model_forward_spec, mtp_draft, ...).
+
+There is no CPU path: importing works without a GPU (so symbols can be inspected), but every
+compute call needs the CUDA library and a B200.  A missing library raises immediately.
+
+The directory name has a hyphen: import it with
+    importlib.import_module("little-gemma_b200")
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "liblg_b200.so")
+
+_i32p = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")
+_f32p = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
+
+# every symbol include/lg_b200.h declares
+ABI_SYMBOLS = [
+    "model_kv_host", "kvcache_init", "kvcache_free", "kvcache_save_prefix", "kvcache_restore_prefix",
+    "model_forward", "model_forward_next", "model_prefill", "model_prefill_embd", "model_prefill_mixed",
+    "model_prefill_reserve", "model_forward_spec", "mtp_draft_device", "mtp_draft_chain_device", "mtp_free_device",
+    "lg_forward_spec_n", "lg_set_replay", "lg_rounds_begin", "lg_rounds_enqueue", "lg_rounds_collect",
+    "lg_weight_bytes", "lg_round_launches", "lg_last_hidden", "lg_kv_row", "lg_stream", "lg_engine_release",
+    "lg_dequant_host", "lg_gemv_host", "lg_flash_decode_host",
+]
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load liblg_b200.so (built by build.py); raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(f"{LIB_PATH} is missing: run `python little-gemma_b200/build.py` (needs nvcc). "
+                          "There is no fallback path.")
+    L = C.CDLL(LIB_PATH)
+    L.lgs_open.restype = C.c_void_p
+    L.lgs_open.argtypes = [C.c_char_p, C.c_char_p, C.c_int, C.c_int]
+    L.lgs_close.argtypes = [C.c_void_p]
+    for n in ("lgs_n_vocab", "lgs_n_embd", "lgs_n_layer", "lgs_has_head"):
+        getattr(L, n).argtypes = [C.c_void_p]; getattr(L, n).restype = C.c_int
+    for n in ("lgs_model", "lgs_kv", "lgs_head"):
+        getattr(L, n).argtypes = [C.c_void_p]; getattr(L, n).restype = C.c_void_p
+    L.lgs_set_mtp_n.argtypes = [C.c_void_p, C.c_int]
+    L.lgs_forward.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+    L.lgs_last_hidden.argtypes = [C.c_void_p, _f32p]
+    L.lgs_next.argtypes = [C.c_void_p, C.c_int, C.c_int]; L.lgs_next.restype = C.c_int
+    L.lgs_prefill.argtypes = [C.c_void_p, _i32p, C.c_int, C.c_int]
+    L.lgs_spec.argtypes = [C.c_void_p, _i32p, C.c_int, _i32p]; L.lgs_spec.restype = C.c_int
+    L.lgs_draft.argtypes = [C.c_void_p, C.c_int, C.c_int]; L.lgs_draft.restype = C.c_int
+    L.lgs_draft_chain.argtypes = [C.c_void_p, C.c_int, C.c_int]; L.lgs_draft_chain.restype = C.c_int
+    L.lgs_kv_row.argtypes = [C.c_void_p, C.c_int, C.c_int, _f32p, _f32p]; L.lgs_kv_row.restype = C.c_int
+    L.lgs_generate.argtypes = [C.c_void_p, _i32p, C.c_int, C.c_int, _i32p, C.c_int, C.c_void_p, _i32p]
+    L.lgs_generate.restype = C.c_int
+    L.lgs_generate_device.argtypes = [C.c_void_p, _i32p, C.c_int, C.c_int, _i32p, C.c_int, C.c_void_p, C.c_int, _i32p]
+    L.lgs_generate_device.restype = C.c_int
+    L.lg_dequant_host.argtypes = [C.c_int, C.c_void_p, C.c_int, C.c_int, _f32p]; L.lg_dequant_host.restype = C.c_int
+    L.lg_gemv_host.argtypes = [C.c_int, C.c_void_p, C.c_int, C.c_int, _f32p, C.c_int, C.c_int, _f32p]
+    L.lg_gemv_host.restype = C.c_int
+    L.lg_flash_decode_host.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                       C.c_int, _f32p]
+    L.lg_flash_decode_host.restype = C.c_int
+    L.lg_set_replay.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
+    L.lg_rounds_begin.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int]
+    L.lg_rounds_enqueue.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
+    L.lg_rounds_enqueue.restype = C.c_int
+    L.lg_rounds_collect.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, _i32p]
+    L.lg_rounds_collect.restype = C.c_int
+    L.lg_weight_bytes.argtypes = [C.c_void_p]; L.lg_weight_bytes.restype = C.c_longlong
+    L.lg_round_launches.argtypes = [C.c_void_p]; L.lg_round_launches.restype = C.c_longlong
+    L.lg_stream.argtypes = [C.c_void_p]; L.lg_stream.restype = C.c_void_p
+    _lib = L
+    return L
+
+
+def dequant(ggml_type: int, raw: np.ndarray, n_rows: int, k: int) -> np.ndarray:
+    """Decode file-format blocks on the GPU (bit-exact to the reference decode)."""
+    L = load()
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    out = np.empty((n_rows, k), dtype=np.float32)
+    rc = L.lg_dequant_host(ggml_type, raw.ctypes.data_as(C.c_void_p), n_rows, k, out.reshape(-1))
+    if rc:
+        raise ValueError(f"lg_dequant_host failed ({rc})")
+    return out
+
+
+def gemv(ggml_type: int, raw: np.ndarray, m: int, k: int, x: np.ndarray, kslices: int = 0) -> np.ndarray:
+    """y[tok] = W x[tok] through the production matmul kernel; x is [M, k] f32, M <= 8."""
+    L = load()
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    M = x.shape[0]
+    y = np.empty((M, m), dtype=np.float32)
+    rc = L.lg_gemv_host(ggml_type, raw.ctypes.data_as(C.c_void_p), m, k, x.reshape(-1), M, kslices, y.reshape(-1))
+    if rc:
+        raise ValueError(f"lg_gemv_host failed ({rc})")
+    return y
+
+
+def flash_decode(q: np.ndarray, k: np.ndarray, v: np.ndarray, n_head_kv: int, window: int, pos: int) -> np.ndarray:
+    """q [M, H, hd]; k, v [seq, Hkv*hd] (rounded to f16 on upload); query j sits at pos + j."""
+    L = load()
+    q = np.ascontiguousarray(q, dtype=np.float32); k = np.ascontiguousarray(k, dtype=np.float32)
+    v = np.ascontiguousarray(v, dtype=np.float32)
+    M, H, hd = q.shape
+    out = np.empty_like(q)
+    rc = L.lg_flash_decode_host(q.reshape(-1), k.reshape(-1), v.reshape(-1), M, H, n_head_kv, hd, k.shape[0], window,
+                                pos, out.reshape(-1))
+    if rc:
+        raise ValueError(f"lg_flash_decode_host failed ({rc})")
+    return out
+
+
+class Session:
+    """One loaded target model (+ optional draft head) with its KV cache on the GPU."""
+
+    def __init__(self, target: str, head: str | None = None, max_seq: int = 4096, mtp_n: int = 4):
+        self.L = load()
+        self.h = self.L.lgs_open(target.encode(), (head or "").encode(), max_seq, 1)
+        if not self.h:
+            raise RuntimeError(f"cannot open {target}")
+        self.n_vocab = self.L.lgs_n_vocab(self.h)
+        self.n_embd = self.L.lgs_n_embd(self.h)
+        self.n_layer = self.L.lgs_n_layer(self.h)
+        self.mtp_n = mtp_n
+        self.L.lgs_set_mtp_n(self.h, mtp_n)
+        self.model = self.L.lgs_model(self.h)
+        self.kv = self.L.lgs_kv(self.h)
+        self.head = self.L.lgs_head(self.h)
+
+    def close(self):
+        if self.h:
+            self.L.lgs_close(self.h)
+            self.h = None
+
+    def __enter__(self): return self
+    def __exit__(self, *a): self.close()
+
+    def forward(self, tok: int, pos: int, want_logits: bool = True):
+        if not want_logits:
+            self.L.lgs_forward(self.h, tok, pos, None)
+            return None
+        out = np.empty(self.n_vocab, dtype=np.float32)
+        self.L.lgs_forward(self.h, tok, pos, out.ctypes.data_as(C.c_void_p))
+        return out
+
+    def last_hidden(self) -> np.ndarray:
+        out = np.empty(self.n_embd, dtype=np.float32)
+        self.L.lgs_last_hidden(self.h, out)
+        return out
+
+    def next(self, tok: int, pos: int) -> int:
+        return self.L.lgs_next(self.h, tok, pos)
+
+    def prefill(self, toks, pos0: int = 0):
+        toks = np.ascontiguousarray(toks, dtype=np.int32)
+        self.L.lgs_prefill(self.h, toks, len(toks), pos0)
+
+    def spec(self, toks, pos: int):
+        toks = np.ascontiguousarray(toks, dtype=np.int32)
+        assert len(toks) == self.mtp_n
+        out = np.zeros(8, dtype=np.int32)
+        adv = self.L.lgs_spec(self.h, toks, pos, out)
+        return adv, out[:self.mtp_n]
+
+    def draft(self, tok: int, pos: int) -> int:
+        return self.L.lgs_draft(self.h, tok, pos)
+
+    def draft_chain(self, tok: int, pos: int) -> int:
+        return self.L.lgs_draft_chain(self.h, tok, pos)
+
+    def kv_row(self, layer: int, pos: int, kv_dim: int):
+        k = np.empty(kv_dim, dtype=np.float32); v = np.empty(kv_dim, dtype=np.float32)
+        d = self.L.lgs_kv_row(self.h, layer, pos, k, v)
+        return (k[:d], v[:d]) if d else (None, None)
+
+    def generate(self, prompt, n_gen: int, mode: int = 0, replay=None):
+        """Host-driven generation through the reference-shaped blocking calls."""
+        prompt = np.ascontiguousarray(prompt, dtype=np.int32)
+        out = np.zeros(n_gen + 8, dtype=np.int32); stats = np.zeros(2, dtype=np.int32)
+        rp = None
+        if replay is not None:
+            replay = np.ascontiguousarray(np.concatenate([replay, np.zeros(8, np.int32)]), dtype=np.int32)
+            rp = replay.ctypes.data_as(C.c_void_p)
+        n = self.L.lgs_generate(self.h, prompt, len(prompt), n_gen, out, mode, rp, stats)
+        return out[:n], (int(stats[0]), int(stats[1]))
+
+    def generate_device(self, prompt, n_gen: int, mode: int = 0, replay=None):
+        """Device-resident rounds: one host synchronisation for the whole generation."""
+        prompt = np.ascontiguousarray(prompt, dtype=np.int32)
+        out = np.zeros(n_gen + 8, dtype=np.int32); stats = np.zeros(2, dtype=np.int32)
+        rp, nr = None, 0
+        if replay is not None:
+            replay = np.ascontiguousarray(np.concatenate([replay, np.zeros(8, np.int32)]), dtype=np.int32)
+            rp, nr = replay.ctypes.data_as(C.c_void_p), len(replay)
+        n = self.L.lgs_generate_device(self.h, prompt, len(prompt), n_gen, out, mode, rp, nr, stats)
+        if n < 0:
+            raise RuntimeError("device rounds unavailable (no draft head?)")
+        return out[:n], (int(stats[0]), int(stats[1]))
+
+    # device-resident rounds, raw
+    def rounds_begin(self, first: int, pos: int, n_emitted: int = 1):
+        self.L.lg_rounds_begin(self.model, first, pos, n_emitted)
+
+    def set_replay(self, replay):
+        replay = np.ascontiguousarray(replay, dtype=np.int32)
+        self.L.lg_set_replay(self.model, replay.ctypes.data_as(C.c_void_p), len(replay))
+
+    def rounds_enqueue(self, n: int, mode: int, n_rounds: int, use_head: bool = True) -> int:
+        return self.L.lg_rounds_enqueue(self.model, self.kv, self.head if use_head else None, n, mode, n_rounds)
+
+    def rounds_collect(self, from_: int = 1, cap: int = 0):
+        stats = np.zeros(4, dtype=np.int32)
+        toks = np.zeros(max(cap, 1), dtype=np.int32)
+        n = self.L.lg_rounds_collect(self.model, toks.ctypes.data_as(C.c_void_p), from_, cap, stats)
+        return toks[:n], dict(pos=int(stats[0]), n_emitted=int(stats[1]), n_draft=int(stats[2]), n_accept=int(stats[3]))
+
+    def weight_bytes(self) -> int:
+        return int(self.L.lg_weight_bytes(self.model))
+
+    def round_launches(self) -> int:
+        return int(self.L.lg_round_launches(self.model))
+
+    def stream(self) -> int:
+        return int(self.L.lg_stream(self.model) or 0)

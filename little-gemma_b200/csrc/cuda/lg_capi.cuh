@@ -1,0 +1,95 @@
+// lg_capi.cuh -- kernel-level entry points: host buffers in, host buffers out.  They run the
+// SAME kernels the engine launches (repack, panel quantisation, tensor-core matmul, split-KV
+// flash-decode) on caller-supplied data so each can be checked in isolation.
+// Included at the end of lg_engine.cu (one translation unit).
+
+namespace {
+Engine *scratch_engine() {
+    static Engine *e = nullptr;
+    if (!e) {
+        set_kernel_attributes();
+        e = new Engine();
+        int dev = 0;
+        LG_CHECK(cudaGetDevice(&dev));
+        LG_CHECK(cudaDeviceGetAttribute(&e->sm_count, cudaDevAttrMultiProcessorCount, dev));
+        LG_CHECK(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
+        e->head_ctas = e->sm_count * 4;
+        e->err = dalloc<int>(1);
+    }
+    return e;
+}
+}  // namespace
+
+extern "C" int lg_dequant_host(int type, const void *blocks, int n_rows, int k, float *out) {
+    Engine *e = scratch_engine();
+    size_t bytes = ggml_nbytes((uint32_t)type, (int64_t)n_rows * k);
+    if (!bytes) return -1;
+    uint8_t *d_src = nullptr; float *d_out = nullptr;
+    LG_CHECK(cudaMalloc(&d_src, bytes));
+    LG_CHECK(cudaMalloc(&d_out, (size_t)n_rows * k * 4));
+    LG_CHECK(cudaMemcpyAsync(d_src, blocks, bytes, cudaMemcpyHostToDevice, e->stream));
+    lg_dequant_rows<<<n_rows, 256, 0, e->stream>>>(d_src, type, k, nullptr, 0, 1.0f, d_out, k);
+    LG_CHECK(cudaGetLastError());
+    LG_CHECK(cudaMemcpyAsync(out, d_out, (size_t)n_rows * k * 4, cudaMemcpyDeviceToHost, e->stream));
+    LG_CHECK(cudaStreamSynchronize(e->stream));
+    cudaFree(d_src); cudaFree(d_out);
+    return 0;
+}
+
+extern "C" int lg_gemv_host(int type, const void *blocks, int m, int k, const float *x, int M, int kslices, float *y) {
+    if (M < 1 || M > LG_MAXM || k % 64 || (type != GGML_TYPE_Q4_0 && type != GGML_TYPE_Q4_K)) return -1;
+    if (type == GGML_TYPE_Q4_K && k % 256) return -1;
+    Engine *e = scratch_engine();
+    struct gguf_tensor t;
+    memset(&t, 0, sizeof t);
+    char name[] = "lg_gemv_host";
+    t.name = name; t.n_dims = 2; t.dims[0] = k; t.dims[1] = m; t.dims[2] = t.dims[3] = 1; t.type = type; t.data = (void *)blocks;
+    WMat W = build_wmat(e, {&t});
+    LgPanel P = panel_alloc(k);
+    float *d_x = dalloc<float>((size_t)M * k);
+    float *d_out = dalloc<float>((size_t)e->max_ks * LG_MAXM * W.ldo);
+    LG_CHECK(cudaMemcpyAsync(d_x, x, (size_t)M * k * 4, cudaMemcpyHostToDevice, e->stream));
+    lg_quant_rows<<<dim3((k / 32 + 7) / 8, M), 256, 0, e->stream>>>(d_x, k, k, P);
+    LG_CHECK(cudaGetLastError());
+    int ks = 1;
+    launch_gemv(e, W, P, M, d_out, LG_EPI_STORE, kslices, 0, nullptr, nullptr, nullptr, &ks);
+    std::vector<float> h((size_t)ks * LG_MAXM * W.ldo);
+    LG_CHECK(cudaMemcpyAsync(h.data(), d_out, h.size() * 4, cudaMemcpyDeviceToHost, e->stream));
+    check_err(e);
+    for (int tok = 0; tok < M; tok++)
+        for (int r = 0; r < m; r++) {
+            float s = 0.0f;
+            for (int p = 0; p < ks; p++) s += h[((size_t)p * LG_MAXM + tok) * W.ldo + r];
+            y[(size_t)tok * m + r] = s;
+        }
+    free_wmat(W); panel_free(P); cudaFree(d_x); cudaFree(d_out);
+    return 0;
+}
+
+extern "C" int lg_flash_decode_host(const float *q, const float *k, const float *v, int M, int H, int Hkv, int hd,
+                                    int seq, int window, int pos, float *out) {
+    if (M < 1 || M > LG_MAXM || hd % 32 || hd > 512 || H % Hkv) return -1;
+    Engine *e = scratch_engine();
+    const int kv_dim = Hkv * hd;
+    std::vector<__half> hk((size_t)seq * kv_dim), hv((size_t)seq * kv_dim);
+    for (size_t i = 0; i < hk.size(); i++) { hk[i] = __float2half_rn(k[i]); hv[i] = __float2half_rn(v[i]); }
+    __half *d_k = dalloc<__half>(hk.size()), *d_v = dalloc<__half>(hv.size());
+    float *d_q = dalloc<float>((size_t)M * H * hd), *d_o = dalloc<float>((size_t)M * H * hd);
+    int *d_pos = dalloc<int>(1);
+    int max_seq = pos + M > seq ? pos + M : seq;
+    int slots = tiles_for(window, max_seq, M);
+    float *d_part = dalloc<float>((size_t)slots * M * H * (hd + 2));
+    LG_CHECK(cudaMemcpyAsync(d_k, hk.data(), hk.size() * 2, cudaMemcpyHostToDevice, e->stream));
+    LG_CHECK(cudaMemcpyAsync(d_v, hv.data(), hv.size() * 2, cudaMemcpyHostToDevice, e->stream));
+    LG_CHECK(cudaMemcpyAsync(d_q, q, (size_t)M * H * hd * 4, cudaMemcpyHostToDevice, e->stream));
+    LG_CHECK(cudaMemcpyAsync(d_pos, &pos, 4, cudaMemcpyHostToDevice, e->stream));
+    LgAttnArgs a{};
+    a.q = d_q; a.kc = d_k; a.vc = d_v; a.seq = seq; a.kv_dim = kv_dim; a.H = H; a.Hkv = Hkv; a.hd = hd; a.M = M;
+    a.S = ATTN_TILE; a.n_slots = slots; a.window = window; a.qpos_off = 0; a.win_shrink = 0; a.pos = d_pos;
+    a.part = d_part; a.out.q = nullptr; a.out_f32 = d_o;
+    launch_attn(e, a, slots);
+    LG_CHECK(cudaMemcpyAsync(out, d_o, (size_t)M * H * hd * 4, cudaMemcpyDeviceToHost, e->stream));
+    LG_CHECK(cudaStreamSynchronize(e->stream));
+    cudaFree(d_k); cudaFree(d_v); cudaFree(d_q); cudaFree(d_o); cudaFree(d_pos); cudaFree(d_part);
+    return 0;
+}

@@ -1,0 +1,992 @@
+// lg_engine.cu -- the sm_100a backend behind the little-gemma model API.
+//
+// Exports the backend symbol set the host C links against (kvcache_*, model_forward*,
+// model_prefill*, model_forward_spec, mtp_*_device, model_kv_host; see include/lg_b200.h for
+// the reference line each one replaces) plus the device-resident round API and a few
+// kernel-level entry points used by the parity tests.
+//
+// One engine per process (the reference keeps its device state in file-scope statics too):
+// weights are uploaded and repacked on first use, every forward is a CUDA graph of fused
+// kernels whose parameters never change -- position and token ids live in device memory.
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <cmath>
+#include <vector>
+#include <map>
+#include <string>
+#include "lg_kernels.cuh"
+#include "lg_host.h"
+#include "lg_b200.h"
+
+#define LG_CHECK(x) do { cudaError_t e_ = (x); if (e_ != cudaSuccess) { \
+    fprintf(stderr, "lg_b200: CUDA error %s at %s:%d\n", cudaGetErrorString(e_), __FILE__, __LINE__); exit(1); } } while (0)
+
+extern "C" const int model_kv_host = 0;      // cache rows live on the device: mtp.c must call the device hooks
+
+namespace {
+
+constexpr int RING_SPARE = 1024;             // ring rows beyond the window (covers the widest block written before its queries run)
+constexpr int ATTN_TILE = 64;                // keys per flash-decode tile (absolute boundaries)
+constexpr int LOG_CAP = 1 << 20;
+
+struct WMat {
+    uint4 *wq = nullptr; uint2 *ws = nullptr; uint2 *wd = nullptr;
+    int fmt = 0, m = 0, k = 0, nkp = 0, n_row_tiles = 0, ldo = 0;
+    size_t file_bytes = 0;
+};
+
+struct Panel { LgPanel p{}; };
+
+struct LayerW {
+    WMat qkv, o, gateup, down, inp_gate, proj;
+    float *attn_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr, *post_attn = nullptr, *ffn_norm = nullptr,
+          *post_ffw = nullptr, *post_norm = nullptr;
+    float out_scale = 1.0f;
+    int has_v = 1, owns_kv = 1, src = 0, local = 0, hd = 0, nkv = 0, nff = 0;
+};
+
+struct DraftBlockW {
+    WMat q, o, gateup, down;
+    float *attn_norm, *q_norm, *post_attn, *ffn_norm, *post_ffw;
+    float out_scale; int hd, local, src;
+};
+struct DraftW {
+    WMat pre, post, head;
+    float *out_norm = nullptr;
+    std::vector<DraftBlockW> blk;
+    int ni = 0, nb = 0, nff = 0, n_head = 0, n_vocab = 0, has_post = 0;
+    float eps = 0, base_full = 0, base_swa = 0, softcap = 0;
+    // activations (one token)
+    float *cat = nullptr, *x = nullptr, *hbuf = nullptr, *qbuf = nullptr, *qrot = nullptr, *obuf = nullptr, *gu = nullptr, *part = nullptr;
+    float *amax_val = nullptr; int *amax_idx = nullptr, *best = nullptr;
+    LgPanel p_cat{}, p_ni{}, p_attn{}, p_ff{};
+    int n_slots_local = 0, n_slots_global = 0;
+    std::map<std::string, cudaGraphExec_t> graphs;
+};
+
+struct Engine {
+    const struct model *m = nullptr;
+    const struct gguf_context *ctx = nullptr;
+    cudaStream_t stream = nullptr;
+    int sm_count = 148;
+    // weights
+    std::vector<LayerW> L;
+    WMat head, pmp;                           // token_embd (tied head), per_layer_model_proj
+    uint8_t *ple_table = nullptr; int ple_table_type = 0;   // per_layer_token_embd, file layout
+    float *out_norm = nullptr, *ple_proj_norm = nullptr, *rope_div = nullptr;
+    int has_ple = 0;
+    size_t weight_bytes = 0;
+    // activations
+    float *x = nullptr, *qkv = nullptr, *qrot = nullptr, *oout = nullptr, *gu = nullptr, *dout = nullptr, *hidden = nullptr,
+          *h_prev = nullptr, *part = nullptr, *tokrow = nullptr, *pproj = nullptr, *ipl = nullptr, *pg = nullptr, *logits = nullptr;
+    float *amax_val = nullptr; int *amax_idx = nullptr;
+    LgPanel p_ne{}, p_attn{}, p_ff{}, p_ple{};
+    int max_ks = 4, head_ctas = 0;
+    int part_slots = 0;
+    // session
+    LgRoundState *st = nullptr;               // device
+    LgRoundState *st_host = nullptr;          // pinned mirror for uploads / downloads
+    int *log = nullptr, *replay = nullptr; int n_replay = 0;
+    int *err = nullptr;
+    std::map<std::string, cudaGraphExec_t> graphs;
+    const struct kvcache *kv_bound = nullptr;
+    DraftW *draft = nullptr; const struct mtp *draft_owner = nullptr;
+    float *pick_rows = nullptr;               // host logits rows for model_pick
+    long long launches = 0;                   // kernels enqueued by the most recent graph build
+    long long round_launches = 0;             // kernels in one captured round (lg_rounds_enqueue)
+};
+
+Engine *g_eng = nullptr;
+
+template <typename T> T *dalloc(size_t n) { T *p = nullptr; LG_CHECK(cudaMalloc(&p, n * sizeof(T) > 0 ? n * sizeof(T) : 16)); LG_CHECK(cudaMemset(p, 0, n * sizeof(T))); return p; }
+
+LgPanel panel_alloc(int k) {
+    LgPanel P;
+    P.nsb = k / 32;
+    P.q = dalloc<int8_t>((size_t)2 * P.nsb * 256);
+    P.s = dalloc<float2>((size_t)2 * P.nsb * 4);
+    return P;
+}
+void panel_free(LgPanel &P) { cudaFree(P.q); cudaFree(P.s); P.q = nullptr; P.s = nullptr; }
+
+float *upload_f32(const float *src, size_t n) {
+    float *d = dalloc<float>(n);
+    LG_CHECK(cudaMemcpy(d, src, n * 4, cudaMemcpyHostToDevice));
+    return d;
+}
+
+const struct gguf_tensor *find_t(const struct gguf_context *g, int L, const char *leaf) {
+    char name[96];
+    if (L >= 0) snprintf(name, sizeof name, "blk.%d.%s", L, leaf); else snprintf(name, sizeof name, "%s", leaf);
+    return gguf_find_tensor(g, name);
+}
+float *upload_norm(const struct gguf_context *g, int L, const char *leaf) {
+    const struct gguf_tensor *t = find_t(g, L, leaf);
+    if (!t) return nullptr;
+    if (t->type != GGML_TYPE_F32) { fprintf(stderr, "lg_b200: %s must be f32\n", t->name); exit(1); }
+    return upload_f32((const float *)t->data, (size_t)t->dims[0]);
+}
+
+// Upload file-format tensors and repack them, stacked row-wise, into one tile-major matrix.
+WMat build_wmat(Engine *e, std::vector<const struct gguf_tensor *> parts) {
+    WMat W;
+    const struct gguf_tensor *t0 = parts[0];
+    if (t0->type != GGML_TYPE_Q4_0 && t0->type != GGML_TYPE_Q4_K) {
+        fprintf(stderr, "lg_b200: weight %s has ggml type %u; this backend runs q4_0 and q4_K matrices\n", t0->name, t0->type);
+        exit(1);
+    }
+    W.fmt = t0->type == GGML_TYPE_Q4_0 ? LG_FMT_Q4_0 : LG_FMT_Q4_K;
+    W.k = (int)t0->dims[0];
+    if (W.k % 64) { fprintf(stderr, "lg_b200: %s: contraction length %d is not a multiple of 64\n", t0->name, W.k); exit(1); }
+    for (auto t : parts) {
+        if (t->type != t0->type || (int)t->dims[0] != W.k) { fprintf(stderr, "lg_b200: cannot stack %s onto %s\n", t->name, t0->name); exit(1); }
+        if (t != parts.back() && t->dims[1] % 16) { fprintf(stderr, "lg_b200: %s: %d rows is not a multiple of 16\n", t->name, (int)t->dims[1]); exit(1); }
+        W.m += (int)t->dims[1];
+    }
+    W.nkp = W.k / 64;
+    W.n_row_tiles = (W.m + 15) / 16;
+    W.ldo = W.n_row_tiles * 16;
+    size_t tiles = (size_t)W.n_row_tiles * W.nkp;
+    W.wq = dalloc<uint4>(tiles * 32);
+    W.ws = dalloc<uint2>(tiles * 8);
+    if (W.fmt == LG_FMT_Q4_K) W.wd = dalloc<uint2>(tiles * 8);
+    int row_off = 0;
+    for (auto t : parts) {
+        int rows = (int)t->dims[1], nsb = W.k / 32;
+        size_t bytes = ggml_nbytes(t->type, (int64_t)rows * W.k);
+        uint8_t *stage = nullptr;
+        LG_CHECK(cudaMalloc(&stage, bytes));
+        LG_CHECK(cudaMemcpy(stage, t->data, bytes, cudaMemcpyHostToDevice));
+        int rts = (rows + 15) / 16;
+        size_t threads = (size_t)rts * W.nkp * 32;
+        size_t toff = (size_t)(row_off / 16) * W.nkp;
+        unsigned blocks = (unsigned)((threads + 255) / 256);
+        if (W.fmt == LG_FMT_Q4_0)
+            lg_repack_q4_0<<<blocks, 256, 0, e->stream>>>(stage, W.wq + toff * 32, W.ws + toff * 8, rows, nsb, rts);
+        else
+            lg_repack_q4_K<<<blocks, 256, 0, e->stream>>>(stage, W.wq + toff * 32, W.ws + toff * 8, W.wd + toff * 8, rows, nsb, rts);
+        LG_CHECK(cudaGetLastError());
+        LG_CHECK(cudaStreamSynchronize(e->stream));
+        cudaFree(stage);
+        row_off += rows;
+        W.file_bytes += bytes;
+    }
+    e->weight_bytes += W.file_bytes;
+    return W;
+}
+void free_wmat(WMat &W) { cudaFree(W.wq); cudaFree(W.ws); cudaFree(W.wd); W = WMat(); }
+
+// ------------------------------------------------------------------------------------------
+// launch helpers
+// ------------------------------------------------------------------------------------------
+struct GemvPlan { int ks, gx; size_t smem; };
+constexpr size_t GEMV_SMEM_MAX = 200 * 1024, ATTN_SMEM_MAX = 200 * 1024;
+
+// Opt every kernel into large dynamic shared memory once, outside any stream capture.
+void set_kernel_attributes() {
+    static bool done = false;
+    if (done) return;
+    done = true;
+#define LG_ATTR(K) LG_CHECK(cudaFuncSetAttribute(K, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMV_SMEM_MAX))
+    LG_ATTR((lg_gemv_kernel<1, LG_FMT_Q4_0, LG_EPI_STORE>)); LG_ATTR((lg_gemv_kernel<1, LG_FMT_Q4_0, LG_EPI_HEAD>));
+    LG_ATTR((lg_gemv_kernel<2, LG_FMT_Q4_0, LG_EPI_STORE>)); LG_ATTR((lg_gemv_kernel<2, LG_FMT_Q4_0, LG_EPI_HEAD>));
+    LG_ATTR((lg_gemv_kernel<1, LG_FMT_Q4_K, LG_EPI_STORE>)); LG_ATTR((lg_gemv_kernel<1, LG_FMT_Q4_K, LG_EPI_HEAD>));
+    LG_ATTR((lg_gemv_kernel<2, LG_FMT_Q4_K, LG_EPI_STORE>)); LG_ATTR((lg_gemv_kernel<2, LG_FMT_Q4_K, LG_EPI_HEAD>));
+#undef LG_ATTR
+    LG_CHECK(cudaFuncSetAttribute(lg_attn_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
+}
+
+GemvPlan plan_gemv(const Engine *e, const WMat &W, int np, int want_ks) {
+    GemvPlan p;
+    p.ks = want_ks;
+    if (p.ks <= 0) { p.ks = 1; while (W.nkp / p.ks > 72 && p.ks < e->max_ks && W.nkp % (p.ks * 2) == 0) p.ks *= 2; }
+    int nkp_s = (W.nkp + p.ks - 1) / p.ks + 1;
+    p.smem = (size_t)np * nkp_s * 2 * (256 + 32) + (size_t)LG_GEMV_WARPS * np * 64 * 4 + 16;
+    int ctas = e->sm_count * 2;
+    p.gx = W.n_row_tiles < ctas / p.ks ? W.n_row_tiles : ctas / p.ks;
+    if (p.gx < 1) p.gx = 1;
+    return p;
+}
+
+template <int NP, int FMT, int EPI>
+void launch_gemv_t(Engine *e, const LgGemvArgs &a, const GemvPlan &p) {
+    if (p.smem > GEMV_SMEM_MAX) { fprintf(stderr, "lg_b200: matmul slice needs %zu bytes of shared memory\n", p.smem); exit(1); }
+    dim3 grid(p.gx, p.ks);
+    lg_gemv_kernel<NP, FMT, EPI><<<grid, LG_GEMV_WARPS * 32, p.smem, e->stream>>>(a);
+    LG_CHECK(cudaGetLastError());
+    e->launches++;
+}
+
+// out[ks][tok][ldo] partial sums (EPI_STORE) or the head epilogue.
+void launch_gemv(Engine *e, const WMat &W, const LgPanel &X, int M, float *out, int epi, int force_ks,
+                 float softcap = 0.0f, float *logits = nullptr, float *amax_val = nullptr, int *amax_idx = nullptr,
+                 int *ks_out = nullptr, int *gx_out = nullptr) {
+    int np = M > 4 ? 2 : 1;
+    GemvPlan p = plan_gemv(e, W, np, epi == LG_EPI_HEAD ? 1 : force_ks);
+    if (epi == LG_EPI_HEAD) { p.gx = e->head_ctas < W.n_row_tiles ? e->head_ctas : W.n_row_tiles; }
+    LgGemvArgs a{};
+    a.wq = W.wq; a.ws = W.ws; a.wd = W.wd; a.x = X; a.nkp = W.nkp; a.n_row_tiles = W.n_row_tiles; a.kslices = p.ks;
+    a.out = out; a.ldo = W.ldo; a.M = M; a.softcap = softcap; a.logits = logits; a.n_valid_rows = W.m;
+    a.amax_val = amax_val; a.amax_idx = amax_idx; a.err = e->err;
+    if (X.nsb * 32 != W.k) { fprintf(stderr, "lg_b200: panel width %d does not match matrix k %d\n", X.nsb * 32, W.k); exit(1); }
+    if (ks_out) *ks_out = p.ks;
+    if (gx_out) *gx_out = p.gx;
+#define LG_DISPATCH(NPv, FMTv) \
+    if (epi == LG_EPI_HEAD) launch_gemv_t<NPv, FMTv, LG_EPI_HEAD>(e, a, p); else launch_gemv_t<NPv, FMTv, LG_EPI_STORE>(e, a, p);
+    if (np == 1) { if (W.fmt == LG_FMT_Q4_0) { LG_DISPATCH(1, LG_FMT_Q4_0) } else { LG_DISPATCH(1, LG_FMT_Q4_K) } }
+    else         { if (W.fmt == LG_FMT_Q4_0) { LG_DISPATCH(2, LG_FMT_Q4_0) } else { LG_DISPATCH(2, LG_FMT_Q4_K) } }
+#undef LG_DISPATCH
+}
+
+void launch_norm(Engine *e, int M, float *x, int ldx, int n, float eps,
+                 const float *add_src, int n_parts, size_t part_stride, int ld_add, const float *add_w, float out_scale,
+                 const float *norm_w, const LgPanel *panel, float *y, int ldy) {
+    LgNormArgs a{};
+    a.x = x; a.ldx = ldx; a.add_src = add_src; a.n_parts = n_parts; a.part_stride = part_stride; a.ld_add = ld_add;
+    a.add_w = add_w; a.out_scale = out_scale; a.norm_w = norm_w;
+    if (panel) { a.panel = *panel; a.want_panel = 1; }
+    a.y = y; a.ldy = ldy; a.n = n; a.eps = eps;
+    int threads = n >= 2048 ? 1024 : (n >= 512 ? 512 : 256);
+    lg_norm_kernel<<<M, threads, (size_t)(n + 32) * 4, e->stream>>>(a);
+    LG_CHECK(cudaGetLastError());
+    e->launches++;
+}
+
+size_t attn_smem(int nq, int hd) { return (size_t)nq * hd * 4 + (size_t)ATTN_TILE * (hd + 8) * 2 + (size_t)nq * ATTN_TILE * 4; }
+
+void launch_attn(Engine *e, LgAttnArgs a, int n_tiles_max) {
+    int nq = (a.H / a.Hkv) * a.M;
+    size_t sm = attn_smem(nq, a.hd);
+    if (sm > ATTN_SMEM_MAX) { fprintf(stderr, "lg_b200: attention tile needs %zu bytes of shared memory\n", sm); exit(1); }
+    lg_attn_split_kernel<<<dim3(a.Hkv, n_tiles_max), LG_ATTN_THREADS, sm, e->stream>>>(a);
+    LG_CHECK(cudaGetLastError());
+    lg_attn_combine_kernel<<<dim3(a.H, a.M), a.hd, 0, e->stream>>>(a);
+    LG_CHECK(cudaGetLastError());
+    e->launches += 2;
+}
+
+int tiles_for(int window, int max_seq, int M) {
+    if (window > 0 && window + M < max_seq) return (window + M + ATTN_TILE - 1) / ATTN_TILE + 1;
+    return (max_seq + ATTN_TILE - 1) / ATTN_TILE + 1;
+}
+
+// ------------------------------------------------------------------------------------------
+// engine construction
+// ------------------------------------------------------------------------------------------
+void engine_free(Engine *e);
+
+Engine *engine_for(const struct model *m) {
+    if (g_eng && g_eng->m == m && g_eng->ctx == m->ctx) return g_eng;
+    if (g_eng) { engine_free(g_eng); g_eng = nullptr; }
+    set_kernel_attributes();
+    Engine *e = new Engine();
+    e->m = m; e->ctx = m->ctx;
+    const struct config *c = &m->cfg;
+    const struct gguf_context *g = m->ctx;
+    int dev = 0;
+    LG_CHECK(cudaGetDevice(&dev));
+    LG_CHECK(cudaDeviceGetAttribute(&e->sm_count, cudaDevAttrMultiProcessorCount, dev));
+    LG_CHECK(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
+    e->head_ctas = e->sm_count * 4;
+    e->err = dalloc<int>(1);
+
+    const int ne = c->n_embd, H = c->n_head, ple = c->n_embd_per_layer;
+    const struct gguf_tensor *emb = find_t(g, -1, "token_embd.weight");
+    if (!emb) { fprintf(stderr, "lg_b200: token_embd.weight is missing\n"); exit(1); }
+    e->head = build_wmat(e, {emb});
+    e->out_norm = upload_norm(g, -1, "output_norm.weight");
+    e->rope_div = upload_norm(g, -1, "rope_freqs.weight");
+    const struct gguf_tensor *pte = ple > 0 ? find_t(g, -1, "per_layer_token_embd.weight") : nullptr;
+    e->has_ple = pte != nullptr;
+    if (e->has_ple) {
+        size_t bytes = ggml_nbytes(pte->type, (int64_t)pte->dims[0] * pte->dims[1]);
+        if (!bytes) { fprintf(stderr, "lg_b200: per_layer_token_embd has unsupported type %u\n", pte->type); exit(1); }
+        LG_CHECK(cudaMalloc(&e->ple_table, bytes));
+        LG_CHECK(cudaMemcpy(e->ple_table, pte->data, bytes, cudaMemcpyHostToDevice));
+        e->ple_table_type = (int)pte->type;
+        e->pmp = build_wmat(e, {find_t(g, -1, "per_layer_model_proj.weight")});
+        e->ple_proj_norm = upload_norm(g, -1, "per_layer_proj_norm.weight");
+    }
+    int max_qkv = 0, max_q = 0, max_ff = 0, max_hd = 0;
+    e->L.resize(c->n_layer);
+    for (int l = 0; l < c->n_layer; l++) {
+        LayerW &w = e->L[l];
+        w.hd = m->head_dim[l]; w.nkv = m->n_head_kv[l]; w.local = m->is_local[l]; w.nff = m->ffn_len[l];
+        w.owns_kv = l < c->n_kv_start;
+        w.src = w.owns_kv ? l : c->n_kv_start - (w.local ? 2 : 1);
+        std::vector<const struct gguf_tensor *> parts{find_t(g, l, "attn_q.weight")};
+        if (w.owns_kv) {
+            parts.push_back(find_t(g, l, "attn_k.weight"));
+            const struct gguf_tensor *v = find_t(g, l, "attn_v.weight");
+            w.has_v = v != nullptr;
+            if (v) parts.push_back(v);
+        }
+        w.qkv = build_wmat(e, parts);
+        w.o = build_wmat(e, {find_t(g, l, "attn_output.weight")});
+        w.gateup = build_wmat(e, {find_t(g, l, "ffn_gate.weight"), find_t(g, l, "ffn_up.weight")});
+        w.down = build_wmat(e, {find_t(g, l, "ffn_down.weight")});
+        if (e->has_ple) {
+            w.inp_gate = build_wmat(e, {find_t(g, l, "inp_gate.weight")});
+            w.proj = build_wmat(e, {find_t(g, l, "proj.weight")});
+            w.post_norm = upload_norm(g, l, "post_norm.weight");
+        }
+        w.attn_norm = upload_norm(g, l, "attn_norm.weight");
+        w.q_norm = upload_norm(g, l, "attn_q_norm.weight");
+        w.k_norm = upload_norm(g, l, "attn_k_norm.weight");
+        w.post_attn = upload_norm(g, l, "post_attention_norm.weight");
+        w.ffn_norm = upload_norm(g, l, "ffn_norm.weight");
+        w.post_ffw = upload_norm(g, l, "post_ffw_norm.weight");
+        const struct gguf_tensor *os = find_t(g, l, "layer_output_scale.weight");
+        w.out_scale = os ? ((const float *)os->data)[0] : 1.0f;
+        if (w.qkv.ldo > max_qkv) max_qkv = w.qkv.ldo;
+        if (H * w.hd > max_q) max_q = H * w.hd;
+        if (w.gateup.ldo > max_ff) max_ff = w.gateup.ldo;
+        if (w.hd > max_hd) max_hd = w.hd;
+        if (w.hd % 32 || w.hd > 512) { fprintf(stderr, "lg_b200: head size %d unsupported\n", w.hd); exit(1); }
+    }
+    const int M8 = LG_MAXM;
+    e->x = dalloc<float>((size_t)M8 * ne);
+    e->qkv = dalloc<float>((size_t)M8 * max_qkv);
+    e->qrot = dalloc<float>((size_t)M8 * max_q);
+    e->oout = dalloc<float>((size_t)e->max_ks * M8 * (ne + 16));
+    e->gu = dalloc<float>((size_t)M8 * max_ff);
+    e->dout = dalloc<float>((size_t)e->max_ks * M8 * (ne + 16));
+    e->hidden = dalloc<float>((size_t)M8 * ne);
+    e->h_prev = dalloc<float>(ne);
+    e->p_ne = panel_alloc(ne);
+    e->p_attn = panel_alloc(max_q);
+    e->p_ff = panel_alloc(c->n_ff);
+    if (e->has_ple) {
+        size_t total = (size_t)ple * c->n_layer;
+        e->tokrow = dalloc<float>(M8 * total);
+        e->pproj = dalloc<float>((size_t)M8 * e->pmp.ldo);
+        e->ipl = dalloc<float>(M8 * total);
+        e->pg = dalloc<float>((size_t)M8 * (ple + 16));
+        e->p_ple = panel_alloc(ple);
+    }
+    e->amax_val = dalloc<float>((size_t)e->head_ctas * LG_MAXM);
+    e->amax_idx = dalloc<int>((size_t)e->head_ctas * LG_MAXM);
+    e->st = dalloc<LgRoundState>(1);
+    LG_CHECK(cudaMallocHost(&e->st_host, sizeof(LgRoundState)));
+    memset(e->st_host, 0, sizeof(LgRoundState));
+    e->log = dalloc<int>(LOG_CAP);
+    g_eng = e;
+    return e;
+}
+
+void free_graphs(std::map<std::string, cudaGraphExec_t> &gs) {
+    for (auto &kv : gs) cudaGraphExecDestroy(kv.second);
+    gs.clear();
+}
+
+void draft_free(DraftW *d) {
+    if (!d) return;
+    free_graphs(d->graphs);
+    free_wmat(d->pre); free_wmat(d->post); free_wmat(d->head);
+    for (auto &b : d->blk) {
+        free_wmat(b.q); free_wmat(b.o); free_wmat(b.gateup); free_wmat(b.down);
+        cudaFree(b.attn_norm); cudaFree(b.q_norm); cudaFree(b.post_attn); cudaFree(b.ffn_norm); cudaFree(b.post_ffw);
+    }
+    cudaFree(d->out_norm); cudaFree(d->cat); cudaFree(d->x); cudaFree(d->hbuf); cudaFree(d->qbuf); cudaFree(d->qrot);
+    cudaFree(d->obuf); cudaFree(d->gu); cudaFree(d->part); cudaFree(d->amax_val); cudaFree(d->amax_idx); cudaFree(d->best);
+    panel_free(d->p_cat); panel_free(d->p_ni); panel_free(d->p_attn); panel_free(d->p_ff);
+    delete d;
+}
+
+void engine_free(Engine *e) {
+    if (!e) return;
+    cudaStreamSynchronize(e->stream);
+    free_graphs(e->graphs);
+    draft_free(e->draft);
+    for (auto &w : e->L) {
+        free_wmat(w.qkv); free_wmat(w.o); free_wmat(w.gateup); free_wmat(w.down); free_wmat(w.inp_gate); free_wmat(w.proj);
+        cudaFree(w.attn_norm); cudaFree(w.q_norm); cudaFree(w.k_norm); cudaFree(w.post_attn); cudaFree(w.ffn_norm);
+        cudaFree(w.post_ffw); cudaFree(w.post_norm);
+    }
+    free_wmat(e->head); free_wmat(e->pmp);
+    cudaFree(e->ple_table); cudaFree(e->out_norm); cudaFree(e->ple_proj_norm); cudaFree(e->rope_div);
+    cudaFree(e->x); cudaFree(e->qkv); cudaFree(e->qrot); cudaFree(e->oout); cudaFree(e->gu); cudaFree(e->dout);
+    cudaFree(e->hidden); cudaFree(e->h_prev); cudaFree(e->part); cudaFree(e->tokrow); cudaFree(e->pproj); cudaFree(e->ipl);
+    cudaFree(e->pg); cudaFree(e->logits); cudaFree(e->amax_val); cudaFree(e->amax_idx);
+    panel_free(e->p_ne); panel_free(e->p_attn); panel_free(e->p_ff); panel_free(e->p_ple);
+    cudaFree(e->st); cudaFreeHost(e->st_host); cudaFree(e->log); cudaFree(e->replay); cudaFree(e->err);
+    free(e->pick_rows);
+    cudaStreamDestroy(e->stream);
+    delete e;
+}
+
+// Scratch for the flash-decode partials depends on the cache geometry; (re)bind when the cache changes.
+void bind_kv(Engine *e, const struct kvcache *kv) {
+    if (e->kv_bound == kv && e->part) return;
+    LG_CHECK(cudaStreamSynchronize(e->stream));
+    free_graphs(e->graphs);
+    if (e->draft) free_graphs(e->draft->graphs);
+    const struct config *c = &e->m->cfg;
+    int slots = 0, maxhd = 0;
+    for (int l = 0; l < c->n_layer; l++) {
+        int s = tiles_for(e->L[l].local ? c->sliding_window : 0, kv->max_seq, LG_MAXM);
+        if (s > slots) slots = s;
+        if (e->L[l].hd > maxhd) maxhd = e->L[l].hd;
+    }
+    cudaFree(e->part);
+    e->part_slots = slots;
+    e->part = dalloc<float>((size_t)slots * LG_MAXM * c->n_head * (maxhd + 2));
+    e->kv_bound = kv;
+}
+
+// ------------------------------------------------------------------------------------------
+// the forward of M token rows (enqueue only; captured into graphs by the callers)
+// ------------------------------------------------------------------------------------------
+enum { F_HEAD = 1, F_LOGITS = 2, F_ACCEPT = 4, F_ADVANCE = 8 };
+
+void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags) {
+    const struct model *m = e->m;
+    const struct config *c = &m->cfg;
+    const int ne = c->n_embd, H = c->n_head, ple = c->n_embd_per_layer, nl = c->n_layer;
+    cudaStream_t s = e->stream;
+    const int *d_toks = e->st->toks, *d_pos = &e->st->pos;
+
+    lg_embed_rows<<<M, 256, 0, s>>>(e->head.wq, e->head.ws, e->head.wd, e->head.fmt, e->head.nkp, d_toks,
+                                    sqrtf((float)ne), e->x, ne);
+    LG_CHECK(cudaGetLastError()); e->launches++;
+    const int total = ple * nl;
+    if (e->has_ple) {
+        lg_dequant_rows<<<M, 256, 0, s>>>(e->ple_table, e->ple_table_type, total, d_toks, 0, sqrtf((float)ple), e->tokrow, total);
+        LG_CHECK(cudaGetLastError());
+        lg_quant_rows<<<dim3((ne / 32 + 7) / 8, M), 256, 0, s>>>(e->x, ne, ne, e->p_ne);
+        LG_CHECK(cudaGetLastError());
+        e->launches += 2;
+        launch_gemv(e, e->pmp, e->p_ne, M, e->pproj, LG_EPI_STORE, 1);
+        lg_ple_build_kernel<<<dim3(nl, M), ple, 0, s>>>(e->pproj, e->tokrow, e->ple_proj_norm, e->ipl, ple, e->pmp.ldo,
+                                                       1.0f / sqrtf((float)ne), c->rms_eps);
+        LG_CHECK(cudaGetLastError()); e->launches++;
+    }
+    launch_norm(e, M, e->x, ne, ne, c->rms_eps, nullptr, 0, 0, 0, nullptr, 1.0f, e->L[0].attn_norm, &e->p_ne, nullptr, 0);
+
+    for (int l = 0; l < nl; l++) {
+        LayerW &w = e->L[l];
+        const int hd = w.hd, src = w.src;
+        launch_gemv(e, w.qkv, e->p_ne, M, e->qkv, LG_EPI_STORE, 1);
+        LgQkvArgs qa{};
+        qa.qkv = e->qkv; qa.ld = w.qkv.ldo; qa.H = H; qa.Hkv = w.nkv; qa.hd = hd; qa.has_v = w.has_v; qa.owns_kv = w.owns_kv;
+        qa.q_norm = w.q_norm; qa.k_norm = w.k_norm; qa.rope_div = w.local ? nullptr : e->rope_div;
+        qa.rope_base = w.local ? c->rope_freq_base_swa : c->rope_freq_base; qa.eps = c->rms_eps; qa.pos = d_pos;
+        qa.q_out = e->qrot; qa.kc = (__half *)kv->k[src]; qa.vc = (__half *)kv->v[src]; qa.seq = kv->seq[src]; qa.kv_dim = kv->kv_dim[src];
+        lg_qkv_post_kernel<<<dim3(H + 2 * w.nkv, M), hd / 2, 0, s>>>(qa);
+        LG_CHECK(cudaGetLastError()); e->launches++;
+
+        LgAttnArgs aa{};
+        aa.q = e->qrot; aa.kc = (const __half *)kv->k[src]; aa.vc = (const __half *)kv->v[src]; aa.seq = kv->seq[src];
+        aa.kv_dim = kv->kv_dim[src]; aa.H = H; aa.Hkv = w.nkv; aa.hd = hd; aa.M = M; aa.S = ATTN_TILE;
+        aa.window = w.local ? c->sliding_window : 0; aa.qpos_off = 0; aa.win_shrink = 0; aa.pos = d_pos;
+        aa.n_slots = e->part_slots; aa.part = e->part; aa.out_f32 = nullptr;
+        LgPanel pa = e->p_attn; pa.nsb = H * hd / 32;
+        aa.out = pa;
+        launch_attn(e, aa, tiles_for(aa.window, kv->max_seq, M));
+
+        int ks_o = 1;
+        launch_gemv(e, w.o, pa, M, e->oout, LG_EPI_STORE, 0, 0, nullptr, nullptr, nullptr, &ks_o);
+        launch_norm(e, M, e->x, ne, ne, c->rms_eps, e->oout, ks_o, (size_t)LG_MAXM * w.o.ldo, w.o.ldo, w.post_attn, 1.0f,
+                    w.ffn_norm, &e->p_ne, nullptr, 0);
+        launch_gemv(e, w.gateup, e->p_ne, M, e->gu, LG_EPI_STORE, 1);
+        LgPanel pf = e->p_ff; pf.nsb = w.nff / 32;
+        lg_geglu_kernel<<<dim3((w.nff / 32 + 7) / 8, M), 256, 0, s>>>(e->gu, e->gu + w.nff, w.gateup.ldo, w.gateup.ldo, w.nff, pf);
+        LG_CHECK(cudaGetLastError()); e->launches++;
+        int ks_d = 1;
+        launch_gemv(e, w.down, pf, M, e->dout, LG_EPI_STORE, 0, 0, nullptr, nullptr, nullptr, &ks_d);
+
+        const bool last = l == nl - 1;
+        const float *next_w = last ? ((flags & F_HEAD) ? e->out_norm : nullptr) : e->L[l + 1].attn_norm;
+        float *y = (last && (flags & F_HEAD)) ? e->hidden : nullptr;
+        const LgPanel *next_p = next_w ? &e->p_ne : nullptr;
+        if (e->has_ple) {
+            launch_norm(e, M, e->x, ne, ne, c->rms_eps, e->dout, ks_d, (size_t)LG_MAXM * w.down.ldo, w.down.ldo, w.post_ffw, 1.0f,
+                        nullptr, &e->p_ne, nullptr, 0);                         // panel of x itself
+            launch_gemv(e, w.inp_gate, e->p_ne, M, e->pg, LG_EPI_STORE, 1);
+            lg_geglu_kernel<<<dim3((ple / 32 + 7) / 8, M), 256, 0, s>>>(e->pg, e->ipl + (size_t)l * ple, w.inp_gate.ldo, total, ple, e->p_ple);
+            LG_CHECK(cudaGetLastError()); e->launches++;
+            launch_gemv(e, w.proj, e->p_ple, M, e->oout, LG_EPI_STORE, 1);
+            launch_norm(e, M, e->x, ne, ne, c->rms_eps, e->oout, 1, 0, w.proj.ldo, w.post_norm, w.out_scale,
+                        next_w, next_p, y, ne);
+        } else {
+            launch_norm(e, M, e->x, ne, ne, c->rms_eps, e->dout, ks_d, (size_t)LG_MAXM * w.down.ldo, w.down.ldo, w.post_ffw, w.out_scale,
+                        next_w, next_p, y, ne);
+        }
+    }
+    if (flags & F_HEAD) {
+        float *lg = nullptr;
+        if (flags & F_LOGITS) {
+            if (!e->logits) e->logits = dalloc<float>((size_t)LG_MAXM * e->head.ldo);
+            lg = e->logits;
+        }
+        int gx = 0;
+        launch_gemv(e, e->head, e->p_ne, M, nullptr, LG_EPI_HEAD, 1, c->logit_softcap, lg, e->amax_val, e->amax_idx, nullptr, &gx);
+        lg_argmax_final<<<M, 256, 0, s>>>(e->amax_val, e->amax_idx, gx, e->st->out);
+        LG_CHECK(cudaGetLastError()); e->launches++;
+        if (flags & F_ACCEPT) {
+            lg_accept_kernel<<<1, 256, 0, s>>>(e->st, M, e->hidden, ne, ne, e->h_prev, e->log, LOG_CAP, (flags & F_ADVANCE) ? 1 : 0);
+            LG_CHECK(cudaGetLastError()); e->launches++;
+        }
+    }
+}
+
+// Run (capturing on first use) the forward graph for (M, flags).
+void run_forward(Engine *e, const struct kvcache *kv, int M, int flags) {
+    bind_kv(e, kv);
+    char key[48];
+    snprintf(key, sizeof key, "f%d_%d", M, flags);
+    auto it = e->graphs.find(key);
+    if (it == e->graphs.end()) {
+        e->launches = 0;
+        cudaGraph_t graph;
+        if ((flags & F_LOGITS) && !e->logits) e->logits = dalloc<float>((size_t)LG_MAXM * e->head.ldo);   // not inside capture
+        LG_CHECK(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeRelaxed));
+        enqueue_forward(e, kv, M, flags);
+        LG_CHECK(cudaStreamEndCapture(e->stream, &graph));
+        cudaGraphExec_t exec;
+        LG_CHECK(cudaGraphInstantiate(&exec, graph, 0));
+        LG_CHECK(cudaGraphDestroy(graph));
+        it = e->graphs.emplace(key, exec).first;
+    }
+    LG_CHECK(cudaGraphLaunch(it->second, e->stream));
+}
+
+void upload_round(Engine *e, const int *toks, int n, int pos) {
+    LgRoundState *h = e->st_host;
+    h->pos = pos;
+    for (int j = 0; j < n; j++) h->toks[j] = toks[j];
+    // pos and toks[] are the first 1 + LG_MAXM ints of the state
+    LG_CHECK(cudaMemcpyAsync(e->st, h, sizeof(int) * (1 + n), cudaMemcpyHostToDevice, e->stream));
+}
+
+void check_err(Engine *e) {
+    int err = 0;
+    LG_CHECK(cudaMemcpyAsync(&err, e->err, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
+    LG_CHECK(cudaStreamSynchronize(e->stream));
+    if (err) { fprintf(stderr, "lg_b200: device status %d (a bounded wait inside a kernel gave up)\n", err); exit(1); }
+}
+
+// ------------------------------------------------------------------------------------------
+// draft head
+// ------------------------------------------------------------------------------------------
+DraftW *draft_build(Engine *e, struct mtp *t, const struct kvcache *kv) {
+    const struct model *m = e->m;
+    DraftW *d = new DraftW();
+    d->ni = t->n_inner; d->nb = t->n_bb; d->nff = t->n_ff; d->n_head = t->n_head; d->n_vocab = t->n_vocab;
+    d->eps = t->eps; d->base_full = t->base_full; d->base_swa = t->base_swa; d->softcap = t->softcap;
+    d->pre = build_wmat(e, {t->pre});
+    d->head = build_wmat(e, {t->head});
+    d->has_post = t->post && t->post->n_dims == 2 && (int)t->post->dims[0] == t->n_inner && (int)t->post->dims[1] == t->n_bb;
+    if (d->has_post) d->post = build_wmat(e, {t->post});
+    d->out_norm = upload_f32(t->out_norm, d->ni);
+    int qmax = 0, maxhd = 0;
+    for (int L = 0; L < t->n_layer; L++) {
+        const struct mtp_layer *s = &t->l[L];
+        DraftBlockW b{};
+        b.q = build_wmat(e, {s->q}); b.o = build_wmat(e, {s->o});
+        b.gateup = build_wmat(e, {s->gate, s->up}); b.down = build_wmat(e, {s->down});
+        b.attn_norm = upload_f32(s->attn_norm, d->ni); b.q_norm = upload_f32(s->q_norm, s->hd);
+        b.post_attn = upload_f32(s->post_attn, d->ni); b.ffn_norm = upload_f32(s->ffn_norm, d->ni);
+        b.post_ffw = upload_f32(s->post_ffw, d->ni);
+        b.out_scale = s->out_scale ? s->out_scale[0] : 1.0f;
+        b.hd = s->hd; b.local = s->local; b.src = s->src;
+        if (d->n_head * s->hd > qmax) qmax = d->n_head * s->hd;
+        if (s->hd > maxhd) maxhd = s->hd;
+        if (d->n_head % m->n_head_kv[s->src]) { fprintf(stderr, "lg_b200: draft head count does not divide the target's KV heads\n"); exit(1); }
+        d->blk.push_back(b);
+    }
+    d->cat = dalloc<float>(2 * d->nb); d->x = dalloc<float>(d->ni); d->hbuf = dalloc<float>(d->ni);
+    d->qbuf = dalloc<float>((size_t)LG_MAXM * (qmax + 16)); d->qrot = dalloc<float>(qmax);
+    d->obuf = dalloc<float>((size_t)e->max_ks * LG_MAXM * (std::max(d->ni, d->nb) + 16));
+    d->gu = dalloc<float>((size_t)2 * d->nff + 32);
+    int slots = tiles_for(0, kv->max_seq, 1);
+    d->n_slots_global = slots;
+    d->part = dalloc<float>((size_t)slots * d->n_head * (maxhd + 2));
+    d->amax_val = dalloc<float>((size_t)e->head_ctas * LG_MAXM); d->amax_idx = dalloc<int>((size_t)e->head_ctas * LG_MAXM);
+    d->best = dalloc<int>(LG_MAXM);
+    d->p_cat = panel_alloc(2 * d->nb); d->p_ni = panel_alloc(d->ni); d->p_attn = panel_alloc(qmax); d->p_ff = panel_alloc(d->nff);
+    return d;
+}
+
+// One draft: cat[0:nb] = embed(toks[slot-1]) * sqrt(nb); cat[nb:] = h_prev (first draft) or post(x) (chained);
+// the head's forward; argmax -> st->toks[slot].  Position = st->dpos.
+void enqueue_draft(Engine *e, DraftW *d, const struct kvcache *kv, int slot, bool chained) {
+    const struct model *m = e->m;
+    const struct config *c = &m->cfg;
+    cudaStream_t s = e->stream;
+    const int ni = d->ni, nb = d->nb;
+    lg_embed_rows<<<1, 256, 0, s>>>(e->head.wq, e->head.ws, e->head.wd, e->head.fmt, e->head.nkp, e->st->toks + (slot - 1),
+                                    sqrtf((float)nb), d->cat, 2 * nb);
+    LG_CHECK(cudaGetLastError()); e->launches++;
+    if (chained) {
+        // h_prev = post(x): x still holds the previous draft's normed hidden, p_ni its panel
+        launch_gemv(e, d->post, d->p_ni, 1, d->obuf, LG_EPI_STORE, 1);
+        lg_copy_f32<<<(nb + 255) / 256, 256, 0, s>>>(d->cat + nb, d->obuf, nb);
+    } else {
+        lg_copy_f32<<<(nb + 255) / 256, 256, 0, s>>>(d->cat + nb, e->h_prev, nb);
+    }
+    LG_CHECK(cudaGetLastError()); e->launches++;
+    lg_quant_rows<<<dim3((2 * nb / 32 + 7) / 8, 1), 256, 0, s>>>(d->cat, 2 * nb, 2 * nb, d->p_cat);
+    LG_CHECK(cudaGetLastError()); e->launches++;
+    launch_gemv(e, d->pre, d->p_cat, 1, d->obuf, LG_EPI_STORE, 1);
+    lg_copy_f32<<<(ni + 255) / 256, 256, 0, s>>>(d->x, d->obuf, ni);
+    LG_CHECK(cudaGetLastError()); e->launches++;
+    launch_norm(e, 1, d->x, ni, ni, d->eps, nullptr, 0, 0, 0, nullptr, 1.0f, d->blk[0].attn_norm, &d->p_ni, nullptr, 0);
+    for (size_t L = 0; L < d->blk.size(); L++) {
+        DraftBlockW &b = d->blk[L];
+        const int hd = b.hd, src = b.src, Hkv = m->n_head_kv[src];
+        launch_gemv(e, b.q, d->p_ni, 1, d->qbuf, LG_EPI_STORE, 1);
+        LgQkvArgs qa{};
+        qa.qkv = d->qbuf; qa.ld = b.q.ldo; qa.H = d->n_head; qa.Hkv = Hkv; qa.hd = hd; qa.has_v = 0; qa.owns_kv = 0;
+        qa.q_norm = b.q_norm; qa.k_norm = nullptr; qa.rope_div = nullptr;
+        qa.rope_base = b.local ? d->base_swa : d->base_full; qa.eps = d->eps; qa.pos = &e->st->dpos; qa.q_out = d->qrot;
+        lg_qkv_post_kernel<<<dim3(d->n_head, 1), hd / 2, 0, s>>>(qa);
+        LG_CHECK(cudaGetLastError()); e->launches++;
+        LgAttnArgs aa{};
+        aa.q = d->qrot; aa.kc = (const __half *)kv->k[src]; aa.vc = (const __half *)kv->v[src]; aa.seq = kv->seq[src];
+        aa.kv_dim = kv->kv_dim[src]; aa.H = d->n_head; aa.Hkv = Hkv; aa.hd = hd; aa.M = 1; aa.S = ATTN_TILE;
+        aa.window = (b.local && c->sliding_window > 0) ? c->sliding_window : 0;
+        aa.qpos_off = -1; aa.win_shrink = aa.window > 0 ? 1 : 0; aa.pos = &e->st->dpos;
+        aa.n_slots = d->n_slots_global; aa.part = d->part;
+        LgPanel pa = d->p_attn; pa.nsb = d->n_head * hd / 32;
+        aa.out = pa; aa.out_f32 = nullptr;
+        launch_attn(e, aa, tiles_for(aa.window, kv->max_seq, 1));
+        int ks_o = 1;
+        launch_gemv(e, b.o, pa, 1, d->obuf, LG_EPI_STORE, 0, 0, nullptr, nullptr, nullptr, &ks_o);
+        launch_norm(e, 1, d->x, ni, ni, d->eps, d->obuf, ks_o, (size_t)LG_MAXM * b.o.ldo, b.o.ldo, b.post_attn, 1.0f,
+                    b.ffn_norm, &d->p_ni, nullptr, 0);
+        launch_gemv(e, b.gateup, d->p_ni, 1, d->gu, LG_EPI_STORE, 1);
+        lg_geglu_kernel<<<dim3((d->nff / 32 + 7) / 8, 1), 256, 0, s>>>(d->gu, d->gu + d->nff, b.gateup.ldo, b.gateup.ldo, d->nff, d->p_ff);
+        LG_CHECK(cudaGetLastError()); e->launches++;
+        int ks_d = 1;
+        launch_gemv(e, b.down, d->p_ff, 1, d->obuf, LG_EPI_STORE, 0, 0, nullptr, nullptr, nullptr, &ks_d);
+        bool last = L + 1 == d->blk.size();
+        launch_norm(e, 1, d->x, ni, ni, d->eps, d->obuf, ks_d, (size_t)LG_MAXM * b.down.ldo, b.down.ldo, b.post_ffw, b.out_scale,
+                    last ? d->out_norm : d->blk[L + 1].attn_norm, &d->p_ni, last ? d->hbuf : nullptr, ni);
+    }
+    int gx = 0;
+    launch_gemv(e, d->head, d->p_ni, 1, nullptr, LG_EPI_HEAD, 1, d->softcap, nullptr, d->amax_val, d->amax_idx, nullptr, &gx);
+    lg_argmax_final<<<1, 256, 0, s>>>(d->amax_val, d->amax_idx, gx, d->best);
+    lg_store_draft<<<1, 1, 0, s>>>(e->st, slot, d->best);
+    LG_CHECK(cudaGetLastError()); e->launches += 2;
+}
+
+DraftW *draft_for(Engine *e, struct mtp *t, const struct kvcache *kv) {
+    if (t->cuda == (void *)-1) return nullptr;
+    if (e->draft && e->draft_owner == t) return e->draft;
+    if (e->draft) { draft_free(e->draft); e->draft = nullptr; }
+    e->draft = draft_build(e, t, kv);
+    e->draft_owner = t;
+    t->cuda = e->draft;
+    return e->draft;
+}
+
+void run_draft(Engine *e, DraftW *d, const struct kvcache *kv, int slot, bool chained) {
+    bind_kv(e, kv);
+    char key[32];
+    snprintf(key, sizeof key, "d%d_%d", slot, chained ? 1 : 0);
+    auto it = d->graphs.find(key);
+    if (it == d->graphs.end()) {
+        cudaGraph_t graph;
+        LG_CHECK(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeRelaxed));
+        enqueue_draft(e, d, kv, slot, chained);
+        LG_CHECK(cudaStreamEndCapture(e->stream, &graph));
+        cudaGraphExec_t exec;
+        LG_CHECK(cudaGraphInstantiate(&exec, graph, 0));
+        LG_CHECK(cudaGraphDestroy(graph));
+        it = d->graphs.emplace(key, exec).first;
+    }
+    LG_CHECK(cudaGraphLaunch(it->second, e->stream));
+}
+
+int spec_n(struct model *m, struct kvcache *kv, int n, const int *toks, int pos, int *out) {
+    Engine *e = engine_for(m);
+    upload_round(e, toks, n, pos);
+    int flags = F_HEAD | F_ACCEPT | (model_pick ? F_LOGITS : 0);
+    run_forward(e, kv, n, flags);
+    const struct config *c = &m->cfg;
+    if (model_pick) {
+        if (!e->pick_rows) e->pick_rows = (float *)malloc((size_t)LG_MAXM * c->n_vocab * sizeof(float));
+        for (int j = 0; j < n; j++)
+            LG_CHECK(cudaMemcpyAsync(e->pick_rows + (size_t)j * c->n_vocab, e->logits + (size_t)j * e->head.ldo,
+                                     (size_t)c->n_vocab * 4, cudaMemcpyDeviceToHost, e->stream));
+        LG_CHECK(cudaStreamSynchronize(e->stream));
+        for (int j = 0; j < n; j++) out[j] = model_pick(e->pick_rows + (size_t)j * c->n_vocab, c->n_vocab);
+        int adv = 1;
+        while (adv < n && out[adv - 1] == toks[adv]) adv++;
+        LG_CHECK(cudaMemcpyAsync(e->h_prev, e->hidden + (size_t)(adv - 1) * c->n_embd, (size_t)c->n_embd * 4,
+                                 cudaMemcpyDeviceToDevice, e->stream));
+        return adv;
+    }
+    LG_CHECK(cudaMemcpyAsync(e->st_host->out, e->st->out, sizeof(int) * (LG_MAXM + 1), cudaMemcpyDeviceToHost, e->stream));
+    LG_CHECK(cudaStreamSynchronize(e->stream));
+    for (int j = 0; j < n; j++) out[j] = e->st_host->out[j];
+    return e->st_host->adv;
+}
+
+}  // namespace
+
+// ==========================================================================================
+// exported backend symbols
+// ==========================================================================================
+extern "C" {
+
+int kvcache_init(struct kvcache *kv, const struct model *m, int max_seq) {
+    const struct config *c = &m->cfg;
+    kv->n_layer = c->n_layer; kv->max_seq = max_seq; kv->px_k = kv->px_v = nullptr;
+    kv->kv_dim = (int *)calloc(c->n_layer, sizeof(int));
+    kv->seq = (int *)calloc(c->n_layer, sizeof(int));
+    kv->f16 = (int *)calloc(c->n_layer, sizeof(int));
+    kv->k = (void **)calloc(c->n_layer, sizeof(void *));
+    kv->v = (void **)calloc(c->n_layer, sizeof(void *));
+    if (!kv->kv_dim || !kv->seq || !kv->f16 || !kv->k || !kv->v) return -1;
+    for (int L = 0; L < c->n_layer; L++) {
+        kv->kv_dim[L] = m->n_head_kv[L] * m->head_dim[L];
+        if (L >= c->n_kv_start) continue;
+        int seq = max_seq;
+        if (m->is_local[L] && c->sliding_window > 0 && c->sliding_window + RING_SPARE < max_seq)
+            seq = c->sliding_window + RING_SPARE;
+        kv->seq[L] = seq;
+        kv->f16[L] = 1;
+        size_t bytes = (size_t)seq * kv->kv_dim[L] * 2;
+        LG_CHECK(cudaMalloc(&kv->k[L], bytes)); LG_CHECK(cudaMemset(kv->k[L], 0, bytes));
+        LG_CHECK(cudaMalloc(&kv->v[L], bytes)); LG_CHECK(cudaMemset(kv->v[L], 0, bytes));
+    }
+    return 0;
+}
+
+void kvcache_free(struct kvcache *kv) {
+    if (!kv || !kv->k) return;
+    if (g_eng && g_eng->kv_bound == kv) {
+        cudaStreamSynchronize(g_eng->stream);
+        free_graphs(g_eng->graphs);
+        if (g_eng->draft) free_graphs(g_eng->draft->graphs);
+        g_eng->kv_bound = nullptr;
+    }
+    for (int L = 0; L < kv->n_layer; L++) { cudaFree(kv->k[L]); cudaFree(kv->v[L]); }
+    if (kv->px_k) for (int L = 0; L < kv->n_layer; L++) { cudaFree(kv->px_k[L]); cudaFree(kv->px_v[L]); }
+    free(kv->px_k); free(kv->px_v); free(kv->k); free(kv->v); free(kv->kv_dim); free(kv->seq); free(kv->f16);
+    kv->k = kv->v = kv->px_k = kv->px_v = nullptr;
+    kv->kv_dim = kv->seq = kv->f16 = nullptr;
+}
+
+void kvcache_save_prefix(struct kvcache *kv, int n) {
+    kv->px_k = (void **)calloc(kv->n_layer, sizeof(void *));
+    kv->px_v = (void **)calloc(kv->n_layer, sizeof(void *));
+    if (!kv->px_k || !kv->px_v) return;
+    if (g_eng) LG_CHECK(cudaStreamSynchronize(g_eng->stream));
+    for (int L = 0; L < kv->n_layer; L++) {
+        if (!kv->k[L]) continue;
+        int rows = n < kv->seq[L] ? n : kv->seq[L];
+        size_t bytes = (size_t)rows * kv->kv_dim[L] * 2;
+        LG_CHECK(cudaMalloc(&kv->px_k[L], bytes)); LG_CHECK(cudaMalloc(&kv->px_v[L], bytes));
+        LG_CHECK(cudaMemcpy(kv->px_k[L], kv->k[L], bytes, cudaMemcpyDeviceToDevice));
+        LG_CHECK(cudaMemcpy(kv->px_v[L], kv->v[L], bytes, cudaMemcpyDeviceToDevice));
+    }
+}
+
+void kvcache_restore_prefix(struct kvcache *kv, int n) {
+    if (!kv->px_k) return;
+    cudaStream_t s = g_eng ? g_eng->stream : 0;
+    for (int L = 0; L < kv->n_layer; L++) {
+        if (!kv->px_k[L]) continue;
+        int rows = n < kv->seq[L] ? n : kv->seq[L];
+        size_t bytes = (size_t)rows * kv->kv_dim[L] * 2;
+        LG_CHECK(cudaMemcpyAsync(kv->k[L], kv->px_k[L], bytes, cudaMemcpyDeviceToDevice, s));
+        LG_CHECK(cudaMemcpyAsync(kv->v[L], kv->px_v[L], bytes, cudaMemcpyDeviceToDevice, s));
+    }
+}
+
+void model_forward(struct model *m, struct kvcache *kv, int token, int pos, float *logits) {
+    Engine *e = engine_for(m);
+    upload_round(e, &token, 1, pos);
+    run_forward(e, kv, 1, logits ? (F_HEAD | F_LOGITS | F_ACCEPT) : 0);
+    if (logits) LG_CHECK(cudaMemcpyAsync(logits, e->logits, (size_t)m->cfg.n_vocab * 4, cudaMemcpyDeviceToHost, e->stream));
+    if (logits && m->last_hidden)
+        LG_CHECK(cudaMemcpyAsync(m->last_hidden, e->hidden, (size_t)m->cfg.n_embd * 4, cudaMemcpyDeviceToHost, e->stream));
+    check_err(e);
+}
+
+int model_forward_next(struct model *m, struct kvcache *kv, int token, int pos) {
+    int out[LG_MAXM];
+    spec_n(m, kv, 1, &token, pos, out);
+    return out[0];
+}
+
+void model_prefill(struct model *m, struct kvcache *kv, const int *tokens, int n, int pos0) {
+    Engine *e = engine_for(m);
+    for (int i = 0; i < n; i += LG_MAXM) {
+        int b = n - i < LG_MAXM ? n - i : LG_MAXM;
+        upload_round(e, tokens + i, b, pos0 + i);
+        run_forward(e, kv, b, 0);
+        LG_CHECK(cudaStreamSynchronize(e->stream));      // st_host is reused by the next upload
+    }
+}
+
+void model_prefill_embd(struct model *m, struct kvcache *kv, const float *rows, int n, int pos0) {
+    (void)m; (void)kv; (void)rows; (void)n; (void)pos0;
+    fprintf(stderr, "lg_b200: model_prefill_embd (media rows) is outside the speculative-decode path and not built\n");
+    exit(1);
+}
+void model_prefill_mixed(struct model *m, struct kvcache *kv, const float *rows, const int *ids, int n, int pos0) {
+    for (int i = 0; i < n; i++) if (ids[i] < 0) { model_prefill_embd(m, kv, rows, n, pos0); return; }
+    model_prefill(m, kv, ids, n, pos0);
+}
+void model_prefill_reserve(void) {}
+
+int model_forward_spec(struct model *m, struct kvcache *kv, const int *toks, int pos, int *out) {
+    return spec_n(m, kv, LG_MTP_N, toks, pos, out);
+}
+
+int lg_forward_spec_n(struct model *m, struct kvcache *kv, int n, const int *toks, int pos, int *out) {
+    if (n < 1 || n > LG_MAXM) return -1;
+    return spec_n(m, kv, n, toks, pos, out);
+}
+
+int mtp_draft_device(struct mtp *t, const struct model *m, const struct kvcache *kv, int token, int pos) {
+    Engine *e = engine_for(m);
+    DraftW *d = draft_for(e, t, kv);
+    if (!d) return -1;
+    LgRoundState *h = e->st_host;
+    h->pos = pos; h->toks[0] = token;
+    LG_CHECK(cudaMemcpyAsync(e->st, h, sizeof(int) * 2, cudaMemcpyHostToDevice, e->stream));
+    LG_CHECK(cudaMemcpyAsync(&e->st->dpos, &h->pos, sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    run_draft(e, d, kv, 1, false);
+    LG_CHECK(cudaMemcpyAsync(&h->toks[1], &e->st->toks[1], sizeof(int), cudaMemcpyDeviceToHost, e->stream));
+    LG_CHECK(cudaStreamSynchronize(e->stream));
+    return h->toks[1];
+}
+
+// token sits at pos-1's successor slot: the caller passes (previous draft, its position)
+int mtp_draft_chain_device(struct mtp *t, const struct model *m, const struct kvcache *kv, int token, int pos) {
+    Engine *e = engine_for(m);
+    DraftW *d = (t->cuda && t->cuda != (void *)-1) ? draft_for(e, t, kv) : nullptr;
+    if (!d || !d->has_post) return -1;
+    LgRoundState *h = e->st_host;
+    int slot = pos - h->pos + 1;                         // chained draft j lands in toks[j], drafted at pos + j - 1
+    if (slot < 2 || slot >= LG_MAXM) return -1;
+    h->toks[slot - 1] = token; h->dpos = pos;
+    LG_CHECK(cudaMemcpyAsync(&e->st->toks[slot - 1], &h->toks[slot - 1], sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    LG_CHECK(cudaMemcpyAsync(&e->st->dpos, &h->dpos, sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    run_draft(e, d, kv, slot, true);
+    LG_CHECK(cudaMemcpyAsync(&h->toks[slot], &e->st->toks[slot], sizeof(int), cudaMemcpyDeviceToHost, e->stream));
+    LG_CHECK(cudaStreamSynchronize(e->stream));
+    return h->toks[slot];
+}
+
+void mtp_free_device(struct mtp *t) {
+    if (!t || !t->cuda || t->cuda == (void *)-1) return;
+    if (g_eng && g_eng->draft == t->cuda) { draft_free(g_eng->draft); g_eng->draft = nullptr; g_eng->draft_owner = nullptr; }
+    t->cuda = nullptr;
+}
+
+// ---- extensions beyond the reference seam ---------------------------------------------------
+
+void lg_engine_release(void) { if (g_eng) { engine_free(g_eng); g_eng = nullptr; } }
+
+long long lg_weight_bytes(struct model *m) { return (long long)engine_for(m)->weight_bytes; }
+
+int lg_last_hidden(struct model *m, float *out) {
+    Engine *e = engine_for(m);
+    LG_CHECK(cudaMemcpyAsync(out, e->h_prev, (size_t)m->cfg.n_embd * 4, cudaMemcpyDeviceToHost, e->stream));
+    LG_CHECK(cudaStreamSynchronize(e->stream));
+    return 0;
+}
+
+int lg_kv_row(struct model *m, struct kvcache *kv, int layer, int pos, float *k, float *v) {
+    Engine *e = engine_for(m);
+    if (layer < 0 || layer >= kv->n_layer || !kv->k[layer]) return 0;
+    int d = kv->kv_dim[layer];
+    std::vector<__half> hk(d), hv(d);
+    LG_CHECK(cudaStreamSynchronize(e->stream));
+    size_t off = (size_t)(pos % kv->seq[layer]) * d;
+    LG_CHECK(cudaMemcpy(hk.data(), (__half *)kv->k[layer] + off, d * 2, cudaMemcpyDeviceToHost));
+    LG_CHECK(cudaMemcpy(hv.data(), (__half *)kv->v[layer] + off, d * 2, cudaMemcpyDeviceToHost));
+    for (int i = 0; i < d; i++) { k[i] = __half2float(hk[i]); v[i] = __half2float(hv[i]); }
+    return d;
+}
+
+// Device-resident rounds: no host synchronisation between rounds.  Starting from chosen token
+// `first` at position `pos`, run `n_rounds` rounds of [drafts -> verify of width n -> accept]
+// back to back on the stream.  Drafts come from the head `t` (mode 1), from the replay table set
+// with lg_set_replay (mode 2: the head still runs when `t` is given, its tokens are overridden),
+// and n == 1 is plain greedy decode.  Emitted tokens accumulate in a device log; the call
+// returns after ONE synchronisation at the end.  Returns the number of tokens emitted.
+int lg_set_replay(struct model *m, const int *replay, int n) {
+    Engine *e = engine_for(m);
+    LG_CHECK(cudaStreamSynchronize(e->stream));
+    cudaFree(e->replay); e->replay = nullptr; e->n_replay = 0;
+    if (n > 0) {
+        e->replay = dalloc<int>(n);
+        LG_CHECK(cudaMemcpy(e->replay, replay, (size_t)n * 4, cudaMemcpyHostToDevice));
+        e->n_replay = n;
+    }
+    return 0;
+}
+
+int lg_rounds_begin(struct model *m, int first, int pos, int n_emitted) {
+    Engine *e = engine_for(m);
+    LgRoundState *h = e->st_host;
+    memset(h, 0, sizeof *h);
+    h->pos = pos; h->toks[0] = first; h->n_emitted = n_emitted;
+    LG_CHECK(cudaMemcpyAsync(e->st, h, sizeof *h, cudaMemcpyHostToDevice, e->stream));
+    LG_CHECK(cudaStreamSynchronize(e->stream));
+    return 0;
+}
+
+int lg_rounds_enqueue(struct model *m, struct kvcache *kv, struct mtp *t, int n, int mode, int n_rounds) {
+    Engine *e = engine_for(m);
+    if (n < 1 || n > LG_MAXM) return -1;
+    DraftW *d = (t && n > 1) ? draft_for(e, t, kv) : nullptr;
+    if (mode == 1 && n > 1 && !d) return -1;
+    bind_kv(e, kv);
+    char key[48];
+    snprintf(key, sizeof key, "r%d_%d_%d", n, mode, d ? 1 : 0);
+    auto it = e->graphs.find(key);
+    if (it == e->graphs.end()) {
+        cudaGraph_t graph;
+        e->launches = 0;
+        LG_CHECK(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeRelaxed));
+        if (d) {
+            for (int j = 1; j < n; j++) {
+                if (j >= 2 && !d->has_post) break;
+                lg_set_draft_pos<<<1, 1, 0, e->stream>>>(e->st, j - 1);
+                e->launches++;
+                enqueue_draft(e, d, kv, j, j >= 2);
+            }
+        }
+        if (mode == 2 && n > 1) {
+            lg_replay_drafts_kernel<<<1, 32, 0, e->stream>>>(e->st, n, e->replay, e->n_replay);
+            e->launches++;
+        }
+        enqueue_forward(e, kv, n, F_HEAD | F_ACCEPT | F_ADVANCE);
+        LG_CHECK(cudaStreamEndCapture(e->stream, &graph));
+        cudaGraphExec_t exec;
+        LG_CHECK(cudaGraphInstantiate(&exec, graph, 0));
+        LG_CHECK(cudaGraphDestroy(graph));
+        it = e->graphs.emplace(key, exec).first;
+        e->round_launches = e->launches;
+    }
+    for (int r = 0; r < n_rounds; r++) LG_CHECK(cudaGraphLaunch(it->second, e->stream));
+    return 0;
+}
+
+// Wait for the enqueued rounds; copies the state and up to `cap` log entries starting at `from`.
+int lg_rounds_collect(struct model *m, int *tokens, int from, int cap, int *stats /* pos, n_emitted, n_draft, n_accept */) {
+    Engine *e = engine_for(m);
+    LG_CHECK(cudaMemcpyAsync(e->st_host, e->st, sizeof(LgRoundState), cudaMemcpyDeviceToHost, e->stream));
+    check_err(e);
+    LgRoundState *h = e->st_host;
+    int n = h->n_emitted - from;
+    if (n > cap) n = cap;
+    if (n > 0 && tokens) LG_CHECK(cudaMemcpy(tokens, e->log + from, (size_t)n * 4, cudaMemcpyDeviceToHost));
+    if (stats) { stats[0] = h->pos; stats[1] = h->n_emitted; stats[2] = h->n_draft; stats[3] = h->n_accept; }
+    return n > 0 ? n : 0;
+}
+
+void *lg_stream(struct model *m) { return (void *)engine_for(m)->stream; }
+long long lg_round_launches(struct model *m) { return engine_for(m)->round_launches; }
+
+}  // extern "C"
+#include "lg_capi.cuh"

@@ -26,11 +26,22 @@ def port_lib_path() -> str:
 
 class _Oracle:
     prefix = ""
+    fresh_copy = False
 
     def __init__(self, lib_path: str, target: str, head: str | None, max_seq: int, kv_f16_all: bool):
         if not os.path.exists(lib_path):
             raise FileNotFoundError(lib_path)
-        self.lib = L = C.CDLL(lib_path)
+        if self.fresh_copy:
+            # The reference keeps per-process statics sized by the first model it sees (its greedy
+            # pick buffer, src/cpu/model-cpu.c:466-470), so every session gets its own image.
+            import shutil, tempfile
+            fd, tmp = tempfile.mkstemp(suffix=".so", prefix="libref_")
+            os.close(fd)
+            shutil.copyfile(lib_path, tmp)
+            self.lib = L = C.CDLL(tmp)
+            os.unlink(tmp)
+        else:
+            self.lib = L = C.CDLL(lib_path)
         p = self.prefix
         f = lambda name: getattr(L, p + name)
         f("open").restype = C.c_void_p
@@ -117,6 +128,7 @@ class _Oracle:
 
 class RefOracle(_Oracle):
     prefix = "ref_"
+    fresh_copy = True
 
     def __init__(self, target, head=None, max_seq=4096, kv_f16_all=False, mtp_n=4):
         super().__init__(ref_lib_path(mtp_n), target, head, max_seq, kv_f16_all)

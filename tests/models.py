@@ -1,0 +1,38 @@
+"""Named, seeded test models (shapes small enough for the CPU oracle to finish in seconds)."""
+import dataclasses
+import os
+
+from tests.conftest import synth_module
+
+
+def shapes():
+    s = synth_module()
+    tiny = s.TINY
+    return {
+        # the benchmark plan's tiny configuration (4 layers, hd 64, PLE 64) and its 1-block head
+        "tiny": (tiny, s.TINY_HEAD, 0, 1),
+        # same, q-norm weight hd^-0.5: a well-conditioned twin for end-to-end logit gates
+        "tiny_cond": (dataclasses.replace(tiny, q_norm_scale=64 ** -0.5), s.TINY_HEAD, 0, 1),
+        # every optional branch: softcap, layer_output_scale, rope_freqs, V = K projection, KV sharing
+        "var": (dataclasses.replace(tiny, n_layer=8, shared_kv_layers=4, softcap=30.0, layer_output_scale=True,
+                                    rope_freqs=True, drop_attn_v=True, q_norm_scale=64 ** -0.5),
+                dataclasses.replace(s.TINY_HEAD, softcap=20.0, layer_output_scale=True, n_layer=2), 3, 4),
+        # head size 256 with grouped queries, short window (ring wraps early), no PLE
+        "mid": (s.TargetShape(n_layer=6, n_embd=512, n_head=8, n_head_kv=2, head_dim=256, n_ff=2048, n_vocab=8192,
+                              window=64, local_per_global=2, ple=0, q_norm_scale=256 ** -0.5),
+                s.HeadShape(n_layer=2, n_inner=256, n_head=8, n_ff=512), 5, 6),
+        # q4_K weights (super-blocks of 256)
+        "mid_k": (s.TargetShape(n_layer=3, n_embd=512, n_head=8, n_head_kv=2, head_dim=256, n_ff=2048, n_vocab=8192,
+                                window=64, local_per_global=2, ple=0, q_norm_scale=256 ** -0.5, wtype=s.Q4_K),
+                  None, 7, 8),
+        # all-zero weights: every logit ties at 0, the argmax must be index 0
+        "zero": (dataclasses.replace(tiny, sigma=0.0, ple=0), None, 9, 10),
+    }
+
+
+def build(name: str, cache: str):
+    s = synth_module()
+    target, head, seed_t, seed_h = shapes()[name]
+    tp = s.cached(cache, f"{name}.gguf", s.write_target, target, seed_t)
+    hp = s.cached(cache, f"{name}_head.gguf", s.write_head, head, target, seed_h) if head is not None else None
+    return tp, hp
