@@ -28,7 +28,7 @@ extern "C" int lg_dequant_host(int type, const void *blocks, int n_rows, int k, 
     LG_CHECK(cudaMalloc(&d_src, bytes));
     LG_CHECK(cudaMalloc(&d_out, (size_t)n_rows * k * 4));
     LG_CHECK(cudaMemcpyAsync(d_src, blocks, bytes, cudaMemcpyHostToDevice, e->stream));
-    lg_dequant_rows<<<n_rows, 256, 0, e->stream>>>(d_src, type, k, nullptr, 0, 1.0f, d_out, k);
+    lg_dequant_rows<<<n_rows, 256, 0, e->stream>>>(d_src, type, k, nullptr, n_rows, 0, 1.0f, d_out, k);
     LG_CHECK(cudaGetLastError());
     LG_CHECK(cudaMemcpyAsync(out, d_out, (size_t)n_rows * k * 4, cudaMemcpyDeviceToHost, e->stream));
     LG_CHECK(cudaStreamSynchronize(e->stream));

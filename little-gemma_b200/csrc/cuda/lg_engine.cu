@@ -99,7 +99,15 @@ struct Engine {
 
 Engine *g_eng = nullptr;
 
-template <typename T> T *dalloc(size_t n) { T *p = nullptr; LG_CHECK(cudaMalloc(&p, n * sizeof(T) > 0 ? n * sizeof(T) : 16)); LG_CHECK(cudaMemset(p, 0, n * sizeof(T))); return p; }
+// Zero-filled device allocation.  The fill runs on the legacy stream, which does not order against the
+// engine's non-blocking stream, so wait for it before anyone can use the buffer.
+template <typename T> T *dalloc(size_t n) {
+    T *p = nullptr;
+    LG_CHECK(cudaMalloc(&p, n * sizeof(T) > 0 ? n * sizeof(T) : 16));
+    LG_CHECK(cudaMemset(p, 0, n * sizeof(T)));
+    LG_CHECK(cudaDeviceSynchronize());
+    return p;
+}
 
 LgPanel panel_alloc(int k) {
     LgPanel P;
@@ -110,9 +118,17 @@ LgPanel panel_alloc(int k) {
 }
 void panel_free(LgPanel &P) { cudaFree(P.q); cudaFree(P.s); P.q = nullptr; P.s = nullptr; }
 
+// Host -> device copy that is complete on return.  A pageable-source cudaMemcpy may return while
+// its last DMA is still in flight on the legacy stream, which the engine's non-blocking stream does
+// not order against, so wait for the device.
+void h2d_sync(void *dst, const void *src, size_t bytes) {
+    LG_CHECK(cudaMemcpy(dst, src, bytes, cudaMemcpyHostToDevice));
+    LG_CHECK(cudaDeviceSynchronize());
+}
+
 float *upload_f32(const float *src, size_t n) {
     float *d = dalloc<float>(n);
-    LG_CHECK(cudaMemcpy(d, src, n * 4, cudaMemcpyHostToDevice));
+    h2d_sync(d, src, n * 4);
     return d;
 }
 
@@ -157,7 +173,7 @@ WMat build_wmat(Engine *e, std::vector<const struct gguf_tensor *> parts) {
         size_t bytes = ggml_nbytes(t->type, (int64_t)rows * W.k);
         uint8_t *stage = nullptr;
         LG_CHECK(cudaMalloc(&stage, bytes));
-        LG_CHECK(cudaMemcpy(stage, t->data, bytes, cudaMemcpyHostToDevice));
+        h2d_sync(stage, t->data, bytes);
         int rts = (rows + 15) / 16;
         size_t threads = (size_t)rts * W.nkp * 32;
         size_t toff = (size_t)(row_off / 16) * W.nkp;
@@ -201,6 +217,8 @@ GemvPlan plan_gemv(const Engine *e, const WMat &W, int np, int want_ks) {
     GemvPlan p;
     p.ks = want_ks;
     if (p.ks <= 0) { p.ks = 1; while (W.nkp / p.ks > 72 && p.ks < e->max_ks && W.nkp % (p.ks * 2) == 0) p.ks *= 2; }
+    if (p.ks > e->max_ks) p.ks = e->max_ks;
+    if (p.ks > W.nkp) p.ks = W.nkp;
     int nkp_s = (W.nkp + p.ks - 1) / p.ks + 1;
     p.smem = (size_t)np * nkp_s * 2 * (256 + 32) + (size_t)LG_GEMV_WARPS * np * 64 * 4 + 16;
     int ctas = e->sm_count * 2;
@@ -303,7 +321,7 @@ Engine *engine_for(const struct model *m) {
         size_t bytes = ggml_nbytes(pte->type, (int64_t)pte->dims[0] * pte->dims[1]);
         if (!bytes) { fprintf(stderr, "lg_b200: per_layer_token_embd has unsupported type %u\n", pte->type); exit(1); }
         LG_CHECK(cudaMalloc(&e->ple_table, bytes));
-        LG_CHECK(cudaMemcpy(e->ple_table, pte->data, bytes, cudaMemcpyHostToDevice));
+        h2d_sync(e->ple_table, pte->data, bytes);
         e->ple_table_type = (int)pte->type;
         e->pmp = build_wmat(e, {find_t(g, -1, "per_layer_model_proj.weight")});
         e->ple_proj_norm = upload_norm(g, -1, "per_layer_proj_norm.weight");
@@ -447,12 +465,12 @@ void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags) {
     cudaStream_t s = e->stream;
     const int *d_toks = e->st->toks, *d_pos = &e->st->pos;
 
-    lg_embed_rows<<<M, 256, 0, s>>>(e->head.wq, e->head.ws, e->head.wd, e->head.fmt, e->head.nkp, d_toks,
+    lg_embed_rows<<<M, 256, 0, s>>>(e->head.wq, e->head.ws, e->head.wd, e->head.fmt, e->head.nkp, e->head.m, d_toks,
                                     sqrtf((float)ne), e->x, ne);
     LG_CHECK(cudaGetLastError()); e->launches++;
     const int total = ple * nl;
     if (e->has_ple) {
-        lg_dequant_rows<<<M, 256, 0, s>>>(e->ple_table, e->ple_table_type, total, d_toks, 0, sqrtf((float)ple), e->tokrow, total);
+        lg_dequant_rows<<<M, 256, 0, s>>>(e->ple_table, e->ple_table_type, total, d_toks, c->n_vocab, 0, sqrtf((float)ple), e->tokrow, total);
         LG_CHECK(cudaGetLastError());
         lg_quant_rows<<<dim3((ne / 32 + 7) / 8, M), 256, 0, s>>>(e->x, ne, ne, e->p_ne);
         LG_CHECK(cudaGetLastError());
@@ -616,8 +634,8 @@ void enqueue_draft(Engine *e, DraftW *d, const struct kvcache *kv, int slot, boo
     const struct config *c = &m->cfg;
     cudaStream_t s = e->stream;
     const int ni = d->ni, nb = d->nb;
-    lg_embed_rows<<<1, 256, 0, s>>>(e->head.wq, e->head.ws, e->head.wd, e->head.fmt, e->head.nkp, e->st->toks + (slot - 1),
-                                    sqrtf((float)nb), d->cat, 2 * nb);
+    lg_embed_rows<<<1, 256, 0, s>>>(e->head.wq, e->head.ws, e->head.wd, e->head.fmt, e->head.nkp, e->head.m,
+                                    e->st->toks + (slot - 1), sqrtf((float)nb), d->cat, 2 * nb);
     LG_CHECK(cudaGetLastError()); e->launches++;
     if (chained) {
         // h_prev = post(x): x still holds the previous draft's normed hidden, p_ni its panel
@@ -753,6 +771,7 @@ int kvcache_init(struct kvcache *kv, const struct model *m, int max_seq) {
         LG_CHECK(cudaMalloc(&kv->k[L], bytes)); LG_CHECK(cudaMemset(kv->k[L], 0, bytes));
         LG_CHECK(cudaMalloc(&kv->v[L], bytes)); LG_CHECK(cudaMemset(kv->v[L], 0, bytes));
     }
+    LG_CHECK(cudaDeviceSynchronize());        // the fills ran on the legacy stream; forwards use their own
     return 0;
 }
 
@@ -784,6 +803,7 @@ void kvcache_save_prefix(struct kvcache *kv, int n) {
         LG_CHECK(cudaMemcpy(kv->px_k[L], kv->k[L], bytes, cudaMemcpyDeviceToDevice));
         LG_CHECK(cudaMemcpy(kv->px_v[L], kv->v[L], bytes, cudaMemcpyDeviceToDevice));
     }
+    LG_CHECK(cudaDeviceSynchronize());
 }
 
 void kvcache_restore_prefix(struct kvcache *kv, int n) {
@@ -919,7 +939,7 @@ int lg_set_replay(struct model *m, const int *replay, int n) {
     cudaFree(e->replay); e->replay = nullptr; e->n_replay = 0;
     if (n > 0) {
         e->replay = dalloc<int>(n);
-        LG_CHECK(cudaMemcpy(e->replay, replay, (size_t)n * 4, cudaMemcpyHostToDevice));
+        h2d_sync(e->replay, replay, (size_t)n * 4);
         e->n_replay = n;
     }
     return 0;
@@ -950,7 +970,11 @@ int lg_rounds_enqueue(struct model *m, struct kvcache *kv, struct mtp *t, int n,
         LG_CHECK(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeRelaxed));
         if (d) {
             for (int j = 1; j < n; j++) {
-                if (j >= 2 && !d->has_post) break;
+                if (j >= 2 && !d->has_post) {           // no chaining: pad like the reference caller does
+                    lg_pad_drafts<<<1, 1, 0, e->stream>>>(e->st, j, n);
+                    e->launches++;
+                    break;
+                }
                 lg_set_draft_pos<<<1, 1, 0, e->stream>>>(e->st, j - 1);
                 e->launches++;
                 enqueue_draft(e, d, kv, j, j >= 2);

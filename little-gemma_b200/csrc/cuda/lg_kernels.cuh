@@ -222,9 +222,10 @@ __global__ void lg_repack_q4_K(const uint8_t *__restrict__ src, uint4 *__restric
 // ---------------------------------------------------------------------------------------------
 // out[i][0..k) = scale * decode(row ids[i]) for q4_0 (type 2) / q4_K (type 12) / f32 (0) / f16 (1)
 __global__ void lg_dequant_rows(const uint8_t *__restrict__ src, int type, int k, const int *__restrict__ ids,
-                                int row0, float scale, float *__restrict__ out, int ldo) {
+                                int n_rows, int row0, float scale, float *__restrict__ out, int ldo) {
     int r = blockIdx.x;
     long long row = ids ? (long long)ids[r] : (long long)row0 + r;
+    row = row < 0 ? 0 : (row >= n_rows ? n_rows - 1 : row);        // an out-of-range id must not read outside the table
     float *o = out + (size_t)r * ldo;
     if (type == 2) {
         const uint8_t *base = src + (size_t)row * (k / 32) * 18;
@@ -444,10 +445,10 @@ __global__ void lg_argmax_final(const float *__restrict__ val, const int *__rest
 // x[tok][0..ne) = decode(token_embd row toks[tok]) * sqrt(ne) from the TILE-MAJOR copy (the same
 // matrix is the output head).  Bit-identical to decoding the file row: value = d * (nibble-8).
 __global__ void lg_embed_rows(const uint4 *__restrict__ wq, const uint2 *__restrict__ ws, const uint2 *__restrict__ wd,
-                              int fmt, int nkp, const int *__restrict__ toks, float scale,
+                              int fmt, int nkp, int n_rows, const int *__restrict__ toks, float scale,
                               float *__restrict__ out, int ldo) {
     int tok = blockIdx.x;
-    int row = toks[tok];
+    int row = min(max(toks[tok], 0), n_rows - 1);               // an out-of-range id must not read outside the table
     int rt = row >> 4, r = row & 15, g = r & 7, hi8 = r >> 3;
     const uint32_t *wq32 = (const uint32_t *)wq;
     for (int e = threadIdx.x; e < nkp * 64; e += blockDim.x) {
@@ -825,4 +826,6 @@ __global__ void lg_copy_f32(float *__restrict__ dst, const float *__restrict__ s
     if (i < n) dst[i] = src[i];
 }
 __global__ void lg_set_draft_pos(LgRoundState *st, int j) { st->dpos = st->pos + j; }
+// slots a head cannot draft repeat the previous token, so the verify simply rejects them
+__global__ void lg_pad_drafts(LgRoundState *st, int from, int M) { for (int j = from; j < M; j++) st->toks[j] = st->toks[j - 1]; }
 __global__ void lg_store_draft(LgRoundState *st, int j, const int *best) { st->toks[j] = *best; }

@@ -1,0 +1,150 @@
+"""GPU parity tests of the individual kernels, called through the C ABI."""
+import numpy as np
+import pytest
+
+from tests.conftest import model_files, synth_module
+
+pytestmark = pytest.mark.gpu
+
+
+def _oracle():
+    from oracle.pyref import PortOracle
+    tp, _ = model_files("tiny")
+    return PortOracle(tp, None, 64, False, 4)
+
+
+# ---- E1: q4 decode is bit-exact ---------------------------------------------------------
+
+def test_dequant_bit_exact_golden(lg, golden):
+    s = synth_module()
+    a = lg.dequant(s.Q4_0, golden["kat_q4_0_raw"], 1, 2048).reshape(-1)
+    b = lg.dequant(s.Q4_K, golden["kat_q4_K_raw"], 1, 2048).reshape(-1)
+    assert np.array_equal(a.view(np.uint32), golden["kat_q4_0_out"].view(np.uint32))
+    assert np.array_equal(b.view(np.uint32), golden["kat_q4_K_out"].view(np.uint32))
+
+
+@pytest.mark.parametrize("wtype", ["q4_0", "q4_K"])
+def test_dequant_bit_exact_random_blocks(lg, port_built, wtype):
+    s = synth_module()
+    rng = np.random.default_rng(5)
+    o = _oracle()
+    if wtype == "q4_0":
+        # all byte patterns incl. subnormal / negative / huge f16 scales (inf and nan scales excluded)
+        raw = rng.integers(0, 256, size=(4096, 18), dtype=np.uint8)
+        raw[:, 1] = np.where((raw[:, 1] & 0x7C) == 0x7C, raw[:, 1] & 0x83, raw[:, 1])
+        t, n = s.Q4_0, 4096 * 32
+    else:
+        raw = rng.integers(0, 256, size=(512, 144), dtype=np.uint8)
+        for c in (1, 3):
+            raw[:, c] = np.where((raw[:, c] & 0x7C) == 0x7C, raw[:, c] & 0x83, raw[:, c])
+        t, n = s.Q4_K, 512 * 256
+    want = o.dequant(t, raw.reshape(-1), n)
+    o.close()
+    got = lg.dequant(t, raw.reshape(-1), 8, n // 8).reshape(-1)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+# ---- the small-M matmul ------------------------------------------------------------------
+
+def _ref_matvec(w_f32, x):
+    return (w_f32.astype(np.float64) @ x.astype(np.float64).T).T
+
+
+@pytest.mark.parametrize("wtype,m,k", [("q4_0", 256, 256), ("q4_0", 1024, 3840), ("q4_0", 80, 15360),
+                                        ("q4_0", 4096, 64), ("q4_K", 512, 1024), ("q4_K", 48, 15360)])
+@pytest.mark.parametrize("M", [1, 4, 5, 8])
+def test_gemv_matches_oracle(lg, port_built, wtype, m, k, M):
+    s = synth_module()
+    rng = np.random.default_rng(m + k + M)
+    o = _oracle()
+    if wtype == "q4_0":
+        raw, t = s.quantize_q4_0(rng.standard_normal(m * k).astype(np.float32) * 0.02), s.Q4_0
+    else:
+        raw, t = s.random_q4_K(rng, m * k), s.Q4_K
+    w = o.dequant(t, raw, m * k).reshape(m, k)
+    o.close()
+    # heavy-tailed activations: per-group scales must cope with a few large entries
+    x = (rng.standard_normal((M, k)) * np.exp(rng.standard_normal((M, k)))).astype(np.float32)
+    want = _ref_matvec(w, x)
+    got = lg.gemv(t, raw, m, k, x)
+    scale = np.abs(want).max()
+    err = np.abs(got - want).max() / scale
+    assert err < 2e-4, err                     # 16-bit activations: ~1e-5 typical
+    # k-sliced partial sums add up to the same thing (within f32 re-association)
+    if k >= 512:
+        got2 = lg.gemv(t, raw, m, k, x, kslices=2)
+        assert np.abs(got2 - want).max() / scale < 2e-4
+
+
+def test_gemv_column_is_independent_of_block_width(lg):
+    """Row j of an M-wide block is bit-identical to the same row run alone (MTP == plain)."""
+    s = synth_module()
+    rng = np.random.default_rng(3)
+    m, k = 512, 3840
+    raw = s.quantize_q4_0(rng.standard_normal(m * k).astype(np.float32) * 0.02)
+    x = rng.standard_normal((8, k)).astype(np.float32)
+    full = lg.gemv(s.Q4_0, raw, m, k, x)
+    for j in (0, 3, 4, 7):
+        alone = lg.gemv(s.Q4_0, raw, m, k, x[j:j + 1])
+        assert np.array_equal(alone[0].view(np.uint32), full[j].view(np.uint32))
+    four = lg.gemv(s.Q4_0, raw, m, k, x[:4])
+    assert np.array_equal(four.view(np.uint32), full[:4].view(np.uint32))
+
+
+def test_gemv_zero_and_ragged(lg):
+    s = synth_module()
+    rng = np.random.default_rng(9)
+    m, k = 40, 128                               # rows not a multiple of 16
+    raw = s.quantize_q4_0(rng.standard_normal(m * k).astype(np.float32))
+    x = np.zeros((2, k), dtype=np.float32)
+    x[1] = rng.standard_normal(k)
+    got = lg.gemv(s.Q4_0, raw, m, k, x)
+    assert np.all(got[0] == 0)
+    want = _ref_matvec(s.dequantize_q4_0(raw).reshape(m, k), x)
+    assert np.abs(got - want).max() / np.abs(want).max() < 2e-4
+
+
+# ---- split-KV flash-decode ---------------------------------------------------------------
+
+def _attn_ref(q, k, v, Hkv, window, pos):
+    M, H, hd = q.shape
+    seq = k.shape[0]
+    k16 = k.astype(np.float16).astype(np.float64); v16 = v.astype(np.float16).astype(np.float64)
+    out = np.zeros_like(q, dtype=np.float64)
+    for j in range(M):
+        p = pos + j
+        lo = max(0, p - window + 1) if window > 0 else 0
+        rows = [t % seq for t in range(lo, p + 1)]
+        for h in range(H):
+            c = (h // (H // Hkv)) * hd
+            kk, vv = k16[rows, c:c + hd], v16[rows, c:c + hd]
+            sc = kk @ q[j, h].astype(np.float64)
+            w = np.exp(sc - sc.max()); w /= w.sum()
+            out[j, h] = w @ vv
+    return out
+
+
+@pytest.mark.parametrize("H,Hkv,hd", [(4, 1, 64), (8, 2, 256), (16, 8, 256)])
+@pytest.mark.parametrize("M,window,seq,pos", [(1, 0, 512, 0), (4, 0, 512, 200), (4, 128, 200, 130), (8, 128, 200, 1000),
+                                               (5, 64, 160, 63), (4, 0, 300, 296)])
+def test_flash_decode_matches_reference(lg, H, Hkv, hd, M, window, seq, pos):
+    rng = np.random.default_rng(H * hd + M + pos)
+    q = (rng.standard_normal((M, H, hd)) * 0.3).astype(np.float32)
+    k = rng.standard_normal((seq, Hkv * hd)).astype(np.float32)
+    v = rng.standard_normal((seq, Hkv * hd)).astype(np.float32)
+    want = _attn_ref(q, k, v, Hkv, window, pos)
+    got = lg.flash_decode(q, k, v, Hkv, window, pos)
+    assert np.abs(got - want).max() < 2e-4 * max(1.0, np.abs(want).max())
+
+
+def test_flash_decode_row_equals_single_query(lg):
+    """A query at position p gives bit-identical output as row 2 of a block at p-2 or alone at p."""
+    rng = np.random.default_rng(1)
+    H, Hkv, hd, seq = 8, 2, 256, 1200
+    k = rng.standard_normal((seq, Hkv * hd)).astype(np.float32)
+    v = rng.standard_normal((seq, Hkv * hd)).astype(np.float32)
+    q = (rng.standard_normal((4, H, hd)) * 0.3).astype(np.float32)
+    for window in (0, 256):
+        blk = lg.flash_decode(q, k, v, Hkv, window, 700)
+        one = lg.flash_decode(q[2:3], k, v, Hkv, window, 702)
+        assert np.array_equal(blk[2].view(np.uint32), one[0].view(np.uint32))
