@@ -29,6 +29,7 @@ ABI_SYMBOLS = [
     "model_prefill_reserve", "model_forward_spec", "mtp_draft_device", "mtp_draft_chain_device", "mtp_free_device",
     "lg_forward_spec_n", "lg_set_replay", "lg_rounds_begin", "lg_rounds_enqueue", "lg_rounds_collect",
     "lg_weight_bytes", "lg_round_launches", "lg_last_hidden", "lg_kv_row", "lg_stream", "lg_engine_release",
+    "lg_bench_matmul_pass",
     "lg_dequant_host", "lg_gemv_host", "lg_flash_decode_host",
 ]
 
@@ -79,6 +80,9 @@ def load() -> C.CDLL:
     L.lg_weight_bytes.argtypes = [C.c_void_p]; L.lg_weight_bytes.restype = C.c_longlong
     L.lg_round_launches.argtypes = [C.c_void_p]; L.lg_round_launches.restype = C.c_longlong
     L.lg_stream.argtypes = [C.c_void_p]; L.lg_stream.restype = C.c_void_p
+    L.lg_bench_matmul_pass.argtypes = [C.c_void_p, C.c_int]; L.lg_bench_matmul_pass.restype = C.c_int
+    L.lgs_rounds_host.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _i32p, C.c_int, C.c_void_p, _i32p]
+    L.lgs_rounds_host.restype = C.c_int
     _lib = L
     return L
 
@@ -207,6 +211,19 @@ class Session:
         if n < 0:
             raise RuntimeError("device rounds unavailable (no draft head?)")
         return out[:n], (int(stats[0]), int(stats[1]))
+
+    def rounds_host(self, best: int, pos: int, n_emitted: int, n_gen: int, n_rounds: int, mode: int, replay=None):
+        """Host-driven rounds from a given state; returns (tokens[n_emitted:], stats dict)."""
+        out = np.zeros(n_gen + 8, dtype=np.int32); stats = np.zeros(4, dtype=np.int32)
+        rp = None
+        if replay is not None:
+            replay = np.ascontiguousarray(np.concatenate([replay, np.zeros(8, np.int32)]), dtype=np.int32)
+            rp = replay.ctypes.data_as(C.c_void_p)
+        g = self.L.lgs_rounds_host(self.h, best, pos, n_emitted, n_gen, n_rounds, out, mode, rp, stats)
+        return out[n_emitted:g], dict(n_draft=int(stats[0]), n_accept=int(stats[1]), pos=int(stats[2]), best=int(stats[3]))
+
+    def matmul_pass(self, n: int) -> int:
+        return int(self.L.lg_bench_matmul_pass(self.model, n))
 
     # device-resident rounds, raw
     def rounds_begin(self, first: int, pos: int, n_emitted: int = 1):

@@ -1009,6 +1009,32 @@ int lg_rounds_collect(struct model *m, int *tokens, int from, int cap, int *stat
     return n > 0 ? n : 0;
 }
 
+// Enqueue, on the engine's stream, exactly the weight matmuls of one verify step of width n (every
+// layer's qkv / o / gate+up / down / PLE pair and the output head) and nothing else: lets a caller
+// time the streaming kernel alone, on cold weights, with events around the call.
+int lg_bench_matmul_pass(struct model *m, int n) {
+    Engine *e = engine_for(m);
+    if (n < 1 || n > LG_MAXM) return -1;
+    int count = 0;
+    for (size_t l = 0; l < e->L.size(); l++) {
+        LayerW &w = e->L[l];
+        LgPanel pa = e->p_attn; pa.nsb = w.o.k / 32;
+        LgPanel pf = e->p_ff; pf.nsb = w.down.k / 32;
+        launch_gemv(e, w.qkv, e->p_ne, n, e->qkv, LG_EPI_STORE, 1);
+        launch_gemv(e, w.o, pa, n, e->oout, LG_EPI_STORE, 0);
+        launch_gemv(e, w.gateup, e->p_ne, n, e->gu, LG_EPI_STORE, 1);
+        launch_gemv(e, w.down, pf, n, e->dout, LG_EPI_STORE, 0);
+        count += 4;
+        if (e->has_ple) {
+            launch_gemv(e, w.inp_gate, e->p_ne, n, e->pg, LG_EPI_STORE, 1);
+            launch_gemv(e, w.proj, e->p_ple, n, e->oout, LG_EPI_STORE, 1);
+            count += 2;
+        }
+    }
+    launch_gemv(e, e->head, e->p_ne, n, nullptr, LG_EPI_HEAD, 1, 0.0f, nullptr, e->amax_val, e->amax_idx);
+    return count + 1;
+}
+
 void *lg_stream(struct model *m) { return (void *)engine_for(m)->stream; }
 long long lg_round_launches(struct model *m) { return engine_for(m)->round_launches; }
 

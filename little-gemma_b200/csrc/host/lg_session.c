@@ -77,29 +77,32 @@ int  lgs_dequant(unsigned type, const void *src, float *out, long long n) {
     return lg_dequant_host((int)type, src, 1, (int)n, out);
 }
 
-/* Host-driven generation through the reference-shaped calls: one blocking call per draft and
- * per verify, exactly like src/run.c.  mode 0 plain, 1 head drafts, 2 replayed drafts. */
-int lgs_generate(void *p, const int *prompt, int n_prompt, int n_gen, int *out_toks, int mode,
-                 const int *replay, int *stats) {
+/* Host-driven rounds through the reference-shaped calls -- one blocking call per draft and per
+ * verify, exactly like src/run.c:54-71.  Starts from chosen token `best` at position `pos` with
+ * g tokens already emitted; runs until n_gen tokens are out or n_rounds rounds are done.
+ * mode 0 plain decode, 1 head drafts, 2 replayed drafts (replay[i] = draft for stream index i),
+ * 3 head drafts computed through the API but replaced by the replayed ones (the acceptance
+ * rate is then the table's while the head's cost is still paid). */
+int lgs_rounds_host(void *p, int best, int pos, int g, int n_gen, int n_rounds, int *out_toks, int mode,
+                    const int *replay, int *stats) {
     struct lg_session *s = p;
-    int g = 0, nd = 0, na = 0, N = s->mtp_n;
-    if (n_prompt > 1) model_prefill(&s->m, &s->kv, prompt, n_prompt - 1, 0);
-    int pos = n_prompt - 1;
-    int best = model_forward_next(&s->m, &s->kv, prompt[n_prompt - 1], pos++);
-    out_toks[g++] = best;
-    while (g < n_gen) {
+    int nd = 0, na = 0, N = s->mtp_n, rounds = 0;
+    while (g < n_gen && (n_rounds <= 0 || rounds < n_rounds)) {
+        rounds++;
         if (!mode) { best = model_forward_next(&s->m, &s->kv, best, pos++); out_toks[g++] = best; continue; }
         int toks[8], out[8];
         toks[0] = best;
-        if (mode == 2) {
-            for (int j = 1; j < N; j++) toks[j] = replay[g + j - 1];
-        } else {
+        if (mode == 1 || mode == 3) {
             int d = mtp_draft(s->head, &s->m, &s->kv, best, pos);
             toks[1] = d >= 0 ? d : best;
+            if (mode == 3) toks[1] = replay[g];
             for (int j = 2; j < N; j++) {
                 int dj = mtp_draft_chain(s->head, &s->m, &s->kv, toks[j - 1], pos + j - 1);
                 toks[j] = dj >= 0 ? dj : toks[j - 1];
+                if (mode == 3) toks[j] = replay[g + j - 1];
             }
+        } else {
+            for (int j = 1; j < N; j++) toks[j] = replay[g + j - 1];
         }
         int adv = lg_forward_spec_n(&s->m, &s->kv, N, toks, pos, out);
         nd += N - 1; na += adv - 1;
@@ -108,7 +111,21 @@ int lgs_generate(void *p, const int *prompt, int n_prompt, int n_gen, int *out_t
         pos += adv;
         if (g < n_gen) out_toks[g++] = best;
     }
-    if (stats) { stats[0] = nd; stats[1] = na; }
+    if (stats) { stats[0] = nd; stats[1] = na; stats[2] = pos; stats[3] = best; }
+    return g;
+}
+
+/* Prompt then host-driven rounds: the generate loop of src/run.c:697-785. */
+int lgs_generate(void *p, const int *prompt, int n_prompt, int n_gen, int *out_toks, int mode,
+                 const int *replay, int *stats) {
+    struct lg_session *s = p;
+    int st[4];
+    if (n_prompt > 1) model_prefill(&s->m, &s->kv, prompt, n_prompt - 1, 0);
+    int pos = n_prompt - 1;
+    int best = model_forward_next(&s->m, &s->kv, prompt[n_prompt - 1], pos++);
+    out_toks[0] = best;
+    int g = lgs_rounds_host(p, best, pos, 1, n_gen, 0, out_toks, mode, replay, st);
+    if (stats) { stats[0] = st[0]; stats[1] = st[1]; }
     return g;
 }
 
