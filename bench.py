@@ -149,6 +149,8 @@ def main():
     ap.add_argument("--mtp-n", type=int, default=4)
     ap.add_argument("--cpu-tokens", type=int, default=4)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--profile-step", action="store_true",
+                    help="short path for profilers: load, prefill, W warm-up rounds, K rounds, exit")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
     t_shape, h_shape, label = shapes(a.config)
@@ -213,6 +215,21 @@ def main():
     sess.prefill(prompt[:-1], 0)
     first = sess.next(int(prompt[-1]), a.depth - 1)
     pos0 = a.depth
+
+    if a.profile_step:
+        sess.set_replay(np.zeros(n_gen + 8, dtype=np.int32))
+        sess.rounds_begin(first, pos0, 1)
+        sess.rounds_enqueue(M, 2, a.warmup)
+        sess.rounds_collect(1, 0)
+        e0, e1 = ev(), ev()
+        e0.record(stream)
+        sess.rounds_enqueue(M, 2, a.steps)
+        e1.record(stream)
+        e1.synchronize()
+        print(json.dumps({"profile_step": True, "ms_per_round": e0.elapsed_time(e1) / a.steps,
+                          "launches_per_round": sess.round_launches(), "config": base["config"]}), flush=True)
+        sess.close()
+        return
 
     # the plain-greedy stream the drafts are replayed from (device-resident plain decode)
     sess.rounds_begin(first, pos0, 1)

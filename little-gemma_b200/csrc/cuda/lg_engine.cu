@@ -196,44 +196,75 @@ void free_wmat(WMat &W) { cudaFree(W.wq); cudaFree(W.ws); cudaFree(W.wd); W = WM
 // ------------------------------------------------------------------------------------------
 // launch helpers
 // ------------------------------------------------------------------------------------------
-struct GemvPlan { int ks, gx; size_t smem; };
+struct GemvPlan { int r, ks, gx; size_t smem; };
 constexpr size_t GEMV_SMEM_MAX = 200 * 1024, ATTN_SMEM_MAX = 200 * 1024;
 
+template <int R, int NP, int FMT, int EPI> void gemv_attr() {
+    LG_CHECK(cudaFuncSetAttribute(lg_gemv_kernel<R, NP, FMT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMV_SMEM_MAX));
+}
+template <int R> void gemv_attr_r() {
+    gemv_attr<R, 1, LG_FMT_Q4_0, LG_EPI_STORE>(); gemv_attr<R, 1, LG_FMT_Q4_0, LG_EPI_HEAD>();
+    gemv_attr<R, 2, LG_FMT_Q4_0, LG_EPI_STORE>(); gemv_attr<R, 2, LG_FMT_Q4_0, LG_EPI_HEAD>();
+    gemv_attr<R, 1, LG_FMT_Q4_K, LG_EPI_STORE>(); gemv_attr<R, 1, LG_FMT_Q4_K, LG_EPI_HEAD>();
+    gemv_attr<R, 2, LG_FMT_Q4_K, LG_EPI_STORE>(); gemv_attr<R, 2, LG_FMT_Q4_K, LG_EPI_HEAD>();
+}
 // Opt every kernel into large dynamic shared memory once, outside any stream capture.
 void set_kernel_attributes() {
     static bool done = false;
     if (done) return;
     done = true;
-#define LG_ATTR(K) LG_CHECK(cudaFuncSetAttribute(K, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMV_SMEM_MAX))
-    LG_ATTR((lg_gemv_kernel<1, LG_FMT_Q4_0, LG_EPI_STORE>)); LG_ATTR((lg_gemv_kernel<1, LG_FMT_Q4_0, LG_EPI_HEAD>));
-    LG_ATTR((lg_gemv_kernel<2, LG_FMT_Q4_0, LG_EPI_STORE>)); LG_ATTR((lg_gemv_kernel<2, LG_FMT_Q4_0, LG_EPI_HEAD>));
-    LG_ATTR((lg_gemv_kernel<1, LG_FMT_Q4_K, LG_EPI_STORE>)); LG_ATTR((lg_gemv_kernel<1, LG_FMT_Q4_K, LG_EPI_HEAD>));
-    LG_ATTR((lg_gemv_kernel<2, LG_FMT_Q4_K, LG_EPI_STORE>)); LG_ATTR((lg_gemv_kernel<2, LG_FMT_Q4_K, LG_EPI_HEAD>));
-#undef LG_ATTR
+    gemv_attr_r<1>(); gemv_attr_r<2>(); gemv_attr_r<4>();
     LG_CHECK(cudaFuncSetAttribute(lg_attn_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
 }
 
-GemvPlan plan_gemv(const Engine *e, const WMat &W, int np, int want_ks) {
+int env_int(const char *name, int fb) { const char *v = getenv(name); return v && v[0] ? atoi(v) : fb; }
+
+// Decomposition of one matmul into CTA work items: R row tiles x one of ks column slices.
+// Few slices (each slice's partial costs an extra pass in the consumer) and as many row tiles per
+// item as still leave about two items per SM.
+GemvPlan plan_gemv(const Engine *e, const WMat &W, int np, int want_ks, bool head) {
     GemvPlan p;
-    p.ks = want_ks;
-    if (p.ks <= 0) { p.ks = 1; while (W.nkp / p.ks > 72 && p.ks < e->max_ks && W.nkp % (p.ks * 2) == 0) p.ks *= 2; }
+    const int want_items = e->sm_count * 2 - e->sm_count / 4;
+    static const int force_r = env_int("LG_GEMV_R", 0), force_ks = env_int("LG_GEMV_KS", 0);
+    p.r = 0; p.ks = want_ks;
+    int ks_lo = want_ks > 0 ? want_ks : 1, ks_hi = want_ks > 0 ? want_ks : e->max_ks;
+    for (int ks = ks_lo; ks <= ks_hi && !p.r; ks *= 2) {
+        if (W.nkp / ks > 80 && ks < ks_hi) continue;                      // keep a slice's panel below ~45 KB
+        if (ks > W.nkp) break;
+        for (int r = 4; r >= 1; r >>= 1)
+            if (((W.n_row_tiles + r - 1) / r) * ks >= want_items || (ks == ks_hi && r == 1)) { p.r = r; p.ks = ks; break; }
+    }
+    if (!p.r) { p.r = 1; p.ks = ks_lo; }
+    if (head) { p.r = 4; p.ks = 1; }
+    if (force_r && !head) p.r = force_r;
+    if (force_ks && want_ks <= 0 && !head) p.ks = force_ks;
     if (p.ks > e->max_ks) p.ks = e->max_ks;
     if (p.ks > W.nkp) p.ks = W.nkp;
     int nkp_s = (W.nkp + p.ks - 1) / p.ks + 1;
-    p.smem = (size_t)np * nkp_s * 2 * (256 + 32) + (size_t)LG_GEMV_WARPS * np * 64 * 4 + 16;
+    p.smem = (size_t)np * nkp_s * 2 * (256 + 32) + (size_t)LG_GEMV_WARPS * p.r * np * 64 * 4 + 16;
+    int groups = (W.n_row_tiles + p.r - 1) / p.r;
     int ctas = e->sm_count * 2;
-    p.gx = W.n_row_tiles < ctas / p.ks ? W.n_row_tiles : ctas / p.ks;
+    p.gx = groups < ctas / p.ks ? groups : ctas / p.ks;
+    if (head) p.gx = e->head_ctas < groups ? e->head_ctas : groups;
     if (p.gx < 1) p.gx = 1;
     return p;
 }
 
-template <int NP, int FMT, int EPI>
+template <int R, int NP, int FMT, int EPI>
 void launch_gemv_t(Engine *e, const LgGemvArgs &a, const GemvPlan &p) {
     if (p.smem > GEMV_SMEM_MAX) { fprintf(stderr, "lg_b200: matmul slice needs %zu bytes of shared memory\n", p.smem); exit(1); }
     dim3 grid(p.gx, p.ks);
-    lg_gemv_kernel<NP, FMT, EPI><<<grid, LG_GEMV_WARPS * 32, p.smem, e->stream>>>(a);
+    lg_gemv_kernel<R, NP, FMT, EPI><<<grid, LG_GEMV_WARPS * 32, p.smem, e->stream>>>(a);
     LG_CHECK(cudaGetLastError());
     e->launches++;
+}
+template <int R, int NP>
+void launch_gemv_rn(Engine *e, const LgGemvArgs &a, const GemvPlan &p, int fmt, int epi) {
+    if (fmt == LG_FMT_Q4_0) {
+        if (epi == LG_EPI_HEAD) launch_gemv_t<R, NP, LG_FMT_Q4_0, LG_EPI_HEAD>(e, a, p); else launch_gemv_t<R, NP, LG_FMT_Q4_0, LG_EPI_STORE>(e, a, p);
+    } else {
+        if (epi == LG_EPI_HEAD) launch_gemv_t<R, NP, LG_FMT_Q4_K, LG_EPI_HEAD>(e, a, p); else launch_gemv_t<R, NP, LG_FMT_Q4_K, LG_EPI_STORE>(e, a, p);
+    }
 }
 
 // out[ks][tok][ldo] partial sums (EPI_STORE) or the head epilogue.
@@ -241,8 +272,7 @@ void launch_gemv(Engine *e, const WMat &W, const LgPanel &X, int M, float *out, 
                  float softcap = 0.0f, float *logits = nullptr, float *amax_val = nullptr, int *amax_idx = nullptr,
                  int *ks_out = nullptr, int *gx_out = nullptr) {
     int np = M > 4 ? 2 : 1;
-    GemvPlan p = plan_gemv(e, W, np, epi == LG_EPI_HEAD ? 1 : force_ks);
-    if (epi == LG_EPI_HEAD) { p.gx = e->head_ctas < W.n_row_tiles ? e->head_ctas : W.n_row_tiles; }
+    GemvPlan p = plan_gemv(e, W, np, epi == LG_EPI_HEAD ? 1 : force_ks, epi == LG_EPI_HEAD);
     LgGemvArgs a{};
     a.wq = W.wq; a.ws = W.ws; a.wd = W.wd; a.x = X; a.nkp = W.nkp; a.n_row_tiles = W.n_row_tiles; a.kslices = p.ks;
     a.out = out; a.ldo = W.ldo; a.M = M; a.softcap = softcap; a.logits = logits; a.n_valid_rows = W.m;
@@ -250,11 +280,11 @@ void launch_gemv(Engine *e, const WMat &W, const LgPanel &X, int M, float *out, 
     if (X.nsb * 32 != W.k) { fprintf(stderr, "lg_b200: panel width %d does not match matrix k %d\n", X.nsb * 32, W.k); exit(1); }
     if (ks_out) *ks_out = p.ks;
     if (gx_out) *gx_out = p.gx;
-#define LG_DISPATCH(NPv, FMTv) \
-    if (epi == LG_EPI_HEAD) launch_gemv_t<NPv, FMTv, LG_EPI_HEAD>(e, a, p); else launch_gemv_t<NPv, FMTv, LG_EPI_STORE>(e, a, p);
-    if (np == 1) { if (W.fmt == LG_FMT_Q4_0) { LG_DISPATCH(1, LG_FMT_Q4_0) } else { LG_DISPATCH(1, LG_FMT_Q4_K) } }
-    else         { if (W.fmt == LG_FMT_Q4_0) { LG_DISPATCH(2, LG_FMT_Q4_0) } else { LG_DISPATCH(2, LG_FMT_Q4_K) } }
-#undef LG_DISPATCH
+    if (np == 1) {
+        if (p.r == 4) launch_gemv_rn<4, 1>(e, a, p, W.fmt, epi); else if (p.r == 2) launch_gemv_rn<2, 1>(e, a, p, W.fmt, epi); else launch_gemv_rn<1, 1>(e, a, p, W.fmt, epi);
+    } else {
+        if (p.r == 4) launch_gemv_rn<4, 2>(e, a, p, W.fmt, epi); else if (p.r == 2) launch_gemv_rn<2, 2>(e, a, p, W.fmt, epi); else launch_gemv_rn<1, 2>(e, a, p, W.fmt, epi);
+    }
 }
 
 void launch_norm(Engine *e, int M, float *x, int ldx, int n, float eps,

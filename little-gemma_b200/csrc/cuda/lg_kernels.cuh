@@ -97,19 +97,19 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)_
 // streaming 16-byte weight load: read-only path, do not keep in L1
 __device__ __forceinline__ uint4 ldg_stream16(const uint4 *p) {
     uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+    asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
 __device__ __forceinline__ uint2 ldg_stream8(const uint2 *p) {
     uint2 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    asm("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
     return v;
 }
 
 __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                        uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
@@ -285,21 +285,52 @@ enum { LG_EPI_STORE = 0, LG_EPI_HEAD = 1 };
 
 #define LG_GEMV_WARPS 8
 
-// Dynamic shared memory: [NP][nkp_slice*2][256] int8 | [NP][nkp_slice*2][4] float2 | reduction | mbarrier
-template <int NP, int FMT, int EPI>
-__global__ void __launch_bounds__(LG_GEMV_WARPS * 32)
+// One weight fetch of a warp: R row tiles at the same 64-column tile position.
+template <int R, int FMT> struct LgWFrag {
+    uint4 w[R];
+    uint2 sc[R];
+    uint2 dd[FMT == LG_FMT_Q4_K ? R : 1];
+};
+
+template <int R, int FMT>
+__device__ __forceinline__ void gemv_fetch(LgWFrag<R, FMT> &f, const LgGemvArgs &a, int rt0, int kp, int lane, int g) {
+    #pragma unroll
+    for (int r = 0; r < R; r++) {
+        int rt = rt0 + r;
+        if (rt < a.n_row_tiles) {
+            size_t tile = (size_t)rt * a.nkp + kp;
+            f.w[r] = ldg_stream16(a.wq + tile * 32 + lane);
+            f.sc[r] = ldg_stream8(a.ws + tile * 8 + g);
+            if (FMT == LG_FMT_Q4_K) f.dd[r] = ldg_stream8(a.wd + tile * 8 + g);
+        } else {
+            f.w[r] = make_uint4(0, 0, 0, 0); f.sc[r] = make_uint2(0, 0);
+            if (FMT == LG_FMT_Q4_K) f.dd[r] = make_uint2(0, 0);
+        }
+    }
+}
+
+// A CTA works on items = (group of R consecutive row tiles) x (its k slice, blockIdx.y).  Its 8
+// warps split the slice's 64-column tile positions; for each position a warp loads the B fragment
+// once from shared memory and applies it to the R row tiles (R independent 16-byte weight loads in
+// flight per lane, the next position's loads issued before the current one is consumed).  The
+// activation panel slice is staged once per CTA by a bulk copy whose completion is awaited only
+// after the first weight loads are in flight.  Partial sums of the 8 warps are added in warp order.
+// Dynamic shared memory: [NP][nsb_s][256] int8 | [NP][nsb_s][4] float2 | [8][R*NP*64] f32 | mbarrier
+template <int R, int NP, int FMT, int EPI>
+__global__ void __launch_bounds__(LG_GEMV_WARPS * 32, 2)
 lg_gemv_kernel(LgGemvArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int ks = blockIdx.y;
     const int kp0 = (int)((long long)a.nkp * ks / a.kslices), kp1 = (int)((long long)a.nkp * (ks + 1) / a.kslices);
-    const int nsb_s = (kp1 - kp0) * 2;                      // sub-blocks in this slice
-    int8_t *sq = (int8_t *)smem;                            // [NP][nsb_s][256]
-    float2 *ss = (float2 *)(smem + (size_t)NP * nsb_s * 256);   // [NP][nsb_s][4]
-    float *red = (float *)(ss + (size_t)NP * nsb_s * 4);    // [WARPS][NP][64]
-    uint64_t *bar = (uint64_t *)(red + LG_GEMV_WARPS * NP * 64);
+    const int nsb_s = (kp1 - kp0) * 2;
+    int8_t *sq = (int8_t *)smem;
+    float2 *ss = (float2 *)(smem + (size_t)NP * nsb_s * 256);
+    float *red = (float *)(ss + (size_t)NP * nsb_s * 4);
+    uint64_t *bar = (uint64_t *)(red + LG_GEMV_WARPS * R * NP * 64);
+    constexpr int SLOTS = (R * NP * 64 + LG_GEMV_WARPS * 32 - 1) / (LG_GEMV_WARPS * 32);
+    const int n_groups = (a.n_row_tiles + R - 1) / R;
 
-    // stage this slice of the activation panel with bulk copies
     if (threadIdx.x == 0) mbar_init(bar, 1);
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -311,102 +342,125 @@ lg_gemv_kernel(LgGemvArgs a) {
             bulk_g2s(ss + (size_t)p * nsb_s * 4, a.x.s + ((size_t)p * a.x.nsb + kp0 * 2) * 4, sb, bar);
         }
     }
-    if (!mbar_wait(bar, 0)) { if (threadIdx.x == 0) atomicOr(a.err, LG_ERR_MBAR_TIMEOUT); }
+    bool staged = false;
 
-    float best_v = -INFINITY; int best_i = 0x7fffffff;       // head epilogue state of this thread's (tok,row)
+    float best_v[SLOTS]; int best_i[SLOTS];
+    #pragma unroll
+    for (int j = 0; j < SLOTS; j++) { best_v[j] = -INFINITY; best_i[j] = 0x7fffffff; }
 
-    for (int rt = blockIdx.x; rt < a.n_row_tiles; rt += gridDim.x) {
-        float acc[NP][2];
+    for (int grp = blockIdx.x; grp < n_groups; grp += gridDim.x) {
+        const int rt0 = grp * R;
+        float acc[R][NP][2];
         #pragma unroll
-        for (int p = 0; p < NP; p++) acc[p][0] = acc[p][1] = 0.0f;
+        for (int r = 0; r < R; r++)
+            #pragma unroll
+            for (int p = 0; p < NP; p++) acc[r][p][0] = acc[r][p][1] = 0.0f;
 
-        const uint4 *wq = a.wq + ((size_t)rt * a.nkp) * 32 + lane;
-        const uint2 *ws = a.ws + ((size_t)rt * a.nkp) * 8 + g;
-        const uint2 *wd = FMT == LG_FMT_Q4_K ? a.wd + ((size_t)rt * a.nkp) * 8 + g : nullptr;
-
-        #pragma unroll 4
-        for (int kp = kp0 + warp; kp < kp1; kp += LG_GEMV_WARPS) {
-            uint4 w = ldg_stream16(wq + (size_t)kp * 32);
-            uint2 sc = ldg_stream8(ws + (size_t)kp * 8);
-            float dw[2][2], mw[2][2];                        // [sub-block][row g / g+8]
-            if (FMT == LG_FMT_Q4_0) {
-                float2 f0 = __half22float2(*(const __half2 *)&sc.x), f1 = __half22float2(*(const __half2 *)&sc.y);
-                dw[0][0] = f0.x; dw[0][1] = f0.y; dw[1][0] = f1.x; dw[1][1] = f1.y;
-            } else {
-                uint2 dd = ldg_stream8(wd + (size_t)kp * 8);
-                float2 r0 = __half22float2(*(const __half2 *)&dd.x), r1 = __half22float2(*(const __half2 *)&dd.y);
-                #pragma unroll
-                for (int s = 0; s < 2; s++) {
-                    uint32_t v = s ? sc.y : sc.x;
-                    float s0 = (float)(v & 0xff), m0 = (float)((v >> 8) & 0xff);
-                    float s1 = (float)((v >> 16) & 0xff), m1 = (float)(v >> 24);
-                    dw[s][0] = r0.x * s0; mw[s][0] = 8.0f * dw[s][0] - r0.y * m0;
-                    dw[s][1] = r1.x * s1; mw[s][1] = 8.0f * dw[s][1] - r1.y * m1;
-                }
-            }
+        LgWFrag<R, FMT> cur, nxt;
+        int kp = kp0 + warp;
+        if (kp < kp1) gemv_fetch<R, FMT>(cur, a, rt0, kp, lane, g);
+        if (!staged) {
+            if (!mbar_wait(bar, 0)) { if (threadIdx.x == 0) atomicOr(a.err, LG_ERR_MBAR_TIMEOUT); }
+            staged = true;
+        }
+        for (; kp < kp1; kp += LG_GEMV_WARPS) {
+            const bool more = kp + LG_GEMV_WARPS < kp1;
+            if (more) gemv_fetch<R, FMT>(nxt, a, rt0, kp + LG_GEMV_WARPS, lane, g);
             #pragma unroll
             for (int s = 0; s < 2; s++) {
-                uint32_t wg = s ? w.z : w.x, wh = s ? w.w : w.y;
-                uint32_t a0 = (wg << 4) & 0xF0F0F0F0u, a2 = wg & 0xF0F0F0F0u;
-                uint32_t a1 = (wh << 4) & 0xF0F0F0F0u, a3 = wh & 0xF0F0F0F0u;
-                int sbl = (kp - kp0) * 2 + s;
+                const int sbl = (kp - kp0) * 2 + s;
+                uint2 b[NP]; float2 xs[NP];
                 #pragma unroll
                 for (int p = 0; p < NP; p++) {
-                    uint2 b = *(const uint2 *)(sq + ((size_t)p * nsb_s + sbl) * 256 + lane * 8);
-                    float2 xs = ss[((size_t)p * nsb_s + sbl) * 4 + t];
-                    int c[4] = {0, 0, 0, 0};
-                    mma_s8(c, a0, a1, a2, a3, b.x, b.y);
-                    float v0 = (float)((c[0] << 8) + c[1]) * xs.x;      // row g,   token 4p+t
-                    float v1 = (float)((c[2] << 8) + c[3]) * xs.x;      // row g+8
-                    acc[p][0] = fmaf(v0, dw[s][0], acc[p][0]);
-                    acc[p][1] = fmaf(v1, dw[s][1], acc[p][1]);
-                    if (FMT == LG_FMT_Q4_K) {                          // weights are 16*(q-8): add back 16*(8 d sc - dmin m) * sum(x)
-                        acc[p][0] = fmaf(16.0f * mw[s][0], xs.y, acc[p][0]);
-                        acc[p][1] = fmaf(16.0f * mw[s][1], xs.y, acc[p][1]);
+                    b[p] = *(const uint2 *)(sq + ((size_t)p * nsb_s + sbl) * 256 + lane * 8);
+                    xs[p] = ss[((size_t)p * nsb_s + sbl) * 4 + t];
+                }
+                #pragma unroll
+                for (int r = 0; r < R; r++) {
+                    uint32_t wg = s ? cur.w[r].z : cur.w[r].x, wh = s ? cur.w[r].w : cur.w[r].y;
+                    uint32_t a0 = (wg << 4) & 0xF0F0F0F0u, a2 = wg & 0xF0F0F0F0u;
+                    uint32_t a1 = (wh << 4) & 0xF0F0F0F0u, a3 = wh & 0xF0F0F0F0u;
+                    float d0, d1, m0 = 0.0f, m1 = 0.0f;
+                    uint32_t sw = s ? cur.sc[r].y : cur.sc[r].x;
+                    if (FMT == LG_FMT_Q4_0) {
+                        float2 f = __half22float2(*(const __half2 *)&sw);
+                        d0 = f.x; d1 = f.y;
+                    } else {
+                        float2 r0 = __half22float2(*(const __half2 *)&cur.dd[r].x), r1 = __half22float2(*(const __half2 *)&cur.dd[r].y);
+                        d0 = r0.x * (float)(sw & 0xff); m0 = 16.0f * (8.0f * d0 - r0.y * (float)((sw >> 8) & 0xff));
+                        d1 = r1.x * (float)((sw >> 16) & 0xff); m1 = 16.0f * (8.0f * d1 - r1.y * (float)(sw >> 24));
+                    }
+                    #pragma unroll
+                    for (int p = 0; p < NP; p++) {
+                        int c[4] = {0, 0, 0, 0};
+                        mma_s8(c, a0, a1, a2, a3, b[p].x, b[p].y);
+                        float v0 = (float)((c[0] << 8) + c[1]) * xs[p].x;      // row g,   token 4p+t
+                        float v1 = (float)((c[2] << 8) + c[3]) * xs[p].x;      // row g+8
+                        acc[r][p][0] = fmaf(v0, d0, acc[r][p][0]);
+                        acc[r][p][1] = fmaf(v1, d1, acc[r][p][1]);
+                        if (FMT == LG_FMT_Q4_K) {     // nibbles are stored as (q-8): add back (8 d sc - dmin m) * sum(x)
+                            acc[r][p][0] = fmaf(m0, xs[p].y, acc[r][p][0]);
+                            acc[r][p][1] = fmaf(m1, xs[p].y, acc[r][p][1]);
+                        }
                     }
                 }
             }
+            if (more) cur = nxt;
         }
 
-        // fixed-order sum over the warps that shared this row tile
+        // fixed-order sum over the 8 warps
         #pragma unroll
-        for (int p = 0; p < NP; p++) {
-            red[(warp * NP + p) * 64 + t * 16 + g] = acc[p][0];
-            red[(warp * NP + p) * 64 + t * 16 + g + 8] = acc[p][1];
-        }
-        __syncthreads();
-        if (threadIdx.x < NP * 64) {
-            int p = threadIdx.x >> 6, tok = p * 4 + ((threadIdx.x >> 4) & 3), r = threadIdx.x & 15;
-            float sum = 0.0f;
+        for (int r = 0; r < R; r++)
             #pragma unroll
-            for (int w2 = 0; w2 < LG_GEMV_WARPS; w2++) sum += red[(w2 * NP + p) * 64 + (threadIdx.x & 63)];
-            sum *= 0.0625f;
-            int row = rt * 16 + r;
-            if (EPI == LG_EPI_STORE) {
-                if (tok < a.M) a.out[((size_t)ks * LG_MAXM + tok) * a.ldo + row] = sum;
-            } else {
-                if (a.softcap > 0.0f) sum = a.softcap * tanhf(sum / a.softcap);
-                if (tok < a.M && row < a.n_valid_rows) {
-                    if (a.logits) a.logits[(size_t)tok * a.ldo + row] = sum;
-                    if (sum > best_v) { best_v = sum; best_i = row; }   // rows ascend per thread: first max wins
+            for (int p = 0; p < NP; p++) {
+                red[(warp * R * NP + r * NP + p) * 64 + t * 16 + g] = acc[r][p][0];
+                red[(warp * R * NP + r * NP + p) * 64 + t * 16 + g + 8] = acc[r][p][1];
+            }
+        __syncthreads();
+        #pragma unroll
+        for (int j = 0; j < SLOTS; j++) {
+            int idx = threadIdx.x + j * LG_GEMV_WARPS * 32;
+            if (idx < R * NP * 64) {
+                int rp = idx >> 6, r = rp / NP, p = rp % NP, tok = p * 4 + ((idx >> 4) & 3);
+                float sum = 0.0f;
+                #pragma unroll
+                for (int w2 = 0; w2 < LG_GEMV_WARPS; w2++) sum += red[w2 * R * NP * 64 + idx];
+                sum *= 0.0625f;
+                int row = (rt0 + r) * 16 + (idx & 15);
+                if (rt0 + r < a.n_row_tiles && tok < a.M) {
+                    if (EPI == LG_EPI_STORE) {
+                        a.out[((size_t)ks * LG_MAXM + tok) * a.ldo + row] = sum;
+                    } else if (row < a.n_valid_rows) {
+                        if (a.softcap > 0.0f) sum = a.softcap * tanhf(sum / a.softcap);
+                        if (a.logits) a.logits[(size_t)tok * a.ldo + row] = sum;
+                        if (sum > best_v[j]) { best_v[j] = sum; best_i[j] = row; }   // rows ascend per slot: first max wins
+                    }
                 }
             }
         }
         __syncthreads();
     }
 
-    if (EPI == LG_EPI_HEAD && threadIdx.x < NP * 64) {
-        // the 16 lanes of one token: keep the larger value, lower index on ties
+    if (EPI == LG_EPI_HEAD) {
+        // candidates of this CTA: one per (slot, thread); merge per token (larger value, lower index on ties)
+        float *cv = red; int *ci = (int *)(red + R * NP * 64);
         #pragma unroll
-        for (int o = 8; o > 0; o >>= 1) {
-            float ov = __shfl_xor_sync(0xffffffffu, best_v, o);
-            int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-            if (ov > best_v || (ov == best_v && oi < best_i)) { best_v = ov; best_i = oi; }
+        for (int j = 0; j < SLOTS; j++) {
+            int idx = threadIdx.x + j * LG_GEMV_WARPS * 32;
+            if (idx < R * NP * 64) { cv[idx] = best_v[j]; ci[idx] = best_i[j]; }
         }
-        int tok = (threadIdx.x >> 6) * 4 + ((threadIdx.x >> 4) & 3);
-        if ((threadIdx.x & 15) == 0 && tok < a.M) {
-            a.amax_val[(size_t)blockIdx.x * LG_MAXM + tok] = best_v;
-            a.amax_idx[(size_t)blockIdx.x * LG_MAXM + tok] = best_i;
+        __syncthreads();
+        if (threadIdx.x < a.M) {
+            int tok = threadIdx.x, p = tok >> 2, tl = tok & 3;
+            float bv = -INFINITY; int bi = 0x7fffffff;
+            for (int r = 0; r < R; r++)
+                for (int row = 0; row < 16; row++) {
+                    int idx = ((r * NP + p) * 4 + tl) * 16 + row;
+                    float v = cv[idx]; int i2 = ci[idx];
+                    if (v > bv || (v == bv && i2 < bi)) { bv = v; bi = i2; }
+                }
+            a.amax_val[(size_t)blockIdx.x * LG_MAXM + tok] = bv;
+            a.amax_idx[(size_t)blockIdx.x * LG_MAXM + tok] = bi;
         }
     }
 }
