@@ -85,9 +85,11 @@ long long lg_round_launches(struct model *m);        /* kernels in one captured 
 int   lg_last_hidden(struct model *m, float *out);   /* h_prev (n_embd floats) */
 int   lg_kv_row(struct model *m, struct kvcache *kv, int layer, int pos, float *k, float *v);
 void *lg_stream(struct model *m);                    /* the cudaStream_t all work is issued on */
-/* Enqueue only the weight matmuls of one verify step of width n (for timing the streaming
- * kernel alone); returns the number of launches. */
-int   lg_bench_matmul_pass(struct model *m, int n);
+/* Enqueue only selected kernel classes of one verify step of width n (for timing kernels in
+ * isolation); classes is a mask (1 qkv, 2 o, 4 gate/up, 8 down, 16 head, 32 per-layer-embedding
+ * matmuls, 64 norms, 128 q/k/v post-processing, 256 attention, 512 the rest; <= 0 = all weight
+ * matmuls); returns the number of launches.  A forward must have run before. */
+int   lg_bench_matmul_pass(struct model *m, int n, int classes);
 void  lg_engine_release(void);                       /* free all device state of the loaded model */
 
 /* Kernel-level entry points (host buffers in, host buffers out) used by the parity tests.

@@ -80,7 +80,7 @@ def load() -> C.CDLL:
     L.lg_weight_bytes.argtypes = [C.c_void_p]; L.lg_weight_bytes.restype = C.c_longlong
     L.lg_round_launches.argtypes = [C.c_void_p]; L.lg_round_launches.restype = C.c_longlong
     L.lg_stream.argtypes = [C.c_void_p]; L.lg_stream.restype = C.c_void_p
-    L.lg_bench_matmul_pass.argtypes = [C.c_void_p, C.c_int]; L.lg_bench_matmul_pass.restype = C.c_int
+    L.lg_bench_matmul_pass.argtypes = [C.c_void_p, C.c_int, C.c_int]; L.lg_bench_matmul_pass.restype = C.c_int
     L.lgs_rounds_host.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _i32p, C.c_int, C.c_void_p, _i32p]
     L.lgs_rounds_host.restype = C.c_int
     _lib = L
@@ -222,8 +222,9 @@ class Session:
         g = self.L.lgs_rounds_host(self.h, best, pos, n_emitted, n_gen, n_rounds, out, mode, rp, stats)
         return out[n_emitted:g], dict(n_draft=int(stats[0]), n_accept=int(stats[1]), pos=int(stats[2]), best=int(stats[3]))
 
-    def matmul_pass(self, n: int) -> int:
-        return int(self.L.lg_bench_matmul_pass(self.model, n))
+    def matmul_pass(self, n: int, classes: int = 0) -> int:
+        """Enqueue the weight matmuls of one verify step (classes: 1 qkv, 2 o, 4 gate/up, 8 down, 16 head, 32 PLE)."""
+        return int(self.L.lg_bench_matmul_pass(self.model, n, classes))
 
     # device-resident rounds, raw
     def rounds_begin(self, first: int, pos: int, n_emitted: int = 1):

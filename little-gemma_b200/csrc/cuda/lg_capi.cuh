@@ -13,8 +13,9 @@ Engine *scratch_engine() {
         LG_CHECK(cudaGetDevice(&dev));
         LG_CHECK(cudaDeviceGetAttribute(&e->sm_count, cudaDevAttrMultiProcessorCount, dev));
         LG_CHECK(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
-        e->head_ctas = e->sm_count * 4;
+        e->head_ctas = e->sm_count * 2;
         e->err = dalloc<int>(1);
+        e->tickets = dalloc<int>(MAX_KV_HEADS);
     }
     return e;
 }
@@ -28,7 +29,7 @@ extern "C" int lg_dequant_host(int type, const void *blocks, int n_rows, int k, 
     LG_CHECK(cudaMalloc(&d_src, bytes));
     LG_CHECK(cudaMalloc(&d_out, (size_t)n_rows * k * 4));
     LG_CHECK(cudaMemcpyAsync(d_src, blocks, bytes, cudaMemcpyHostToDevice, e->stream));
-    lg_dequant_rows<<<n_rows, 256, 0, e->stream>>>(d_src, type, k, nullptr, n_rows, 0, 1.0f, d_out, k);
+    launch_k(e, lg_dequant_rows, dim3(n_rows), dim3(256), 0, d_src, type, k, nullptr, n_rows, 0, 1.0f, d_out, k);
     LG_CHECK(cudaGetLastError());
     LG_CHECK(cudaMemcpyAsync(out, d_out, (size_t)n_rows * k * 4, cudaMemcpyDeviceToHost, e->stream));
     LG_CHECK(cudaStreamSynchronize(e->stream));
@@ -49,10 +50,11 @@ extern "C" int lg_gemv_host(int type, const void *blocks, int m, int k, const fl
     float *d_x = dalloc<float>((size_t)M * k);
     float *d_out = dalloc<float>((size_t)e->max_ks * LG_MAXM * W.ldo);
     LG_CHECK(cudaMemcpyAsync(d_x, x, (size_t)M * k * 4, cudaMemcpyHostToDevice, e->stream));
-    lg_quant_rows<<<dim3((k / 32 + 7) / 8, M), 256, 0, e->stream>>>(d_x, k, k, P);
+    launch_k(e, lg_quant_rows, dim3((k / 32 + 7) / 8, M), dim3(256), 0, d_x, k, k, P);
     LG_CHECK(cudaGetLastError());
     int ks = 1;
-    launch_gemv(e, W, P, M, d_out, LG_EPI_STORE, kslices, 0, nullptr, nullptr, nullptr, &ks);
+    GemvExtra gx; gx.ks_out = &ks;
+    launch_gemv(e, W, P, M, d_out, LG_EPI_STORE, kslices, gx);
     std::vector<float> h((size_t)ks * LG_MAXM * W.ldo);
     LG_CHECK(cudaMemcpyAsync(h.data(), d_out, h.size() * 4, cudaMemcpyDeviceToHost, e->stream));
     check_err(e);
@@ -68,7 +70,7 @@ extern "C" int lg_gemv_host(int type, const void *blocks, int m, int k, const fl
 
 extern "C" int lg_flash_decode_host(const float *q, const float *k, const float *v, int M, int H, int Hkv, int hd,
                                     int seq, int window, int pos, float *out) {
-    if (M < 1 || M > LG_MAXM || hd % 32 || hd > 512 || H % Hkv) return -1;
+    if (M < 1 || M > LG_MAXM || (hd != 64 && hd != 128 && hd != 256 && hd != 512) || H % Hkv) return -1;
     Engine *e = scratch_engine();
     const int kv_dim = Hkv * hd;
     std::vector<__half> hk((size_t)seq * kv_dim), hv((size_t)seq * kv_dim);
@@ -84,8 +86,9 @@ extern "C" int lg_flash_decode_host(const float *q, const float *k, const float 
     LG_CHECK(cudaMemcpyAsync(d_q, q, (size_t)M * H * hd * 4, cudaMemcpyHostToDevice, e->stream));
     LG_CHECK(cudaMemcpyAsync(d_pos, &pos, 4, cudaMemcpyHostToDevice, e->stream));
     LgAttnArgs a{};
-    a.q = d_q; a.kc = d_k; a.vc = d_v; a.seq = seq; a.kv_dim = kv_dim; a.H = H; a.Hkv = Hkv; a.hd = hd; a.M = M;
-    a.S = ATTN_TILE; a.n_slots = slots; a.window = window; a.qpos_off = 0; a.win_shrink = 0; a.pos = d_pos;
+    a.qkv = d_q; a.ld = 0; a.q_ready = 1; a.has_v = 1; a.owns_kv = 0; a.eps = 0.0f;
+    a.kc = d_k; a.vc = d_v; a.seq = seq; a.kv_dim = kv_dim; a.H = H; a.Hkv = Hkv; a.hd = hd; a.M = M;
+    a.n_slots = slots; a.window = window; a.qpos_off = 0; a.win_shrink = 0; a.pos = d_pos;
     a.part = d_part; a.out.q = nullptr; a.out_f32 = d_o;
     launch_attn(e, a, slots);
     LG_CHECK(cudaMemcpyAsync(out, d_o, (size_t)M * H * hd * 4, cudaMemcpyDeviceToHost, e->stream));

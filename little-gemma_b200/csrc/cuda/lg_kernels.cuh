@@ -92,6 +92,13 @@ __device__ __forceinline__ void quant_group_store(float y, int lane, int tok, in
     if (lane == 0) P.s[((size_t)(tok >> 2) * P.nsb + sb) * 4 + (tok & 3)] = make_float2(d, d * (float)isum);
 }
 
+// Programmatic dependent launch: every kernel of a forward may be started before its predecessor
+// has finished.  pdl_launch() lets the successor begin its own prologue; pdl_wait() blocks until the
+// predecessor grid has completed and its writes are visible.  Nothing produced by an earlier kernel
+// may be read, and nothing may be written, before pdl_wait().  (No-ops for a plain launch.)
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 // streaming 16-byte weight load: read-only path, do not keep in L1
@@ -142,8 +149,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
 // weight repack (runs once per tensor at load)
 // ---------------------------------------------------------------------------------------------
 // q4_0 file blocks [m][k/32][18 B]  ->  tile-major nibbles + f16 scales.  One thread per (tile, lane).
-__global__ void lg_repack_q4_0(const uint8_t *__restrict__ src, uint4 *__restrict__ wq, uint2 *__restrict__ ws,
-                               int m, int nsb, int n_row_tiles) {
+// With src_b set, tile rt is made of rows [8rt, 8rt+8) of src followed by the same rows of src_b
+// (gate and up interleaved, so one thread's two accumulators are gate_i and up_i).
+__global__ void lg_repack_q4_0(const uint8_t *__restrict__ src, const uint8_t *__restrict__ src_b,
+                               uint4 *__restrict__ wq, uint2 *__restrict__ ws, int m, int nsb, int n_row_tiles) {
     int nkp = nsb >> 1;
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     size_t total = (size_t)n_row_tiles * nkp * 32;
@@ -156,10 +165,10 @@ __global__ void lg_repack_q4_0(const uint8_t *__restrict__ src, uint4 *__restric
     uint16_t d[4];
     #pragma unroll
     for (int j = 0; j < 4; j++) {
-        int row = rt * 16 + g + (j & 1) * 8, sb = kp * 2 + (j >> 1);
+        int row = src_b ? rt * 8 + g : rt * 16 + g + (j & 1) * 8, sb = kp * 2 + (j >> 1);
         w[j] = 0; d[j] = 0;
         if (row < m) {
-            const uint8_t *b = src + ((size_t)row * nsb + sb) * 18;
+            const uint8_t *b = ((src_b && (j & 1)) ? src_b : src) + ((size_t)row * nsb + sb) * 18;
             d[j] = (uint16_t)(b[0] | (b[1] << 8));
             const uint8_t *qs = b + 2 + 4 * t;
             w[j] = ((uint32_t)qs[0] | ((uint32_t)qs[1] << 8) | ((uint32_t)qs[2] << 16) | ((uint32_t)qs[3] << 24)) ^ 0x88888888u;
@@ -177,7 +186,8 @@ __device__ __forceinline__ void q4k_pair(const uint8_t *p, int j, int &sc, int &
 // q4_K file super-blocks [m][k/256][144 B] -> the same tile-major nibbles; per (row, sub-block) the
 // scales array holds {f16 d, f16 dmin, u8 sc, u8 mn} spread over two arrays: ws (uint2 per tile
 // lane-group: 4 x (sc | mn<<8) as u16) and wd (uint2 per (tile, g): {d,dmin} of row g and row g+8).
-__global__ void lg_repack_q4_K(const uint8_t *__restrict__ src, uint4 *__restrict__ wq, uint2 *__restrict__ ws,
+__global__ void lg_repack_q4_K(const uint8_t *__restrict__ src, const uint8_t *__restrict__ src_b,
+                               uint4 *__restrict__ wq, uint2 *__restrict__ ws,
                                uint2 *__restrict__ wd, int m, int nsb, int n_row_tiles) {
     int nkp = nsb >> 1;
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -191,10 +201,10 @@ __global__ void lg_repack_q4_K(const uint8_t *__restrict__ src, uint4 *__restric
     uint16_t sm[4];
     #pragma unroll
     for (int j = 0; j < 4; j++) {
-        int row = rt * 16 + g + (j & 1) * 8, sb = kp * 2 + (j >> 1);
+        int row = src_b ? rt * 8 + g : rt * 16 + g + (j & 1) * 8, sb = kp * 2 + (j >> 1);
         w[j] = 0; sm[j] = 0;
         if (row < m) {
-            const uint8_t *b = src + ((size_t)row * (nsb >> 3) + (sb >> 3)) * 144;
+            const uint8_t *b = ((src_b && (j & 1)) ? src_b : src) + ((size_t)row * (nsb >> 3) + (sb >> 3)) * 144;
             int js = sb & 7, sc, mn;
             q4k_pair(b + 4, js, sc, mn);
             sm[j] = (uint16_t)(sc | (mn << 8));
@@ -223,6 +233,7 @@ __global__ void lg_repack_q4_K(const uint8_t *__restrict__ src, uint4 *__restric
 // out[i][0..k) = scale * decode(row ids[i]) for q4_0 (type 2) / q4_K (type 12) / f32 (0) / f16 (1)
 __global__ void lg_dequant_rows(const uint8_t *__restrict__ src, int type, int k, const int *__restrict__ ids,
                                 int n_rows, int row0, float scale, float *__restrict__ out, int ldo) {
+    pdl_launch(); pdl_wait();
     int r = blockIdx.x;
     long long row = ids ? (long long)ids[r] : (long long)row0 + r;
     row = row < 0 ? 0 : (row >= n_rows ? n_rows - 1 : row);        // an out-of-range id must not read outside the table
@@ -260,6 +271,20 @@ __global__ void lg_dequant_rows(const uint8_t *__restrict__ src, int type, int k
 // ---------------------------------------------------------------------------------------------
 // the small-M matmul: out[tok][row] = sum_k W[row][k] * x[tok][k]
 // ---------------------------------------------------------------------------------------------
+// One CTA per token row.
+//   if (add_src)  x += rmsnorm(sum of n_parts partials of add_src) * add_w ; x *= out_scale
+//   if (norm_w)   y  = rmsnorm(x) * norm_w  -> panel (quantised) and/or y_f32
+// Either half may be absent.  rmsnorm(v) = v * (1/sqrt(mean(v^2) + eps)).
+struct LgNormArgs {
+    float *x; int ldx;                   // residual stream rows [M][ldx]
+    const float *add_src; int n_parts; size_t part_stride; int ld_add;   // partial p at add_src + p*part_stride + tok*ld_add
+    const float *add_w; float out_scale;
+    const float *norm_w;
+    LgPanel panel; int want_panel;
+    float *y; int ldy;                   // optional f32 copy of the normed row
+    int n; float eps;
+};
+
 struct LgGemvArgs {
     const uint4 *wq;           // tile-major nibbles
     const uint2 *ws;           // q4_0: 4 f16 scales per (tile, g); q4_K: 4 x (sc|mn<<8)
@@ -278,75 +303,127 @@ struct LgGemvArgs {
     float *amax_val;           // [gridDim.x][LG_MAXM] per-CTA best logit
     int *amax_idx;
     int *err;
+    // GeGLU epilogue: rows are interleaved (tile = 8 gate rows then the 8 matching up rows);
+    // y = gelu_tanh(gate) * up goes straight into the next matmul's panel
+    LgPanel outp;
 };
 
 enum { LG_FMT_Q4_0 = 0, LG_FMT_Q4_K = 1 };
-enum { LG_EPI_STORE = 0, LG_EPI_HEAD = 1 };
+enum { LG_EPI_STORE = 0, LG_EPI_HEAD = 1, LG_EPI_GEGLU = 2 };
 
-#define LG_GEMV_WARPS 8
+#define LG_GEMV_CW 8                    // consumer warps per CTA
+#define LG_GEMV_THREADS ((LG_GEMV_CW + 1) * 32)   // + one producer warp
+#define LG_GEMV_STAGES 3               // ring depth
+#define LG_GEMV_STAGE_TILES 32         // 16x64 weight tiles per stage (R row tiles x 32/R positions)
 
-// One weight fetch of a warp: R row tiles at the same 64-column tile position.
-template <int R, int FMT> struct LgWFrag {
-    uint4 w[R];
-    uint2 sc[R];
-    uint2 dd[FMT == LG_FMT_Q4_K ? R : 1];
-};
-
-template <int R, int FMT>
-__device__ __forceinline__ void gemv_fetch(LgWFrag<R, FMT> &f, const LgGemvArgs &a, int rt0, int kp, int lane, int g) {
-    #pragma unroll
-    for (int r = 0; r < R; r++) {
-        int rt = rt0 + r;
-        if (rt < a.n_row_tiles) {
-            size_t tile = (size_t)rt * a.nkp + kp;
-            f.w[r] = ldg_stream16(a.wq + tile * 32 + lane);
-            f.sc[r] = ldg_stream8(a.ws + tile * 8 + g);
-            if (FMT == LG_FMT_Q4_K) f.dd[r] = ldg_stream8(a.wd + tile * 8 + g);
-        } else {
-            f.w[r] = make_uint4(0, 0, 0, 0); f.sc[r] = make_uint2(0, 0);
-            if (FMT == LG_FMT_Q4_K) f.dd[r] = make_uint2(0, 0);
-        }
-    }
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void consumer_sync() {       // the consumer warps only; the producer warp never joins
+    asm volatile("bar.sync 1, %0;" :: "n"(LG_GEMV_CW * 32) : "memory");
 }
 
-// A CTA works on items = (group of R consecutive row tiles) x (its k slice, blockIdx.y).  Its 8
-// warps split the slice's 64-column tile positions; for each position a warp loads the B fragment
-// once from shared memory and applies it to the R row tiles (R independent 16-byte weight loads in
-// flight per lane, the next position's loads issued before the current one is consumed).  The
-// activation panel slice is staged once per CTA by a bulk copy whose completion is awaited only
-// after the first weight loads are in flight.  Partial sums of the 8 warps are added in warp order.
-// Dynamic shared memory: [NP][nsb_s][256] int8 | [NP][nsb_s][4] float2 | [8][R*NP*64] f32 | mbarrier
+// Bytes of one ring stage: nibbles, scales (and the {d,dmin} pairs of q4_K)
+template <int FMT> __host__ __device__ constexpr int gemv_stage_bytes() {
+    return LG_GEMV_STAGE_TILES * (512 + 64 + (FMT == LG_FMT_Q4_K ? 64 : 0));
+}
+
+// The small-M matmul.  A CTA walks items = (group of R consecutive row tiles) x (its k slice,
+// blockIdx.y), item after item (blockIdx.x, +gridDim.x, ...).
+//   * One producer thread streams the items' weight tiles HBM -> shared memory with bulk copies
+//     (cp.async.bulk, TMA) into a ring of LG_GEMV_STAGES stages of 32 tiles (18 KB); each stage is
+//     R row tiles x P = 32/R consecutive tile positions, completed on a "full" mbarrier and handed
+//     back on an "empty" one.  The producer runs ahead of the consumers across item boundaries, so
+//     up to 55 KB per CTA is in flight without occupying a single register.
+//   * The activation panel slice is staged once per CTA by the same thread (after the first weight
+//     stages are in flight -- they do not depend on the previous kernel).
+//   * LG_GEMV_CW consumer warps split a stage's positions; for each position a warp reads the B
+//     fragment once and applies it to the R row tiles: A fragments are one conflict-free 16-byte
+//     shared load per lane, `mma.sync.m16n8k32.s8`, f32 scale-accumulate.  Partial sums of the
+//     warps are added in warp order.
+// Every wait is bounded; a timeout raises LG_ERR_MBAR_TIMEOUT and the kernel runs to its end.
+// Dynamic shared memory: panel q | panel s | ring | reduction | mbarriers
 template <int R, int NP, int FMT, int EPI>
-__global__ void __launch_bounds__(LG_GEMV_WARPS * 32, 2)
+__global__ void __launch_bounds__(LG_GEMV_THREADS)
 lg_gemv_kernel(LgGemvArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
+    constexpr int P = LG_GEMV_STAGE_TILES / R;               // tile positions per stage
+    constexpr int NS = LG_GEMV_STAGES;
+    constexpr int STAGE = gemv_stage_bytes<FMT>();
+    constexpr int SC_OFF = LG_GEMV_STAGE_TILES * 512;        // scales after the nibbles, {d,dmin} after the scales
+    constexpr int DD_OFF = SC_OFF + LG_GEMV_STAGE_TILES * 64;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int ks = blockIdx.y;
     const int kp0 = (int)((long long)a.nkp * ks / a.kslices), kp1 = (int)((long long)a.nkp * (ks + 1) / a.kslices);
-    const int nsb_s = (kp1 - kp0) * 2;
-    int8_t *sq = (int8_t *)smem;
-    float2 *ss = (float2 *)(smem + (size_t)NP * nsb_s * 256);
-    float *red = (float *)(ss + (size_t)NP * nsb_s * 4);
-    uint64_t *bar = (uint64_t *)(red + LG_GEMV_WARPS * R * NP * 64);
-    constexpr int SLOTS = (R * NP * 64 + LG_GEMV_WARPS * 32 - 1) / (LG_GEMV_WARPS * 32);
+    const int nkp_s = kp1 - kp0, nsb_s = nkp_s * 2;
+    const int n_chunks = (nkp_s + P - 1) / P;
     const int n_groups = (a.n_row_tiles + R - 1) / R;
 
-    if (threadIdx.x == 0) mbar_init(bar, 1);
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        uint32_t qb = (uint32_t)nsb_s * 256, sb = (uint32_t)nsb_s * 32;
-        mbar_expect_tx(bar, NP * (qb + sb));
-        #pragma unroll
-        for (int p = 0; p < NP; p++) {
-            bulk_g2s(sq + (size_t)p * qb, a.x.q + ((size_t)p * a.x.nsb + kp0 * 2) * 256, qb, bar);
-            bulk_g2s(ss + (size_t)p * nsb_s * 4, a.x.s + ((size_t)p * a.x.nsb + kp0 * 2) * 4, sb, bar);
-        }
-    }
-    bool staged = false;
+    int8_t *sq = (int8_t *)smem;
+    float2 *ss = (float2 *)(smem + (size_t)NP * nsb_s * 256);
+    unsigned char *ring = (unsigned char *)(ss + (size_t)NP * nsb_s * 4);
+    ring = (unsigned char *)(((uintptr_t)ring + 127) & ~(uintptr_t)127);
+    float *red = (float *)(ring + (size_t)NS * STAGE);
+    uint64_t *full = (uint64_t *)(red + LG_GEMV_CW * R * NP * 64);
+    uint64_t *empty = full + NS, *pbar = empty + NS;
 
+    pdl_launch();
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < NS; i++) { mbar_init(full + i, 1); mbar_init(empty + i, LG_GEMV_CW); }
+        mbar_init(pbar, 1);
+    }
+    __syncthreads();
+
+    if (warp == LG_GEMV_CW) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0; bool panel_sent = false, ok = true;
+            for (int grp = blockIdx.x; grp < n_groups && ok; grp += gridDim.x) {
+                const size_t tile_base = (size_t)grp * R * a.nkp + kp0;
+                for (int c = 0; c < n_chunks && ok; c++) {
+                    if (!mbar_wait(empty + stage, phase ^ 1)) { atomicOr(a.err, LG_ERR_MBAR_TIMEOUT); ok = false; break; }
+                    const int np = min(P, nkp_s - c * P);
+                    const uint32_t tile_bytes = (uint32_t)np * (512 + 64 + (FMT == LG_FMT_Q4_K ? 64 : 0));
+                    unsigned char *st = ring + (size_t)stage * STAGE;
+                    mbar_expect_tx(full + stage, R * tile_bytes);
+                    #pragma unroll
+                    for (int r = 0; r < R; r++) {
+                        const size_t tile = tile_base + (size_t)r * a.nkp + (size_t)c * P;
+                        bulk_g2s(st + (size_t)r * P * 512, a.wq + tile * 32, (uint32_t)np * 512, full + stage);
+                        bulk_g2s(st + SC_OFF + (size_t)r * P * 64, a.ws + tile * 8, (uint32_t)np * 64, full + stage);
+                        if (FMT == LG_FMT_Q4_K)
+                            bulk_g2s(st + DD_OFF + (size_t)r * P * 64, a.wd + tile * 8, (uint32_t)np * 64, full + stage);
+                    }
+                    if (++stage == NS) { stage = 0; phase ^= 1; }
+                    if (!panel_sent && (stage == NS - 1 || c == n_chunks - 1)) {
+                        // weights are in flight; now the activations, which the previous kernel produced
+                        pdl_wait();
+                        uint32_t qb = (uint32_t)nsb_s * 256, sb = (uint32_t)nsb_s * 32;
+                        mbar_expect_tx(pbar, NP * (qb + sb));
+                        #pragma unroll
+                        for (int p = 0; p < NP; p++) {
+                            bulk_g2s(sq + (size_t)p * qb, a.x.q + ((size_t)p * a.x.nsb + kp0 * 2) * 256, qb, pbar);
+                            bulk_g2s(ss + (size_t)p * nsb_s * 4, a.x.s + ((size_t)p * a.x.nsb + kp0 * 2) * 4, sb, pbar);
+                        }
+                        panel_sent = true;
+                    }
+                }
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    constexpr int CT = LG_GEMV_CW * 32;
+    constexpr int SLOTS = (R * NP * 64 + CT - 1) / CT;
     float best_v[SLOTS]; int best_i[SLOTS];
     #pragma unroll
     for (int j = 0; j < SLOTS; j++) { best_v[j] = -INFINITY; best_i[j] = 0x7fffffff; }
+
+    pdl_wait();
+    bool ok = mbar_wait(pbar, 0);
+    if (!ok && threadIdx.x == 0) atomicOr(a.err, LG_ERR_MBAR_TIMEOUT);
+    int stage = 0; uint32_t phase = 0;
 
     for (int grp = blockIdx.x; grp < n_groups; grp += gridDim.x) {
         const int rt0 = grp * R;
@@ -356,59 +433,63 @@ lg_gemv_kernel(LgGemvArgs a) {
             #pragma unroll
             for (int p = 0; p < NP; p++) acc[r][p][0] = acc[r][p][1] = 0.0f;
 
-        LgWFrag<R, FMT> cur, nxt;
-        int kp = kp0 + warp;
-        if (kp < kp1) gemv_fetch<R, FMT>(cur, a, rt0, kp, lane, g);
-        if (!staged) {
-            if (!mbar_wait(bar, 0)) { if (threadIdx.x == 0) atomicOr(a.err, LG_ERR_MBAR_TIMEOUT); }
-            staged = true;
-        }
-        for (; kp < kp1; kp += LG_GEMV_WARPS) {
-            const bool more = kp + LG_GEMV_WARPS < kp1;
-            if (more) gemv_fetch<R, FMT>(nxt, a, rt0, kp + LG_GEMV_WARPS, lane, g);
-            #pragma unroll
-            for (int s = 0; s < 2; s++) {
-                const int sbl = (kp - kp0) * 2 + s;
-                uint2 b[NP]; float2 xs[NP];
+        for (int c = 0; c < n_chunks; c++) {
+            if (ok && !mbar_wait(full + stage, phase)) { ok = false; if (lane == 0) atomicOr(a.err, LG_ERR_MBAR_TIMEOUT); }
+            const int np = min(P, nkp_s - c * P);
+            const unsigned char *st = ring + (size_t)stage * STAGE;
+            for (int pp = warp; pp < np; pp += LG_GEMV_CW) {
+                uint2 b[2][NP]; float2 xs[2][NP];
                 #pragma unroll
-                for (int p = 0; p < NP; p++) {
-                    b[p] = *(const uint2 *)(sq + ((size_t)p * nsb_s + sbl) * 256 + lane * 8);
-                    xs[p] = ss[((size_t)p * nsb_s + sbl) * 4 + t];
-                }
-                #pragma unroll
-                for (int r = 0; r < R; r++) {
-                    uint32_t wg = s ? cur.w[r].z : cur.w[r].x, wh = s ? cur.w[r].w : cur.w[r].y;
-                    uint32_t a0 = (wg << 4) & 0xF0F0F0F0u, a2 = wg & 0xF0F0F0F0u;
-                    uint32_t a1 = (wh << 4) & 0xF0F0F0F0u, a3 = wh & 0xF0F0F0F0u;
-                    float d0, d1, m0 = 0.0f, m1 = 0.0f;
-                    uint32_t sw = s ? cur.sc[r].y : cur.sc[r].x;
-                    if (FMT == LG_FMT_Q4_0) {
-                        float2 f = __half22float2(*(const __half2 *)&sw);
-                        d0 = f.x; d1 = f.y;
-                    } else {
-                        float2 r0 = __half22float2(*(const __half2 *)&cur.dd[r].x), r1 = __half22float2(*(const __half2 *)&cur.dd[r].y);
-                        d0 = r0.x * (float)(sw & 0xff); m0 = 16.0f * (8.0f * d0 - r0.y * (float)((sw >> 8) & 0xff));
-                        d1 = r1.x * (float)((sw >> 16) & 0xff); m1 = 16.0f * (8.0f * d1 - r1.y * (float)(sw >> 24));
-                    }
+                for (int s = 0; s < 2; s++)
                     #pragma unroll
                     for (int p = 0; p < NP; p++) {
-                        int c[4] = {0, 0, 0, 0};
-                        mma_s8(c, a0, a1, a2, a3, b[p].x, b[p].y);
-                        float v0 = (float)((c[0] << 8) + c[1]) * xs[p].x;      // row g,   token 4p+t
-                        float v1 = (float)((c[2] << 8) + c[3]) * xs[p].x;      // row g+8
-                        acc[r][p][0] = fmaf(v0, d0, acc[r][p][0]);
-                        acc[r][p][1] = fmaf(v1, d1, acc[r][p][1]);
-                        if (FMT == LG_FMT_Q4_K) {     // nibbles are stored as (q-8): add back (8 d sc - dmin m) * sum(x)
-                            acc[r][p][0] = fmaf(m0, xs[p].y, acc[r][p][0]);
-                            acc[r][p][1] = fmaf(m1, xs[p].y, acc[r][p][1]);
+                        const int sbl = (c * P + pp) * 2 + s;
+                        b[s][p] = *(const uint2 *)(sq + ((size_t)p * nsb_s + sbl) * 256 + lane * 8);
+                        xs[s][p] = ss[((size_t)p * nsb_s + sbl) * 4 + t];
+                    }
+                #pragma unroll
+                for (int r = 0; r < R; r++) {
+                    // this lane's 16 bytes: {row g, row g+8} words of sub-block 0, then of sub-block 1
+                    const uint4 w = *(const uint4 *)(st + (size_t)(r * P + pp) * 512 + lane * 16);
+                    const uint2 sw2 = *(const uint2 *)(st + SC_OFF + (size_t)(r * P + pp) * 64 + g * 8);
+                    uint2 dd = make_uint2(0, 0);
+                    if (FMT == LG_FMT_Q4_K) dd = *(const uint2 *)(st + DD_OFF + (size_t)(r * P + pp) * 64 + g * 8);
+                    #pragma unroll
+                    for (int s = 0; s < 2; s++) {
+                        const uint32_t wg = s ? w.z : w.x, wh = s ? w.w : w.y, sw = s ? sw2.y : sw2.x;
+                        uint32_t a0 = (wg << 4) & 0xF0F0F0F0u, a2 = wg & 0xF0F0F0F0u;
+                        uint32_t a1 = (wh << 4) & 0xF0F0F0F0u, a3 = wh & 0xF0F0F0F0u;
+                        float d0, d1, m0 = 0.0f, m1 = 0.0f;
+                        if (FMT == LG_FMT_Q4_0) {
+                            float2 fd = __half22float2(*(const __half2 *)&sw);
+                            d0 = fd.x; d1 = fd.y;
+                        } else {
+                            float2 r0 = __half22float2(*(const __half2 *)&dd.x), r1 = __half22float2(*(const __half2 *)&dd.y);
+                            d0 = r0.x * (float)(sw & 0xff); m0 = 16.0f * (8.0f * d0 - r0.y * (float)((sw >> 8) & 0xff));
+                            d1 = r1.x * (float)((sw >> 16) & 0xff); m1 = 16.0f * (8.0f * d1 - r1.y * (float)(sw >> 24));
+                        }
+                        #pragma unroll
+                        for (int p = 0; p < NP; p++) {
+                            int cc[4] = {0, 0, 0, 0};
+                            mma_s8(cc, a0, a1, a2, a3, b[s][p].x, b[s][p].y);
+                            float v0 = (float)((cc[0] << 8) + cc[1]) * xs[s][p].x;      // row g,   token 4p+t
+                            float v1 = (float)((cc[2] << 8) + cc[3]) * xs[s][p].x;      // row g+8
+                            acc[r][p][0] = fmaf(v0, d0, acc[r][p][0]);
+                            acc[r][p][1] = fmaf(v1, d1, acc[r][p][1]);
+                            if (FMT == LG_FMT_Q4_K) {     // nibbles are stored as (q-8): add back (8 d sc - dmin m) * sum(x)
+                                acc[r][p][0] = fmaf(m0, xs[s][p].y, acc[r][p][0]);
+                                acc[r][p][1] = fmaf(m1, xs[s][p].y, acc[r][p][1]);
+                            }
                         }
                     }
                 }
             }
-            if (more) cur = nxt;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty + stage);
+            if (++stage == NS) { stage = 0; phase ^= 1; }
         }
 
-        // fixed-order sum over the 8 warps
+        // fixed-order sum over the consumer warps
         #pragma unroll
         for (int r = 0; r < R; r++)
             #pragma unroll
@@ -416,29 +497,42 @@ lg_gemv_kernel(LgGemvArgs a) {
                 red[(warp * R * NP + r * NP + p) * 64 + t * 16 + g] = acc[r][p][0];
                 red[(warp * R * NP + r * NP + p) * 64 + t * 16 + g + 8] = acc[r][p][1];
             }
-        __syncthreads();
-        #pragma unroll
-        for (int j = 0; j < SLOTS; j++) {
-            int idx = threadIdx.x + j * LG_GEMV_WARPS * 32;
-            if (idx < R * NP * 64) {
-                int rp = idx >> 6, r = rp / NP, p = rp % NP, tok = p * 4 + ((idx >> 4) & 3);
-                float sum = 0.0f;
+        consumer_sync();
+        if (EPI == LG_EPI_GEGLU) {
+            // one warp per token: lane o = output (r, row8) of this item's 32 outputs
+            for (int tok = warp; tok < NP * 4 && tok < a.M; tok += LG_GEMV_CW) {
+                const int p = tok >> 2, tl = tok & 3, r = lane >> 3, row8 = lane & 7;
+                const int ig = ((r * NP + p) * 4 + tl) * 16 + row8;
+                float gate = 0.0f, up = 0.0f;
                 #pragma unroll
-                for (int w2 = 0; w2 < LG_GEMV_WARPS; w2++) sum += red[w2 * R * NP * 64 + idx];
-                sum *= 0.0625f;
-                int row = (rt0 + r) * 16 + (idx & 15);
-                if (rt0 + r < a.n_row_tiles && tok < a.M) {
-                    if (EPI == LG_EPI_STORE) {
-                        a.out[((size_t)ks * LG_MAXM + tok) * a.ldo + row] = sum;
-                    } else if (row < a.n_valid_rows) {
-                        if (a.softcap > 0.0f) sum = a.softcap * tanhf(sum / a.softcap);
-                        if (a.logits) a.logits[(size_t)tok * a.ldo + row] = sum;
-                        if (sum > best_v[j]) { best_v[j] = sum; best_i[j] = row; }   // rows ascend per slot: first max wins
+                for (int w2 = 0; w2 < LG_GEMV_CW; w2++) { gate += red[w2 * R * NP * 64 + ig]; up += red[w2 * R * NP * 64 + ig + 8]; }
+                float y = __fmul_rn(gelu_tanh(gate * 0.0625f), up * 0.0625f);
+                quant_group_store(y, lane, tok, rt0 / R, a.outp);
+            }
+        } else {
+            #pragma unroll
+            for (int j = 0; j < SLOTS; j++) {
+                int idx = threadIdx.x + j * CT;
+                if (idx < R * NP * 64) {
+                    int rp = idx >> 6, r = rp / NP, p = rp % NP, tok = p * 4 + ((idx >> 4) & 3);
+                    float sum = 0.0f;
+                    #pragma unroll
+                    for (int w2 = 0; w2 < LG_GEMV_CW; w2++) sum += red[w2 * R * NP * 64 + idx];
+                    sum *= 0.0625f;
+                    int row = (rt0 + r) * 16 + (idx & 15);
+                    if (rt0 + r < a.n_row_tiles && tok < a.M) {
+                        if (EPI == LG_EPI_STORE) {
+                            a.out[((size_t)ks * LG_MAXM + tok) * a.ldo + row] = sum;
+                        } else if (row < a.n_valid_rows) {
+                            if (a.softcap > 0.0f) sum = a.softcap * tanhf(sum / a.softcap);
+                            if (a.logits) a.logits[(size_t)tok * a.ldo + row] = sum;
+                            if (sum > best_v[j]) { best_v[j] = sum; best_i[j] = row; }   // rows ascend per slot: first max wins
+                        }
                     }
                 }
             }
         }
-        __syncthreads();
+        consumer_sync();
     }
 
     if (EPI == LG_EPI_HEAD) {
@@ -446,10 +540,10 @@ lg_gemv_kernel(LgGemvArgs a) {
         float *cv = red; int *ci = (int *)(red + R * NP * 64);
         #pragma unroll
         for (int j = 0; j < SLOTS; j++) {
-            int idx = threadIdx.x + j * LG_GEMV_WARPS * 32;
+            int idx = threadIdx.x + j * CT;
             if (idx < R * NP * 64) { cv[idx] = best_v[j]; ci[idx] = best_i[j]; }
         }
-        __syncthreads();
+        consumer_sync();
         if (threadIdx.x < a.M) {
             int tok = threadIdx.x, p = tok >> 2, tl = tok & 3;
             float bv = -INFINITY; int bi = 0x7fffffff;
@@ -467,6 +561,7 @@ lg_gemv_kernel(LgGemvArgs a) {
 
 // Merge the per-CTA argmax candidates: out[tok] = index of the largest logit, lowest index on ties.
 __global__ void lg_argmax_final(const float *__restrict__ val, const int *__restrict__ idx, int n_parts, int *out) {
+    pdl_launch(); pdl_wait();
     int tok = blockIdx.x;
     float bv = -INFINITY; int bi = 0x7fffffff;
     for (int i = threadIdx.x; i < n_parts; i += blockDim.x) {
@@ -501,6 +596,7 @@ __global__ void lg_argmax_final(const float *__restrict__ val, const int *__rest
 __global__ void lg_embed_rows(const uint4 *__restrict__ wq, const uint2 *__restrict__ ws, const uint2 *__restrict__ wd,
                               int fmt, int nkp, int n_rows, const int *__restrict__ toks, float scale,
                               float *__restrict__ out, int ldo) {
+    pdl_launch(); pdl_wait();
     int tok = blockIdx.x;
     int row = min(max(toks[tok], 0), n_rows - 1);               // an out-of-range id must not read outside the table
     int rt = row >> 4, r = row & 15, g = r & 7, hi8 = r >> 3;
@@ -533,20 +629,8 @@ __global__ void lg_embed_rows(const uint4 *__restrict__ wq, const uint2 *__restr
 // ---------------------------------------------------------------------------------------------
 // norms
 // ---------------------------------------------------------------------------------------------
-// One CTA per token row.
-//   if (add_src)  x += rmsnorm(sum of n_parts partials of add_src) * add_w ; x *= out_scale
-//   if (norm_w)   y  = rmsnorm(x) * norm_w  -> panel (quantised) and/or y_f32
-// Either half may be absent.  rmsnorm(v) = v * (1/sqrt(mean(v^2) + eps)).
-struct LgNormArgs {
-    float *x; int ldx;                   // residual stream rows [M][ldx]
-    const float *add_src; int n_parts; size_t part_stride; int ld_add;   // partial p at add_src + p*part_stride + tok*ld_add
-    const float *add_w; float out_scale;
-    const float *norm_w;
-    LgPanel panel; int want_panel;
-    float *y; int ldy;                   // optional f32 copy of the normed row
-    int n; float eps;
-};
 __global__ void lg_norm_kernel(LgNormArgs a) {
+    pdl_launch(); pdl_wait();
     extern __shared__ float row[];       // n floats + 32
     float *red = row + a.n;
     const int tok = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -589,6 +673,7 @@ __global__ void lg_norm_kernel(LgNormArgs a) {
 
 // Quantise f32 rows into a panel (used where the producer is not one of the fused kernels).
 __global__ void lg_quant_rows(const float *__restrict__ x, int ldx, int n, LgPanel P) {
+    pdl_launch(); pdl_wait();
     int tok = blockIdx.y, lane = threadIdx.x & 31;
     int sb = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (sb * 32 >= n) return;
@@ -596,206 +681,313 @@ __global__ void lg_quant_rows(const float *__restrict__ x, int ldx, int n, LgPan
 }
 
 // ---------------------------------------------------------------------------------------------
-// per-head q/k/v post-processing: rmsnorm, NeoX RoPE at pos+tok, f16 KV write
+// attention: q/k/v post-processing + split-KV flash-decode on tensor cores + combine, one launch
 // ---------------------------------------------------------------------------------------------
-// qkv: [M][ld] rows = [q (H*hd) | k (Hkv*hd) | v (Hkv*hd)] from the matmul (v absent: v = k projection).
-// grid (H + 2*Hkv, M), block hd/2 threads ... each thread owns the pair (i, i+hd/2).
-struct LgQkvArgs {
-    const float *qkv; int ld;
-    int H, Hkv, hd; int has_v; int owns_kv;
-    const float *q_norm, *k_norm;        // [hd]
-    const float *rope_div;               // [hd/2] or null
-    float rope_base; float eps;
-    const int *pos;                      // device position of token 0
-    float *q_out;                        // [M][H*hd] f32 (normed + rotated)
-    __half *kc, *vc; int seq, kv_dim;    // cache of this layer
-};
-__global__ void lg_qkv_post_kernel(LgQkvArgs a) {
-    __shared__ float red[32];
-    const int head = blockIdx.x, tok = blockIdx.y, i = threadIdx.x, half = a.hd >> 1;
-    const int pos = *a.pos + tok;
-    int kind = head < a.H ? 0 : (head < a.H + a.Hkv ? 1 : 2);   // q, k, v
-    if (kind && !a.owns_kv) return;
-    int hh = kind == 0 ? head : (kind == 1 ? head - a.H : head - a.H - a.Hkv);
-    size_t col = kind == 0 ? (size_t)hh * a.hd
-               : (kind == 1 || !a.has_v) ? (size_t)(a.H + hh) * a.hd
-               : (size_t)(a.H + a.Hkv + hh) * a.hd;
-    const float *src = a.qkv + (size_t)tok * a.ld + col;
-    float v0 = src[i], v1 = src[i + half];
-    float ss = block_sum(v0 * v0 + v1 * v1, red);
-    float s = 1.0f / sqrtf(ss / (float)a.hd + a.eps);
-    if (kind == 2) {
-        size_t r = (size_t)(pos % a.seq) * a.kv_dim + (size_t)hh * a.hd;
-        a.vc[r + i] = __float2half_rn(__fmul_rn(v0, s));
-        a.vc[r + i + half] = __float2half_rn(__fmul_rn(v1, s));
-        return;
-    }
-    const float *w = kind == 0 ? a.q_norm : a.k_norm;
-    v0 = __fmul_rn(__fmul_rn(v0, s), w[i]);
-    v1 = __fmul_rn(__fmul_rn(v1, s), w[i + half]);
-    float freq = powf(a.rope_base, -2.0f * (float)i / (float)a.hd);
-    float ang = (float)pos * freq / (a.rope_div ? a.rope_div[i] : 1.0f);
-    float c = cosf(ang), sn = sinf(ang);
-    float r0 = __fsub_rn(__fmul_rn(v0, c), __fmul_rn(v1, sn));
-    float r1 = __fadd_rn(__fmul_rn(v0, sn), __fmul_rn(v1, c));
-    if (kind == 0) {
-        float *q = a.q_out + ((size_t)tok * a.H + hh) * a.hd;
-        q[i] = r0; q[i + half] = r1;
-    } else {
-        size_t r = (size_t)(pos % a.seq) * a.kv_dim + (size_t)hh * a.hd;
-        a.kc[r + i] = __float2half_rn(r0);
-        a.kc[r + i + half] = __float2half_rn(r1);
-    }
-}
-
-// ---------------------------------------------------------------------------------------------
-// split-KV flash-decode over the f16 cache
-// ---------------------------------------------------------------------------------------------
-// Keys are partitioned on ABSOLUTE position boundaries: tile T covers positions [T*S, (T+1)*S).
+// Keys are partitioned on ABSOLUTE position boundaries: tile T covers positions [T*64, (T+1)*64).
 // Query j (token j of the block, position p_j = pos + j + qpos_off) attends positions
-// [max(0, p_j - window + 1), p_j]  (window <= 0: from 0).  A CTA handles one KV head and one tile
-// for all queries of the block (gqa heads x M tokens); per (query, tile) it emits the partial
-// (max, sum, acc[hd]) of an online softmax.  The combine kernel merges a query's tiles in
-// ascending order.  A partial depends only on (query position, tile), never on M or on which
-// other queries share the launch.
+// [max(0, p_j + win_shrink - window + 1), p_j]  (window <= 0: from 0).
+// A CTA handles one KV head and one tile for all of that head's queries (gqa heads x M tokens):
+//   1. per-head RMSNorm + NeoX RoPE of its queries from the raw projection (f32), split into an
+//      f16 hi + f16 lo pair so the tensor-core dot keeps ~22 bits of q; the CTA whose tile holds a
+//      new position also normalises / rotates that position's K row and normalises its V row and
+//      writes both to the f16 cache (round to nearest even) before loading the tile;
+//   2. S = Q K^T and O = P V with mma.sync.m16n8k16 (f16 operands, f32 accumulate), K/V tile brought
+//      in with cp.async, P also as hi + lo; scale 1.0, masks per query;
+//   3. the partial (max, sum, acc[hd]) of each (query, tile) goes to scratch; the LAST CTA of a KV
+//      head to finish (ticket counter) merges that head's queries over their tiles in ascending
+//      order, normalises and writes the o-projection's panel.
+// A partial depends only on (query position, tile) and the merge order is fixed, so a row's result
+// does not depend on M or on which other queries share the launch.
 struct LgAttnArgs {
-    const float *q;            // [M][H][hd]
-    const __half *kc, *vc; int seq, kv_dim;
+    // raw projection rows [M][ld] = [q (H*hd) | k (Hkv*hd) | v (Hkv*hd)]; q_ready: q is [M][H][hd], final
+    const float *qkv; int ld; int q_ready;
+    int has_v, owns_kv;                  // v projection present; this layer writes K/V rows
+    const float *q_norm, *k_norm, *rope_div; float rope_base, eps;
+    __half *kc, *vc; int seq, kv_dim;
     int H, Hkv, hd, M;
-    int S;                     // tile size (keys)
     int n_slots;               // tile slots in the scratch (>= tiles a block can touch)
     int window;                // <=0: full causal
     int qpos_off;              // 0 for the target; -1 for the draft head (query at pos sees keys < pos)
-    int win_shrink;            // draft head: window start stays pos-W+1 (one fewer key)
+    int win_shrink;            // draft head: the window start stays pos-W+1 (one key fewer)
     const int *pos;
     float *part;               // [n_slots][M][H][hd+2]  (acc[hd], max, sum)
-    LgPanel out; float *out_f32;   // combine output: panel of [M][H*hd] and/or f32
+    int *tickets;              // [Hkv], zero between launches
+    LgPanel out; float *out_f32;   // merged output: panel of [M][H*hd] and/or f32 [M][H][hd]
 };
 
-#define LG_ATTN_THREADS 256
-// dynamic smem: q [nq][hd] f32 | kv tile [S][hd+8] f16 | scores [nq][S] f32
-__global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_split_kernel(LgAttnArgs a) {
-    extern __shared__ __align__(128) unsigned char smem[];
-    const int kvh = blockIdx.x, gqa = a.H / a.Hkv, nq = gqa * a.M, hd = a.hd, S = a.S;
-    const int pos0 = *a.pos;
-    // tile range touched by this block of queries
-    int p_first = pos0 + a.qpos_off, p_last = pos0 + a.M - 1 + a.qpos_off;
-    if (p_last < 0) return;
-    int lo_first = a.window > 0 ? max(0, p_first + a.win_shrink - a.window + 1) : 0;
-    int t_lo = lo_first / S, t_hi = p_last / S;
-    int T = t_lo + blockIdx.y;
-    if (T > t_hi) return;
-    const int slot = T % a.n_slots;
+#define LG_ATTN_THREADS 128
+#define LG_ATTN_S 64
 
-    float *sq = (float *)smem;                                   // [nq][hd]
-    __half *skv = (__half *)(sq + (size_t)nq * hd);              // [S][hd+8]
-    float *sc = (float *)(skv + (size_t)S * (hd + 8));           // [nq][S]
-    const int ldk = hd + 8;
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void *p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void *p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(void *dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
-    for (int i = threadIdx.x; i < nq * hd; i += blockDim.x) {
-        int qi = i / hd, d = i % hd, tok = qi / gqa, hq = kvh * gqa + qi % gqa;
-        sq[i] = a.q[((size_t)tok * a.H + hq) * hd + d];
+// RMSNorm (optional weight) + optional NeoX RoPE of one head vector by one warp.
+// lane owns pairs i = lane*PER + e (e < PER) and their partners i + hd/2;  out_lo[i], out_hi[i] returned in v0/v1.
+template <int HD>
+__device__ __forceinline__ void head_norm_rope(const float *src, const float *w, bool rope, const float *div, float base,
+                                               float eps, int pos, int lane, float (&v0)[HD / 64], float (&v1)[HD / 64]) {
+    constexpr int PER = HD / 64, HALF = HD / 2;
+    float ss = 0.0f;
+    #pragma unroll
+    for (int e = 0; e < PER; e++) {
+        int i = lane * PER + e;
+        v0[e] = src[i]; v1[e] = src[i + HALF];
+        ss += v0[e] * v0[e] + v1[e] * v1[e];
     }
-    // K tile -> smem (16-byte chunks)
-    const int chunks = hd / 8;
-    for (int i = threadIdx.x; i < S * chunks; i += blockDim.x) {
-        int key = i / chunks, c = i % chunks;
-        int p = T * S + key;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (p <= p_last) v = *(const uint4 *)(a.kc + (size_t)(p % a.seq) * a.kv_dim + (size_t)kvh * hd + c * 8);
-        *(uint4 *)(skv + (size_t)key * ldk + c * 8) = v;
-    }
-    __syncthreads();
-    // scores
-    for (int i = threadIdx.x; i < nq * S; i += blockDim.x) {
-        int qi = i / S, key = i % S;
-        int p = T * S + key;
-        int pj = pos0 + qi / gqa + a.qpos_off;
-        int lo = a.window > 0 ? max(0, pj + a.win_shrink - a.window + 1) : 0;
-        float s = -INFINITY;
-        if (p >= lo && p <= pj) {
-            s = 0.0f;
-            const float *qv = sq + (size_t)qi * hd;
-            const __half *kr = skv + (size_t)key * ldk;
-            for (int d = 0; d < hd; d += 8) {
-                uint4 kk = *(const uint4 *)(kr + d);
-                const __half2 *h2 = (const __half2 *)&kk;
-                float4 qa = *(const float4 *)(qv + d), qb = *(const float4 *)(qv + d + 4);
-                float2 k0 = __half22float2(h2[0]), k1 = __half22float2(h2[1]), k2 = __half22float2(h2[2]), k3 = __half22float2(h2[3]);
-                s = fmaf(qa.x, k0.x, s); s = fmaf(qa.y, k0.y, s); s = fmaf(qa.z, k1.x, s); s = fmaf(qa.w, k1.y, s);
-                s = fmaf(qb.x, k2.x, s); s = fmaf(qb.y, k2.y, s); s = fmaf(qb.z, k3.x, s); s = fmaf(qb.w, k3.y, s);
-            }
+    ss = warp_sum(ss);
+    float s = 1.0f / sqrtf(ss / (float)HD + eps);
+    #pragma unroll
+    for (int e = 0; e < PER; e++) {
+        int i = lane * PER + e;
+        float a = __fmul_rn(v0[e], s), b = __fmul_rn(v1[e], s);
+        if (w) { a = __fmul_rn(a, w[i]); b = __fmul_rn(b, w[i + HALF]); }
+        if (rope) {
+            float freq = powf(base, -2.0f * (float)i / (float)HD);
+            float ang = (float)pos * freq / (div ? div[i] : 1.0f);
+            float c = cosf(ang), sn = sinf(ang);
+            float r0 = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, sn));
+            float r1 = __fadd_rn(__fmul_rn(a, sn), __fmul_rn(b, c));
+            a = r0; b = r1;
         }
-        sc[i] = s;
-    }
-    __syncthreads();
-    // V tile -> smem (reuses the K buffer)
-    for (int i = threadIdx.x; i < S * chunks; i += blockDim.x) {
-        int key = i / chunks, c = i % chunks;
-        int p = T * S + key;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (p <= p_last) v = *(const uint4 *)(a.vc + (size_t)(p % a.seq) * a.kv_dim + (size_t)kvh * hd + c * 8);
-        *(uint4 *)(skv + (size_t)key * ldk + c * 8) = v;
-    }
-    // per-query tile softmax: one warp per query
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    for (int qi = warp; qi < nq; qi += nw) {
-        float mx = -INFINITY;
-        for (int k2 = lane; k2 < S; k2 += 32) mx = fmaxf(mx, sc[qi * S + k2]);
-        mx = warp_max(mx);
-        float sum = 0.0f;
-        for (int k2 = lane; k2 < S; k2 += 32) {
-            float s = sc[qi * S + k2];
-            float e = (s == -INFINITY) ? 0.0f : expf(s - mx);
-            sc[qi * S + k2] = e;
-            sum += e;
-        }
-        sum = warp_sum(sum);
-        if (lane == 0) {
-            int tok = qi / gqa, hq = kvh * gqa + qi % gqa;
-            float *pp = a.part + (((size_t)slot * a.M + tok) * a.H + hq) * (hd + 2);
-            pp[hd] = mx; pp[hd + 1] = sum;
-        }
-    }
-    __syncthreads();
-    // P V: thread owns a dim pair for a subset of queries
-    const int npair = hd / 2, qstep = blockDim.x / npair;      // hd 256: 128 pairs, 2 query lanes; hd 64: 32 pairs, 8
-    const int dp = threadIdx.x % npair;
-    for (int qi = threadIdx.x / npair; qi < nq; qi += qstep) {
-        float a0 = 0.0f, a1 = 0.0f;
-        const float *pr = sc + (size_t)qi * S;
-        for (int key = 0; key < S; key++) {
-            float2 vv = __half22float2(*(const __half2 *)(skv + (size_t)key * ldk + dp * 2));
-            float pw = pr[key];
-            a0 = fmaf(pw, vv.x, a0); a1 = fmaf(pw, vv.y, a1);
-        }
-        int tok = qi / gqa, hq = kvh * gqa + qi % gqa;
-        float *pp = a.part + (((size_t)slot * a.M + tok) * a.H + hq) * (hd + 2);
-        pp[dp * 2] = a0; pp[dp * 2 + 1] = a1;
+        v0[e] = a; v1[e] = b;
     }
 }
 
-// grid (H, M), block hd threads: merge the tiles of one (token, head) in ascending tile order.
-__global__ void lg_attn_combine_kernel(LgAttnArgs a) {
-    const int hq = blockIdx.x, tok = blockIdx.y, d = threadIdx.x, hd = a.hd, S = a.S;
-    const int pj = *a.pos + tok + a.qpos_off;
-    float acc = 0.0f, m = -INFINITY, l = 0.0f;
-    if (pj >= 0) {
-        int lo = a.window > 0 ? max(0, pj + a.win_shrink - a.window + 1) : 0;
-        for (int T = lo / S; T <= pj / S; T++) {
-            const float *pp = a.part + (((size_t)(T % a.n_slots) * a.M + tok) * a.H + hq) * (hd + 2);
-            float pm = pp[hd], pl = pp[hd + 1];
-            if (pl <= 0.0f) continue;
-            float nm = fmaxf(m, pm);
-            float s_old = (m == -INFINITY) ? 0.0f : expf(m - nm), s_new = expf(pm - nm);
-            acc = acc * s_old + pp[d] * s_new;
-            l = l * s_old + pl * s_new;
-            m = nm;
+// dynamic smem: Qhi | Qlo [NQ16][HD+8] f16 | K [64][HD+8] | V [64][HD+8] | S [NQ16][64] f32 | Phi | Plo [NQ16][72] f16 | ml [NQ16][2]
+template <int HD>
+__global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) {
+    pdl_launch(); pdl_wait();
+    extern __shared__ __align__(128) unsigned char smem[];
+    constexpr int S = LG_ATTN_S, LDH = HD + 8, LDP = S + 8, PER = HD / 64, HALF = HD / 2;
+    const int kvh = blockIdx.x, gqa = a.H / a.Hkv, nq = gqa * a.M, nq16 = (nq + 15) & ~15;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int pos0 = *a.pos;
+    const int p_first = pos0 + a.qpos_off, p_last = pos0 + a.M - 1 + a.qpos_off;
+    if (p_last < 0) return;
+    const int lo_first = a.window > 0 ? max(0, p_first + a.win_shrink - a.window + 1) : 0;
+    const int t_lo = lo_first / S, t_hi = p_last / S;
+    const int T = t_lo + blockIdx.y;
+    if (T > t_hi) return;
+    const int slot = T % a.n_slots;
+
+    __half *qhi = (__half *)smem, *qlo = qhi + (size_t)nq16 * LDH;
+    __half *sk = qlo + (size_t)nq16 * LDH, *sv = sk + (size_t)S * LDH;
+    float *sc = (float *)(sv + (size_t)S * LDH);
+    __half *phi = (__half *)(sc + (size_t)nq16 * S), *plo = phi + (size_t)nq16 * LDP;
+    float *ml = (float *)(plo + (size_t)nq16 * LDP);
+
+    // ---- 1. queries (and the new K/V rows this tile owns) ----
+    for (int qi = warp; qi < nq16; qi += 4) {
+        float v0[PER], v1[PER];
+        if (qi < nq) {
+            const int tok = qi / gqa, hq = kvh * gqa + qi % gqa;
+            if (a.q_ready) {
+                const float *src = a.qkv + ((size_t)tok * a.H + hq) * HD;
+                #pragma unroll
+                for (int e = 0; e < PER; e++) { v0[e] = src[lane * PER + e]; v1[e] = src[lane * PER + e + HALF]; }
+            } else {
+                head_norm_rope<HD>(a.qkv + (size_t)tok * a.ld + (size_t)hq * HD, a.q_norm, true, a.rope_div, a.rope_base, a.eps,
+                                   pos0 + tok, lane, v0, v1);
+            }
+        } else {
+            #pragma unroll
+            for (int e = 0; e < PER; e++) v0[e] = v1[e] = 0.0f;
+        }
+        #pragma unroll
+        for (int e = 0; e < PER; e++) {
+            int i = lane * PER + e;
+            __half h0 = __float2half_rn(v0[e]), h1 = __float2half_rn(v1[e]);
+            qhi[(size_t)qi * LDH + i] = h0; qhi[(size_t)qi * LDH + i + HALF] = h1;
+            qlo[(size_t)qi * LDH + i] = __float2half_rn(v0[e] - __half2float(h0));
+            qlo[(size_t)qi * LDH + i + HALF] = __float2half_rn(v1[e] - __half2float(h1));
         }
     }
-    float y = l > 0.0f ? acc / l : 0.0f;
-    if (a.out_f32) a.out_f32[((size_t)tok * a.H + hq) * hd + d] = y;
-    if (a.out.q) quant_group_store(y, d & 31, tok, (hq * hd + d) >> 5, a.out);
+    if (a.owns_kv && !a.q_ready) {
+        // rows of the new positions that fall into this tile: K (norm + rope) and V (plain norm), f16 RNE
+        for (int j = warp; j < 2 * a.M; j += 4) {
+            const int tok = j >> 1, isv = j & 1, p = pos0 + tok;
+            if (p / S != T) continue;
+            float v0[PER], v1[PER];
+            const float *src = a.qkv + (size_t)tok * a.ld + (size_t)(a.H + ((isv && a.has_v) ? a.Hkv : 0) + kvh) * HD;
+            head_norm_rope<HD>(src, isv ? nullptr : a.k_norm, !isv, a.rope_div, a.rope_base, a.eps, p, lane, v0, v1);
+            __half *dst = (isv ? a.vc : a.kc) + (size_t)(p % a.seq) * a.kv_dim + (size_t)kvh * HD;
+            #pragma unroll
+            for (int e = 0; e < PER; e++) {
+                dst[lane * PER + e] = __float2half_rn(v0[e]);
+                dst[lane * PER + e + HALF] = __float2half_rn(v1[e]);
+            }
+        }
+    }
+    __syncthreads();                       // the rows just written are visible to this CTA's tile load
+
+    // ---- 2. K and V tiles -> shared memory ----
+    constexpr int CH = HD / 8;
+    for (int i = threadIdx.x; i < S * CH; i += LG_ATTN_THREADS) {
+        const int key = i / CH, c = i % CH, p = T * S + key;
+        __half *dk = sk + (size_t)key * LDH + c * 8, *dv = sv + (size_t)key * LDH + c * 8;
+        if (p <= p_last) {
+            const size_t off = (size_t)(p % a.seq) * a.kv_dim + (size_t)kvh * HD + c * 8;
+            cp_async16(dk, a.kc + off);
+            cp_async16(dv, a.vc + off);
+        } else {
+            *(uint4 *)dk = make_uint4(0, 0, 0, 0);
+            *(uint4 *)dv = make_uint4(0, 0, 0, 0);
+        }
+    }
+    cp_async_wait_all();
+    __syncthreads();
+
+    // ---- 3. scores: warp w takes keys [16w, 16w+16) ----
+    const int g = lane >> 2, t = lane & 3;
+    for (int mt = 0; mt < nq16 / 16; mt++) {
+        float c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
+        const __half *qa_hi = qhi + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + (lane >> 4) * 8;
+        const __half *qa_lo = qlo + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + (lane >> 4) * 8;
+        const __half *kb = sk + (size_t)(warp * 16 + (lane & 7) + (lane >> 4) * 8) * LDH + ((lane >> 3) & 1) * 8;
+        #pragma unroll 4
+        for (int k0 = 0; k0 < HD; k0 += 16) {
+            uint32_t ah[4], al[4], b[4];
+            ldsm_x4(ah, qa_hi + k0); ldsm_x4(al, qa_lo + k0); ldsm_x4(b, kb + k0);
+            mma_f16(c0, ah, b[0], b[1]); mma_f16(c0, al, b[0], b[1]);
+            mma_f16(c1, ah, b[2], b[3]); mma_f16(c1, al, b[2], b[3]);
+        }
+        #pragma unroll
+        for (int h2 = 0; h2 < 2; h2++) {
+            const int qi = mt * 16 + g + h2 * 8;
+            const int pj = pos0 + qi / gqa + a.qpos_off;
+            const int lo = a.window > 0 ? max(0, pj + a.win_shrink - a.window + 1) : 0;
+            #pragma unroll
+            for (int nt = 0; nt < 2; nt++)
+                #pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const int key = warp * 16 + nt * 8 + t * 2 + e, p = T * S + key;
+                    float v = nt ? c1[h2 * 2 + e] : c0[h2 * 2 + e];
+                    sc[(size_t)qi * S + key] = (qi < nq && p >= lo && p <= pj) ? v : -INFINITY;
+                }
+        }
+    }
+    __syncthreads();
+
+    // ---- 4. per-query softmax over the tile ----
+    for (int qi = warp; qi < nq16; qi += 4) {
+        float s0 = sc[(size_t)qi * S + lane], s1 = sc[(size_t)qi * S + lane + 32];
+        float mx = warp_max(fmaxf(s0, s1));
+        float e0 = (s0 == -INFINITY) ? 0.0f : expf(s0 - mx), e1 = (s1 == -INFINITY) ? 0.0f : expf(s1 - mx);
+        float sum = warp_sum(e0 + e1);
+        __half h0 = __float2half_rn(e0), h1 = __float2half_rn(e1);
+        phi[(size_t)qi * LDP + lane] = h0; phi[(size_t)qi * LDP + lane + 32] = h1;
+        plo[(size_t)qi * LDP + lane] = __float2half_rn(e0 - __half2float(h0));
+        plo[(size_t)qi * LDP + lane + 32] = __float2half_rn(e1 - __half2float(h1));
+        if (lane == 0) { ml[qi * 2] = mx; ml[qi * 2 + 1] = sum; }
+    }
+    __syncthreads();
+
+    // ---- 5. O = P V: warp w takes dims [w*HD/4, (w+1)*HD/4) ----
+    constexpr int NT = HD / 4 / 8;                 // 8-wide output tiles per warp
+    for (int mt = 0; mt < nq16 / 16; mt++) {
+        float o[NT][4];
+        #pragma unroll
+        for (int n = 0; n < NT; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
+        const __half *pa_hi = phi + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDP + (lane >> 4) * 8;
+        const __half *pa_lo = plo + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDP + (lane >> 4) * 8;
+        #pragma unroll
+        for (int k0 = 0; k0 < S; k0 += 16) {
+            uint32_t ah[4], al[4];
+            ldsm_x4(ah, pa_hi + k0); ldsm_x4(al, pa_lo + k0);
+            const __half *vb = sv + (size_t)(k0 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + warp * (HD / 4) + (lane >> 4) * 8;
+            #pragma unroll
+            for (int n = 0; n < NT; n += 2) {
+                uint32_t b[4];
+                ldsm_x4_t(b, vb + n * 8);
+                mma_f16(o[n], ah, b[0], b[1]); mma_f16(o[n], al, b[0], b[1]);
+                mma_f16(o[n + 1], ah, b[2], b[3]); mma_f16(o[n + 1], al, b[2], b[3]);
+            }
+        }
+        #pragma unroll
+        for (int h2 = 0; h2 < 2; h2++) {
+            const int qi = mt * 16 + g + h2 * 8;
+            if (qi < nq) {
+                const int tok = qi / gqa, hq = kvh * gqa + qi % gqa;
+                float *pp = a.part + (((size_t)slot * a.M + tok) * a.H + hq) * (HD + 2);
+                #pragma unroll
+                for (int n = 0; n < NT; n++)
+                    *(float2 *)(pp + warp * (HD / 4) + n * 8 + t * 2) = make_float2(o[n][h2 * 2], o[n][h2 * 2 + 1]);
+                if (warp == 0 && t == 0) { pp[HD] = ml[qi * 2]; pp[HD + 1] = ml[qi * 2 + 1]; }
+            }
+        }
+    }
+
+    // ---- 6. the last CTA of this KV head merges ----
+    __shared__ int s_last;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        s_last = atomicAdd(a.tickets + kvh, 1) == t_hi - t_lo;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // (a) every (query, tile) max and sum -> shared memory (the K/V tile area is free now)
+    const int nt_all = t_hi - t_lo + 1;
+    float2 *mls = (float2 *)sk;                               // [nq][nt_all]: (max, sum) then (weight, -)
+    float *invl = ml;                                         // [nq]
+    for (int i = threadIdx.x; i < nq * nt_all; i += LG_ATTN_THREADS) {
+        const int qi = i / nt_all, T2 = t_lo + i % nt_all;
+        const int tok = qi / gqa, hq = kvh * gqa + qi % gqa;
+        const float *pp = a.part + (((size_t)(T2 % a.n_slots) * a.M + tok) * a.H + hq) * (HD + 2);
+        mls[i] = make_float2(__ldcg(pp + HD), __ldcg(pp + HD + 1));
+    }
+    __syncthreads();
+    // (b) per query: global max over its tiles, weights exp(m_t - max), 1 / sum of weighted sums (fixed order)
+    for (int qi = warp; qi < nq; qi += 4) {
+        const int pj = pos0 + qi / gqa + a.qpos_off;
+        const int lo = a.window > 0 ? max(0, pj + a.win_shrink - a.window + 1) : 0;
+        const int i0 = pj >= 0 ? lo / S - t_lo : 0, i1 = pj >= 0 ? pj / S - t_lo : -1;
+        float mx = -INFINITY;
+        for (int i = i0 + lane; i <= i1; i += 32) { float2 v = mls[qi * nt_all + i]; if (v.y > 0.0f) mx = fmaxf(mx, v.x); }
+        mx = warp_max(mx);
+        float lsum = 0.0f;
+        for (int i = lane; i < nt_all; i += 32) {
+            float2 v = mls[qi * nt_all + i];
+            float w = (i >= i0 && i <= i1 && v.y > 0.0f) ? expf(v.x - mx) : 0.0f;
+            mls[qi * nt_all + i].x = w;
+            lsum += w * v.y;
+        }
+        lsum = warp_sum(lsum);
+        if (lane == 0) invl[qi] = lsum > 0.0f ? 1.0f / lsum : 0.0f;
+    }
+    __syncthreads();
+    // (c) weighted sum of the tiles' accumulators in ascending tile order, one warp per (query, 32 dims)
+    for (int u = warp; u < nq * (HD / 32); u += 4) {
+        const int qi = u / (HD / 32), grp = u % (HD / 32), d = grp * 32 + lane;
+        const int tok = qi / gqa, hq = kvh * gqa + qi % gqa;
+        float acc = 0.0f;
+        #pragma unroll 8
+        for (int i = 0; i < nt_all; i++) {
+            const float w = mls[qi * nt_all + i].x;
+            const float *pp = a.part + (((size_t)((t_lo + i) % a.n_slots) * a.M + tok) * a.H + hq) * (HD + 2);
+            acc = fmaf(w, __ldcg(pp + d), acc);
+        }
+        const float y = acc * invl[qi];
+        if (a.out_f32) a.out_f32[((size_t)tok * a.H + hq) * HD + d] = y;
+        if (a.out.q) quant_group_store(y, lane, tok, (hq * HD + d) >> 5, a.out);
+    }
+    if (threadIdx.x == 0) a.tickets[kvh] = 0;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -804,6 +996,7 @@ __global__ void lg_attn_combine_kernel(LgAttnArgs a) {
 // y = gelu_tanh(gate) * up -> panel.  gate/up are f32 rows; `up` may be a per-token vector (PLE).
 __global__ void lg_geglu_kernel(const float *__restrict__ gate, const float *__restrict__ up, int ld_g, int ld_u,
                                 int n, LgPanel P) {
+    pdl_launch(); pdl_wait();
     int tok = blockIdx.y, lane = threadIdx.x & 31;
     int sb = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (sb * 32 >= n) return;
@@ -817,6 +1010,7 @@ __global__ void lg_geglu_kernel(const float *__restrict__ gate, const float *__r
 __global__ void lg_ple_build_kernel(const float *__restrict__ proj, const float *__restrict__ tokrow,
                                     const float *__restrict__ w, float *__restrict__ ipl, int ple, int total,
                                     float inv_sqrt_ne, float eps) {
+    pdl_launch(); pdl_wait();
     __shared__ float red[32];
     int L = blockIdx.x, tok = blockIdx.y, i = threadIdx.x;
     size_t o = (size_t)tok * total + (size_t)L * ple + i;
@@ -846,6 +1040,7 @@ struct LgRoundState {          // lives in device memory; one per session
 __global__ void lg_accept_kernel(LgRoundState *st, int M, const float *__restrict__ hidden, int ld, int ne,
                                  float *__restrict__ h_prev, int *__restrict__ log, int log_cap,
                                  int advance_state) {
+    pdl_launch(); pdl_wait();
     __shared__ int s_adv;
     if (threadIdx.x == 0) {
         int adv = 1;
@@ -870,16 +1065,18 @@ __global__ void lg_accept_kernel(LgRoundState *st, int M, const float *__restric
 
 // drafts for the coming round: slot j <- replay[n_emitted + j - 1] (oracle-replayed drafts)
 __global__ void lg_replay_drafts_kernel(LgRoundState *st, int M, const int *__restrict__ replay, int n_replay) {
+    pdl_launch(); pdl_wait();
     int j = threadIdx.x + 1;
     if (j < M) { int i = st->n_emitted + j - 1; st->toks[j] = i < n_replay ? replay[i] : 0; }
 }
 
 // draft-head input: cat = [ embed(tok)*sqrt(nb) , h_prev ] is assembled by lg_embed_rows + this copy
 __global__ void lg_copy_f32(float *__restrict__ dst, const float *__restrict__ src, int n) {
+    pdl_launch(); pdl_wait();
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) dst[i] = src[i];
 }
-__global__ void lg_set_draft_pos(LgRoundState *st, int j) { st->dpos = st->pos + j; }
+__global__ void lg_set_draft_pos(LgRoundState *st, int j) { pdl_launch(); pdl_wait(); st->dpos = st->pos + j; }
 // slots a head cannot draft repeat the previous token, so the verify simply rejects them
-__global__ void lg_pad_drafts(LgRoundState *st, int from, int M) { for (int j = from; j < M; j++) st->toks[j] = st->toks[j - 1]; }
-__global__ void lg_store_draft(LgRoundState *st, int j, const int *best) { st->toks[j] = *best; }
+__global__ void lg_pad_drafts(LgRoundState *st, int from, int M) { pdl_launch(); pdl_wait(); for (int j = from; j < M; j++) st->toks[j] = st->toks[j - 1]; }
+__global__ void lg_store_draft(LgRoundState *st, int j, const int *best) { pdl_launch(); pdl_wait(); st->toks[j] = *best; }
