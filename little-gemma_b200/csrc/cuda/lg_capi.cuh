@@ -80,19 +80,20 @@ extern "C" int lg_flash_decode_host(const float *q, const float *k, const float 
     int *d_pos = dalloc<int>(1);
     int max_seq = pos + M > seq ? pos + M : seq;
     int slots = tiles_for(window, max_seq, M);
-    float *d_part = dalloc<float>((size_t)slots * M * H * (hd + 2));
+    float *d_part = dalloc<float>((size_t)slots * M * H * hd);
+    float2 *d_ml = dalloc<float2>((size_t)slots * M * H);
     LG_CHECK(cudaMemcpyAsync(d_k, hk.data(), hk.size() * 2, cudaMemcpyHostToDevice, e->stream));
     LG_CHECK(cudaMemcpyAsync(d_v, hv.data(), hv.size() * 2, cudaMemcpyHostToDevice, e->stream));
     LG_CHECK(cudaMemcpyAsync(d_q, q, (size_t)M * H * hd * 4, cudaMemcpyHostToDevice, e->stream));
     LG_CHECK(cudaMemcpyAsync(d_pos, &pos, 4, cudaMemcpyHostToDevice, e->stream));
     LgAttnArgs a{};
-    a.qkv = d_q; a.ld = 0; a.q_ready = 1; a.has_v = 1; a.owns_kv = 0; a.eps = 0.0f;
+    a.qkv = d_q; a.ld = 0; a.q_ready = 1; a.has_v = 1; a.owns_kv = 0; a.eps = 0.0f; a.rope = nullptr;
     a.kc = d_k; a.vc = d_v; a.seq = seq; a.kv_dim = kv_dim; a.H = H; a.Hkv = Hkv; a.hd = hd; a.M = M;
     a.n_slots = slots; a.window = window; a.qpos_off = 0; a.win_shrink = 0; a.pos = d_pos;
-    a.part = d_part; a.out.q = nullptr; a.out_f32 = d_o;
+    a.part = d_part; a.part_ml = d_ml; a.out.q = nullptr; a.out_f32 = d_o;
     launch_attn(e, a, slots);
     LG_CHECK(cudaMemcpyAsync(out, d_o, (size_t)M * H * hd * 4, cudaMemcpyDeviceToHost, e->stream));
     LG_CHECK(cudaStreamSynchronize(e->stream));
-    cudaFree(d_k); cudaFree(d_v); cudaFree(d_q); cudaFree(d_o); cudaFree(d_pos); cudaFree(d_part);
+    cudaFree(d_k); cudaFree(d_v); cudaFree(d_q); cudaFree(d_o); cudaFree(d_pos); cudaFree(d_part); cudaFree(d_ml);
     return 0;
 }

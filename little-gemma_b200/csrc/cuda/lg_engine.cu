@@ -60,7 +60,9 @@ struct DraftW {
     // activations (one token)
     float *cat = nullptr, *x = nullptr, *hbuf = nullptr, *qbuf = nullptr, *qrot = nullptr, *obuf = nullptr, *gu = nullptr, *part = nullptr;
     float *amax_val = nullptr; int *amax_idx = nullptr, *best = nullptr;
+    float2 *part_ml = nullptr;
     LgPanel p_cat{}, p_ni{}, p_attn{}, p_ff{};
+    float2 *rope_local = nullptr, *rope_global = nullptr; int hd_local = 0, hd_global = 0;
     int n_slots_local = 0, n_slots_global = 0;
     std::map<std::string, cudaGraphExec_t> graphs;
 };
@@ -75,12 +77,14 @@ struct Engine {
     WMat head, pmp;                           // token_embd (tied head), per_layer_model_proj
     uint8_t *ple_table = nullptr; int ple_table_type = 0;   // per_layer_token_embd, file layout
     float *out_norm = nullptr, *ple_proj_norm = nullptr, *rope_div = nullptr;
+    float2 *rope_local = nullptr, *rope_global = nullptr; int hd_local = 0, hd_global = 0;
     int has_ple = 0;
     size_t weight_bytes = 0;
     // activations
     float *x = nullptr, *qkv = nullptr, *qrot = nullptr, *oout = nullptr, *gu = nullptr, *dout = nullptr, *hidden = nullptr,
           *h_prev = nullptr, *part = nullptr, *tokrow = nullptr, *pproj = nullptr, *ipl = nullptr, *pg = nullptr, *logits = nullptr;
     float *amax_val = nullptr; int *amax_idx = nullptr;
+    float2 *part_ml = nullptr;
     LgPanel p_ne{}, p_attn{}, p_ff{}, p_ple{};
     int max_ks = 4, head_ctas = 0;
     int part_slots = 0;
@@ -357,7 +361,7 @@ void launch_norm(Engine *e, int M, float *x, int ldx, int n, float eps,
     if (panel) { a.panel = *panel; a.want_panel = 1; }
     a.y = y; a.ldy = ldy; a.n = n; a.eps = eps;
     int threads = n >= 2048 ? 1024 : (n >= 512 ? 512 : 256);
-    launch_k(e, lg_norm_kernel, dim3(M), dim3(threads), (size_t)(n + 32) * 4, a);
+    launch_k(e, lg_norm_kernel, dim3(M), dim3(threads), (size_t)(2 * n + 32) * 4, a);
 }
 
 size_t attn_smem(int nq, int hd) {
@@ -464,7 +468,8 @@ Engine *engine_for(const struct model *m) {
         if (H * w.hd > max_q) max_q = H * w.hd;
         if (w.gateup.ldo > max_ff) max_ff = w.gateup.ldo;
         if (w.hd > max_hd) max_hd = w.hd;
-        if (w.hd % 32 || w.hd > 512) { fprintf(stderr, "lg_b200: head size %d unsupported\n", w.hd); exit(1); }
+        if (w.local) { if (e->hd_local && e->hd_local != w.hd) { fprintf(stderr, "lg_b200: sliding-window layers disagree on the head size\n"); exit(1); } e->hd_local = w.hd; }
+        else         { if (e->hd_global && e->hd_global != w.hd) { fprintf(stderr, "lg_b200: global layers disagree on the head size\n"); exit(1); } e->hd_global = w.hd; }
     }
     const int M8 = LG_MAXM;
     e->x = dalloc<float>((size_t)M8 * ne);
@@ -475,6 +480,10 @@ Engine *engine_for(const struct model *m) {
     e->dout = dalloc<float>((size_t)e->max_ks * M8 * (ne + 64));
     e->hidden = dalloc<float>((size_t)M8 * ne);
     e->h_prev = dalloc<float>(ne);
+    if (!e->hd_local) e->hd_local = e->hd_global;
+    if (!e->hd_global) e->hd_global = e->hd_local;
+    e->rope_local = dalloc<float2>((size_t)M8 * e->hd_local / 2);
+    e->rope_global = dalloc<float2>((size_t)M8 * e->hd_global / 2);
     e->p_ne = panel_alloc(ne);
     e->p_attn = panel_alloc(max_q);
     e->p_ff = panel_alloc(c->n_ff);
@@ -510,6 +519,7 @@ void draft_free(DraftW *d) {
         cudaFree(b.attn_norm); cudaFree(b.q_norm); cudaFree(b.post_attn); cudaFree(b.ffn_norm); cudaFree(b.post_ffw);
     }
     cudaFree(d->out_norm); cudaFree(d->cat); cudaFree(d->x); cudaFree(d->hbuf); cudaFree(d->qbuf); cudaFree(d->qrot);
+    cudaFree(d->rope_local); cudaFree(d->rope_global); cudaFree(d->part_ml);
     cudaFree(d->obuf); cudaFree(d->gu); cudaFree(d->part); cudaFree(d->amax_val); cudaFree(d->amax_idx); cudaFree(d->best);
     panel_free(d->p_cat); panel_free(d->p_ni); panel_free(d->p_attn); panel_free(d->p_ff);
     delete d;
@@ -526,6 +536,7 @@ void engine_free(Engine *e) {
         cudaFree(w.post_ffw); cudaFree(w.post_norm);
     }
     free_wmat(e->head); free_wmat(e->pmp);
+    cudaFree(e->rope_local); cudaFree(e->rope_global); cudaFree(e->part_ml);
     cudaFree(e->ple_table); cudaFree(e->out_norm); cudaFree(e->ple_proj_norm); cudaFree(e->rope_div);
     cudaFree(e->x); cudaFree(e->qkv); cudaFree(e->qrot); cudaFree(e->oout); cudaFree(e->gu); cudaFree(e->dout);
     cudaFree(e->hidden); cudaFree(e->h_prev); cudaFree(e->part); cudaFree(e->tokrow); cudaFree(e->pproj); cudaFree(e->ipl);
@@ -552,7 +563,9 @@ void bind_kv(Engine *e, const struct kvcache *kv) {
     }
     cudaFree(e->part);
     e->part_slots = slots;
-    e->part = dalloc<float>((size_t)slots * LG_MAXM * c->n_head * (maxhd + 2));
+    e->part = dalloc<float>((size_t)slots * LG_MAXM * c->n_head * maxhd);
+    cudaFree(e->part_ml);
+    e->part_ml = dalloc<float2>((size_t)slots * LG_MAXM * c->n_head);
     e->kv_bound = kv;
 }
 
@@ -582,6 +595,11 @@ void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags, int 
         if (only & C_MISC) launch_k(e, lg_ple_build_kernel, dim3(nl, M), dim3(ple), 0, e->pproj, e->tokrow, e->ple_proj_norm, e->ipl, ple, e->pmp.ldo,
                                                        1.0f / sqrtf((float)ne), c->rms_eps);
     }
+    // rotation tables of this block's positions, one per layer kind
+    if (only & (C_ATTN | C_MISC)) {
+        launch_k(e, lg_rope_table_kernel, dim3(1), dim3(256), 0, d_pos, M, e->hd_local, c->rope_freq_base_swa, (const float *)nullptr, e->rope_local);
+        launch_k(e, lg_rope_table_kernel, dim3(1), dim3(256), 0, d_pos, M, e->hd_global, c->rope_freq_base, (const float *)e->rope_div, e->rope_global);
+    }
     if (only & C_NORM) launch_norm(e, M, e->x, ne, ne, c->rms_eps, nullptr, 0, 0, 0, nullptr, 1.0f, e->L[0].attn_norm, &e->p_ne, nullptr, 0);
 
     for (int l = 0; l < nl; l++) {
@@ -590,12 +608,12 @@ void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags, int 
         if (only & C_QKV) launch_gemv(e, w.qkv, e->p_ne, M, e->qkv, LG_EPI_STORE, 1);
         LgAttnArgs aa{};
         aa.qkv = e->qkv; aa.ld = w.qkv.ldo; aa.q_ready = 0; aa.has_v = w.has_v; aa.owns_kv = w.owns_kv;
-        aa.q_norm = w.q_norm; aa.k_norm = w.k_norm; aa.rope_div = w.local ? nullptr : e->rope_div;
-        aa.rope_base = w.local ? c->rope_freq_base_swa : c->rope_freq_base; aa.eps = c->rms_eps;
+        aa.q_norm = w.q_norm; aa.k_norm = w.k_norm; aa.eps = c->rms_eps;
+        aa.rope = w.local ? e->rope_local : e->rope_global;
         aa.kc = (__half *)kv->k[src]; aa.vc = (__half *)kv->v[src]; aa.seq = kv->seq[src]; aa.kv_dim = kv->kv_dim[src];
         aa.H = H; aa.Hkv = w.nkv; aa.hd = hd; aa.M = M;
         aa.window = w.local ? c->sliding_window : 0; aa.qpos_off = 0; aa.win_shrink = 0; aa.pos = d_pos;
-        aa.n_slots = e->part_slots; aa.part = e->part; aa.out_f32 = nullptr;
+        aa.n_slots = e->part_slots; aa.part = e->part; aa.part_ml = e->part_ml; aa.out_f32 = nullptr;
         LgPanel pa = e->p_attn; pa.nsb = H * hd / 32;
         aa.out = pa;
         if (only & C_ATTN) launch_attn(e, aa, tiles_for(aa.window, kv->max_seq, M));
@@ -712,6 +730,7 @@ DraftW *draft_build(Engine *e, struct mtp *t, const struct kvcache *kv) {
         b.hd = s->hd; b.local = s->local; b.src = s->src;
         if (d->n_head * s->hd > qmax) qmax = d->n_head * s->hd;
         if (s->hd > maxhd) maxhd = s->hd;
+        if (s->local) d->hd_local = s->hd; else d->hd_global = s->hd;
         if (d->n_head % m->n_head_kv[s->src]) { fprintf(stderr, "lg_b200: draft head count does not divide the target's KV heads\n"); exit(1); }
         d->blk.push_back(b);
     }
@@ -721,9 +740,14 @@ DraftW *draft_build(Engine *e, struct mtp *t, const struct kvcache *kv) {
     d->gu = dalloc<float>(32);
     int slots = tiles_for(0, kv->max_seq, 1);
     d->n_slots_global = slots;
-    d->part = dalloc<float>((size_t)slots * d->n_head * (maxhd + 2));
+    d->part = dalloc<float>((size_t)slots * d->n_head * maxhd);
+    d->part_ml = dalloc<float2>((size_t)slots * d->n_head);
     d->amax_val = dalloc<float>((size_t)e->head_ctas * LG_MAXM); d->amax_idx = dalloc<int>((size_t)e->head_ctas * LG_MAXM);
     d->best = dalloc<int>(LG_MAXM);
+    if (!d->hd_local) d->hd_local = d->hd_global;
+    if (!d->hd_global) d->hd_global = d->hd_local;
+    d->rope_local = dalloc<float2>(d->hd_local / 2);
+    d->rope_global = dalloc<float2>(d->hd_global / 2);
     d->p_cat = panel_alloc(2 * d->nb); d->p_ni = panel_alloc(d->ni); d->p_attn = panel_alloc(qmax); d->p_ff = panel_alloc(d->nff);
     return d;
 }
@@ -747,6 +771,8 @@ void enqueue_draft(Engine *e, DraftW *d, const struct kvcache *kv, int slot, boo
     launch_k(e, lg_quant_rows, dim3((2 * nb / 32 + 7) / 8, 1), dim3(256), 0, d->cat, 2 * nb, 2 * nb, d->p_cat);
     launch_gemv(e, d->pre, d->p_cat, 1, d->obuf, LG_EPI_STORE, 1);
     launch_k(e, lg_copy_f32, dim3((ni + 255) / 256), dim3(256), 0, d->x, d->obuf, ni);
+    launch_k(e, lg_rope_table_kernel, dim3(1), dim3(256), 0, (const int *)&e->st->dpos, 1, d->hd_local, d->base_swa, (const float *)nullptr, d->rope_local);
+    launch_k(e, lg_rope_table_kernel, dim3(1), dim3(256), 0, (const int *)&e->st->dpos, 1, d->hd_global, d->base_full, (const float *)nullptr, d->rope_global);
     launch_norm(e, 1, d->x, ni, ni, d->eps, nullptr, 0, 0, 0, nullptr, 1.0f, d->blk[0].attn_norm, &d->p_ni, nullptr, 0);
     for (size_t L = 0; L < d->blk.size(); L++) {
         DraftBlockW &b = d->blk[L];
@@ -754,13 +780,13 @@ void enqueue_draft(Engine *e, DraftW *d, const struct kvcache *kv, int slot, boo
         launch_gemv(e, b.q, d->p_ni, 1, d->qbuf, LG_EPI_STORE, 1);
         LgAttnArgs aa{};
         aa.qkv = d->qbuf; aa.ld = b.q.ldo; aa.q_ready = 0; aa.has_v = 0; aa.owns_kv = 0;
-        aa.q_norm = b.q_norm; aa.k_norm = nullptr; aa.rope_div = nullptr;
-        aa.rope_base = b.local ? d->base_swa : d->base_full; aa.eps = d->eps;
+        aa.q_norm = b.q_norm; aa.k_norm = nullptr; aa.eps = d->eps;
+        aa.rope = b.local ? d->rope_local : d->rope_global;
         aa.kc = (__half *)kv->k[src]; aa.vc = (__half *)kv->v[src]; aa.seq = kv->seq[src]; aa.kv_dim = kv->kv_dim[src];
         aa.H = d->n_head; aa.Hkv = Hkv; aa.hd = hd; aa.M = 1;
         aa.window = (b.local && c->sliding_window > 0) ? c->sliding_window : 0;
         aa.qpos_off = -1; aa.win_shrink = aa.window > 0 ? 1 : 0; aa.pos = &e->st->dpos;
-        aa.n_slots = d->n_slots_global; aa.part = d->part;
+        aa.n_slots = d->n_slots_global; aa.part = d->part; aa.part_ml = d->part_ml;
         LgPanel pa = d->p_attn; pa.nsb = d->n_head * hd / 32;
         aa.out = pa; aa.out_f32 = nullptr;
         launch_attn(e, aa, tiles_for(aa.window, kv->max_seq, 1));

@@ -631,37 +631,40 @@ __global__ void lg_embed_rows(const uint4 *__restrict__ wq, const uint2 *__restr
 // ---------------------------------------------------------------------------------------------
 __global__ void lg_norm_kernel(LgNormArgs a) {
     pdl_launch(); pdl_wait();
-    extern __shared__ float row[];       // n floats + 32
-    float *red = row + a.n;
+    extern __shared__ float row[];       // 2n floats + 32
+    float *rowx = row + a.n, *red = rowx + a.n;
     const int tok = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     float *x = a.x + (size_t)tok * a.ldx;
+    float ss2 = 0.0f;
     if (a.add_src) {
+        // the partial sums and the residual row are fetched together (one memory latency)
         float ss = 0.0f;
         for (int i = threadIdx.x; i < a.n; i += blockDim.x) {
             float v = 0.0f;
             for (int p = 0; p < a.n_parts; p++) v += a.add_src[(size_t)p * a.part_stride + (size_t)tok * a.ld_add + i];
+            rowx[i] = x[i];
             row[i] = v;
             ss += v * v;
         }
         ss = block_sum(ss, red);
         float s = 1.0f / sqrtf(ss / (float)a.n + a.eps);
         for (int i = threadIdx.x; i < a.n; i += blockDim.x) {
-            float v = __fadd_rn(x[i], __fmul_rn(__fmul_rn(row[i], s), a.add_w[i]));
+            float v = __fadd_rn(rowx[i], __fmul_rn(__fmul_rn(row[i], s), a.add_w[i]));
             v = __fmul_rn(v, a.out_scale);
             x[i] = v;
             row[i] = v;
+            ss2 += v * v;
         }
     } else {
-        for (int i = threadIdx.x; i < a.n; i += blockDim.x) row[i] = x[i];
+        for (int i = threadIdx.x; i < a.n; i += blockDim.x) { float v = x[i]; row[i] = v; ss2 += v * v; }
     }
     if (!a.norm_w && !a.want_panel && !a.y) return;
-    __syncthreads();
     float s = 1.0f;
     if (a.norm_w) {
-        float ss = 0.0f;
-        for (int i = threadIdx.x; i < a.n; i += blockDim.x) ss += row[i] * row[i];
-        ss = block_sum(ss, red);
-        s = 1.0f / sqrtf(ss / (float)a.n + a.eps);
+        ss2 = block_sum(ss2, red);
+        s = 1.0f / sqrtf(ss2 / (float)a.n + a.eps);
+    } else {
+        __syncthreads();
     }
     for (int sb = warp; sb * 32 < a.n; sb += nw) {
         int i = sb * 32 + lane;
@@ -702,7 +705,8 @@ struct LgAttnArgs {
     // raw projection rows [M][ld] = [q (H*hd) | k (Hkv*hd) | v (Hkv*hd)]; q_ready: q is [M][H][hd], final
     const float *qkv; int ld; int q_ready;
     int has_v, owns_kv;                  // v projection present; this layer writes K/V rows
-    const float *q_norm, *k_norm, *rope_div; float rope_base, eps;
+    const float *q_norm, *k_norm; float eps;
+    const float2 *rope;                  // [M][hd/2] (cos, sin) of this layer kind at the block's positions
     __half *kc, *vc; int seq, kv_dim;
     int H, Hkv, hd, M;
     int n_slots;               // tile slots in the scratch (>= tiles a block can touch)
@@ -710,12 +714,13 @@ struct LgAttnArgs {
     int qpos_off;              // 0 for the target; -1 for the draft head (query at pos sees keys < pos)
     int win_shrink;            // draft head: the window start stays pos-W+1 (one key fewer)
     const int *pos;
-    float *part;               // [n_slots][M][H][hd+2]  (acc[hd], max, sum)
+    float *part;               // [n_slots][M][H][hd] un-normalised tile accumulators
+    float2 *part_ml;           // [n_slots][M][H] (max, sum) of each (query, tile)
     int *tickets;              // [Hkv], zero between launches
     LgPanel out; float *out_f32;   // merged output: panel of [M][H*hd] and/or f32 [M][H][hd]
 };
 
-#define LG_ATTN_THREADS 128
+#define LG_ATTN_THREADS 256
 #define LG_ATTN_S 64
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void *p) {
@@ -736,11 +741,24 @@ __device__ __forceinline__ void cp_async16(void *dst, const void *src) {
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
+// cos / sin of the NeoX rotation angles of the block's M positions, computed once per forward and
+// shared by every CTA of every layer of that kind: tab[tok][i] = (cos, sin)(pos_tok * base^(-2i/hd) / div[i]).
+__global__ void lg_rope_table_kernel(const int *pos, int M, int hd, float base, const float *div, float2 *tab) {
+    pdl_launch(); pdl_wait();
+    const int half = hd >> 1;
+    for (int u = threadIdx.x; u < M * half; u += blockDim.x) {
+        const int tok = u / half, i = u % half;
+        float freq = powf(base, -2.0f * (float)i / (float)hd);
+        float ang = (float)(*pos + tok) * freq / (div ? div[i] : 1.0f);
+        tab[u] = make_float2(cosf(ang), sinf(ang));
+    }
+}
+
 // RMSNorm (optional weight) + optional NeoX RoPE of one head vector by one warp.
 // lane owns pairs i = lane*PER + e (e < PER) and their partners i + hd/2;  out_lo[i], out_hi[i] returned in v0/v1.
 template <int HD>
-__device__ __forceinline__ void head_norm_rope(const float *src, const float *w, bool rope, const float *div, float base,
-                                               float eps, int pos, int lane, float (&v0)[HD / 64], float (&v1)[HD / 64]) {
+__device__ __forceinline__ void head_norm_rope(const float *src, const float *w, const float2 *rope, float eps, int lane,
+                                               float (&v0)[HD / 64], float (&v1)[HD / 64]) {
     constexpr int PER = HD / 64, HALF = HD / 2;
     float ss = 0.0f;
     #pragma unroll
@@ -757,9 +775,8 @@ __device__ __forceinline__ void head_norm_rope(const float *src, const float *w,
         float a = __fmul_rn(v0[e], s), b = __fmul_rn(v1[e], s);
         if (w) { a = __fmul_rn(a, w[i]); b = __fmul_rn(b, w[i + HALF]); }
         if (rope) {
-            float freq = powf(base, -2.0f * (float)i / (float)HD);
-            float ang = (float)pos * freq / (div ? div[i] : 1.0f);
-            float c = cosf(ang), sn = sinf(ang);
+            const float2 cs = rope[i];
+            const float c = cs.x, sn = cs.y;
             float r0 = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, sn));
             float r1 = __fadd_rn(__fmul_rn(a, sn), __fmul_rn(b, c));
             a = r0; b = r1;
@@ -773,7 +790,7 @@ template <int HD>
 __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) {
     pdl_launch(); pdl_wait();
     extern __shared__ __align__(128) unsigned char smem[];
-    constexpr int S = LG_ATTN_S, LDH = HD + 8, LDP = S + 8, PER = HD / 64, HALF = HD / 2;
+    constexpr int S = LG_ATTN_S, LDH = HD + 8, LDP = S + 8, PER = HD / 64, HALF = HD / 2, NW = LG_ATTN_THREADS / 32;
     const int kvh = blockIdx.x, gqa = a.H / a.Hkv, nq = gqa * a.M, nq16 = (nq + 15) & ~15;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int pos0 = *a.pos;
@@ -784,6 +801,7 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) 
     const int T = t_lo + blockIdx.y;
     if (T > t_hi) return;
     const int slot = T % a.n_slots;
+    const bool writes_kv = a.owns_kv && !a.q_ready;
 
     __half *qhi = (__half *)smem, *qlo = qhi + (size_t)nq16 * LDH;
     __half *sk = qlo + (size_t)nq16 * LDH, *sv = sk + (size_t)S * LDH;
@@ -791,8 +809,24 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) 
     __half *phi = (__half *)(sc + (size_t)nq16 * S), *plo = phi + (size_t)nq16 * LDP;
     float *ml = (float *)(plo + (size_t)nq16 * LDP);
 
-    // ---- 1. queries (and the new K/V rows this tile owns) ----
-    for (int qi = warp; qi < nq16; qi += 4) {
+    // ---- 1. cached K and V rows of the tile start streaming into shared memory at once; rows of the
+    //         block's own new positions are produced below and written to the cache and the tile ----
+    constexpr int CH = HD / 8;
+    for (int i = threadIdx.x; i < S * CH; i += LG_ATTN_THREADS) {
+        const int key = i / CH, c = i % CH, p = T * S + key;
+        __half *dk = sk + (size_t)key * LDH + c * 8, *dv = sv + (size_t)key * LDH + c * 8;
+        if (p <= p_last && !(writes_kv && p >= pos0)) {
+            const size_t off = (size_t)(p % a.seq) * a.kv_dim + (size_t)kvh * HD + c * 8;
+            cp_async16(dk, a.kc + off);
+            cp_async16(dv, a.vc + off);
+        } else if (p > p_last) {
+            *(uint4 *)dk = make_uint4(0, 0, 0, 0);
+            *(uint4 *)dv = make_uint4(0, 0, 0, 0);
+        }
+    }
+
+    // ---- 2. queries: per-head RMSNorm + RoPE, split into f16 hi + lo ----
+    for (int qi = warp; qi < nq16; qi += NW) {
         float v0[PER], v1[PER];
         if (qi < nq) {
             const int tok = qi / gqa, hq = kvh * gqa + qi % gqa;
@@ -801,8 +835,7 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) 
                 #pragma unroll
                 for (int e = 0; e < PER; e++) { v0[e] = src[lane * PER + e]; v1[e] = src[lane * PER + e + HALF]; }
             } else {
-                head_norm_rope<HD>(a.qkv + (size_t)tok * a.ld + (size_t)hq * HD, a.q_norm, true, a.rope_div, a.rope_base, a.eps,
-                                   pos0 + tok, lane, v0, v1);
+                head_norm_rope<HD>(a.qkv + (size_t)tok * a.ld + (size_t)hq * HD, a.q_norm, a.rope + (size_t)tok * HALF, a.eps, lane, v0, v1);
             }
         } else {
             #pragma unroll
@@ -817,54 +850,42 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) 
             qlo[(size_t)qi * LDH + i + HALF] = __float2half_rn(v1[e] - __half2float(h1));
         }
     }
-    if (a.owns_kv && !a.q_ready) {
+    if (writes_kv) {
         // rows of the new positions that fall into this tile: K (norm + rope) and V (plain norm), f16 RNE
-        for (int j = warp; j < 2 * a.M; j += 4) {
+        for (int j = warp; j < 2 * a.M; j += NW) {
             const int tok = j >> 1, isv = j & 1, p = pos0 + tok;
             if (p / S != T) continue;
             float v0[PER], v1[PER];
             const float *src = a.qkv + (size_t)tok * a.ld + (size_t)(a.H + ((isv && a.has_v) ? a.Hkv : 0) + kvh) * HD;
-            head_norm_rope<HD>(src, isv ? nullptr : a.k_norm, !isv, a.rope_div, a.rope_base, a.eps, p, lane, v0, v1);
+            head_norm_rope<HD>(src, isv ? nullptr : a.k_norm, isv ? nullptr : a.rope + (size_t)tok * HALF, a.eps, lane, v0, v1);
             __half *dst = (isv ? a.vc : a.kc) + (size_t)(p % a.seq) * a.kv_dim + (size_t)kvh * HD;
+            __half *dsm = (isv ? sv : sk) + (size_t)(p - T * S) * LDH;
             #pragma unroll
             for (int e = 0; e < PER; e++) {
-                dst[lane * PER + e] = __float2half_rn(v0[e]);
-                dst[lane * PER + e + HALF] = __float2half_rn(v1[e]);
+                const __half h0 = __float2half_rn(v0[e]), h1 = __float2half_rn(v1[e]);
+                dst[lane * PER + e] = h0; dst[lane * PER + e + HALF] = h1;
+                dsm[lane * PER + e] = h0; dsm[lane * PER + e + HALF] = h1;
             }
-        }
-    }
-    __syncthreads();                       // the rows just written are visible to this CTA's tile load
-
-    // ---- 2. K and V tiles -> shared memory ----
-    constexpr int CH = HD / 8;
-    for (int i = threadIdx.x; i < S * CH; i += LG_ATTN_THREADS) {
-        const int key = i / CH, c = i % CH, p = T * S + key;
-        __half *dk = sk + (size_t)key * LDH + c * 8, *dv = sv + (size_t)key * LDH + c * 8;
-        if (p <= p_last) {
-            const size_t off = (size_t)(p % a.seq) * a.kv_dim + (size_t)kvh * HD + c * 8;
-            cp_async16(dk, a.kc + off);
-            cp_async16(dv, a.vc + off);
-        } else {
-            *(uint4 *)dk = make_uint4(0, 0, 0, 0);
-            *(uint4 *)dv = make_uint4(0, 0, 0, 0);
         }
     }
     cp_async_wait_all();
     __syncthreads();
 
-    // ---- 3. scores: warp w takes keys [16w, 16w+16) ----
+    // ---- 3. scores: warp w takes keys [8w, 8w+8) ----
     const int g = lane >> 2, t = lane & 3;
     for (int mt = 0; mt < nq16 / 16; mt++) {
-        float c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
+        float c0[4] = {0, 0, 0, 0};
         const __half *qa_hi = qhi + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + (lane >> 4) * 8;
         const __half *qa_lo = qlo + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + (lane >> 4) * 8;
-        const __half *kb = sk + (size_t)(warp * 16 + (lane & 7) + (lane >> 4) * 8) * LDH + ((lane >> 3) & 1) * 8;
-        #pragma unroll 4
-        for (int k0 = 0; k0 < HD; k0 += 16) {
-            uint32_t ah[4], al[4], b[4];
-            ldsm_x4(ah, qa_hi + k0); ldsm_x4(al, qa_lo + k0); ldsm_x4(b, kb + k0);
+        const __half *kb = sk + (size_t)(warp * 8 + (lane & 7)) * LDH + (lane >> 3) * 8;      // 4 matrices: d = k0, +8, +16, +24
+        #pragma unroll 2
+        for (int k0 = 0; k0 < HD; k0 += 32) {
+            uint32_t ah[4], al[4], ah2[4], al2[4], b[4];
+            ldsm_x4(b, kb + k0);
+            ldsm_x4(ah, qa_hi + k0); ldsm_x4(al, qa_lo + k0);
+            ldsm_x4(ah2, qa_hi + k0 + 16); ldsm_x4(al2, qa_lo + k0 + 16);
             mma_f16(c0, ah, b[0], b[1]); mma_f16(c0, al, b[0], b[1]);
-            mma_f16(c1, ah, b[2], b[3]); mma_f16(c1, al, b[2], b[3]);
+            mma_f16(c0, ah2, b[2], b[3]); mma_f16(c0, al2, b[2], b[3]);
         }
         #pragma unroll
         for (int h2 = 0; h2 < 2; h2++) {
@@ -872,19 +893,16 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) 
             const int pj = pos0 + qi / gqa + a.qpos_off;
             const int lo = a.window > 0 ? max(0, pj + a.win_shrink - a.window + 1) : 0;
             #pragma unroll
-            for (int nt = 0; nt < 2; nt++)
-                #pragma unroll
-                for (int e = 0; e < 2; e++) {
-                    const int key = warp * 16 + nt * 8 + t * 2 + e, p = T * S + key;
-                    float v = nt ? c1[h2 * 2 + e] : c0[h2 * 2 + e];
-                    sc[(size_t)qi * S + key] = (qi < nq && p >= lo && p <= pj) ? v : -INFINITY;
-                }
+            for (int e = 0; e < 2; e++) {
+                const int key = warp * 8 + t * 2 + e, p = T * S + key;
+                sc[(size_t)qi * S + key] = (qi < nq && p >= lo && p <= pj) ? c0[h2 * 2 + e] : -INFINITY;
+            }
         }
     }
     __syncthreads();
 
     // ---- 4. per-query softmax over the tile ----
-    for (int qi = warp; qi < nq16; qi += 4) {
+    for (int qi = warp; qi < nq16; qi += NW) {
         float s0 = sc[(size_t)qi * S + lane], s1 = sc[(size_t)qi * S + lane + 32];
         float mx = warp_max(fmaxf(s0, s1));
         float e0 = (s0 == -INFINITY) ? 0.0f : expf(s0 - mx), e1 = (s1 == -INFINITY) ? 0.0f : expf(s1 - mx);
@@ -897,37 +915,42 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) 
     }
     __syncthreads();
 
-    // ---- 5. O = P V: warp w takes dims [w*HD/4, (w+1)*HD/4) ----
-    constexpr int NT = HD / 4 / 8;                 // 8-wide output tiles per warp
-    for (int mt = 0; mt < nq16 / 16; mt++) {
-        float o[NT][4];
-        #pragma unroll
-        for (int n = 0; n < NT; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
-        const __half *pa_hi = phi + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDP + (lane >> 4) * 8;
-        const __half *pa_lo = plo + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDP + (lane >> 4) * 8;
-        #pragma unroll
-        for (int k0 = 0; k0 < S; k0 += 16) {
-            uint32_t ah[4], al[4];
-            ldsm_x4(ah, pa_hi + k0); ldsm_x4(al, pa_lo + k0);
-            const __half *vb = sv + (size_t)(k0 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + warp * (HD / 4) + (lane >> 4) * 8;
+    // ---- 5. O = P V: PVW warps split the head dims ----
+    constexpr int PVW = HD / 16 < NW ? HD / 16 : NW;          // warps that take part
+    constexpr int DW = HD / PVW;                               // dims per warp (a multiple of 16)
+    constexpr int NT = DW / 8;
+    if (warp < PVW) {
+        for (int mt = 0; mt < nq16 / 16; mt++) {
+            float o[NT][4];
             #pragma unroll
-            for (int n = 0; n < NT; n += 2) {
-                uint32_t b[4];
-                ldsm_x4_t(b, vb + n * 8);
-                mma_f16(o[n], ah, b[0], b[1]); mma_f16(o[n], al, b[0], b[1]);
-                mma_f16(o[n + 1], ah, b[2], b[3]); mma_f16(o[n + 1], al, b[2], b[3]);
-            }
-        }
-        #pragma unroll
-        for (int h2 = 0; h2 < 2; h2++) {
-            const int qi = mt * 16 + g + h2 * 8;
-            if (qi < nq) {
-                const int tok = qi / gqa, hq = kvh * gqa + qi % gqa;
-                float *pp = a.part + (((size_t)slot * a.M + tok) * a.H + hq) * (HD + 2);
+            for (int n = 0; n < NT; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
+            const __half *pa_hi = phi + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDP + (lane >> 4) * 8;
+            const __half *pa_lo = plo + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDP + (lane >> 4) * 8;
+            #pragma unroll
+            for (int k0 = 0; k0 < S; k0 += 16) {
+                uint32_t ah[4], al[4];
+                ldsm_x4(ah, pa_hi + k0); ldsm_x4(al, pa_lo + k0);
+                const __half *vb = sv + (size_t)(k0 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + warp * DW + (lane >> 4) * 8;
                 #pragma unroll
-                for (int n = 0; n < NT; n++)
-                    *(float2 *)(pp + warp * (HD / 4) + n * 8 + t * 2) = make_float2(o[n][h2 * 2], o[n][h2 * 2 + 1]);
-                if (warp == 0 && t == 0) { pp[HD] = ml[qi * 2]; pp[HD + 1] = ml[qi * 2 + 1]; }
+                for (int n = 0; n < NT; n += 2) {
+                    uint32_t b[4];
+                    ldsm_x4_t(b, vb + n * 8);
+                    mma_f16(o[n], ah, b[0], b[1]); mma_f16(o[n], al, b[0], b[1]);
+                    mma_f16(o[n + 1], ah, b[2], b[3]); mma_f16(o[n + 1], al, b[2], b[3]);
+                }
+            }
+            #pragma unroll
+            for (int h2 = 0; h2 < 2; h2++) {
+                const int qi = mt * 16 + g + h2 * 8;
+                if (qi < nq) {
+                    const int tok = qi / gqa, hq = kvh * gqa + qi % gqa;
+                    float *pp = a.part + (((size_t)slot * a.M + tok) * a.H + hq) * HD;
+                    #pragma unroll
+                    for (int n = 0; n < NT; n++)
+                        *(float2 *)(pp + warp * DW + n * 8 + t * 2) = make_float2(o[n][h2 * 2], o[n][h2 * 2 + 1]);
+                    if (warp == 0 && t == 0)
+                        a.part_ml[((size_t)slot * a.M + tok) * a.H + hq] = make_float2(ml[qi * 2], ml[qi * 2 + 1]);
+                }
             }
         }
     }
@@ -949,12 +972,11 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) 
     for (int i = threadIdx.x; i < nq * nt_all; i += LG_ATTN_THREADS) {
         const int qi = i / nt_all, T2 = t_lo + i % nt_all;
         const int tok = qi / gqa, hq = kvh * gqa + qi % gqa;
-        const float *pp = a.part + (((size_t)(T2 % a.n_slots) * a.M + tok) * a.H + hq) * (HD + 2);
-        mls[i] = make_float2(__ldcg(pp + HD), __ldcg(pp + HD + 1));
+        mls[i] = __ldcg(a.part_ml + ((size_t)(T2 % a.n_slots) * a.M + tok) * a.H + hq);
     }
     __syncthreads();
     // (b) per query: global max over its tiles, weights exp(m_t - max), 1 / sum of weighted sums (fixed order)
-    for (int qi = warp; qi < nq; qi += 4) {
+    for (int qi = warp; qi < nq; qi += NW) {
         const int pj = pos0 + qi / gqa + a.qpos_off;
         const int lo = a.window > 0 ? max(0, pj + a.win_shrink - a.window + 1) : 0;
         const int i0 = pj >= 0 ? lo / S - t_lo : 0, i1 = pj >= 0 ? pj / S - t_lo : -1;
@@ -972,18 +994,48 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) 
         if (lane == 0) invl[qi] = lsum > 0.0f ? 1.0f / lsum : 0.0f;
     }
     __syncthreads();
-    // (c) weighted sum of the tiles' accumulators in ascending tile order, one warp per (query, 32 dims)
-    for (int u = warp; u < nq * (HD / 32); u += 4) {
-        const int qi = u / (HD / 32), grp = u % (HD / 32), d = grp * 32 + lane;
-        const int tok = qi / gqa, hq = kvh * gqa + qi % gqa;
-        float acc = 0.0f;
-        #pragma unroll 8
-        for (int i = 0; i < nt_all; i++) {
-            const float w = mls[qi * nt_all + i].x;
-            const float *pp = a.part + (((size_t)((t_lo + i) % a.n_slots) * a.M + tok) * a.H + hq) * (HD + 2);
-            acc = fmaf(w, __ldcg(pp + d), acc);
+    // (c) weighted sum of the tiles' accumulators in ascending tile order: a thread owns 4 consecutive
+    //     dims of a query, 16-byte loads, 8 tiles in flight; results staged in shared memory
+    float *ybuf = (float *)qhi;                                // [nq][HD] f32 (the query area is free now)
+    const size_t slot_stride = (size_t)a.M * a.H * HD;
+    for (int u = threadIdx.x; u < nq * (HD / 4); u += LG_ATTN_THREADS) {
+        const int qi = u / (HD / 4), d4 = (u % (HD / 4)) * 4;
+        const float *base = a.part + ((size_t)(qi / gqa) * a.H + kvh * gqa + qi % gqa) * HD + d4;
+        const float2 *wq = mls + (size_t)qi * nt_all;
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        int i = 0;
+        for (; i + 8 <= nt_all; i += 8) {
+            float4 v[8];
+            #pragma unroll
+            for (int j = 0; j < 8; j++) v[j] = __ldcg((const float4 *)(base + (size_t)((t_lo + i + j) % a.n_slots) * slot_stride));
+            #pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const float w = wq[i + j].x;
+                acc.x = fmaf(w, v[j].x, acc.x); acc.y = fmaf(w, v[j].y, acc.y);
+                acc.z = fmaf(w, v[j].z, acc.z); acc.w = fmaf(w, v[j].w, acc.w);
+            }
         }
-        const float y = acc * invl[qi];
+        {
+            float4 v[8];
+            #pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (i + j < nt_all) v[j] = __ldcg((const float4 *)(base + (size_t)((t_lo + i + j) % a.n_slots) * slot_stride));
+            #pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (i + j < nt_all) {
+                    const float w = wq[i + j].x;
+                    acc.x = fmaf(w, v[j].x, acc.x); acc.y = fmaf(w, v[j].y, acc.y);
+                    acc.z = fmaf(w, v[j].z, acc.z); acc.w = fmaf(w, v[j].w, acc.w);
+                }
+        }
+        const float il = invl[qi];
+        *(float4 *)(ybuf + (size_t)qi * HD + d4) = make_float4(acc.x * il, acc.y * il, acc.z * il, acc.w * il);
+    }
+    __syncthreads();
+    for (int u = warp; u < nq * (HD / 32); u += NW) {
+        const int qi = u / (HD / 32), d = (u % (HD / 32)) * 32 + lane;
+        const int tok = qi / gqa, hq = kvh * gqa + qi % gqa;
+        const float y = ybuf[(size_t)qi * HD + d];
         if (a.out_f32) a.out_f32[((size_t)tok * a.H + hq) * HD + d] = y;
         if (a.out.q) quant_group_store(y, lane, tok, (hq * HD + d) >> 5, a.out);
     }
