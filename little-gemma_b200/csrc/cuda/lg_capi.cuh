@@ -14,6 +14,7 @@ Engine *scratch_engine() {
         LG_CHECK(cudaDeviceGetAttribute(&e->sm_count, cudaDevAttrMultiProcessorCount, dev));
         LG_CHECK(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
         e->head_ctas = e->sm_count * 2;
+        e->pdl = env_int("LG_PDL", 1);
         e->err = dalloc<int>(1);
         e->tickets = dalloc<int>(MAX_KV_HEADS);
     }
@@ -79,7 +80,7 @@ extern "C" int lg_flash_decode_host(const float *q, const float *k, const float 
     float *d_q = dalloc<float>((size_t)M * H * hd), *d_o = dalloc<float>((size_t)M * H * hd);
     int *d_pos = dalloc<int>(1);
     int max_seq = pos + M > seq ? pos + M : seq;
-    int slots = tiles_for(window, max_seq, M);
+    int slots = tiles_for(window, max_seq, M, hd);
     float *d_part = dalloc<float>((size_t)slots * M * H * hd);
     float2 *d_ml = dalloc<float2>((size_t)slots * M * H);
     LG_CHECK(cudaMemcpyAsync(d_k, hk.data(), hk.size() * 2, cudaMemcpyHostToDevice, e->stream));

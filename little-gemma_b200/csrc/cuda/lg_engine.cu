@@ -27,7 +27,7 @@ extern "C" const int model_kv_host = 0;      // cache rows live on the device: m
 namespace {
 
 constexpr int RING_SPARE = 1024;             // ring rows beyond the window (covers the widest block written before its queries run)
-constexpr int ATTN_TILE = LG_ATTN_S;                // keys per flash-decode tile (absolute boundaries)
+
 constexpr int LOG_CAP = 1 << 20;
 
 struct WMat {
@@ -98,7 +98,7 @@ struct Engine {
     DraftW *draft = nullptr; const struct mtp *draft_owner = nullptr;
     float *pick_rows = nullptr;               // host logits rows for model_pick
     long long launches = 0;                   // kernels enqueued by the most recent graph build
-    int pdl = 0;                              // programmatic dependent launch (LG_PDL=1 turns it on; measured slower here)
+    int pdl = 1;                              // programmatic dependent launch (LG_PDL=0 turns it off)
     long long round_launches = 0;
     int mm_launches = 0;                      // kernels in the captured matmul-only pass             // kernels in one captured round (lg_rounds_enqueue)
 };
@@ -241,7 +241,7 @@ void free_wmat(WMat &W) { cudaFree(W.wq); cudaFree(W.ws); cudaFree(W.wd); W = WM
 // launch helpers
 // ------------------------------------------------------------------------------------------
 struct GemvPlan { int r, ks, gx; size_t smem; };
-constexpr size_t GEMV_SMEM_MAX = 200 * 1024, ATTN_SMEM_MAX = 200 * 1024;
+constexpr size_t GEMV_SMEM_MAX = 200 * 1024, ATTN_SMEM_MAX = 220 * 1024;
 constexpr int MAX_KV_HEADS = 64;
 
 template <int R, int NP, int FMT, int EPI> void gemv_attr() {
@@ -274,7 +274,8 @@ int env_int(const char *name, int fb) { const char *v = getenv(name); return v &
 // pass in the consumer), and as many row tiles per item as still leave enough items to balance.
 GemvPlan plan_gemv(const Engine *e, const WMat &W, int np, int want_ks, bool head, bool geglu = false) {
     GemvPlan p;
-    const int ctas = e->sm_count * 2;
+    static const int cta_mult = env_int("LG_GEMV_CTAS_PER_SM", 2);
+    const int ctas = e->sm_count * cta_mult;
     static const int force_r = env_int("LG_GEMV_R", 0), force_ks = env_int("LG_GEMV_KS", 0);
     p.r = 0; p.ks = want_ks;
     int ks_lo = want_ks > 0 ? want_ks : 1, ks_hi = want_ks > 0 ? want_ks : e->max_ks;
@@ -365,8 +366,8 @@ void launch_norm(Engine *e, int M, float *x, int ldx, int n, float eps,
 }
 
 size_t attn_smem(int nq, int hd) {
-    size_t nq16 = (size_t)((nq + 15) & ~15), ldh = hd + 8;
-    return 2 * nq16 * ldh * 2 + 2 * (size_t)LG_ATTN_S * ldh * 2 + nq16 * LG_ATTN_S * 4 + 2 * nq16 * (LG_ATTN_S + 8) * 2 + nq16 * 8 + 64;
+    size_t nq16 = (size_t)((nq + 15) & ~15), ldh = hd + 8, S = lg_attn_tile(hd);
+    return 2 * nq16 * ldh * 2 + 2 * S * ldh * 2 + nq16 * S * 4 + 2 * nq16 * (S + 8) * 2 + nq16 * 8 + 64;
 }
 
 void launch_attn(Engine *e, LgAttnArgs a, int n_tiles_max) {
@@ -374,7 +375,7 @@ void launch_attn(Engine *e, LgAttnArgs a, int n_tiles_max) {
     size_t sm = attn_smem(nq, a.hd);
     if (sm > ATTN_SMEM_MAX) { fprintf(stderr, "lg_b200: attention tile needs %zu bytes of shared memory\n", sm); exit(1); }
     if (a.Hkv > MAX_KV_HEADS) { fprintf(stderr, "lg_b200: more than %d KV heads\n", MAX_KV_HEADS); exit(1); }
-    if ((size_t)nq * n_tiles_max * 8 > 2 * (size_t)LG_ATTN_S * (a.hd + 8) * 2) {
+    if ((size_t)nq * n_tiles_max * 8 > 2 * (size_t)lg_attn_tile(a.hd) * (a.hd + 8) * 2) {
         fprintf(stderr, "lg_b200: %d key tiles x %d queries exceed the merge buffer of the attention kernel\n", n_tiles_max, nq); exit(1);
     }
     a.tickets = e->tickets;
@@ -388,9 +389,10 @@ void launch_attn(Engine *e, LgAttnArgs a, int n_tiles_max) {
     }
 }
 
-int tiles_for(int window, int max_seq, int M) {
-    if (window > 0 && window + M < max_seq) return (window + M + ATTN_TILE - 1) / ATTN_TILE + 1;
-    return (max_seq + ATTN_TILE - 1) / ATTN_TILE + 1;
+int tiles_for(int window, int max_seq, int M, int hd) {
+    const int S = lg_attn_tile(hd);
+    if (window > 0 && window + M < max_seq) return (window + M + S - 1) / S + 1;
+    return (max_seq + S - 1) / S + 1;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -411,7 +413,7 @@ Engine *engine_for(const struct model *m) {
     LG_CHECK(cudaDeviceGetAttribute(&e->sm_count, cudaDevAttrMultiProcessorCount, dev));
     LG_CHECK(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
     e->head_ctas = e->sm_count * 2;
-    e->pdl = env_int("LG_PDL", 0);
+    e->pdl = env_int("LG_PDL", 1);
     e->err = dalloc<int>(1);
     e->tickets = dalloc<int>(MAX_KV_HEADS);
 
@@ -557,7 +559,7 @@ void bind_kv(Engine *e, const struct kvcache *kv) {
     const struct config *c = &e->m->cfg;
     int slots = 0, maxhd = 0;
     for (int l = 0; l < c->n_layer; l++) {
-        int s = tiles_for(e->L[l].local ? c->sliding_window : 0, kv->max_seq, LG_MAXM);
+        int s = tiles_for(e->L[l].local ? c->sliding_window : 0, kv->max_seq, LG_MAXM, e->L[l].hd);
         if (s > slots) slots = s;
         if (e->L[l].hd > maxhd) maxhd = e->L[l].hd;
     }
@@ -616,7 +618,7 @@ void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags, int 
         aa.n_slots = e->part_slots; aa.part = e->part; aa.part_ml = e->part_ml; aa.out_f32 = nullptr;
         LgPanel pa = e->p_attn; pa.nsb = H * hd / 32;
         aa.out = pa;
-        if (only & C_ATTN) launch_attn(e, aa, tiles_for(aa.window, kv->max_seq, M));
+        if (only & C_ATTN) launch_attn(e, aa, tiles_for(aa.window, kv->max_seq, M, hd));
 
         // o-projection, then x += norm(o)*w_post_attn and the ffn_norm panel
         int ks_o = 1;
@@ -738,7 +740,7 @@ DraftW *draft_build(Engine *e, struct mtp *t, const struct kvcache *kv) {
     d->qbuf = dalloc<float>((size_t)LG_MAXM * (qmax + 64)); d->qrot = dalloc<float>(qmax);
     d->obuf = dalloc<float>((size_t)e->max_ks * LG_MAXM * (std::max(d->ni, d->nb) + 64));
     d->gu = dalloc<float>(32);
-    int slots = tiles_for(0, kv->max_seq, 1);
+    int slots = tiles_for(0, kv->max_seq, 1, 512);
     d->n_slots_global = slots;
     d->part = dalloc<float>((size_t)slots * d->n_head * maxhd);
     d->part_ml = dalloc<float2>((size_t)slots * d->n_head);
@@ -789,7 +791,7 @@ void enqueue_draft(Engine *e, DraftW *d, const struct kvcache *kv, int slot, boo
         aa.n_slots = d->n_slots_global; aa.part = d->part; aa.part_ml = d->part_ml;
         LgPanel pa = d->p_attn; pa.nsb = d->n_head * hd / 32;
         aa.out = pa; aa.out_f32 = nullptr;
-        launch_attn(e, aa, tiles_for(aa.window, kv->max_seq, 1));
+        launch_attn(e, aa, tiles_for(aa.window, kv->max_seq, 1, hd));
         int ks_o = 1;
         GemvExtra xo; xo.ks_out = &ks_o;
         launch_gemv(e, b.o, pa, 1, d->obuf, LG_EPI_STORE, 0, xo);

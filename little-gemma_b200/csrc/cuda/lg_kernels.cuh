@@ -686,7 +686,7 @@ __global__ void lg_quant_rows(const float *__restrict__ x, int ldx, int n, LgPan
 // ---------------------------------------------------------------------------------------------
 // attention: q/k/v post-processing + split-KV flash-decode on tensor cores + combine, one launch
 // ---------------------------------------------------------------------------------------------
-// Keys are partitioned on ABSOLUTE position boundaries: tile T covers positions [T*64, (T+1)*64).
+// Keys are partitioned on ABSOLUTE position boundaries: tile T covers positions [T*S, (T+1)*S), S = lg_attn_tile(hd).
 // Query j (token j of the block, position p_j = pos + j + qpos_off) attends positions
 // [max(0, p_j + win_shrink - window + 1), p_j]  (window <= 0: from 0).
 // A CTA handles one KV head and one tile for all of that head's queries (gqa heads x M tokens):
@@ -721,7 +721,8 @@ struct LgAttnArgs {
 };
 
 #define LG_ATTN_THREADS 256
-#define LG_ATTN_S 64
+// keys per tile: 128, or 64 for head sizes whose K/V tiles would not fit in shared memory otherwise
+__host__ __device__ constexpr int lg_attn_tile(int hd) { return hd > 256 ? 64 : 128; }
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void *p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -785,12 +786,12 @@ __device__ __forceinline__ void head_norm_rope(const float *src, const float *w,
     }
 }
 
-// dynamic smem: Qhi | Qlo [NQ16][HD+8] f16 | K [64][HD+8] | V [64][HD+8] | S [NQ16][64] f32 | Phi | Plo [NQ16][72] f16 | ml [NQ16][2]
+// dynamic smem: Qhi | Qlo [NQ16][HD+8] f16 | K [S][HD+8] | V [S][HD+8] | scores [NQ16][S] f32 | Phi | Plo [NQ16][S+8] f16 | ml [NQ16][2]
 template <int HD>
 __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) {
     pdl_launch(); pdl_wait();
     extern __shared__ __align__(128) unsigned char smem[];
-    constexpr int S = LG_ATTN_S, LDH = HD + 8, LDP = S + 8, PER = HD / 64, HALF = HD / 2, NW = LG_ATTN_THREADS / 32;
+    constexpr int S = lg_attn_tile(HD), LDH = HD + 8, LDP = S + 8, PER = HD / 64, HALF = HD / 2, NW = LG_ATTN_THREADS / 32;
     const int kvh = blockIdx.x, gqa = a.H / a.Hkv, nq = gqa * a.M, nq16 = (nq + 15) & ~15;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int pos0 = *a.pos;
@@ -871,21 +872,28 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) 
     cp_async_wait_all();
     __syncthreads();
 
-    // ---- 3. scores: warp w takes keys [8w, 8w+8) ----
+    // ---- 3. scores: warp w takes keys [w*S/8, (w+1)*S/8) ----
     const int g = lane >> 2, t = lane & 3;
+    constexpr int KPW = S / NW, NKT = KPW / 8;                  // keys and 8-key tiles per warp
     for (int mt = 0; mt < nq16 / 16; mt++) {
-        float c0[4] = {0, 0, 0, 0};
+        float c0[NKT][4];
+        #pragma unroll
+        for (int n = 0; n < NKT; n++) c0[n][0] = c0[n][1] = c0[n][2] = c0[n][3] = 0.0f;
         const __half *qa_hi = qhi + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + (lane >> 4) * 8;
         const __half *qa_lo = qlo + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + (lane >> 4) * 8;
-        const __half *kb = sk + (size_t)(warp * 8 + (lane & 7)) * LDH + (lane >> 3) * 8;      // 4 matrices: d = k0, +8, +16, +24
+        const __half *kb = sk + (size_t)(warp * KPW + (lane & 7)) * LDH + (lane >> 3) * 8;      // 4 matrices: d = k0, +8, +16, +24
         #pragma unroll 2
         for (int k0 = 0; k0 < HD; k0 += 32) {
-            uint32_t ah[4], al[4], ah2[4], al2[4], b[4];
-            ldsm_x4(b, kb + k0);
+            uint32_t ah[4], al[4], ah2[4], al2[4];
             ldsm_x4(ah, qa_hi + k0); ldsm_x4(al, qa_lo + k0);
             ldsm_x4(ah2, qa_hi + k0 + 16); ldsm_x4(al2, qa_lo + k0 + 16);
-            mma_f16(c0, ah, b[0], b[1]); mma_f16(c0, al, b[0], b[1]);
-            mma_f16(c0, ah2, b[2], b[3]); mma_f16(c0, al2, b[2], b[3]);
+            #pragma unroll
+            for (int n = 0; n < NKT; n++) {
+                uint32_t b[4];
+                ldsm_x4(b, kb + (size_t)n * 8 * LDH + k0);
+                mma_f16(c0[n], ah, b[0], b[1]); mma_f16(c0[n], al, b[0], b[1]);
+                mma_f16(c0[n], ah2, b[2], b[3]); mma_f16(c0[n], al2, b[2], b[3]);
+            }
         }
         #pragma unroll
         for (int h2 = 0; h2 < 2; h2++) {
@@ -893,24 +901,32 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) 
             const int pj = pos0 + qi / gqa + a.qpos_off;
             const int lo = a.window > 0 ? max(0, pj + a.win_shrink - a.window + 1) : 0;
             #pragma unroll
-            for (int e = 0; e < 2; e++) {
-                const int key = warp * 8 + t * 2 + e, p = T * S + key;
-                sc[(size_t)qi * S + key] = (qi < nq && p >= lo && p <= pj) ? c0[h2 * 2 + e] : -INFINITY;
-            }
+            for (int n = 0; n < NKT; n++)
+                #pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const int key = warp * KPW + n * 8 + t * 2 + e, p = T * S + key;
+                    sc[(size_t)qi * S + key] = (qi < nq && p >= lo && p <= pj) ? c0[n][h2 * 2 + e] : -INFINITY;
+                }
         }
     }
     __syncthreads();
 
     // ---- 4. per-query softmax over the tile ----
     for (int qi = warp; qi < nq16; qi += NW) {
-        float s0 = sc[(size_t)qi * S + lane], s1 = sc[(size_t)qi * S + lane + 32];
-        float mx = warp_max(fmaxf(s0, s1));
-        float e0 = (s0 == -INFINITY) ? 0.0f : expf(s0 - mx), e1 = (s1 == -INFINITY) ? 0.0f : expf(s1 - mx);
-        float sum = warp_sum(e0 + e1);
-        __half h0 = __float2half_rn(e0), h1 = __float2half_rn(e1);
-        phi[(size_t)qi * LDP + lane] = h0; phi[(size_t)qi * LDP + lane + 32] = h1;
-        plo[(size_t)qi * LDP + lane] = __float2half_rn(e0 - __half2float(h0));
-        plo[(size_t)qi * LDP + lane + 32] = __float2half_rn(e1 - __half2float(h1));
+        float sv_[S / 32], mx = -INFINITY;
+        #pragma unroll
+        for (int j = 0; j < S / 32; j++) { sv_[j] = sc[(size_t)qi * S + lane + 32 * j]; mx = fmaxf(mx, sv_[j]); }
+        mx = warp_max(mx);
+        float sum = 0.0f;
+        #pragma unroll
+        for (int j = 0; j < S / 32; j++) {
+            const float e = (sv_[j] == -INFINITY) ? 0.0f : expf(sv_[j] - mx);
+            const __half h = __float2half_rn(e);
+            phi[(size_t)qi * LDP + lane + 32 * j] = h;
+            plo[(size_t)qi * LDP + lane + 32 * j] = __float2half_rn(e - __half2float(h));
+            sum += e;
+        }
+        sum = warp_sum(sum);
         if (lane == 0) { ml[qi * 2] = mx; ml[qi * 2 + 1] = sum; }
     }
     __syncthreads();
