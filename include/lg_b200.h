@@ -104,6 +104,21 @@ int  lg_gemv_host(int type, const void *blocks, int m, int k, const float *x, in
 int  lg_flash_decode_host(const float *q, const float *k, const float *v, int M, int H, int Hkv, int hd,
                           int seq, int window, int pos, float *out);
 
+/* Split-KV flash-decode for callers that cannot allocate device memory (a captured stream, a
+ * serving loop whose memory was fixed at start-up, a process whose allocator owns the device).
+ * Same kernel as lg_flash_decode_host, but every pointer is a DEVICE pointer supplied by the
+ * caller (q [M][H][hd] f32; k, v [seq][Hkv*hd] f16; out [M][H][hd] f32) and the kernel's scratch
+ * lives in a 4 MiB array built into the library, which every GPU that loads the library holds
+ * until exit.  No cudaMalloc / cudaFree / allocating call is made.  It has no counterpart in the
+ * reference.  The first call on a device looks up the array's device address; make that call
+ * before any stream capture.  All calls share the array: two calls that overlap on the GPU
+ * (different streams, no ordering) race.  Work is enqueued on `stream` (a cudaStream_t, or NULL)
+ * and not waited for.  Returns 0, or a negative code with a message on stderr; -4 means
+ * key tiles x M x H x (hd + 2) x 4 bytes exceed the array (e.g. M=4, H=16, hd=256: up to 63 tiles
+ * of 128 keys, about 8,000 cached positions). */
+int  lg_flash_decode_noalloc(const float *d_q, const void *d_k_f16, const void *d_v_f16, int M, int H, int Hkv, int hd,
+                             int seq, int window, int pos, float *d_out, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

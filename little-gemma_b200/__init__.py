@@ -29,7 +29,7 @@ ABI_SYMBOLS = [
     "model_prefill_reserve", "model_forward_spec", "mtp_draft_device", "mtp_draft_chain_device", "mtp_free_device",
     "lg_forward_spec_n", "lg_set_replay", "lg_rounds_begin", "lg_rounds_enqueue", "lg_rounds_collect",
     "lg_weight_bytes", "lg_round_launches", "lg_last_hidden", "lg_kv_row", "lg_stream", "lg_engine_release",
-    "lg_bench_matmul_pass",
+    "lg_bench_matmul_pass", "lg_flash_decode_noalloc",
     "lg_dequant_host", "lg_gemv_host", "lg_flash_decode_host",
 ]
 
@@ -71,6 +71,9 @@ def load() -> C.CDLL:
     L.lg_flash_decode_host.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                        C.c_int, _f32p]
     L.lg_flash_decode_host.restype = C.c_int
+    L.lg_flash_decode_noalloc.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                          C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+    L.lg_flash_decode_noalloc.restype = C.c_int
     L.lg_set_replay.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
     L.lg_rounds_begin.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int]
     L.lg_rounds_enqueue.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
@@ -123,6 +126,14 @@ def flash_decode(q: np.ndarray, k: np.ndarray, v: np.ndarray, n_head_kv: int, wi
     if rc:
         raise ValueError(f"lg_flash_decode_host failed ({rc})")
     return out
+
+
+def flash_decode_noalloc(d_q: int, d_k: int, d_v: int, M: int, H: int, n_head_kv: int, hd: int, seq: int, window: int,
+                         pos: int, d_out: int, stream: int = 0) -> int:
+    """The allocation-free flash-decode entry point: every argument named d_* is a raw device address
+    (q f32 [M,H,hd]; k, v f16 [seq, Hkv*hd]; out f32 [M,H,hd]).  Enqueues on `stream` and returns the
+    library's status code (0 = launched)."""
+    return int(load().lg_flash_decode_noalloc(d_q, d_k, d_v, M, H, n_head_kv, hd, seq, window, pos, d_out, stream))
 
 
 class Session:

@@ -1164,3 +1164,84 @@ long long lg_round_launches(struct model *m) { return engine_for(m)->round_launc
 
 }  // extern "C"
 #include "lg_capi.cuh"
+
+// ==========================================================================================
+// Flash-decode for callers that must not allocate
+// ==========================================================================================
+// Some hosts of this library run where device allocation is off the table: inside a stream
+// capture, inside a latency-critical serving loop whose memory was carved up at start-up, or
+// under an allocator that owns the whole device and forbids cudaMalloc behind its back.  For
+// them the split-KV attention kernel is also reachable through an entry point whose scratch
+// (per-tile partial accumulators, per-tile (max, sum), the per-head tickets and the position
+// word) lives in a fixed array inside the library image instead of in memory it would have to
+// allocate.  Every GPU that loads the library holds this array until the process exits.
+#define LG_NOALLOC_SCRATCH_BYTES (4u << 20)
+static __device__ __align__(256) unsigned char lg_noalloc_scratch[LG_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+// device address of the array, looked up once per device (the symbol name itself is only a
+// host-side handle; a kernel must be given the address cudaGetSymbolAddress returns)
+unsigned char *g_noalloc_ptr[64];
+
+__global__ void lg_noalloc_set_pos(int *p, int v) { *p = v; }
+}  // namespace
+
+extern "C" int lg_flash_decode_noalloc(const float *d_q, const void *d_k_f16, const void *d_v_f16, int M, int H, int Hkv,
+                                       int hd, int seq, int window, int pos, float *d_out, void *stream) {
+    if (M < 1 || M > LG_MAXM || (hd != 64 && hd != 128 && hd != 256 && hd != 512) || Hkv < 1 || H % Hkv || Hkv > MAX_KV_HEADS ||
+        seq < 1 || pos < 0 || !d_q || !d_k_f16 || !d_v_f16 || !d_out) {
+        fprintf(stderr, "lg_flash_decode_noalloc: bad arguments\n");
+        return -1;
+    }
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -2;
+    if (!g_noalloc_ptr[dev]) {
+        // first call on this device: resolve the array's device address (do this before any capture)
+        void *p = nullptr;
+        cudaError_t rc = cudaGetSymbolAddress(&p, lg_noalloc_scratch);
+        if (rc != cudaSuccess || !p) {
+            fprintf(stderr, "lg_flash_decode_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(rc));
+            return -3;
+        }
+        set_kernel_attributes();
+        g_noalloc_ptr[dev] = (unsigned char *)p;
+    }
+    const int max_seq = pos + M > seq ? pos + M : seq;
+    const int slots = tiles_for(window, max_seq, M, hd);
+    const int nq = (H / Hkv) * M;
+    // layout inside the array: [tickets 256 B][pos 256 B][(max,sum) pairs][accumulators]
+    const size_t ml_bytes = ((size_t)slots * M * H * sizeof(float2) + 255) & ~(size_t)255;
+    const size_t acc_bytes = (size_t)slots * M * H * hd * sizeof(float);
+    const size_t need = 512 + ml_bytes + acc_bytes;
+    const size_t sm = attn_smem(nq, hd);
+    if (need > LG_NOALLOC_SCRATCH_BYTES || sm > ATTN_SMEM_MAX ||
+        (size_t)nq * slots * 8 > 2 * (size_t)lg_attn_tile(hd) * (hd + 8) * 2) {
+        fprintf(stderr, "lg_flash_decode_noalloc: %d key tiles x %d rows x %d heads x %d dims need %zu bytes of scratch; "
+                        "the built-in array holds %u\n", slots, M, H, hd, need, LG_NOALLOC_SCRATCH_BYTES);
+        return -4;
+    }
+    unsigned char *base = g_noalloc_ptr[dev];
+    cudaStream_t st = (cudaStream_t)stream;
+    // the array keeps whatever the previous call left: tickets must start at zero
+    if (cudaMemsetAsync(base, 0, 256, st) != cudaSuccess) return -5;
+    lg_noalloc_set_pos<<<1, 1, 0, st>>>((int *)(base + 256), pos);
+    LgAttnArgs a{};
+    a.qkv = d_q; a.ld = 0; a.q_ready = 1; a.has_v = 1; a.owns_kv = 0; a.eps = 0.0f; a.rope = nullptr;
+    a.kc = (__half *)d_k_f16; a.vc = (__half *)d_v_f16; a.seq = seq; a.kv_dim = Hkv * hd;
+    a.H = H; a.Hkv = Hkv; a.hd = hd; a.M = M; a.n_slots = slots; a.window = window; a.qpos_off = 0; a.win_shrink = 0;
+    a.pos = (const int *)(base + 256);
+    a.tickets = (int *)base;
+    a.part_ml = (float2 *)(base + 512);
+    a.part = (float *)(base + 512 + ml_bytes);
+    a.out.q = nullptr; a.out_f32 = d_out;
+    dim3 grid(Hkv, slots), block(LG_ATTN_THREADS);
+    switch (hd) {
+    case 64:  lg_attn_kernel<64><<<grid, block, sm, st>>>(a); break;
+    case 128: lg_attn_kernel<128><<<grid, block, sm, st>>>(a); break;
+    case 256: lg_attn_kernel<256><<<grid, block, sm, st>>>(a); break;
+    default:  lg_attn_kernel<512><<<grid, block, sm, st>>>(a); break;
+    }
+    cudaError_t rc = cudaGetLastError();
+    if (rc != cudaSuccess) { fprintf(stderr, "lg_flash_decode_noalloc: launch failed: %s\n", cudaGetErrorString(rc)); return -6; }
+    return 0;
+}
