@@ -361,6 +361,23 @@ void launch_norm(Engine *e, int M, float *x, int ldx, int n, float eps,
     a.add_w = add_w; a.out_scale = out_scale; a.norm_w = norm_w;
     if (panel) { a.panel = *panel; a.want_panel = 1; }
     a.y = y; a.ldy = ldy; a.n = n; a.eps = eps;
+    static const int use_cluster = env_int("LG_NORM_CLUSTER", 1);
+    if (use_cluster && n >= 32 * LG_NORM_CL) {
+        // one cluster of LG_NORM_CL CTAs per token row
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(M * LG_NORM_CL); cfg.blockDim = dim3(LG_NORM_CL_THREADS);
+        int gpc = ((n >> 5) + LG_NORM_CL - 1) / LG_NORM_CL;
+        cfg.dynamicSmemBytes = (size_t)3 * gpc * 32 * sizeof(float); cfg.stream = e->stream;
+        cudaLaunchAttribute at[2];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = LG_NORM_CL; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at; cfg.numAttrs = e->pdl ? 2 : 1;
+        LG_CHECK(cudaLaunchKernelEx(&cfg, lg_norm_cluster_kernel, a));
+        e->launches++;
+        return;
+    }
     int threads = n >= 2048 ? 1024 : (n >= 512 ? 512 : 256);
     launch_k(e, lg_norm_kernel, dim3(M), dim3(threads), (size_t)(2 * n + 32) * 4, a);
 }

@@ -674,6 +674,92 @@ __global__ void lg_norm_kernel(LgNormArgs a) {
     }
 }
 
+// ---- the same norm spread over a thread-block cluster ------------------------------------------
+// One cluster of LG_NORM_CL CTAs per token row; CTA r owns a contiguous run of 32-element groups.
+// The two sums of squares are exchanged through distributed shared memory (every CTA writes its
+// partial into slot r of every peer, then the slots are added in rank order), so a row's result is
+// fixed by (n, LG_NORM_CL) alone.  Shortens the latency chain of the single-CTA kernel: each CTA
+// touches 1/8 of the row and the whole row is in flight at once.
+#define LG_NORM_CL 8
+#define LG_NORM_CL_THREADS 128
+
+__device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void dsmem_store(float *local_addr, uint32_t rank, float v) {
+    uint32_t la = smem_u32(local_addr), ra;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(la), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" :: "r"(ra), "f"(v) : "memory");
+}
+
+__global__ void __launch_bounds__(LG_NORM_CL_THREADS) lg_norm_cluster_kernel(LgNormArgs a) {
+    extern __shared__ float row[];                       // this CTA's run of the row, then the two weight runs (3 * gpc*32 floats)
+    __shared__ float slots[2][LG_NORM_CL];               // partial sums of squares of every rank, two rounds
+    __shared__ float red[32];
+    const uint32_t rank = cluster_rank();
+    const int tok = blockIdx.x / LG_NORM_CL, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = LG_NORM_CL_THREADS / 32;
+    const int ng = a.n >> 5, gpc = (ng + LG_NORM_CL - 1) / LG_NORM_CL;
+    const int g0 = rank * gpc, g1 = min(ng, g0 + gpc), i0 = g0 * 32, cnt = max(0, (g1 - g0) * 32);
+    float *wa = row + gpc * 32, *wn = wa + gpc * 32;
+    // the norm weights do not depend on the previous kernel (and are cold in HBM): fetch them first
+    pdl_launch();
+    for (int j = threadIdx.x; j < cnt; j += LG_NORM_CL_THREADS) {
+        if (a.add_src) wa[j] = a.add_w[i0 + j];
+        if (a.norm_w) wn[j] = a.norm_w[i0 + j];
+    }
+    pdl_wait();
+    float *x = a.x + (size_t)tok * a.ldx;
+    float ss2 = 0.0f;
+    if (a.add_src) {
+        float ss = 0.0f;
+        for (int j = threadIdx.x; j < cnt; j += LG_NORM_CL_THREADS) {
+            const int i = i0 + j;
+            float v = 0.0f;
+            for (int p = 0; p < a.n_parts; p++) v += a.add_src[(size_t)p * a.part_stride + (size_t)tok * a.ld_add + i];
+            row[j] = v;
+            ss += v * v;
+        }
+        ss = block_sum(ss, red);
+        if (threadIdx.x < LG_NORM_CL) dsmem_store(&slots[0][rank], threadIdx.x, ss);
+        cluster_sync_all();
+        float tot = 0.0f;
+        #pragma unroll
+        for (int r = 0; r < LG_NORM_CL; r++) tot += slots[0][r];
+        const float s = 1.0f / sqrtf(tot / (float)a.n + a.eps);
+        for (int j = threadIdx.x; j < cnt; j += LG_NORM_CL_THREADS) {
+            const int i = i0 + j;
+            float v = __fadd_rn(x[i], __fmul_rn(__fmul_rn(row[j], s), wa[j]));
+            v = __fmul_rn(v, a.out_scale);
+            x[i] = v;
+            row[j] = v;
+            ss2 += v * v;
+        }
+    } else {
+        for (int j = threadIdx.x; j < cnt; j += LG_NORM_CL_THREADS) { float v = x[i0 + j]; row[j] = v; ss2 += v * v; }
+    }
+    if (!a.norm_w && !a.want_panel && !a.y) { cluster_sync_all(); return; }
+    float s = 1.0f;
+    if (a.norm_w) {
+        ss2 = block_sum(ss2, red);
+        if (threadIdx.x < LG_NORM_CL) dsmem_store(&slots[1][rank], threadIdx.x, ss2);
+        cluster_sync_all();
+        float tot = 0.0f;
+        #pragma unroll
+        for (int r = 0; r < LG_NORM_CL; r++) tot += slots[1][r];
+        s = 1.0f / sqrtf(tot / (float)a.n + a.eps);
+    } else {
+        __syncthreads();
+    }
+    for (int gq = g0 + warp; gq < g1; gq += nw) {
+        const int i = gq * 32 + lane;
+        float yv = a.norm_w ? __fmul_rn(__fmul_rn(row[i - i0], s), wn[i - i0]) : row[i - i0];
+        if (a.y) a.y[(size_t)tok * a.ldy + i] = yv;
+        if (a.want_panel) quant_group_store(yv, lane, tok, gq, a.panel);
+    }
+    cluster_sync_all();                                   // no CTA may exit while a peer can still write into its slots
+}
+
 // Quantise f32 rows into a panel (used where the producer is not one of the fused kernels).
 __global__ void lg_quant_rows(const float *__restrict__ x, int ldx, int n, LgPanel P) {
     pdl_launch(); pdl_wait();
@@ -789,8 +875,13 @@ __device__ __forceinline__ void head_norm_rope(const float *src, const float *w,
 // dynamic smem: Qhi | Qlo [NQ16][HD+8] f16 | K [S][HD+8] | V [S][HD+8] | scores [NQ16][S] f32 | Phi | Plo [NQ16][S+8] f16 | ml [NQ16][2]
 template <int HD>
 __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) {
-    pdl_launch(); pdl_wait();
     extern __shared__ __align__(128) unsigned char smem[];
+    // the per-head norm weights are cold in HBM and do not depend on the previous kernel: fetch them first
+    __shared__ float s_qn[HD], s_kn[HD];
+    pdl_launch();
+    if (!a.q_ready)
+        for (int i = threadIdx.x; i < HD; i += LG_ATTN_THREADS) { s_qn[i] = a.q_norm[i]; s_kn[i] = a.k_norm ? a.k_norm[i] : 1.0f; }
+    pdl_wait();
     constexpr int S = lg_attn_tile(HD), LDH = HD + 8, LDP = S + 8, PER = HD / 64, HALF = HD / 2, NW = LG_ATTN_THREADS / 32;
     const int kvh = blockIdx.x, gqa = a.H / a.Hkv, nq = gqa * a.M, nq16 = (nq + 15) & ~15;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -836,7 +927,7 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) 
                 #pragma unroll
                 for (int e = 0; e < PER; e++) { v0[e] = src[lane * PER + e]; v1[e] = src[lane * PER + e + HALF]; }
             } else {
-                head_norm_rope<HD>(a.qkv + (size_t)tok * a.ld + (size_t)hq * HD, a.q_norm, a.rope + (size_t)tok * HALF, a.eps, lane, v0, v1);
+                head_norm_rope<HD>(a.qkv + (size_t)tok * a.ld + (size_t)hq * HD, s_qn, a.rope + (size_t)tok * HALF, a.eps, lane, v0, v1);
             }
         } else {
             #pragma unroll
@@ -858,7 +949,7 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) 
             if (p / S != T) continue;
             float v0[PER], v1[PER];
             const float *src = a.qkv + (size_t)tok * a.ld + (size_t)(a.H + ((isv && a.has_v) ? a.Hkv : 0) + kvh) * HD;
-            head_norm_rope<HD>(src, isv ? nullptr : a.k_norm, isv ? nullptr : a.rope + (size_t)tok * HALF, a.eps, lane, v0, v1);
+            head_norm_rope<HD>(src, isv ? nullptr : s_kn, isv ? nullptr : a.rope + (size_t)tok * HALF, a.eps, lane, v0, v1);
             __half *dst = (isv ? a.vc : a.kc) + (size_t)(p % a.seq) * a.kv_dim + (size_t)kvh * HD;
             __half *dsm = (isv ? sv : sk) + (size_t)(p - T * S) * LDH;
             #pragma unroll
