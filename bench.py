@@ -211,9 +211,14 @@ def main():
         if WORLD > 1:
             dist.barrier()
 
-    # prompt -> cache, first token
-    sess.prefill(prompt[:-1], 0)
-    first = sess.next(int(prompt[-1]), a.depth - 1)
+    # prompt -> cache, first token.  Every timed phase below starts from this state again: a phase
+    # may run past the sliding-window rings' length, after which rewinding the position would read
+    # rows that later positions have overwritten.
+    def restart():
+        sess.prefill(prompt[:-1], 0)
+        return sess.next(int(prompt[-1]), a.depth - 1)
+
+    first = restart()
     pos0 = a.depth
 
     if a.profile_step:
@@ -240,6 +245,7 @@ def main():
     sess.set_replay(replay)
 
     # warm-up rounds (graph capture happens here), then K timed rounds
+    restart()
     sess.rounds_begin(first, pos0, 1)
     sess.rounds_enqueue(M, 2, a.warmup)
     _, st_w = sess.rounds_collect(1, 0)
@@ -262,6 +268,7 @@ def main():
     accept = (st["n_accept"] - st_w["n_accept"]) / max(1, st["n_draft"] - st_w["n_draft"])
 
     # plain decode (verify width 1) for context
+    restart()
     sess.rounds_begin(first, pos0, 1)
     sess.rounds_enqueue(1, 0, a.warmup, use_head=False)
     sess.rounds_collect(1, 0)
@@ -273,6 +280,7 @@ def main():
     plain_ms = p0.elapsed_time(p1) / a.steps
 
     # verify step alone (no draft head) at width M
+    restart()
     sess.rounds_begin(first, pos0, 1)
     sess.rounds_enqueue(M, 2, a.warmup, use_head=False)
     sess.rounds_collect(1, 0)
@@ -298,7 +306,9 @@ def main():
 
     # end to end through the blocking reference-shaped API
     e2e_rounds = max(20, a.steps // 3)
+    restart()
     sess.rounds_host(first, pos0, 1, 8 * M, 4, 3, replay)                       # warm the per-call graphs
+    restart()
     barrier()
     t0 = time.perf_counter()
     toks_h, st_h = sess.rounds_host(first, pos0, 1, n_gen, e2e_rounds, 3, replay)

@@ -738,7 +738,7 @@ __global__ void __launch_bounds__(LG_NORM_CL_THREADS) lg_norm_cluster_kernel(LgN
     } else {
         for (int j = threadIdx.x; j < cnt; j += LG_NORM_CL_THREADS) { float v = x[i0 + j]; row[j] = v; ss2 += v * v; }
     }
-    if (!a.norm_w && !a.want_panel && !a.y) { cluster_sync_all(); return; }
+    if (!a.norm_w && !a.want_panel && !a.y) return;
     float s = 1.0f;
     if (a.norm_w) {
         ss2 = block_sum(ss2, red);
@@ -757,7 +757,7 @@ __global__ void __launch_bounds__(LG_NORM_CL_THREADS) lg_norm_cluster_kernel(LgN
         if (a.y) a.y[(size_t)tok * a.ldy + i] = yv;
         if (a.want_panel) quant_group_store(yv, lane, tok, gq, a.panel);
     }
-    cluster_sync_all();                                   // no CTA may exit while a peer can still write into its slots
+    // every remote write into this CTA's slots precedes a cluster barrier this CTA has passed: safe to exit
 }
 
 // Quantise f32 rows into a panel (used where the producer is not one of the fused kernels).
