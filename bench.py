@@ -52,6 +52,8 @@ if WORLD > 1 and "LG_B200_VISIBLE_SET" not in os.environ:
 import numpy as np  # noqa: E402
 
 CACHE = os.environ.get("LG_B200_CACHE", "/tmp/lg_b200_cache")
+# dram__bytes_read+write / algorithmic bytes of the matmul kernel, from profiles/gemv_e4b_gateup_ncu.md
+DRAM_TRAFFIC_RATIO = 37.793024 / 37.748736
 
 
 def shapes(name):
@@ -114,8 +116,9 @@ def cpu_reference_run(tp, n_tokens, warm=1):
     kind = "reference" if os.path.exists(pyref.ref_lib_path(4)) else "port"
     if kind == "port":
         subprocess.check_call(["make", "-s", "-C", os.path.join(ROOT, "oracle"), "port"])
-    cores = os.cpu_count() or 1
-    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    # all host cores (torchrun pins OMP_NUM_THREADS=1 for its workers; the CPU baseline is not one of them)
+    cores = int(os.environ.get("LG_CPU_THREADS", os.cpu_count() or 1))
+    os.environ["OMP_NUM_THREADS"] = str(cores)
     o = (pyref.RefOracle if kind == "reference" else pyref.PortOracle)(tp, None, 64, False, 4)
     tok, pos = 1, 0
     for _ in range(warm):
@@ -340,7 +343,7 @@ def main():
     agg = import_module("little-gemma_b200.replicas").aggregate([v.tolist() for v in allv])
 
     cpu = None
-    if RANK == 0 and not a.no_cpu:
+    if RANK == 0 and WORLD == 1 and not a.no_cpu:
         try:
             tps, info = cpu_reference_run(tp, a.cpu_tokens)
             cpu = dict(info, value=tps, unit="tok/s")
@@ -353,7 +356,9 @@ def main():
                     e2e={"value": agg["e2e_tok_s"], "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                          "rounds": e2e_rounds, "host_syncs_per_round": M},
                     roofline={"bound": "hbm", "kernel": "lg_gemv_kernel", "achieved": mm_gbs, "peak": peak, "unit": "GB/s",
-                              "frac": mm_gbs / peak, "traffic": None, "peak_source": peak_src,
+                              "frac": mm_gbs / peak, "traffic": int(W * DRAM_TRAFFIC_RATIO), "peak_source": peak_src,
+                              "traffic_note": "dram read+write bytes of the matmul pass: ncu capture of the E4B-class gate/up "
+                                              "launch (37.793 MB moved for 37.749 MB of q4_0) scaled by weight bytes; writes 0",
                               "algorithmic_bytes": W, "launches": n_mm, "ms": mm_ms,
                               "frac_of_8TBs": mm_gbs / 8000.0},
                     cpu_baseline=cpu)
