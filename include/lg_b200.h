@@ -99,6 +99,13 @@ int  lg_dequant_host(int type, const void *blocks, int n_rows, int k, float *out
 /* y[tok][row] = W x[tok] for tok < M <= 8 through the tile-major repack, the 16-bit activation
  * panel and the tensor-core kernel; W is m rows of file-format blocks. */
 int  lg_gemv_host(int type, const void *blocks, int m, int k, const float *x, int M, int kslices, float *y);
+/* The wide (prompt) matmul: out[tok][row] = W x[tok] for tok < n <= 256 at once, x rounded to f16,
+ * weights expanded q4 -> f16 inside the kernel, tcgen05.mma with f32 accumulation.  With blocks_up
+ * != NULL the two matrices are a gate/up pair and out[tok][row] = gelu_tanh(gate.x) * (up.x)
+ * rounded to f16 (the fused epilogue the prompt pass uses).  Replaces the reference's wide-batch
+ * matmul_q_n / matmul_q4k_mma_kernel (src/cuda/model-cuda-i8.cu:1060-1227). */
+int  lg_prefill_matmul_host(int type, const void *blocks, const void *blocks_up, int m, int k, const float *x, int n,
+                            float *out);
 /* Split-KV flash-decode of M query rows over an f16 cache given as f32 host arrays
  * (rounded to f16 on upload): q [M][H][hd], k/v [seq][Hkv*hd], positions pos..pos+M-1. */
 int  lg_flash_decode_host(const float *q, const float *k, const float *v, int M, int H, int Hkv, int hd,

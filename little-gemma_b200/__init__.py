@@ -30,7 +30,7 @@ ABI_SYMBOLS = [
     "lg_forward_spec_n", "lg_set_replay", "lg_rounds_begin", "lg_rounds_enqueue", "lg_rounds_collect",
     "lg_weight_bytes", "lg_round_launches", "lg_last_hidden", "lg_kv_row", "lg_stream", "lg_engine_release",
     "lg_bench_matmul_pass", "lg_flash_decode_noalloc",
-    "lg_dequant_host", "lg_gemv_host", "lg_flash_decode_host",
+    "lg_dequant_host", "lg_gemv_host", "lg_flash_decode_host", "lg_prefill_matmul_host",
 ]
 
 _lib = None
@@ -68,6 +68,8 @@ def load() -> C.CDLL:
     L.lg_dequant_host.argtypes = [C.c_int, C.c_void_p, C.c_int, C.c_int, _f32p]; L.lg_dequant_host.restype = C.c_int
     L.lg_gemv_host.argtypes = [C.c_int, C.c_void_p, C.c_int, C.c_int, _f32p, C.c_int, C.c_int, _f32p]
     L.lg_gemv_host.restype = C.c_int
+    L.lg_prefill_matmul_host.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, _f32p, C.c_int, _f32p]
+    L.lg_prefill_matmul_host.restype = C.c_int
     L.lg_flash_decode_host.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                        C.c_int, _f32p]
     L.lg_flash_decode_host.restype = C.c_int
@@ -111,6 +113,24 @@ def gemv(ggml_type: int, raw: np.ndarray, m: int, k: int, x: np.ndarray, kslices
     rc = L.lg_gemv_host(ggml_type, raw.ctypes.data_as(C.c_void_p), m, k, x.reshape(-1), M, kslices, y.reshape(-1))
     if rc:
         raise ValueError(f"lg_gemv_host failed ({rc})")
+    return y
+
+
+def prefill_matmul(ggml_type: int, raw: np.ndarray, m: int, k: int, x: np.ndarray, raw_up: np.ndarray = None) -> np.ndarray:
+    """y[tok] = W x[tok] for up to 256 rows of x at once through the wide tcgen05 matmul (x rounded to f16).
+    With raw_up, raw/raw_up are a gate/up pair and y = gelu_tanh(gate x) * (up x), rounded to f16."""
+    L = load()
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    n = x.shape[0]
+    y = np.empty((n, m), dtype=np.float32)
+    up = None
+    if raw_up is not None:
+        raw_up = np.ascontiguousarray(raw_up, dtype=np.uint8)
+        up = raw_up.ctypes.data_as(C.c_void_p)
+    rc = L.lg_prefill_matmul_host(ggml_type, raw.ctypes.data_as(C.c_void_p), up, m, k, x.reshape(-1), n, y.reshape(-1))
+    if rc:
+        raise ValueError(f"lg_prefill_matmul_host failed ({rc})")
     return y
 
 

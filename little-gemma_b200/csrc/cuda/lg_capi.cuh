@@ -69,6 +69,45 @@ extern "C" int lg_gemv_host(int type, const void *blocks, int m, int k, const fl
     return 0;
 }
 
+// out[tok][m] = W x[tok]  for n <= 256 rows at once through the wide (tcgen05) matmul; x is rounded to f16 first.
+// geglu != 0: `blocks`/`blocks_up` are the gate and up matrices [m x k]; out[tok][m] = gelu(gate . x) * (up . x), rounded to f16.
+extern "C" int lg_prefill_matmul_host(int type, const void *blocks, const void *blocks_up, int m, int k, const float *x, int n,
+                                      float *out) {
+    if (n < 1 || n > LG_PF_MAXN || k % 64 || (type != GGML_TYPE_Q4_0 && type != GGML_TYPE_Q4_K)) return -1;
+    if (type == GGML_TYPE_Q4_K && k % 256) return -1;
+    Engine *e = scratch_engine();
+    struct gguf_tensor t, u;
+    memset(&t, 0, sizeof t);
+    char name[] = "lg_prefill_matmul_host";
+    t.name = name; t.n_dims = 2; t.dims[0] = k; t.dims[1] = m; t.dims[2] = t.dims[3] = 1; t.type = type; t.data = (void *)blocks;
+    u = t; u.data = (void *)blocks_up;
+    const bool geglu = blocks_up != nullptr;
+    WMat W = geglu ? build_wmat(e, {&t, &u}, true) : build_wmat(e, {&t});
+    float *d_x = dalloc<float>((size_t)n * k);
+    __half *d_xh = dalloc<__half>((size_t)LG_PF_MAXN * k);
+    float *d_out = dalloc<float>((size_t)n * W.ldo);
+    __half *d_act = dalloc<__half>((size_t)n * m);
+    LG_CHECK(cudaMemcpyAsync(d_x, x, (size_t)n * k * 4, cudaMemcpyHostToDevice, e->stream));
+    launch_k(e, lg_f32_to_f16_rows, dim3((k + 255) / 256, n), dim3(256), 0, (const float *)d_x, k, d_xh, k, k);
+    LG_CHECK(cudaGetLastError());
+    launch_pf_gemm(e, W, d_xh, LG_PF_MAXN, n, d_out, d_act, m, geglu ? LG_PF_GEGLU : LG_PF_STORE);
+    LG_CHECK(cudaGetLastError());
+    if (geglu) {
+        std::vector<__half> h((size_t)n * m);
+        LG_CHECK(cudaMemcpyAsync(h.data(), d_act, h.size() * 2, cudaMemcpyDeviceToHost, e->stream));
+        check_err(e);
+        for (size_t i = 0; i < h.size(); i++) out[i] = __half2float(h[i]);
+    } else {
+        std::vector<float> h((size_t)n * W.ldo);
+        LG_CHECK(cudaMemcpyAsync(h.data(), d_out, h.size() * 4, cudaMemcpyDeviceToHost, e->stream));
+        check_err(e);
+        for (int tok = 0; tok < n; tok++)
+            for (int r = 0; r < m; r++) out[(size_t)tok * m + r] = h[(size_t)tok * W.ldo + r];
+    }
+    free_wmat(W); cudaFree(d_x); cudaFree(d_xh); cudaFree(d_out); cudaFree(d_act);
+    return 0;
+}
+
 extern "C" int lg_flash_decode_host(const float *q, const float *k, const float *v, int M, int H, int Hkv, int hd,
                                     int seq, int window, int pos, float *out) {
     if (M < 1 || M > LG_MAXM || (hd != 64 && hd != 128 && hd != 256 && hd != 512) || H % Hkv) return -1;

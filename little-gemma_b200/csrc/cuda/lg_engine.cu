@@ -16,6 +16,7 @@
 #include <map>
 #include <string>
 #include "lg_kernels.cuh"
+#include "lg_prefill.cuh"
 #include "lg_host.h"
 #include "lg_b200.h"
 
@@ -254,6 +255,13 @@ template <int R> void gemv_attr_r() {
     gemv_attr<R, 2, LG_FMT_Q4_K, LG_EPI_STORE>(); gemv_attr<R, 2, LG_FMT_Q4_K, LG_EPI_HEAD>();
 }
 // Opt every kernel into large dynamic shared memory once, outside any stream capture.
+template <int NT, int FMT, int EPI> void pf_attr() {
+    LG_CHECK(cudaFuncSetAttribute(lg_pf_gemm_kernel<NT, FMT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pf_smem_bytes<NT, FMT>()));
+}
+template <int NT> void pf_attr_n() {
+    pf_attr<NT, LG_FMT_Q4_0, LG_PF_STORE>(); pf_attr<NT, LG_FMT_Q4_0, LG_PF_GEGLU>();
+    pf_attr<NT, LG_FMT_Q4_K, LG_PF_STORE>(); pf_attr<NT, LG_FMT_Q4_K, LG_PF_GEGLU>();
+}
 void set_kernel_attributes() {
     static bool done = false;
     if (done) return;
@@ -265,6 +273,7 @@ void set_kernel_attributes() {
     LG_CHECK(cudaFuncSetAttribute(lg_attn_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
     LG_CHECK(cudaFuncSetAttribute(lg_attn_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
     LG_CHECK(cudaFuncSetAttribute(lg_attn_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
+    pf_attr_n<64>(); pf_attr_n<128>(); pf_attr_n<256>();
 }
 
 int env_int(const char *name, int fb) { const char *v = getenv(name); return v && v[0] ? atoi(v) : fb; }
@@ -385,6 +394,57 @@ void launch_norm(Engine *e, int M, float *x, int ldx, int n, float eps,
 size_t attn_smem(int nq, int hd) {
     size_t nq16 = (size_t)((nq + 15) & ~15), ldh = hd + 8, S = lg_attn_tile(hd);
     return 2 * nq16 * ldh * 2 + 2 * S * ldh * 2 + nq16 * S * 4 + 2 * nq16 * (S + 8) * 2 + nq16 * 8 + 64;
+}
+
+// ---- the wide (prompt) matmul -----------------------------------------------------------------
+// Tiled-copy descriptor of an f16 activation block [rows][k] (row-major), box = 64 columns x nt rows,
+// 128-byte swizzle: the layout tcgen05.mma reads as a K-major operand.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+CUtensorMap act_tensor_map(const __half *ptr, int k, int rows, int nt) {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        LG_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr));
+        if (!p || qr != cudaDriverEntryPointSuccess) { fprintf(stderr, "lg_b200: the driver has no cuTensorMapEncodeTiled\n"); exit(1); }
+        fn = (EncodeTiledFn)p;
+    }
+    CUtensorMap map;
+    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+    cuuint32_t box[2] = {(cuuint32_t)LG_PF_BK, (cuuint32_t)nt};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { fprintf(stderr, "lg_b200: cuTensorMapEncodeTiled failed (%d) for k=%d rows=%d\n", (int)r, k, rows); exit(1); }
+    return map;
+}
+
+template <int NT, int FMT> void launch_pf_nt(Engine *e, const CUtensorMap &tm, const LgPfGemmArgs &a, int epi, dim3 grid) {
+    const size_t sm = pf_smem_bytes<NT, FMT>();
+    if (epi == LG_PF_GEGLU) launch_k(e, (lg_pf_gemm_kernel<NT, FMT, LG_PF_GEGLU>), grid, dim3(LG_PF_THREADS), sm, tm, a);
+    else launch_k(e, (lg_pf_gemm_kernel<NT, FMT, LG_PF_STORE>), grid, dim3(LG_PF_THREADS), sm, tm, a);
+}
+
+// out[tok][ldo] (f32) = W x X^T for n_tok <= 256 tokens; X is f16 [x_rows >= token tile][W.k], 16-byte aligned.
+// epi == LG_PF_GEGLU: W holds interleaved gate/up rows and act[tok][ld_act] (f16) receives gelu(gate)*up.
+void launch_pf_gemm(Engine *e, const WMat &W, const __half *X, int x_rows, int n_tok, float *out, __half *act, int ld_act, int epi) {
+    if (n_tok < 1 || n_tok > LG_PF_MAXN) { fprintf(stderr, "lg_b200: wide matmul takes 1..%d tokens\n", LG_PF_MAXN); exit(1); }
+    const int nt = n_tok > 128 ? 256 : n_tok > 64 ? 128 : 64;
+    if (x_rows < nt) { fprintf(stderr, "lg_b200: activation block of %d rows is smaller than the token tile %d\n", x_rows, nt); exit(1); }
+    CUtensorMap tm = act_tensor_map(X, W.k, x_rows, nt);
+    LgPfGemmArgs a{};
+    a.wq = W.wq; a.ws = W.ws; a.wd = W.wd; a.nkp = W.nkp; a.n_row_tiles = W.n_row_tiles; a.n_tok = n_tok;
+    a.out = out; a.ldo = W.ldo; a.n_rows = W.ldo; a.act = act; a.ld_act = ld_act; a.err = e->err;
+    dim3 grid((W.n_row_tiles + 7) / 8, 1);
+    const bool k4 = W.fmt == LG_FMT_Q4_K;
+    switch (nt) {
+    case 64:  if (k4) launch_pf_nt<64, LG_FMT_Q4_K>(e, tm, a, epi, grid); else launch_pf_nt<64, LG_FMT_Q4_0>(e, tm, a, epi, grid); break;
+    case 128: if (k4) launch_pf_nt<128, LG_FMT_Q4_K>(e, tm, a, epi, grid); else launch_pf_nt<128, LG_FMT_Q4_0>(e, tm, a, epi, grid); break;
+    default:  if (k4) launch_pf_nt<256, LG_FMT_Q4_K>(e, tm, a, epi, grid); else launch_pf_nt<256, LG_FMT_Q4_0>(e, tm, a, epi, grid); break;
+    }
 }
 
 void launch_attn(Engine *e, LgAttnArgs a, int n_tiles_max) {
