@@ -90,6 +90,9 @@ void *lg_stream(struct model *m);                    /* the cudaStream_t all wor
  * matmuls, 64 norms, 128 q/k/v post-processing, 256 attention, 512 the rest; <= 0 = all weight
  * matmuls); returns the number of launches.  A forward must have run before. */
 int   lg_bench_matmul_pass(struct model *m, int n, int classes);
+/* Enqueue the kernels of one wide prompt block of n <= 256 tokens restricted to kernel classes
+ * (<= 0: the four layer matmuls); returns the number of launches or -1.  Timing utility. */
+int   lg_bench_prefill_pass(struct model *m, int n, int classes);
 void  lg_engine_release(void);                       /* free all device state of the loaded model */
 
 /* Kernel-level entry points (host buffers in, host buffers out) used by the parity tests.

@@ -29,7 +29,7 @@ ABI_SYMBOLS = [
     "model_prefill_reserve", "model_forward_spec", "mtp_draft_device", "mtp_draft_chain_device", "mtp_free_device",
     "lg_forward_spec_n", "lg_set_replay", "lg_rounds_begin", "lg_rounds_enqueue", "lg_rounds_collect",
     "lg_weight_bytes", "lg_round_launches", "lg_last_hidden", "lg_kv_row", "lg_stream", "lg_engine_release",
-    "lg_bench_matmul_pass", "lg_flash_decode_noalloc",
+    "lg_bench_matmul_pass", "lg_bench_prefill_pass", "lg_flash_decode_noalloc",
     "lg_dequant_host", "lg_gemv_host", "lg_flash_decode_host", "lg_prefill_matmul_host",
 ]
 
@@ -86,6 +86,7 @@ def load() -> C.CDLL:
     L.lg_round_launches.argtypes = [C.c_void_p]; L.lg_round_launches.restype = C.c_longlong
     L.lg_stream.argtypes = [C.c_void_p]; L.lg_stream.restype = C.c_void_p
     L.lg_bench_matmul_pass.argtypes = [C.c_void_p, C.c_int, C.c_int]; L.lg_bench_matmul_pass.restype = C.c_int
+    L.lg_bench_prefill_pass.argtypes = [C.c_void_p, C.c_int, C.c_int]; L.lg_bench_prefill_pass.restype = C.c_int
     L.lgs_rounds_host.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _i32p, C.c_int, C.c_void_p, _i32p]
     L.lgs_rounds_host.restype = C.c_int
     _lib = L
@@ -256,6 +257,10 @@ class Session:
     def matmul_pass(self, n: int, classes: int = 0) -> int:
         """Enqueue the weight matmuls of one verify step (classes: 1 qkv, 2 o, 4 gate/up, 8 down, 16 head, 32 PLE)."""
         return int(self.L.lg_bench_matmul_pass(self.model, n, classes))
+
+    def prefill_pass(self, n: int, classes: int = 0) -> int:
+        """Enqueue the kernels of one wide prompt block of n tokens (classes as in matmul_pass; default the matmuls)."""
+        return int(self.L.lg_bench_prefill_pass(self.model, n, classes))
 
     # device-resident rounds, raw
     def rounds_begin(self, first: int, pos: int, n_emitted: int = 1):

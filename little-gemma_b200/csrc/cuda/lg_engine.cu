@@ -68,6 +68,16 @@ struct DraftW {
     std::map<std::string, cudaGraphExec_t> graphs;
 };
 
+// Buffers of the wide prompt pass (blocks of up to LG_PF_MAXN tokens), allocated at its first use.
+struct PrefillBuf {
+    bool ready = false;
+    __half *a_ne = nullptr, *a_attn = nullptr, *a_ff = nullptr;     // f16 matmul inputs [LG_PF_MAXN][k]
+    float *x = nullptr, *qkv = nullptr, *o = nullptr;               // residual rows, projection rows, o/down rows
+    int *toks = nullptr, *pos = nullptr;                            // token ids; pos[g] = position of the g-th group of 8
+    float2 *rope_local = nullptr, *rope_global = nullptr;
+    int ld_attn = 0, ld_ff = 0;
+};
+
 struct Engine {
     const struct model *m = nullptr;
     const struct gguf_context *ctx = nullptr;
@@ -101,6 +111,7 @@ struct Engine {
     long long launches = 0;                   // kernels enqueued by the most recent graph build
     int pdl = 1;                              // programmatic dependent launch (LG_PDL=0 turns it off)
     long long round_launches = 0;
+    PrefillBuf pf;
     int mm_launches = 0;                      // kernels in the captured matmul-only pass             // kernels in one captured round (lg_rounds_enqueue)
 };
 
@@ -747,6 +758,95 @@ void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags, int 
     }
 }
 
+
+// ------------------------------------------------------------------------------------------
+// the wide prompt pass: blocks of up to LG_PF_MAXN tokens, matmuls on tcgen05
+// ------------------------------------------------------------------------------------------
+void prefill_alloc(Engine *e) {
+    PrefillBuf &b = e->pf;
+    if (b.ready) return;
+    const struct config *c = &e->m->cfg;
+    const int ne = c->n_embd, H = c->n_head;
+    int max_attn = 0, max_ff = 0, max_qkv = 0, max_o = 0, max_hd = 0;
+    for (auto &w : e->L) {
+        max_attn = std::max(max_attn, H * w.hd); max_ff = std::max(max_ff, w.nff);
+        max_qkv = std::max(max_qkv, w.qkv.ldo); max_o = std::max(max_o, std::max(w.o.ldo, w.down.ldo));
+        max_hd = std::max(max_hd, w.hd);
+    }
+    b.ld_attn = max_attn; b.ld_ff = max_ff;
+    b.a_ne = dalloc<__half>((size_t)LG_PF_MAXN * ne);
+    b.a_attn = dalloc<__half>((size_t)LG_PF_MAXN * max_attn);
+    b.a_ff = dalloc<__half>((size_t)LG_PF_MAXN * max_ff);
+    b.x = dalloc<float>((size_t)LG_PF_MAXN * ne);
+    b.qkv = dalloc<float>((size_t)LG_PF_MAXN * max_qkv);
+    b.o = dalloc<float>((size_t)LG_PF_MAXN * max_o);
+    b.toks = dalloc<int>(LG_PF_MAXN);
+    b.pos = dalloc<int>(LG_PF_MAXN / LG_MAXM);
+    b.rope_local = dalloc<float2>((size_t)LG_PF_MAXN * max_hd / 2);
+    b.rope_global = dalloc<float2>((size_t)LG_PF_MAXN * max_hd / 2);
+    b.ready = true;
+}
+
+// x += norm(add)*add_w (optional), x *= out_scale; yh = norm(x)*norm_w as f16 rows.  One CTA per token.
+void launch_norm_pf(Engine *e, int n_tok, float *x, int n, float eps, const float *add, int ld_add, const float *add_w, float out_scale,
+                    const float *norm_w, __half *yh) {
+    LgNormArgs a{};
+    a.x = x; a.ldx = n; a.add_src = add; a.n_parts = 1; a.part_stride = 0; a.ld_add = ld_add; a.add_w = add_w; a.out_scale = out_scale;
+    a.norm_w = norm_w; a.n = n; a.eps = eps; a.yh = norm_w ? yh : nullptr; a.ldyh = n;
+    int threads = n >= 2048 ? 1024 : (n >= 512 ? 512 : 256);
+    launch_k(e, lg_norm_kernel, dim3(n_tok), dim3(threads), (size_t)(2 * n + 32) * 4, a);
+}
+
+// One block of n <= LG_PF_MAXN prompt tokens at positions pos0.. (ids in pf.toks, group positions in pf.pos):
+// fills the KV rows of every layer.  The layer matmuls see all n tokens at once; attention walks the block in
+// groups of LG_MAXM query rows with the decode step's kernel, so a group's keys include the rows of the groups
+// before it.  Models with per-layer embeddings take the narrow path instead.
+void enqueue_prefill_block(Engine *e, const struct kvcache *kv, int n, int only = C_ALL) {
+    const struct config *c = &e->m->cfg;
+    const int ne = c->n_embd, H = c->n_head, nl = c->n_layer;
+    PrefillBuf &b = e->pf;
+    if (only & C_MISC) {
+        launch_k(e, lg_embed_rows, dim3(n), dim3(256), 0, e->head.wq, e->head.ws, e->head.wd, e->head.fmt, e->head.nkp, e->head.m,
+                 (const int *)b.toks, sqrtf((float)ne), b.x, ne);
+        launch_k(e, lg_rope_table_kernel, dim3(1), dim3(1024), 0, (const int *)b.pos, n, e->hd_local, c->rope_freq_base_swa, (const float *)nullptr, b.rope_local);
+        launch_k(e, lg_rope_table_kernel, dim3(1), dim3(1024), 0, (const int *)b.pos, n, e->hd_global, c->rope_freq_base, (const float *)e->rope_div, b.rope_global);
+    }
+    if (only & C_NORM) launch_norm_pf(e, n, b.x, ne, c->rms_eps, nullptr, 0, nullptr, 1.0f, e->L[0].attn_norm, b.a_ne);
+    for (int l = 0; l < nl; l++) {
+        LayerW &w = e->L[l];
+        const int hd = w.hd, src = w.src;
+        if (only & C_QKV) launch_pf_gemm(e, w.qkv, b.a_ne, LG_PF_MAXN, n, b.qkv, nullptr, 0, LG_PF_STORE);
+        if (only & C_ATTN)
+            for (int g0 = 0; g0 < n; g0 += LG_MAXM) {
+                const int M = std::min(LG_MAXM, n - g0);
+                LgAttnArgs aa{};
+                aa.qkv = b.qkv + (size_t)g0 * w.qkv.ldo; aa.ld = w.qkv.ldo; aa.q_ready = 0; aa.has_v = w.has_v; aa.owns_kv = w.owns_kv;
+                aa.q_norm = w.q_norm; aa.k_norm = w.k_norm; aa.eps = c->rms_eps;
+                aa.rope = (w.local ? b.rope_local : b.rope_global) + (size_t)g0 * (hd / 2);
+                aa.kc = (__half *)kv->k[src]; aa.vc = (__half *)kv->v[src]; aa.seq = kv->seq[src]; aa.kv_dim = kv->kv_dim[src];
+                aa.H = H; aa.Hkv = w.nkv; aa.hd = hd; aa.M = M;
+                aa.window = w.local ? c->sliding_window : 0; aa.qpos_off = 0; aa.win_shrink = 0; aa.pos = b.pos + g0 / LG_MAXM;
+                aa.n_slots = e->part_slots; aa.part = e->part; aa.part_ml = e->part_ml; aa.out_f32 = nullptr;
+                aa.out_h = b.a_attn + (size_t)g0 * (H * hd); aa.ld_h = H * hd;
+                launch_attn(e, aa, tiles_for(aa.window, kv->max_seq, M, hd));
+            }
+        if (only & C_O) launch_pf_gemm(e, w.o, b.a_attn, LG_PF_MAXN, n, b.o, nullptr, 0, LG_PF_STORE);
+        if (only & C_NORM) launch_norm_pf(e, n, b.x, ne, c->rms_eps, b.o, w.o.ldo, w.post_attn, 1.0f, w.ffn_norm, b.a_ne);
+        if (only & C_GATEUP) launch_pf_gemm(e, w.gateup, b.a_ne, LG_PF_MAXN, n, nullptr, b.a_ff, w.nff, LG_PF_GEGLU);
+        if (only & C_DOWN) launch_pf_gemm(e, w.down, b.a_ff, LG_PF_MAXN, n, b.o, nullptr, 0, LG_PF_STORE);
+        const float *next_w = l == nl - 1 ? nullptr : e->L[l + 1].attn_norm;
+        if (only & C_NORM) launch_norm_pf(e, n, b.x, ne, c->rms_eps, b.o, w.down.ldo, w.post_ffw, w.out_scale, next_w, b.a_ne);
+    }
+}
+
+// Whether the wide pass can take this model (LG_PREFILL_WIDE=0 keeps every prompt on the narrow path).
+bool prefill_wide_ok(const Engine *e) {
+    static const int on = env_int("LG_PREFILL_WIDE", 1);
+    if (!on || e->has_ple) return false;
+    for (auto &w : e->L) if (w.o.k != e->m->cfg.n_head * w.hd || w.down.k != w.nff) return false;
+    return true;
+}
+
 // Run (capturing on first use) the forward graph for (M, flags).
 void run_forward(Engine *e, const struct kvcache *kv, int M, int flags) {
     bind_kv(e, kv);
@@ -1036,7 +1136,24 @@ int model_forward_next(struct model *m, struct kvcache *kv, int token, int pos) 
 
 void model_prefill(struct model *m, struct kvcache *kv, const int *tokens, int n, int pos0) {
     Engine *e = engine_for(m);
-    for (int i = 0; i < n; i += LG_MAXM) {
+    int i = 0;
+    if (prefill_wide_ok(e) && n >= 4 * LG_MAXM) {
+        // whole blocks of up to LG_PF_MAXN tokens (a multiple of the attention group) on the wide pass
+        bind_kv(e, kv);
+        prefill_alloc(e);
+        int gpos[LG_PF_MAXN / LG_MAXM];
+        while (n - i >= 4 * LG_MAXM) {
+            const int b = std::min(LG_PF_MAXN, (n - i) / LG_MAXM * LG_MAXM);
+            for (int g = 0; g < LG_PF_MAXN / LG_MAXM; g++) gpos[g] = pos0 + i + g * LG_MAXM;
+            LG_CHECK(cudaMemcpyAsync(e->pf.toks, tokens + i, sizeof(int) * b, cudaMemcpyHostToDevice, e->stream));
+            LG_CHECK(cudaMemcpyAsync(e->pf.pos, gpos, sizeof gpos, cudaMemcpyHostToDevice, e->stream));
+            enqueue_prefill_block(e, kv, b);
+            LG_CHECK(cudaStreamSynchronize(e->stream));  // gpos and the caller's ids are read by the copies above
+            i += b;
+        }
+        check_err(e);
+    }
+    for (; i < n; i += LG_MAXM) {
         int b = n - i < LG_MAXM ? n - i : LG_MAXM;
         upload_round(e, tokens + i, b, pos0 + i);
         run_forward(e, kv, b, 0);
@@ -1234,6 +1351,19 @@ int lg_bench_matmul_pass(struct model *m, int n, int classes) {
     }
     LG_CHECK(cudaGraphLaunch(it->second, e->stream));
     return e->mm_launches;
+}
+
+// Enqueue (no synchronisation) the kernels of one wide prompt block of n tokens, restricted to `classes`
+// (<= 0: the four layer matmuls).  Timing utility: whatever ids / activations the block buffers hold are used,
+// and with the attention class the KV rows at the buffered positions are overwritten.
+int lg_bench_prefill_pass(struct model *m, int n, int classes) {
+    Engine *e = engine_for(m);
+    if (n < 1 || n > LG_PF_MAXN || !e->kv_bound || !prefill_wide_ok(e)) return -1;
+    prefill_alloc(e);
+    if (classes <= 0) classes = C_QKV | C_O | C_GATEUP | C_DOWN;
+    long long before = e->launches;
+    enqueue_prefill_block(e, e->kv_bound, n, classes);
+    return (int)(e->launches - before);
 }
 
 void *lg_stream(struct model *m) { return (void *)engine_for(m)->stream; }

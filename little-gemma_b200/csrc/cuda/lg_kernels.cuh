@@ -283,6 +283,7 @@ struct LgNormArgs {
     LgPanel panel; int want_panel;
     float *y; int ldy;                   // optional f32 copy of the normed row
     int n; float eps;
+    __half *yh; int ldyh;                // optional f16 copy (input of the wide prompt matmul; single-CTA kernel only)
 };
 
 struct LgGemvArgs {
@@ -658,7 +659,7 @@ __global__ void lg_norm_kernel(LgNormArgs a) {
     } else {
         for (int i = threadIdx.x; i < a.n; i += blockDim.x) { float v = x[i]; row[i] = v; ss2 += v * v; }
     }
-    if (!a.norm_w && !a.want_panel && !a.y) return;
+    if (!a.norm_w && !a.want_panel && !a.y && !a.yh) return;
     float s = 1.0f;
     if (a.norm_w) {
         ss2 = block_sum(ss2, red);
@@ -670,6 +671,7 @@ __global__ void lg_norm_kernel(LgNormArgs a) {
         int i = sb * 32 + lane;
         float yv = a.norm_w ? __fmul_rn(__fmul_rn(row[i], s), a.norm_w[i]) : row[i];   // no norm_w: the row itself
         if (a.y) a.y[(size_t)tok * a.ldy + i] = yv;
+        if (a.yh) a.yh[(size_t)tok * a.ldyh + i] = __float2half_rn(yv);
         if (a.want_panel) quant_group_store(yv, lane, tok, sb, a.panel);
     }
 }
@@ -804,6 +806,7 @@ struct LgAttnArgs {
     float2 *part_ml;           // [n_slots][M][H] (max, sum) of each (query, tile)
     int *tickets;              // [Hkv], zero between launches
     LgPanel out; float *out_f32;   // merged output: panel of [M][H*hd] and/or f32 [M][H][hd]
+    __half *out_h; int ld_h;       // and/or f16 rows [M][ld_h] (input of the wide prompt matmul)
 };
 
 #define LG_ATTN_THREADS 256
@@ -1144,6 +1147,7 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) 
         const int tok = qi / gqa, hq = kvh * gqa + qi % gqa;
         const float y = ybuf[(size_t)qi * HD + d];
         if (a.out_f32) a.out_f32[((size_t)tok * a.H + hq) * HD + d] = y;
+        if (a.out_h) a.out_h[(size_t)tok * a.ld_h + hq * HD + d] = __float2half_rn(y);
         if (a.out.q) quant_group_store(y, lane, tok, (hq * HD + d) >> 5, a.out);
     }
     if (threadIdx.x == 0) a.tickets[kvh] = 0;

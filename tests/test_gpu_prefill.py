@@ -83,3 +83,43 @@ def test_prefill_matmul_geglu_epilogue(lg, port_built, wtype):
     gelu = 0.5 * g * (1.0 + np.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3)))
     want = gelu * u
     assert np.abs(got - want).max() / np.abs(want).max() < 5e-3      # f16 output + f16 weights
+
+
+# ---- the wide prompt pass through the model API ------------------------------------------------
+
+@pytest.mark.parametrize("name,n", [("mid", 300), ("mid_k", 300), ("mid", 37)])
+def test_wide_prefill_matches_oracle(lg, port_built, name, n):
+    """model_prefill of n tokens (blocks of up to 256 on the tcgen05 path + a narrow tail): cache rows and the
+    logits of the following step against the CPU oracle."""
+    from oracle.pyref import PortOracle
+    s = synth_module()
+    tp, _ = model_files(name)
+    o = PortOracle(tp, None, 512, True, 4)
+    toks = s.prompt_ids(n + 4, o.n_vocab, seed=21)
+    o.prefill(toks[:n], 0)
+    with lg.Session(tp, None, 512) as g:
+        g.prefill(toks[:n], 0)
+        kv_dim = 2 * 256
+        for layer in range(o.n_layer if hasattr(o, "n_layer") else 3):
+            for pos in sorted({max(0, n - 60), n - 33, n - 9, n - 1}):
+                ko, vo = o.kv_row(layer, pos, kv_dim)
+                kg, vg = g.kv_row(layer, pos, kv_dim)
+                assert np.abs(kg - ko).max() < 1e-2 * max(1.0, np.abs(ko).max()), (layer, pos)
+                assert np.abs(vg - vo).max() < 1e-2 * max(1.0, np.abs(vo).max()), (layer, pos)
+        for i in range(n, n + 4):
+            want, got = o.forward(int(toks[i]), i), g.forward(int(toks[i]), i)
+            assert np.abs(got - want).max() / (want.max() - want.min()) <= 1e-2
+    o.close()
+
+
+def test_wide_prefill_then_mtp_equals_plain(lg):
+    """After a wide prompt pass the speculative stream is still byte-identical to plain greedy decoding."""
+    s = synth_module()
+    tp, _ = model_files("mid")
+    with lg.Session(tp, None, 1024, mtp_n=4) as g:
+        prompt = s.prompt_ids(200, g.n_vocab, seed=22)
+        plain, _ = g.generate_device(prompt, 96, 0)
+    with lg.Session(tp, None, 1024, mtp_n=4) as g:
+        rp = s.replay_drafts(plain, g.n_vocab, 0.7)
+        mtp, _ = g.generate_device(prompt, 96, 2, rp)
+    assert np.array_equal(plain[:96], mtp[:96])
