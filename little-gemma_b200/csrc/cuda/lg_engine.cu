@@ -75,6 +75,7 @@ struct PrefillBuf {
     float *x = nullptr, *qkv = nullptr, *o = nullptr;               // residual rows, projection rows, o/down rows
     int *toks = nullptr, *pos = nullptr;                            // token ids; pos[g] = position of the g-th group of 8
     float2 *rope_local = nullptr, *rope_global = nullptr;
+    __half *q_hi = nullptr, *q_lo = nullptr;                        // normed + rotated queries [LG_PF_MAXN][H][hd], f16 hi + lo
     int ld_attn = 0, ld_ff = 0;
 };
 
@@ -285,6 +286,9 @@ void set_kernel_attributes() {
     LG_CHECK(cudaFuncSetAttribute(lg_attn_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
     LG_CHECK(cudaFuncSetAttribute(lg_attn_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
     pf_attr_n<64>(); pf_attr_n<128>(); pf_attr_n<256>();
+    LG_CHECK(cudaFuncSetAttribute(lg_pf_attn_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pf_attn_smem<64>()));
+    LG_CHECK(cudaFuncSetAttribute(lg_pf_attn_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pf_attn_smem<128>()));
+    LG_CHECK(cudaFuncSetAttribute(lg_pf_attn_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pf_attn_smem<256>()));
 }
 
 int env_int(const char *name, int fb) { const char *v = getenv(name); return v && v[0] ? atoi(v) : fb; }
@@ -441,7 +445,16 @@ template <int NT, int FMT> void launch_pf_nt(Engine *e, const CUtensorMap &tm, c
 
 // out[tok][ldo] (f32) = W x X^T for n_tok <= 256 tokens; X is f16 [x_rows >= token tile][W.k], 16-byte aligned.
 // epi == LG_PF_GEGLU: W holds interleaved gate/up rows and act[tok][ld_act] (f16) receives gelu(gate)*up.
-void launch_pf_gemm(Engine *e, const WMat &W, const __half *X, int x_rows, int n_tok, float *out, __half *act, int ld_act, int epi) {
+// k slices of the wide matmul for a matrix with few rows (each slice writes its own plane of `out`)
+int pf_kslices(const Engine *e, const WMat &W, int max_ks) {
+    const int ctas = (W.n_row_tiles + 7) / 8;
+    int ks = 1;
+    while (ks < max_ks && ctas * ks * 2 <= e->sm_count && W.nkp / (ks * 2) >= 8) ks *= 2;
+    return ks;
+}
+
+void launch_pf_gemm(Engine *e, const WMat &W, const __half *X, int x_rows, int n_tok, float *out, __half *act, int ld_act, int epi,
+                    int ks = 1) {
     if (n_tok < 1 || n_tok > LG_PF_MAXN) { fprintf(stderr, "lg_b200: wide matmul takes 1..%d tokens\n", LG_PF_MAXN); exit(1); }
     const int nt = n_tok > 128 ? 256 : n_tok > 64 ? 128 : 64;
     if (x_rows < nt) { fprintf(stderr, "lg_b200: activation block of %d rows is smaller than the token tile %d\n", x_rows, nt); exit(1); }
@@ -449,7 +462,8 @@ void launch_pf_gemm(Engine *e, const WMat &W, const __half *X, int x_rows, int n
     LgPfGemmArgs a{};
     a.wq = W.wq; a.ws = W.ws; a.wd = W.wd; a.nkp = W.nkp; a.n_row_tiles = W.n_row_tiles; a.n_tok = n_tok;
     a.out = out; a.ldo = W.ldo; a.n_rows = W.ldo; a.act = act; a.ld_act = ld_act; a.err = e->err;
-    dim3 grid((W.n_row_tiles + 7) / 8, 1);
+    a.part_stride = (size_t)LG_PF_MAXN * W.ldo;
+    dim3 grid((W.n_row_tiles + 7) / 8, 1, epi == LG_PF_GEGLU ? 1 : ks);
     const bool k4 = W.fmt == LG_FMT_Q4_K;
     switch (nt) {
     case 64:  if (k4) launch_pf_nt<64, LG_FMT_Q4_K>(e, tm, a, epi, grid); else launch_pf_nt<64, LG_FMT_Q4_0>(e, tm, a, epi, grid); break;
@@ -762,6 +776,7 @@ void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags, int 
 // ------------------------------------------------------------------------------------------
 // the wide prompt pass: blocks of up to LG_PF_MAXN tokens, matmuls on tcgen05
 // ------------------------------------------------------------------------------------------
+constexpr int PF_MAX_KS = 4;
 void prefill_alloc(Engine *e) {
     PrefillBuf &b = e->pf;
     if (b.ready) return;
@@ -778,20 +793,22 @@ void prefill_alloc(Engine *e) {
     b.a_attn = dalloc<__half>((size_t)LG_PF_MAXN * max_attn);
     b.a_ff = dalloc<__half>((size_t)LG_PF_MAXN * max_ff);
     b.x = dalloc<float>((size_t)LG_PF_MAXN * ne);
-    b.qkv = dalloc<float>((size_t)LG_PF_MAXN * max_qkv);
-    b.o = dalloc<float>((size_t)LG_PF_MAXN * max_o);
+    b.qkv = dalloc<float>((size_t)PF_MAX_KS * LG_PF_MAXN * max_qkv);
+    b.o = dalloc<float>((size_t)PF_MAX_KS * LG_PF_MAXN * max_o);
     b.toks = dalloc<int>(LG_PF_MAXN);
     b.pos = dalloc<int>(LG_PF_MAXN / LG_MAXM);
     b.rope_local = dalloc<float2>((size_t)LG_PF_MAXN * max_hd / 2);
     b.rope_global = dalloc<float2>((size_t)LG_PF_MAXN * max_hd / 2);
+    b.q_hi = dalloc<__half>((size_t)LG_PF_MAXN * max_attn);
+    b.q_lo = dalloc<__half>((size_t)LG_PF_MAXN * max_attn);
     b.ready = true;
 }
 
 // x += norm(add)*add_w (optional), x *= out_scale; yh = norm(x)*norm_w as f16 rows.  One CTA per token.
-void launch_norm_pf(Engine *e, int n_tok, float *x, int n, float eps, const float *add, int ld_add, const float *add_w, float out_scale,
-                    const float *norm_w, __half *yh) {
+void launch_norm_pf(Engine *e, int n_tok, float *x, int n, float eps, const float *add, int n_parts, int ld_add, const float *add_w,
+                    float out_scale, const float *norm_w, __half *yh) {
     LgNormArgs a{};
-    a.x = x; a.ldx = n; a.add_src = add; a.n_parts = 1; a.part_stride = 0; a.ld_add = ld_add; a.add_w = add_w; a.out_scale = out_scale;
+    a.x = x; a.ldx = n; a.add_src = add; a.n_parts = n_parts; a.part_stride = (size_t)LG_PF_MAXN * ld_add; a.ld_add = ld_add; a.add_w = add_w; a.out_scale = out_scale;
     a.norm_w = norm_w; a.n = n; a.eps = eps; a.yh = norm_w ? yh : nullptr; a.ldyh = n;
     int threads = n >= 2048 ? 1024 : (n >= 512 ? 512 : 256);
     launch_k(e, lg_norm_kernel, dim3(n_tok), dim3(threads), (size_t)(2 * n + 32) * 4, a);
@@ -811,12 +828,37 @@ void enqueue_prefill_block(Engine *e, const struct kvcache *kv, int n, int only 
         launch_k(e, lg_rope_table_kernel, dim3(1), dim3(1024), 0, (const int *)b.pos, n, e->hd_local, c->rope_freq_base_swa, (const float *)nullptr, b.rope_local);
         launch_k(e, lg_rope_table_kernel, dim3(1), dim3(1024), 0, (const int *)b.pos, n, e->hd_global, c->rope_freq_base, (const float *)e->rope_div, b.rope_global);
     }
-    if (only & C_NORM) launch_norm_pf(e, n, b.x, ne, c->rms_eps, nullptr, 0, nullptr, 1.0f, e->L[0].attn_norm, b.a_ne);
+    if (only & C_NORM) launch_norm_pf(e, n, b.x, ne, c->rms_eps, nullptr, 0, 0, nullptr, 1.0f, e->L[0].attn_norm, b.a_ne);
     for (int l = 0; l < nl; l++) {
         LayerW &w = e->L[l];
         const int hd = w.hd, src = w.src;
-        if (only & C_QKV) launch_pf_gemm(e, w.qkv, b.a_ne, LG_PF_MAXN, n, b.qkv, nullptr, 0, LG_PF_STORE);
-        if (only & C_ATTN)
+        const int gqa = H / w.nkv;
+        static const int block_attn = env_int("LG_PREFILL_BLOCK_ATTN", 1);
+        const bool whole = block_attn && (hd == 64 || hd == 128 || hd == 256) && LG_PFA_Q % gqa == 0;
+        const int ks_q = whole ? pf_kslices(e, w.qkv, 2) : 1, ks_o = pf_kslices(e, w.o, PF_MAX_KS), ks_d = pf_kslices(e, w.down, PF_MAX_KS);
+        if (only & C_QKV) launch_pf_gemm(e, w.qkv, b.a_ne, LG_PF_MAXN, n, b.qkv, nullptr, 0, LG_PF_STORE, ks_q);
+        if ((only & C_ATTN) && whole) {
+            // the whole block at once: rows to the cache + f16 queries, then the tiled online-softmax kernel
+            LgPfPrepArgs pa{};
+            pa.qkv = b.qkv; pa.ld = w.qkv.ldo; pa.n_parts = ks_q; pa.part_stride = (size_t)LG_PF_MAXN * w.qkv.ldo; pa.has_v = w.has_v; pa.owns_kv = w.owns_kv; pa.q_norm = w.q_norm; pa.k_norm = w.k_norm;
+            pa.eps = c->rms_eps; pa.rope = w.local ? b.rope_local : b.rope_global;
+            pa.kc = (__half *)kv->k[src]; pa.vc = (__half *)kv->v[src]; pa.seq = kv->seq[src]; pa.kv_dim = kv->kv_dim[src];
+            pa.H = H; pa.Hkv = w.nkv; pa.pos = b.pos; pa.q_hi = b.q_hi; pa.q_lo = b.q_lo;
+            LgPfAttnArgs fa{};
+            fa.q_hi = b.q_hi; fa.q_lo = b.q_lo; fa.kc = pa.kc; fa.vc = pa.vc; fa.seq = pa.seq; fa.kv_dim = pa.kv_dim;
+            fa.H = H; fa.Hkv = w.nkv; fa.n = n; fa.window = w.local ? c->sliding_window : 0; fa.pos = b.pos;
+            fa.out = b.a_attn; fa.ld_out = H * hd;
+            const int qb = LG_PFA_Q / gqa;
+            dim3 grid(w.nkv, (n + qb - 1) / qb);
+            switch (hd) {
+            case 64:  launch_k(e, lg_pf_qkv_prep_kernel<64>, dim3(n), dim3(256), 0, pa);
+                      launch_k(e, lg_pf_attn_kernel<64>, grid, dim3(256), pf_attn_smem<64>(), fa); break;
+            case 128: launch_k(e, lg_pf_qkv_prep_kernel<128>, dim3(n), dim3(256), 0, pa);
+                      launch_k(e, lg_pf_attn_kernel<128>, grid, dim3(256), pf_attn_smem<128>(), fa); break;
+            default:  launch_k(e, lg_pf_qkv_prep_kernel<256>, dim3(n), dim3(256), 0, pa);
+                      launch_k(e, lg_pf_attn_kernel<256>, grid, dim3(256), pf_attn_smem<256>(), fa); break;
+            }
+        } else if (only & C_ATTN)
             for (int g0 = 0; g0 < n; g0 += LG_MAXM) {
                 const int M = std::min(LG_MAXM, n - g0);
                 LgAttnArgs aa{};
@@ -830,12 +872,12 @@ void enqueue_prefill_block(Engine *e, const struct kvcache *kv, int n, int only 
                 aa.out_h = b.a_attn + (size_t)g0 * (H * hd); aa.ld_h = H * hd;
                 launch_attn(e, aa, tiles_for(aa.window, kv->max_seq, M, hd));
             }
-        if (only & C_O) launch_pf_gemm(e, w.o, b.a_attn, LG_PF_MAXN, n, b.o, nullptr, 0, LG_PF_STORE);
-        if (only & C_NORM) launch_norm_pf(e, n, b.x, ne, c->rms_eps, b.o, w.o.ldo, w.post_attn, 1.0f, w.ffn_norm, b.a_ne);
+        if (only & C_O) launch_pf_gemm(e, w.o, b.a_attn, LG_PF_MAXN, n, b.o, nullptr, 0, LG_PF_STORE, ks_o);
+        if (only & C_NORM) launch_norm_pf(e, n, b.x, ne, c->rms_eps, b.o, ks_o, w.o.ldo, w.post_attn, 1.0f, w.ffn_norm, b.a_ne);
         if (only & C_GATEUP) launch_pf_gemm(e, w.gateup, b.a_ne, LG_PF_MAXN, n, nullptr, b.a_ff, w.nff, LG_PF_GEGLU);
-        if (only & C_DOWN) launch_pf_gemm(e, w.down, b.a_ff, LG_PF_MAXN, n, b.o, nullptr, 0, LG_PF_STORE);
+        if (only & C_DOWN) launch_pf_gemm(e, w.down, b.a_ff, LG_PF_MAXN, n, b.o, nullptr, 0, LG_PF_STORE, ks_d);
         const float *next_w = l == nl - 1 ? nullptr : e->L[l + 1].attn_norm;
-        if (only & C_NORM) launch_norm_pf(e, n, b.x, ne, c->rms_eps, b.o, w.down.ldo, w.post_ffw, w.out_scale, next_w, b.a_ne);
+        if (only & C_NORM) launch_norm_pf(e, n, b.x, ne, c->rms_eps, b.o, ks_d, w.down.ldo, w.post_ffw, w.out_scale, next_w, b.a_ne);
     }
 }
 

@@ -9,14 +9,17 @@
 //
 // One CTA owns 128 weight rows (8 row tiles = the 128 TMEM lanes) x NT tokens (TMEM columns) and
 // walks k in blocks of 64 (one tile position = one 128-byte swizzle row of f16):
-//   warp 4 (one thread)  streams the raw q4 tiles + scales of two k blocks per stage with bulk copies;
-//   warp 5 (one thread)  loads the X block [NT tokens x 64] with a tiled TMA copy (128-byte swizzle);
-//   warps 0-3            expand a raw k block to the f16 A operand [128 rows x 64] in the same
-//                        swizzled K-major layout, then fence it to the async proxy;
-//   warp 6 (one thread)  issues four tcgen05.mma (M=128, N=NT, K=16) per k block and commits the
+//   warp 8 (one thread)  streams the raw q4 tiles + scales of two k blocks per stage with bulk copies;
+//   warp 9 (one thread)  loads the X block [NT tokens x 64] with a tiled TMA copy (128-byte swizzle);
+//   warps 0-7            expand a raw k block to the f16 A operand [128 rows x 64] (one row tile per
+//                        warp) in the same swizzled K-major layout, then fence it to the async proxy;
+//   warp 10 (one thread) issues four tcgen05.mma (M=128, N=NT, K=16) per k block and commits the
 //                        stage back to the producers; after the last block it commits the accumulator;
-//   warps 0-3            read the accumulator with tcgen05.ld and store f32 rows, or apply GeGLU on
-//                        interleaved gate/up rows and store the f16 input of the down projection.
+//   warps 0-7            read the accumulator with tcgen05.ld (lane quarter = warp % 4, column half =
+//                        warp / 4) and store f32 rows, or apply GeGLU on interleaved gate/up rows and
+//                        store the f16 input of the down projection.
+// blockIdx.z cuts k into slices whose partial sums go to separate planes of `out` (matrices with
+// few rows would otherwise fill a fraction of the SMs); the consumer adds the planes.
 // Every mbarrier wait is bounded; a timeout raises LG_ERR_MBAR_TIMEOUT, the CTA stops waiting,
 // drains its own copies, frees its tensor memory and returns.
 #pragma once
@@ -27,7 +30,8 @@
 #define LG_PF_BK 64
 #define LG_PF_STAGES 4          // A / B operand stages
 #define LG_PF_RAW_STAGES 3      // raw q4 stages of two k blocks each
-#define LG_PF_THREADS 224
+#define LG_PF_DQ_WARPS 8
+#define LG_PF_THREADS ((LG_PF_DQ_WARPS + 3) * 32)
 #define LG_PF_MAXN 256
 
 enum { LG_PF_STORE = 0, LG_PF_GEGLU = 1 };
@@ -36,7 +40,8 @@ struct LgPfGemmArgs {
     const uint4 *wq; const uint2 *ws; const uint2 *wd;
     int nkp, n_row_tiles;
     int n_tok;                  // valid tokens of the block (columns beyond are computed and dropped)
-    float *out; int ldo;        // STORE: out[tok][ldo]
+    float *out; int ldo;        // STORE: out[slice][tok][ldo], slice = blockIdx.z
+    size_t part_stride;         // floats between the planes of two k slices
     int n_rows;                 // rows >= n_rows are padding and are not stored
     __half *act; int ld_act;    // GEGLU: act[tok][ld_act], element j = gelu(gate_j) * up_j
     int *err;
@@ -109,15 +114,17 @@ __global__ void __launch_bounds__(LG_PF_THREADS) lg_pf_gemm_kernel(const __grid_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rt0 = blockIdx.x * 8, tok0 = blockIdx.y * NT;
-    const int nkb = a.nkp, n_raw = (nkb + 1) >> 1;
+    const int kb_lo = (int)((long long)a.nkp * blockIdx.z / gridDim.z), kb_hi = (int)((long long)a.nkp * (blockIdx.z + 1) / gridDim.z);
+    const int nkb = kb_hi - kb_lo, n_raw = (nkb + 1) >> 1;     // this CTA's k blocks: kb_lo + [0, nkb)
+    constexpr int DQT = LG_PF_DQ_WARPS * 32;
 
     pdl_launch();
     if (threadIdx.x == 0) {
-        for (int i = 0; i < RS; i++) { mbar_init(raw_full + i, 1); mbar_init(raw_empty + i, 128); }
-        for (int i = 0; i < ST; i++) { mbar_init(a_full + i, 128); mbar_init(b_full + i, 1); mbar_init(empty + i, 1); }
+        for (int i = 0; i < RS; i++) { mbar_init(raw_full + i, 1); mbar_init(raw_empty + i, DQT); }
+        for (int i = 0; i < ST; i++) { mbar_init(a_full + i, DQT); mbar_init(b_full + i, 1); mbar_init(empty + i, 1); }
         mbar_init(acc_full, 1);
     }
-    if (warp == 6) {                         // tensor memory: NT f32 columns x 128 lanes
+    if (warp == LG_PF_DQ_WARPS + 2) {        // tensor memory: NT f32 columns x 128 lanes
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(tmem_slot)), "r"(NT) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -126,7 +133,7 @@ __global__ void __launch_bounds__(LG_PF_THREADS) lg_pf_gemm_kernel(const __grid_
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == 4) {
+    if (warp == LG_PF_DQ_WARPS) {
         // ---------------- raw weight producer ----------------
         if (lane == 0) {
             bool ok = true;
@@ -140,7 +147,7 @@ __global__ void __launch_bounds__(LG_PF_THREADS) lg_pf_gemm_kernel(const __grid_
                 #pragma unroll
                 for (int ti = 0; ti < 8; ti++) {
                     const int rt = min(rt0 + ti, a.n_row_tiles - 1);
-                    const size_t tile = (size_t)rt * a.nkp + 2 * r;
+                    const size_t tile = (size_t)rt * a.nkp + kb_lo + 2 * r;
                     bulk_g2s(st + ti * 1024, a.wq + tile * 32, np * 512, raw_full + rs);
                     bulk_g2s(st + RAW_SC + ti * 128, a.ws + tile * 8, np * 64, raw_full + rs);
                     if (FMT == LG_FMT_Q4_K) bulk_g2s(st + RAW_DD + ti * 128, a.wd + tile * 8, np * 64, raw_full + rs);
@@ -150,7 +157,7 @@ __global__ void __launch_bounds__(LG_PF_THREADS) lg_pf_gemm_kernel(const __grid_
             if (!ok)      // drain: the copies already issued must land before the CTA's shared memory is released
                 for (int r = max(0, issued - RS); r < issued; r++) mbar_wait(raw_full + r % RS, (r / RS) & 1);
         }
-    } else if (warp == 5) {
+    } else if (warp == LG_PF_DQ_WARPS + 1) {
         // ---------------- activation producer ----------------
         if (lane == 0) {
             pdl_wait();
@@ -160,13 +167,13 @@ __global__ void __launch_bounds__(LG_PF_THREADS) lg_pf_gemm_kernel(const __grid_
                 const int s = kb % ST;
                 if (kb >= ST && !mbar_wait(empty + s, ((kb / ST) & 1) ^ 1)) { atomicOr(a.err, LG_ERR_MBAR_TIMEOUT); ok = false; break; }
                 mbar_expect_tx(b_full + s, B_BYTES);
-                tma_load_2d(sB + s * B_BYTES, &tmx, kb * LG_PF_BK, tok0, b_full + s);
+                tma_load_2d(sB + s * B_BYTES, &tmx, (kb_lo + kb) * LG_PF_BK, tok0, b_full + s);
                 issued = kb + 1;
             }
             if (!ok)
                 for (int kb = max(0, issued - ST); kb < issued; kb++) mbar_wait(b_full + kb % ST, (kb / ST) & 1);
         }
-    } else if (warp == 6) {
+    } else if (warp == LG_PF_DQ_WARPS + 2) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(LG_PF_BM >> 4) << 24);
@@ -184,7 +191,7 @@ __global__ void __launch_bounds__(LG_PF_THREADS) lg_pf_gemm_kernel(const __grid_
             umma_commit(acc_full);                   // arrives when every MMA above has completed
         }
     } else {
-        // ---------------- expand q4 -> f16 A operand (warps 0-3), then the epilogue ----------------
+        // ---------------- expand q4 -> f16 A operand (one row tile per warp), then the epilogue ----------------
         const int g = lane >> 2, t = lane & 3;
         bool ok = true;
         for (int kb = 0; kb < nkb; kb++) {
@@ -194,9 +201,8 @@ __global__ void __launch_bounds__(LG_PF_THREADS) lg_pf_gemm_kernel(const __grid_
             if (!ok) break;
             const unsigned char *raw = sRaw + rs * RAW;
             unsigned char *dstA = sA + s * A_BYTES;
-            #pragma unroll
-            for (int q = 0; q < 2; q++) {
-                const int ti = warp * 2 + q;                                         // row tile of the CTA's 8
+            {
+                const int ti = warp;                                                 // row tile of the CTA's 8
                 const uint4 w = *(const uint4 *)(raw + ti * 1024 + half * 512 + lane * 16);
                 const uint2 sc = *(const uint2 *)(raw + RAW_SC + ti * 128 + half * 64 + g * 8);
                 uint2 dd = make_uint2(0, 0);
@@ -236,23 +242,25 @@ __global__ void __launch_bounds__(LG_PF_THREADS) lg_pf_gemm_kernel(const __grid_
         }
         if (!ok && lane == 0) atomicOr(a.err, LG_ERR_MBAR_TIMEOUT);
 
-        // ---------------- epilogue: lane l of warp w holds accumulator row 32w + l ----------------
+        // ---------------- epilogue: lane l of warp w holds accumulator row 32 (w % 4) + l ----------------
         if (ok) ok = mbar_wait(acc_full, 0);
         if (!ok && lane == 0) atomicOr(a.err, LG_ERR_MBAR_TIMEOUT);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
-            const int lrow = warp * 32 + lane;                          // row within the CTA's 128
+            const int lq = warp & 3, ch = warp >> 2;                     // TMEM lane quarter, column half
+            const int lrow = lq * 32 + lane;                            // row within the CTA's 128
             const int rt = rt0 + (lrow >> 4);
-            for (int c0 = 0; c0 < NT; c0 += 32) {
+            float *outp = a.out + (size_t)blockIdx.z * a.part_stride;
+            for (int c0 = ch * (NT / 2); c0 < (ch + 1) * (NT / 2); c0 += 32) {
                 if (tok0 + c0 >= a.n_tok) break;                          // uniform per CTA
                 uint32_t v[32];
-                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + c0, v);
+                tmem_ld32(tmem + ((uint32_t)(lq * 32) << 16) + c0, v);
                 if (EPI == LG_PF_STORE) {
                     const int row = rt0 * 16 + lrow;
                     if (rt < a.n_row_tiles && row < a.n_rows) {
                         #pragma unroll
                         for (int j = 0; j < 32; j++)
-                            if (tok0 + c0 + j < a.n_tok) a.out[(size_t)(tok0 + c0 + j) * a.ldo + row] = __uint_as_float(v[j]);
+                            if (tok0 + c0 + j < a.n_tok) outp[(size_t)(tok0 + c0 + j) * a.ldo + row] = __uint_as_float(v[j]);
                     }
                 } else {
                     // tile rows 0-7 are gate rows, rows 8-15 the matching up rows: lane l pairs with lane l+8
@@ -272,7 +280,7 @@ __global__ void __launch_bounds__(LG_PF_THREADS) lg_pf_gemm_kernel(const __grid_
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
     __syncthreads();
-    if (warp == 6) {
+    if (warp == LG_PF_DQ_WARPS + 2) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"(NT) : "memory");
     }
@@ -284,4 +292,247 @@ __global__ void lg_f32_to_f16_rows(const float *__restrict__ src, int ld_src, __
     const int tok = blockIdx.y;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
         dst[(size_t)tok * ld_dst + i] = __float2half_rn(src[(size_t)tok * ld_src + i]);
+}
+
+// ---------------------------------------------------------------------------------------------
+// attention of a prompt block: all query rows of the block in one launch per layer
+// ---------------------------------------------------------------------------------------------
+// Step 1 (lg_pf_qkv_prep_kernel): per token, per-head RMSNorm + NeoX RoPE of the raw projection
+// rows.  Queries go to an f16 hi + lo pair [tok][H][hd]; K (norm + rope) and V (plain norm) rows go
+// to the f16 cache of the owning layer (round to nearest even) at row (pos % seq).  The cache ring
+// of a sliding-window layer has more spare rows than a block has tokens, so writing the whole block
+// first does not overwrite a row an earlier query of the block still attends to.
+struct LgPfPrepArgs {
+    const float *qkv; int ld;            // [n][ld] = [q (H*hd) | k (Hkv*hd) | v (Hkv*hd)], the sum of n_parts planes
+    int n_parts; size_t part_stride;
+    int has_v, owns_kv;
+    const float *q_norm, *k_norm; float eps;
+    const float2 *rope;                  // [n][hd/2]
+    __half *kc, *vc; int seq, kv_dim;
+    int H, Hkv;
+    const int *pos;                      // position of the block's first token
+    __half *q_hi, *q_lo;                 // [n][H][hd]
+};
+
+template <int HD>
+__global__ void __launch_bounds__(256) lg_pf_qkv_prep_kernel(LgPfPrepArgs a) {
+    __shared__ float s_qn[HD], s_kn[HD];
+    __shared__ float s_row[8][HD];       // a warp's head vector with the k-slice planes added
+    pdl_launch();
+    for (int i = threadIdx.x; i < HD; i += 256) { s_qn[i] = a.q_norm[i]; s_kn[i] = a.k_norm ? a.k_norm[i] : 1.0f; }
+    pdl_wait();
+    __syncthreads();
+    constexpr int PER = HD / 64, HALF = HD / 2;
+    const int tok = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int p = *a.pos + tok;
+    const int jobs = a.H + (a.owns_kv ? 2 * a.Hkv : 0);
+    const float2 *rope = a.rope + (size_t)tok * HALF;
+    for (int j = warp; j < jobs; j += 8) {
+        float v0[PER], v1[PER];
+        const int jj = j - a.H, isv = jj >= a.Hkv, kvh = isv ? jj - a.Hkv : jj;
+        const float *src = a.qkv + (size_t)tok * a.ld
+                         + (size_t)(j < a.H ? j : a.H + ((isv && a.has_v) ? a.Hkv : 0) + kvh) * HD;
+        if (a.n_parts > 1) {
+            __syncwarp();
+            for (int i = lane; i < HD; i += 32) {
+                float v = src[i];
+                for (int p = 1; p < a.n_parts; p++) v += src[(size_t)p * a.part_stride + i];
+                s_row[warp][i] = v;
+            }
+            __syncwarp();
+            src = s_row[warp];
+        }
+        if (j < a.H) {
+            head_norm_rope<HD>(src, s_qn, rope, a.eps, lane, v0, v1);
+            __half *dh = a.q_hi + ((size_t)tok * a.H + j) * HD, *dl = a.q_lo + ((size_t)tok * a.H + j) * HD;
+            #pragma unroll
+            for (int e = 0; e < PER; e++) {
+                const int i = lane * PER + e;
+                const __half h0 = __float2half_rn(v0[e]), h1 = __float2half_rn(v1[e]);
+                dh[i] = h0; dh[i + HALF] = h1;
+                dl[i] = __float2half_rn(v0[e] - __half2float(h0)); dl[i + HALF] = __float2half_rn(v1[e] - __half2float(h1));
+            }
+        } else {
+            head_norm_rope<HD>(src, isv ? nullptr : s_kn, isv ? nullptr : rope, a.eps, lane, v0, v1);
+            __half *dst = (isv ? a.vc : a.kc) + (size_t)(p % a.seq) * a.kv_dim + (size_t)kvh * HD;
+            #pragma unroll
+            for (int e = 0; e < PER; e++) {
+                dst[lane * PER + e] = __float2half_rn(v0[e]);
+                dst[lane * PER + e + HALF] = __float2half_rn(v1[e]);
+            }
+        }
+    }
+}
+
+// Step 2 (lg_pf_attn_kernel): one CTA = one KV head x LG_PFA_Q query rows (64 / gqa consecutive
+// tokens x the gqa query heads of that KV head).  It walks the keys of its causal / sliding window
+// in tiles of 64 with an online softmax: S = Q K^T and O += P V on mma.sync.m16n8k16 (f16 operands,
+// f32 accumulate), Q and P as f16 hi + lo pairs like the decode kernel, scale 1.0.  The normalised
+// rows are written as f16 -- the o-projection's input.
+struct LgPfAttnArgs {
+    const __half *q_hi, *q_lo;           // [n][H][hd]
+    const __half *kc, *vc; int seq, kv_dim;
+    int H, Hkv, n;
+    int window;                          // <= 0: full causal
+    const int *pos;
+    __half *out; int ld_out;             // [n][ld_out], head hq at column hq*hd
+};
+#define LG_PFA_Q 64
+#define LG_PFA_S 64
+
+template <int HD>
+__global__ void __launch_bounds__(256) lg_pf_attn_kernel(LgPfAttnArgs a) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    constexpr int NQ = LG_PFA_Q, S = LG_PFA_S, LDH = HD + 8, LDP = S + 8, LDS = S + 4;
+    __half *qhi = (__half *)smem, *qlo = qhi + NQ * LDH;
+    __half *sk = qlo + NQ * LDH, *sv = sk + S * LDH;
+    float *sc = (float *)(sv + S * LDH);                      // [NQ][LDS]
+    __half *phi = (__half *)(sc + NQ * LDS), *plo = phi + NQ * LDP;
+    float *row_m = (float *)(plo + NQ * LDP), *row_l = row_m + NQ, *row_a = row_l + NQ;
+    pdl_launch(); pdl_wait();
+
+    const int kvh = blockIdx.x, gqa = a.H / a.Hkv, qb = NQ / gqa;           // qb tokens per CTA
+    const int t0 = blockIdx.y * qb;
+    if (t0 >= a.n) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int pos0 = *a.pos;
+    const int nt = min(qb, a.n - t0);                                       // valid tokens of this CTA
+    const int p_first = pos0 + t0, p_last = pos0 + t0 + nt - 1;
+    const int lo_first = a.window > 0 ? max(0, p_first - a.window + 1) : 0;
+
+    // queries: row r = (token r / gqa, head kvh*gqa + r % gqa)
+    constexpr int CH = HD / 8;
+    for (int i = threadIdx.x; i < NQ * CH; i += 256) {
+        const int r = i / CH, c = i % CH, tok = t0 + r / gqa, hq = kvh * gqa + r % gqa;
+        uint4 vh = make_uint4(0, 0, 0, 0), vl = vh;
+        if (r / gqa < nt) {
+            vh = *(const uint4 *)(a.q_hi + ((size_t)tok * a.H + hq) * HD + c * 8);
+            vl = *(const uint4 *)(a.q_lo + ((size_t)tok * a.H + hq) * HD + c * 8);
+        }
+        *(uint4 *)(qhi + (size_t)r * LDH + c * 8) = vh;
+        *(uint4 *)(qlo + (size_t)r * LDH + c * 8) = vl;
+    }
+    for (int r = threadIdx.x; r < NQ; r += 256) { row_m[r] = -INFINITY; row_l[r] = 0.0f; }
+
+    // warp roles: m-tile mt = warp & 3 (16 query rows); QK: key half kh = warp >> 2; PV: dim half dh = warp >> 2
+    const int mt = warp & 3, hf = warp >> 2;
+    constexpr int DW = HD / 2, NT = DW / 8;                    // output dims per warp, 8-wide n tiles
+    float o[NT][4];
+    #pragma unroll
+    for (int n2 = 0; n2 < NT; n2++) o[n2][0] = o[n2][1] = o[n2][2] = o[n2][3] = 0.0f;
+
+    for (int k0 = (lo_first / S) * S; k0 <= p_last; k0 += S) {
+        __syncthreads();                                        // previous tile's K/V/P are no longer read
+        for (int i = threadIdx.x; i < S * CH; i += 256) {
+            const int key = i / CH, c = i % CH, p = k0 + key;
+            __half *dk = sk + (size_t)key * LDH + c * 8, *dv = sv + (size_t)key * LDH + c * 8;
+            if (p <= p_last) {
+                const size_t off = (size_t)(p % a.seq) * a.kv_dim + (size_t)kvh * HD + c * 8;
+                cp_async16(dk, a.kc + off);
+                cp_async16(dv, a.vc + off);
+            } else {
+                *(uint4 *)dk = make_uint4(0, 0, 0, 0);
+                *(uint4 *)dv = make_uint4(0, 0, 0, 0);
+            }
+        }
+        cp_async_wait_all();
+        __syncthreads();
+
+        // ---- scores of 16 rows x 32 keys per warp ----
+        {
+            float c0[4][4];
+            #pragma unroll
+            for (int n2 = 0; n2 < 4; n2++) c0[n2][0] = c0[n2][1] = c0[n2][2] = c0[n2][3] = 0.0f;
+            const __half *qa_hi = qhi + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + (lane >> 4) * 8;
+            const __half *qa_lo = qlo + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + (lane >> 4) * 8;
+            const __half *kb = sk + (size_t)(hf * 32 + (lane & 7)) * LDH + (lane >> 3) * 8;
+            #pragma unroll 2
+            for (int d0 = 0; d0 < HD; d0 += 32) {
+                uint32_t ah[4], al[4], ah2[4], al2[4];
+                ldsm_x4(ah, qa_hi + d0); ldsm_x4(al, qa_lo + d0);
+                ldsm_x4(ah2, qa_hi + d0 + 16); ldsm_x4(al2, qa_lo + d0 + 16);
+                #pragma unroll
+                for (int n2 = 0; n2 < 4; n2++) {
+                    uint32_t b[4];
+                    ldsm_x4(b, kb + (size_t)n2 * 8 * LDH + d0);
+                    mma_f16(c0[n2], ah, b[0], b[1]); mma_f16(c0[n2], al, b[0], b[1]);
+                    mma_f16(c0[n2], ah2, b[2], b[3]); mma_f16(c0[n2], al2, b[2], b[3]);
+                }
+            }
+            #pragma unroll
+            for (int h2 = 0; h2 < 2; h2++) {
+                const int r = mt * 16 + g + h2 * 8;
+                const int pj = pos0 + t0 + r / gqa;
+                const int lo = a.window > 0 ? max(0, pj - a.window + 1) : 0;
+                const bool rv = r / gqa < nt;
+                #pragma unroll
+                for (int n2 = 0; n2 < 4; n2++)
+                    #pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        const int key = hf * 32 + n2 * 8 + t * 2 + e, p = k0 + key;
+                        sc[r * LDS + key] = (rv && p >= lo && p <= pj) ? c0[n2][h2 * 2 + e] : -INFINITY;
+                    }
+            }
+        }
+        __syncthreads();
+
+        // ---- online softmax: warp w owns rows 8w .. 8w+7 ----
+        for (int r = warp * 8; r < warp * 8 + 8; r++) {
+            const float s0 = sc[r * LDS + lane], s1 = sc[r * LDS + lane + 32];
+            const float m_old = row_m[r];
+            const float m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
+            const float e0 = s0 == -INFINITY ? 0.0f : expf(s0 - m_new), e1 = s1 == -INFINITY ? 0.0f : expf(s1 - m_new);
+            const __half h0 = __float2half_rn(e0), h1 = __float2half_rn(e1);
+            phi[r * LDP + lane] = h0; phi[r * LDP + lane + 32] = h1;
+            plo[r * LDP + lane] = __float2half_rn(e0 - __half2float(h0));
+            plo[r * LDP + lane + 32] = __float2half_rn(e1 - __half2float(h1));
+            const float sum = warp_sum(e0 + e1);
+            if (lane == 0) {
+                const float alpha = m_old == -INFINITY ? 0.0f : expf(m_old - m_new);     // m_new == -inf: nothing seen yet
+                row_a[r] = alpha;
+                row_l[r] = row_l[r] * alpha + sum;
+                row_m[r] = m_new;
+            }
+        }
+        __syncthreads();
+
+        // ---- O = alpha O + P V: 16 rows x DW dims per warp ----
+        {
+            const float a0 = row_a[mt * 16 + g], a1 = row_a[mt * 16 + g + 8];
+            #pragma unroll
+            for (int n2 = 0; n2 < NT; n2++) { o[n2][0] *= a0; o[n2][1] *= a0; o[n2][2] *= a1; o[n2][3] *= a1; }
+            const __half *pa_hi = phi + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDP + (lane >> 4) * 8;
+            const __half *pa_lo = plo + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDP + (lane >> 4) * 8;
+            #pragma unroll
+            for (int kk = 0; kk < S; kk += 16) {
+                uint32_t ah[4], al[4];
+                ldsm_x4(ah, pa_hi + kk); ldsm_x4(al, pa_lo + kk);
+                const __half *vb = sv + (size_t)(kk + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + hf * DW + (lane >> 4) * 8;
+                #pragma unroll
+                for (int n2 = 0; n2 < NT; n2 += 2) {
+                    uint32_t b[4];
+                    ldsm_x4_t(b, vb + n2 * 8);
+                    mma_f16(o[n2], ah, b[0], b[1]); mma_f16(o[n2], al, b[0], b[1]);
+                    mma_f16(o[n2 + 1], ah, b[2], b[3]); mma_f16(o[n2 + 1], al, b[2], b[3]);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    #pragma unroll
+    for (int h2 = 0; h2 < 2; h2++) {
+        const int r = mt * 16 + g + h2 * 8;
+        if (r / gqa < nt) {
+            const float l = row_l[r], inv = l > 0.0f ? 1.0f / l : 0.0f;
+            __half *dst = a.out + (size_t)(t0 + r / gqa) * a.ld_out + (size_t)(kvh * gqa + r % gqa) * HD + hf * DW;
+            #pragma unroll
+            for (int n2 = 0; n2 < NT; n2++)
+                *(__half2 *)(dst + n2 * 8 + t * 2) = __floats2half2_rn(o[n2][h2 * 2] * inv, o[n2][h2 * 2 + 1] * inv);
+        }
+    }
+}
+
+template <int HD> constexpr size_t pf_attn_smem() {
+    return (size_t)2 * LG_PFA_Q * (HD + 8) * 2 + (size_t)2 * LG_PFA_S * (HD + 8) * 2 + (size_t)LG_PFA_Q * (LG_PFA_S + 4) * 4
+         + (size_t)2 * LG_PFA_Q * (LG_PFA_S + 8) * 2 + 3 * LG_PFA_Q * 4;
 }
