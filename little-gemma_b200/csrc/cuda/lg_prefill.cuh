@@ -28,9 +28,12 @@
 
 #define LG_PF_BM 128
 #define LG_PF_BK 64
-#define LG_PF_STAGES 4          // A / B operand stages
-#define LG_PF_RAW_STAGES 3      // raw q4 stages of two k blocks each
+#define LG_PF_A_STAGES 4        // expanded weight (A operand) stages: a multiple of LG_PF_GROUPS, so a stage belongs to ONE
+                                // expand group and its empty-barrier phases are observed in order by the same threads
+                                // (a parity wait cannot tell "two completions behind" from "done")
+#define LG_PF_SMEM_MAX 232448   // 227 KB: the most dynamic shared memory a CTA can have
 #define LG_PF_DQ_WARPS 8
+#define LG_PF_GROUPS 4          // expand-warp groups working on different k blocks
 #define LG_PF_THREADS ((LG_PF_DQ_WARPS + 3) * 32)
 #define LG_PF_MAXN 256
 
@@ -51,8 +54,19 @@ struct LgPfGemmArgs {
 template <int FMT> __host__ __device__ constexpr int pf_raw_stage_bytes() {
     return 8 * 2 * (512 + 64 + (FMT == LG_FMT_Q4_K ? 64 : 0));
 }
+template <int NT> __host__ __device__ constexpr int pf_a_stages() { return LG_PF_A_STAGES; }
+// activation (B operand) stages (3 stages with a deeper raw ring measured slower at a 256-wide token tile)
+template <int NT> __host__ __device__ constexpr int pf_b_stages() { return 4; }
+// raw q4 stages of two k blocks each: as many as fit beside the operand stages, at most 8 -- the bytes in flight
+// from HBM per SM, which is what keeps the weight stream moving
+template <int NT, int FMT> __host__ __device__ constexpr int pf_raw_stages() {
+    int left = LG_PF_SMEM_MAX - 1024 - 512 - pf_a_stages<NT>() * LG_PF_BM * 128 - pf_b_stages<NT>() * NT * 128;
+    int n = left / pf_raw_stage_bytes<FMT>();
+    return n > 8 ? 8 : n;
+}
 template <int NT, int FMT> __host__ __device__ constexpr size_t pf_smem_bytes() {
-    return 1024 + (size_t)LG_PF_STAGES * (LG_PF_BM * 128 + NT * 128) + (size_t)LG_PF_RAW_STAGES * pf_raw_stage_bytes<FMT>() + 256;
+    return 1024 + (size_t)pf_a_stages<NT>() * LG_PF_BM * 128 + (size_t)pf_b_stages<NT>() * NT * 128
+         + (size_t)pf_raw_stages<NT, FMT>() * pf_raw_stage_bytes<FMT>() + 512;
 }
 
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
@@ -102,14 +116,14 @@ __device__ __forceinline__ uint32_t pf_pair_q4_K(uint32_t n, uint32_t sel, __hal
 template <int NT, int FMT, int EPI>
 __global__ void __launch_bounds__(LG_PF_THREADS) lg_pf_gemm_kernel(const __grid_constant__ CUtensorMap tmx, LgPfGemmArgs a) {
     extern __shared__ unsigned char pf_smem_raw[];
-    constexpr int ST = LG_PF_STAGES, RS = LG_PF_RAW_STAGES, RAW = pf_raw_stage_bytes<FMT>();
+    constexpr int STA = pf_a_stages<NT>(), STB = pf_b_stages<NT>(), RS = pf_raw_stages<NT, FMT>(), RAW = pf_raw_stage_bytes<FMT>();
     constexpr int A_BYTES = LG_PF_BM * 128, B_BYTES = NT * 128;
     constexpr int RAW_SC = 16 * 512, RAW_DD = RAW_SC + 16 * 64;
     unsigned char *base = (unsigned char *)(((uintptr_t)pf_smem_raw + 1023) & ~(uintptr_t)1023);
-    unsigned char *sA = base, *sB = sA + ST * A_BYTES, *sRaw = sB + ST * B_BYTES;
+    unsigned char *sA = base, *sB = sA + STA * A_BYTES, *sRaw = sB + STB * B_BYTES;
     uint64_t *bars = (uint64_t *)(sRaw + RS * RAW);
-    uint64_t *raw_full = bars, *raw_empty = raw_full + RS, *a_full = raw_empty + RS, *b_full = a_full + ST,
-             *empty = b_full + ST, *acc_full = empty + ST;
+    uint64_t *raw_full = bars, *raw_empty = raw_full + RS, *a_full = raw_empty + RS, *b_full = a_full + STA,
+             *a_empty = b_full + STB, *b_empty = a_empty + STA, *acc_full = b_empty + STB;
     uint32_t *tmem_slot = (uint32_t *)(acc_full + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -120,8 +134,9 @@ __global__ void __launch_bounds__(LG_PF_THREADS) lg_pf_gemm_kernel(const __grid_
 
     pdl_launch();
     if (threadIdx.x == 0) {
-        for (int i = 0; i < RS; i++) { mbar_init(raw_full + i, 1); mbar_init(raw_empty + i, DQT); }
-        for (int i = 0; i < ST; i++) { mbar_init(a_full + i, DQT); mbar_init(b_full + i, 1); mbar_init(empty + i, 1); }
+        for (int i = 0; i < RS; i++) { mbar_init(raw_full + i, 1); mbar_init(raw_empty + i, 2 * DQT / LG_PF_GROUPS); }
+        for (int i = 0; i < STA; i++) { mbar_init(a_full + i, DQT / LG_PF_GROUPS); mbar_init(a_empty + i, 1); }
+        for (int i = 0; i < STB; i++) { mbar_init(b_full + i, 1); mbar_init(b_empty + i, 1); }
         mbar_init(acc_full, 1);
     }
     if (warp == LG_PF_DQ_WARPS + 2) {        // tensor memory: NT f32 columns x 128 lanes
@@ -140,7 +155,7 @@ __global__ void __launch_bounds__(LG_PF_THREADS) lg_pf_gemm_kernel(const __grid_
             int issued = 0;
             for (int r = 0; r < n_raw && ok; r++) {
                 const int rs = r % RS;
-                if (r >= RS && !mbar_wait(raw_empty + rs, ((r / RS) & 1) ^ 1)) { atomicOr(a.err, LG_ERR_MBAR_TIMEOUT); ok = false; break; }
+                if (r >= RS && !mbar_wait(raw_empty + rs, ((r / RS) & 1) ^ 1)) { atomicOr(a.err, LG_ERR_MBAR_TIMEOUT | 2); ok = false; break; }
                 const int np = min(2, nkb - 2 * r);
                 unsigned char *st = sRaw + rs * RAW;
                 mbar_expect_tx(raw_full + rs, 8u * np * (512 + 64 + (FMT == LG_FMT_Q4_K ? 64 : 0)));
@@ -164,14 +179,14 @@ __global__ void __launch_bounds__(LG_PF_THREADS) lg_pf_gemm_kernel(const __grid_
             bool ok = true;
             int issued = 0;
             for (int kb = 0; kb < nkb && ok; kb++) {
-                const int s = kb % ST;
-                if (kb >= ST && !mbar_wait(empty + s, ((kb / ST) & 1) ^ 1)) { atomicOr(a.err, LG_ERR_MBAR_TIMEOUT); ok = false; break; }
+                const int s = kb % STB;
+                if (kb >= STB && !mbar_wait(b_empty + s, ((kb / STB) & 1) ^ 1)) { atomicOr(a.err, LG_ERR_MBAR_TIMEOUT | 4); ok = false; break; }
                 mbar_expect_tx(b_full + s, B_BYTES);
                 tma_load_2d(sB + s * B_BYTES, &tmx, (kb_lo + kb) * LG_PF_BK, tok0, b_full + s);
                 issued = kb + 1;
             }
             if (!ok)
-                for (int kb = max(0, issued - ST); kb < issued; kb++) mbar_wait(b_full + kb % ST, (kb / ST) & 1);
+                for (int kb = max(0, issued - STB); kb < issued; kb++) mbar_wait(b_full + kb % STB, (kb / STB) & 1);
         }
     } else if (warp == LG_PF_DQ_WARPS + 2) {
         // ---------------- MMA issuer ----------------
@@ -179,34 +194,51 @@ __global__ void __launch_bounds__(LG_PF_THREADS) lg_pf_gemm_kernel(const __grid_
             constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(LG_PF_BM >> 4) << 24);
             bool ok = true;
             for (int kb = 0; kb < nkb && ok; kb++) {
-                const int s = kb % ST; const uint32_t ph = (kb / ST) & 1;
-                if (!mbar_wait(a_full + s, ph) || !mbar_wait(b_full + s, ph)) { atomicOr(a.err, LG_ERR_MBAR_TIMEOUT); ok = false; break; }
+                const int sa = kb % STA, sb = kb % STB;
+                if (!mbar_wait(a_full + sa, (kb / STA) & 1)) { atomicOr(a.err, LG_ERR_MBAR_TIMEOUT | 8); ok = false; break; }
+                if (!mbar_wait(b_full + sb, (kb / STB) & 1)) { atomicOr(a.err, LG_ERR_MBAR_TIMEOUT | 16); ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t ad = umma_desc_k128(smem_u32(sA + s * A_BYTES)), bd = umma_desc_k128(smem_u32(sB + s * B_BYTES));
+                const uint64_t ad = umma_desc_k128(smem_u32(sA + sa * A_BYTES)), bd = umma_desc_k128(smem_u32(sB + sb * B_BYTES));
                 #pragma unroll
                 for (int j = 0; j < LG_PF_BK / 16; j++)
                     umma_f16(tmem, ad + 2 * j, bd + 2 * j, idesc, (kb | j) ? 1u : 0u);
-                umma_commit(empty + s);              // the stage is free once these MMAs have read it
+                umma_commit(a_empty + sa);           // the stages are free once these MMAs have read them
+                umma_commit(b_empty + sb);
             }
             umma_commit(acc_full);                   // arrives when every MMA above has completed
         }
     } else {
         // ---------------- expand q4 -> f16 A operand (one row tile per warp), then the epilogue ----------------
+        // The expand warps form LG_PF_GROUPS groups; group gi takes the k blocks kb = gi (mod LG_PF_GROUPS), so
+        // several k blocks are being expanded at once and a group's latency chain (wait, expand, proxy fence,
+        // arrive) overlaps the other groups'.  Within a group the warps split the 8 row tiles.
+        // All shared-memory traffic of this loop uses explicit shared-space addresses (32-bit).
+        constexpr int NG = LG_PF_GROUPS, WPG = LG_PF_DQ_WARPS / NG, TPW = 8 / WPG;   // warps per group, tiles per warp
+        static_assert(STA % NG == 0, "a stage must belong to one expand group");
         const int g = lane >> 2, t = lane & 3;
+        const int gi = warp / WPG, wi = warp % WPG;
+        const uint32_t raw0 = smem_u32(sRaw) + lane * 16;
+        const uint32_t rsc0 = smem_u32(sRaw) + RAW_SC + g * 8, rdd0 = smem_u32(sRaw) + RAW_DD + g * 8;
+        // row ti*16 + g (+8): 8-row group (2 ti) (+1), row-in-group g; 16-byte chunk c of a row sits at c ^ g
+        const uint32_t dst0 = smem_u32(sA) + g * 128 + (t & 1) * 8;
+        uint32_t coff[4];                                                            // [sub-block][low / high nibbles]
+        #pragma unroll
+        for (int i = 0; i < 4; i++) coff[i] = (uint32_t)(((4 * (i >> 1) + (t >> 1) + 2 * (i & 1)) ^ g) << 4);
         bool ok = true;
-        for (int kb = 0; kb < nkb; kb++) {
-            const int s = kb % ST, r = kb >> 1, rs = r % RS, half = kb & 1;
-            if (ok && !half && !mbar_wait(raw_full + rs, (r / RS) & 1)) ok = false;
-            if (ok && kb >= ST && !mbar_wait(empty + s, ((kb / ST) & 1) ^ 1)) ok = false;
+        for (int kb = gi; kb < nkb; kb += NG) {
+            const int s = kb % STA, r = kb >> 1, rs = r % RS, half = kb & 1;
+            if (ok && !mbar_wait(raw_full + rs, (r / RS) & 1)) { ok = false; atomicOr(a.err, 32); }
+            if (ok && kb >= STA && !mbar_wait(a_empty + s, ((kb / STA) & 1) ^ 1)) { ok = false; atomicOr(a.err, 64); }
             if (!ok) break;
-            const unsigned char *raw = sRaw + rs * RAW;
-            unsigned char *dstA = sA + s * A_BYTES;
-            {
-                const int ti = warp;                                                 // row tile of the CTA's 8
-                const uint4 w = *(const uint4 *)(raw + ti * 1024 + half * 512 + lane * 16);
-                const uint2 sc = *(const uint2 *)(raw + RAW_SC + ti * 128 + half * 64 + g * 8);
-                uint2 dd = make_uint2(0, 0);
-                if (FMT == LG_FMT_Q4_K) dd = *(const uint2 *)(raw + RAW_DD + ti * 128 + half * 64 + g * 8);
+            #pragma unroll
+            for (int q = 0; q < TPW; q++) {
+                const int ti = wi * TPW + q;                                         // row tile of the CTA's 8
+                const uint32_t roff = rs * RAW + ti * 1024 + half * 512, soff = rs * RAW + ti * 128 + half * 64;
+                uint4 w; uint2 sc, dd = make_uint2(0, 0);
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w) : "r"(raw0 + roff));
+                asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(sc.x), "=r"(sc.y) : "r"(rsc0 + soff));
+                if (FMT == LG_FMT_Q4_K) asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(dd.x), "=r"(dd.y) : "r"(rdd0 + soff));
+                const uint32_t dstS = dst0 + s * A_BYTES + (2 * ti) * 1024;
                 #pragma unroll
                 for (int sbk = 0; sbk < 2; sbk++)
                     #pragma unroll
@@ -216,8 +248,9 @@ __global__ void __launch_bounds__(LG_PF_THREADS) lg_pf_gemm_kernel(const __grid_
                         const uint32_t lo = (word & 0x0F0F0F0Fu) ^ 0x08080808u, hi = ((word >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;
                         uint2 vlo, vhi;
                         if (FMT == LG_FMT_Q4_0) {
-                            const __half d = __ushort_as_half((unsigned short)(h8 ? (sw >> 16) : (sw & 0xffff)));
-                            const __half2 d2 = __half2half2(d);
+                            uint32_t dbits;                                           // the row's scale in both halves
+                            asm("prmt.b32 %0, %1, %1, %2;" : "=r"(dbits) : "r"(sw), "r"(h8 ? 0x3232u : 0x1010u));
+                            const __half2 d2 = *(const __half2 *)&dbits;
                             vlo = make_uint2(pf_pair_q4_0(lo, 0x4140u, d2), pf_pair_q4_0(lo, 0x4342u, d2));
                             vhi = make_uint2(pf_pair_q4_0(hi, 0x4140u, d2), pf_pair_q4_0(hi, 0x4342u, d2));
                         } else {
@@ -228,22 +261,19 @@ __global__ void __launch_bounds__(LG_PF_THREADS) lg_pf_gemm_kernel(const __grid_
                             vlo = make_uint2(pf_pair_q4_K(lo, 0x4140u, dsc2, ndm2), pf_pair_q4_K(lo, 0x4342u, dsc2, ndm2));
                             vhi = make_uint2(pf_pair_q4_K(hi, 0x4140u, dsc2, ndm2), pf_pair_q4_K(hi, 0x4342u, dsc2, ndm2));
                         }
-                        // row (ti*16 + g + 8*h8): row % 8 == g; 16-byte chunk c of the row sits at c ^ g
-                        const int row = ti * 16 + g + 8 * h8;
-                        unsigned char *rowp = dstA + (row >> 3) * 1024 + g * 128 + (t & 1) * 8;
-                        const int c_lo = 4 * sbk + (t >> 1), c_hi = c_lo + 2;
-                        *(uint2 *)(rowp + ((c_lo ^ g) << 4)) = vlo;
-                        *(uint2 *)(rowp + ((c_hi ^ g) << 4)) = vhi;
+                        const uint32_t rowa = dstS + h8 * 1024;
+                        asm volatile("st.shared.v2.u32 [%0], {%1,%2};" :: "r"(rowa + coff[2 * sbk]), "r"(vlo.x), "r"(vlo.y) : "memory");
+                        asm volatile("st.shared.v2.u32 [%0], {%1,%2};" :: "r"(rowa + coff[2 * sbk + 1]), "r"(vhi.x), "r"(vhi.y) : "memory");
                     }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");           // generic-proxy stores -> visible to the MMA
             mbar_arrive(a_full + s);
-            if (half || kb == nkb - 1) mbar_arrive(raw_empty + rs);
+            mbar_arrive(raw_empty + rs);           // every expand thread arrives once per k block it takes
         }
         if (!ok && lane == 0) atomicOr(a.err, LG_ERR_MBAR_TIMEOUT);
 
         // ---------------- epilogue: lane l of warp w holds accumulator row 32 (w % 4) + l ----------------
-        if (ok) ok = mbar_wait(acc_full, 0);
+        if (ok) { ok = mbar_wait(acc_full, 0); if (!ok) atomicOr(a.err, 128); }
         if (!ok && lane == 0) atomicOr(a.err, LG_ERR_MBAR_TIMEOUT);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
