@@ -307,6 +307,34 @@ def main():
     mm_ms = m0.elapsed_time(m1) / reps
     W = t_shape.weight_bytes() - int(t_shape.n_embd * t_shape.ple * t_shape.n_layer * 0.5625)  # proj table is gathered, not multiplied
 
+    # the prompt pass: model_prefill of a 929-token prompt (host call, wall clock, synchronised), and the
+    # wide tcgen05 matmuls of one 256-token block over all layers, event-timed, against the tensor peak
+    prefill_rec = None
+    n_pf = min(929, max_seq - 8)
+    pf_prompt = synth.prompt_ids(n_pf, V, seed=300 + RANK)
+    sess.prefill(pf_prompt, 0)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    sess.prefill(pf_prompt, 0)
+    torch.cuda.synchronize()
+    pf_s = time.perf_counter() - t0
+    prefill_rec = {"tokens": n_pf, "ms": pf_s * 1e3, "tok_s": n_pf / pf_s}
+    if sess.prefill_pass(256, 0) > 0:
+        torch.cuda.synchronize()
+        g0, g1 = ev(), ev()
+        g0.record(stream)
+        for _ in range(5):
+            n_pf_mm = sess.prefill_pass(256, 0)
+        g1.record(stream)
+        g1.synchronize()
+        pf_mm_ms = g0.elapsed_time(g1) / 5
+        ne_, H_, Hkv_, hd_, L_, nff_ = (t_shape.n_embd, t_shape.n_head, t_shape.n_head_kv, t_shape.head_dim, t_shape.n_layer,
+                                        t_shape.n_ff)
+        layer_params = L_ * (ne_ * (H_ + 2 * Hkv_) * hd_ + H_ * hd_ * ne_ + 3 * ne_ * nff_)
+        tfl = 2.0 * layer_params * 256 / (pf_mm_ms * 1e-3) / 1e12
+        prefill_rec["matmul_block"] = {"bound": "tensor", "kernel": "lg_pf_gemm_kernel (tcgen05, f16 operands, f32 accumulate)",
+                                       "tokens": 256, "launches": n_pf_mm, "ms": pf_mm_ms, "achieved": tfl, "unit": "TFLOP/s"}
+
     # end to end through the blocking reference-shaped API
     e2e_rounds = max(20, a.steps // 3)
     restart()
@@ -331,6 +359,11 @@ def main():
     peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "fallback 6650 GB/s"
     kvb = kv_bytes_step(t_shape, a.depth, M)
     mm_gbs = W / (mm_ms * 1e-3) / 1e9
+    if prefill_rec and "matmul_block" in prefill_rec:
+        tpeak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+        prefill_rec["matmul_block"].update(peak=tpeak, frac=prefill_rec["matmul_block"]["achieved"] / tpeak,
+                                           peak_source=("measured (MEASURED_PEAKS.json bf16_tflops_sustained: the pass is 192 "
+                                                        "back-to-back launches)" if peaks else "fallback 1400 TFLOP/s sustained"))
 
     # aggregate over replicas
     my = torch.tensor([float(emitted), float(ms), float(len(toks_h)), float(dt_h), float(identical)], dtype=torch.float64)
@@ -361,7 +394,7 @@ def main():
                                               "launch (37.793 MB moved for 37.749 MB of q4_0) scaled by weight bytes; writes 0",
                               "algorithmic_bytes": W, "launches": n_mm, "ms": mm_ms,
                               "frac_of_8TBs": mm_gbs / 8000.0},
-                    cpu_baseline=cpu)
+                    cpu_baseline=cpu, prefill=prefill_rec)
         line["config"] = dict(line["config"], mtp_n=M, depth=a.depth, p=a.p, launches_per_round=int(launches_per_round),
                               tokens_per_round=emitted / a.steps, acceptance=accept,
                               stream_identical_to_plain_greedy=bool(agg["identical"]),

@@ -394,7 +394,7 @@ __global__ void __launch_bounds__(256) lg_pf_qkv_prep_kernel(LgPfPrepArgs a) {
     }
 }
 
-// Step 2 (lg_pf_attn_kernel): one CTA = one KV head x LG_PFA_Q query rows (64 / gqa consecutive
+// Step 2 (lg_pf_attn_kernel): one CTA = one KV head x LG_PFA_Q query rows (LG_PFA_Q / gqa consecutive
 // tokens x the gqa query heads of that KV head).  It walks the keys of its causal / sliding window
 // in tiles of 64 with an online softmax: S = Q K^T and O += P V on mma.sync.m16n8k16 (f16 operands,
 // f32 accumulate), Q and P as f16 hi + lo pairs like the decode kernel, scale 1.0.  The normalised
@@ -407,7 +407,7 @@ struct LgPfAttnArgs {
     const int *pos;
     __half *out; int ld_out;             // [n][ld_out], head hq at column hq*hd
 };
-#define LG_PFA_Q 64
+#define LG_PFA_Q 32
 #define LG_PFA_S 64
 
 template <int HD>
@@ -444,9 +444,11 @@ __global__ void __launch_bounds__(256) lg_pf_attn_kernel(LgPfAttnArgs a) {
     }
     for (int r = threadIdx.x; r < NQ; r += 256) { row_m[r] = -INFINITY; row_l[r] = 0.0f; }
 
-    // warp roles: m-tile mt = warp & 3 (16 query rows); QK: key half kh = warp >> 2; PV: dim half dh = warp >> 2
-    const int mt = warp & 3, hf = warp >> 2;
-    constexpr int DW = HD / 2, NT = DW / 8;                    // output dims per warp, 8-wide n tiles
+    // warp roles: m-tile mt (16 query rows) x slice hf of the tile's keys (scores) or of the head dims (output)
+    constexpr int MT = NQ / 16, WK = 8 / MT, KPW = S / WK, NKT = KPW / 8;
+    const int mt = warp % MT, hf = warp / MT;
+    constexpr int DW = HD / WK, NT = DW / 8;                   // output dims per warp, 8-wide n tiles
+    static_assert(NT % 2 == 0 && NKT >= 1, "tile split");
     float o[NT][4];
     #pragma unroll
     for (int n2 = 0; n2 < NT; n2++) o[n2][0] = o[n2][1] = o[n2][2] = o[n2][3] = 0.0f;
@@ -468,21 +470,21 @@ __global__ void __launch_bounds__(256) lg_pf_attn_kernel(LgPfAttnArgs a) {
         cp_async_wait_all();
         __syncthreads();
 
-        // ---- scores of 16 rows x 32 keys per warp ----
+        // ---- scores of 16 rows x KPW keys per warp ----
         {
-            float c0[4][4];
+            float c0[NKT][4];
             #pragma unroll
-            for (int n2 = 0; n2 < 4; n2++) c0[n2][0] = c0[n2][1] = c0[n2][2] = c0[n2][3] = 0.0f;
+            for (int n2 = 0; n2 < NKT; n2++) c0[n2][0] = c0[n2][1] = c0[n2][2] = c0[n2][3] = 0.0f;
             const __half *qa_hi = qhi + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + (lane >> 4) * 8;
             const __half *qa_lo = qlo + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + (lane >> 4) * 8;
-            const __half *kb = sk + (size_t)(hf * 32 + (lane & 7)) * LDH + (lane >> 3) * 8;
+            const __half *kb = sk + (size_t)(hf * KPW + (lane & 7)) * LDH + (lane >> 3) * 8;
             #pragma unroll 2
             for (int d0 = 0; d0 < HD; d0 += 32) {
                 uint32_t ah[4], al[4], ah2[4], al2[4];
                 ldsm_x4(ah, qa_hi + d0); ldsm_x4(al, qa_lo + d0);
                 ldsm_x4(ah2, qa_hi + d0 + 16); ldsm_x4(al2, qa_lo + d0 + 16);
                 #pragma unroll
-                for (int n2 = 0; n2 < 4; n2++) {
+                for (int n2 = 0; n2 < NKT; n2++) {
                     uint32_t b[4];
                     ldsm_x4(b, kb + (size_t)n2 * 8 * LDH + d0);
                     mma_f16(c0[n2], ah, b[0], b[1]); mma_f16(c0[n2], al, b[0], b[1]);
@@ -496,18 +498,18 @@ __global__ void __launch_bounds__(256) lg_pf_attn_kernel(LgPfAttnArgs a) {
                 const int lo = a.window > 0 ? max(0, pj - a.window + 1) : 0;
                 const bool rv = r / gqa < nt;
                 #pragma unroll
-                for (int n2 = 0; n2 < 4; n2++)
+                for (int n2 = 0; n2 < NKT; n2++)
                     #pragma unroll
                     for (int e = 0; e < 2; e++) {
-                        const int key = hf * 32 + n2 * 8 + t * 2 + e, p = k0 + key;
+                        const int key = hf * KPW + n2 * 8 + t * 2 + e, p = k0 + key;
                         sc[r * LDS + key] = (rv && p >= lo && p <= pj) ? c0[n2][h2 * 2 + e] : -INFINITY;
                     }
             }
         }
         __syncthreads();
 
-        // ---- online softmax: warp w owns rows 8w .. 8w+7 ----
-        for (int r = warp * 8; r < warp * 8 + 8; r++) {
+        // ---- online softmax: warp w owns NQ/8 consecutive rows ----
+        for (int r = warp * (NQ / 8); r < (warp + 1) * (NQ / 8); r++) {
             const float s0 = sc[r * LDS + lane], s1 = sc[r * LDS + lane + 32];
             const float m_old = row_m[r];
             const float m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
