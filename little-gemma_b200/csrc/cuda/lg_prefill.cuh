@@ -415,8 +415,8 @@ __global__ void __launch_bounds__(256) lg_pf_attn_kernel(LgPfAttnArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     constexpr int NQ = LG_PFA_Q, S = LG_PFA_S, LDH = HD + 8, LDP = S + 8, LDS = S + 4;
     __half *qhi = (__half *)smem, *qlo = qhi + NQ * LDH;
-    __half *sk = qlo + NQ * LDH, *sv = sk + S * LDH;
-    float *sc = (float *)(sv + S * LDH);                      // [NQ][LDS]
+    __half *sk = qlo + NQ * LDH;                              // two buffers of [K tile | V tile], each [S][LDH]
+    float *sc = (float *)(sk + 4 * S * LDH);                  // [NQ][LDS]
     __half *phi = (__half *)(sc + NQ * LDS), *plo = phi + NQ * LDP;
     float *row_m = (float *)(plo + NQ * LDP), *row_l = row_m + NQ, *row_a = row_l + NQ;
     pdl_launch(); pdl_wait();
@@ -453,11 +453,12 @@ __global__ void __launch_bounds__(256) lg_pf_attn_kernel(LgPfAttnArgs a) {
     #pragma unroll
     for (int n2 = 0; n2 < NT; n2++) o[n2][0] = o[n2][1] = o[n2][2] = o[n2][3] = 0.0f;
 
-    for (int k0 = (lo_first / S) * S; k0 <= p_last; k0 += S) {
-        __syncthreads();                                        // previous tile's K/V/P are no longer read
+    // K/V tiles are double-buffered: tile i+1 streams in (cp.async) while tile i is being used
+    auto load_tile = [&](int k0, int buf) {
+        __half *bk = sk + (size_t)buf * 2 * S * LDH, *bv = bk + S * LDH;
         for (int i = threadIdx.x; i < S * CH; i += 256) {
             const int key = i / CH, c = i % CH, p = k0 + key;
-            __half *dk = sk + (size_t)key * LDH + c * 8, *dv = sv + (size_t)key * LDH + c * 8;
+            __half *dk = bk + (size_t)key * LDH + c * 8, *dv = bv + (size_t)key * LDH + c * 8;
             if (p <= p_last) {
                 const size_t off = (size_t)(p % a.seq) * a.kv_dim + (size_t)kvh * HD + c * 8;
                 cp_async16(dk, a.kc + off);
@@ -467,8 +468,15 @@ __global__ void __launch_bounds__(256) lg_pf_attn_kernel(LgPfAttnArgs a) {
                 *(uint4 *)dv = make_uint4(0, 0, 0, 0);
             }
         }
+    };
+    const int k_first = (lo_first / S) * S;
+    load_tile(k_first, 0);
+    int buf = 0;
+    for (int k0 = k_first; k0 <= p_last; k0 += S, buf ^= 1) {
         cp_async_wait_all();
-        __syncthreads();
+        __syncthreads();                                        // tile k0 has landed; the other buffer and P are no longer read
+        if (k0 + S <= p_last) load_tile(k0 + S, buf ^ 1);
+        const __half *sk_t = sk + (size_t)buf * 2 * S * LDH, *sv_t = sk_t + S * LDH;
 
         // ---- scores of 16 rows x KPW keys per warp ----
         {
@@ -477,7 +485,7 @@ __global__ void __launch_bounds__(256) lg_pf_attn_kernel(LgPfAttnArgs a) {
             for (int n2 = 0; n2 < NKT; n2++) c0[n2][0] = c0[n2][1] = c0[n2][2] = c0[n2][3] = 0.0f;
             const __half *qa_hi = qhi + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + (lane >> 4) * 8;
             const __half *qa_lo = qlo + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + (lane >> 4) * 8;
-            const __half *kb = sk + (size_t)(hf * KPW + (lane & 7)) * LDH + (lane >> 3) * 8;
+            const __half *kb = sk_t + (size_t)(hf * KPW + (lane & 7)) * LDH + (lane >> 3) * 8;
             #pragma unroll 2
             for (int d0 = 0; d0 < HD; d0 += 32) {
                 uint32_t ah[4], al[4], ah2[4], al2[4];
@@ -539,7 +547,7 @@ __global__ void __launch_bounds__(256) lg_pf_attn_kernel(LgPfAttnArgs a) {
             for (int kk = 0; kk < S; kk += 16) {
                 uint32_t ah[4], al[4];
                 ldsm_x4(ah, pa_hi + kk); ldsm_x4(al, pa_lo + kk);
-                const __half *vb = sv + (size_t)(kk + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + hf * DW + (lane >> 4) * 8;
+                const __half *vb = sv_t + (size_t)(kk + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + hf * DW + (lane >> 4) * 8;
                 #pragma unroll
                 for (int n2 = 0; n2 < NT; n2 += 2) {
                     uint32_t b[4];
@@ -565,6 +573,6 @@ __global__ void __launch_bounds__(256) lg_pf_attn_kernel(LgPfAttnArgs a) {
 }
 
 template <int HD> constexpr size_t pf_attn_smem() {
-    return (size_t)2 * LG_PFA_Q * (HD + 8) * 2 + (size_t)2 * LG_PFA_S * (HD + 8) * 2 + (size_t)LG_PFA_Q * (LG_PFA_S + 4) * 4
+    return (size_t)2 * LG_PFA_Q * (HD + 8) * 2 + (size_t)4 * LG_PFA_S * (HD + 8) * 2 + (size_t)LG_PFA_Q * (LG_PFA_S + 4) * 4
          + (size_t)2 * LG_PFA_Q * (LG_PFA_S + 8) * 2 + 3 * LG_PFA_Q * 4;
 }
