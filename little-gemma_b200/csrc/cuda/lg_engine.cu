@@ -825,8 +825,8 @@ void enqueue_prefill_block(Engine *e, const struct kvcache *kv, int n, int only 
     if (only & C_MISC) {
         launch_k(e, lg_embed_rows, dim3(n), dim3(256), 0, e->head.wq, e->head.ws, e->head.wd, e->head.fmt, e->head.nkp, e->head.m,
                  (const int *)b.toks, sqrtf((float)ne), b.x, ne);
-        launch_k(e, lg_rope_table_kernel, dim3(1), dim3(1024), 0, (const int *)b.pos, n, e->hd_local, c->rope_freq_base_swa, (const float *)nullptr, b.rope_local);
-        launch_k(e, lg_rope_table_kernel, dim3(1), dim3(1024), 0, (const int *)b.pos, n, e->hd_global, c->rope_freq_base, (const float *)e->rope_div, b.rope_global);
+        launch_k(e, lg_rope_table_kernel, dim3((n + 7) / 8), dim3(256), 0, (const int *)b.pos, n, e->hd_local, c->rope_freq_base_swa, (const float *)nullptr, b.rope_local);
+        launch_k(e, lg_rope_table_kernel, dim3((n + 7) / 8), dim3(256), 0, (const int *)b.pos, n, e->hd_global, c->rope_freq_base, (const float *)e->rope_div, b.rope_global);
     }
     if (only & C_NORM) launch_norm_pf(e, n, b.x, ne, c->rms_eps, nullptr, 0, 0, nullptr, 1.0f, e->L[0].attn_norm, b.a_ne);
     for (int l = 0; l < nl; l++) {
@@ -850,12 +850,13 @@ void enqueue_prefill_block(Engine *e, const struct kvcache *kv, int n, int only 
             fa.out = b.a_attn; fa.ld_out = H * hd;
             const int qb = LG_PFA_Q / gqa;
             dim3 grid(w.nkv, (n + qb - 1) / qb);
+            dim3 prep_grid(n, (H + (w.owns_kv ? 2 * w.nkv : 0) + 7) / 8);           // one head vector per warp
             switch (hd) {
-            case 64:  launch_k(e, lg_pf_qkv_prep_kernel<64>, dim3(n), dim3(256), 0, pa);
+            case 64:  launch_k(e, lg_pf_qkv_prep_kernel<64>, prep_grid, dim3(256), 0, pa);
                       launch_k(e, lg_pf_attn_kernel<64>, grid, dim3(256), pf_attn_smem<64>(), fa); break;
-            case 128: launch_k(e, lg_pf_qkv_prep_kernel<128>, dim3(n), dim3(256), 0, pa);
+            case 128: launch_k(e, lg_pf_qkv_prep_kernel<128>, prep_grid, dim3(256), 0, pa);
                       launch_k(e, lg_pf_attn_kernel<128>, grid, dim3(256), pf_attn_smem<128>(), fa); break;
-            default:  launch_k(e, lg_pf_qkv_prep_kernel<256>, dim3(n), dim3(256), 0, pa);
+            default:  launch_k(e, lg_pf_qkv_prep_kernel<256>, prep_grid, dim3(256), 0, pa);
                       launch_k(e, lg_pf_attn_kernel<256>, grid, dim3(256), pf_attn_smem<256>(), fa); break;
             }
         } else if (only & C_ATTN)

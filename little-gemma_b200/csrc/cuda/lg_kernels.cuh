@@ -836,7 +836,7 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 __global__ void lg_rope_table_kernel(const int *pos, int M, int hd, float base, const float *div, float2 *tab) {
     pdl_launch(); pdl_wait();
     const int half = hd >> 1;
-    for (int u = threadIdx.x; u < M * half; u += blockDim.x) {
+    for (int u = blockIdx.x * blockDim.x + threadIdx.x; u < M * half; u += gridDim.x * blockDim.x) {
         const int tok = u / half, i = u % half;
         float freq = powf(base, -2.0f * (float)i / (float)hd);
         float ang = (float)(*pos + tok) * freq / (div ? div[i] : 1.0f);

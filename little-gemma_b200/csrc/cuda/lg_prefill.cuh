@@ -357,7 +357,7 @@ __global__ void __launch_bounds__(256) lg_pf_qkv_prep_kernel(LgPfPrepArgs a) {
     const int p = *a.pos + tok;
     const int jobs = a.H + (a.owns_kv ? 2 * a.Hkv : 0);
     const float2 *rope = a.rope + (size_t)tok * HALF;
-    for (int j = warp; j < jobs; j += 8) {
+    for (int j = blockIdx.y * 8 + warp; j < jobs; j += 8 * gridDim.y) {     // one head vector per warp
         float v0[PER], v1[PER];
         const int jj = j - a.H, isv = jj >= a.Hkv, kvh = isv ? jj - a.Hkv : jj;
         const float *src = a.qkv + (size_t)tok * a.ld
