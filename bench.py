@@ -62,13 +62,18 @@ def shapes(name):
             "tiny": (s.TINY, s.TINY_HEAD, "tiny q4_0")}[name]
 
 
-def ensure_files(cfg, device):
+def ensure_files(cfg, device, layers=0):
     """Seeded model files under CACHE (rank 0 writes; big ones are generated on the GPU)."""
     s = importlib.import_module("little-gemma_b200.synth")
     t, h, _ = shapes(cfg)
+    tag = cfg
+    if layers > 0:
+        import dataclasses
+        t = dataclasses.replace(t, n_layer=layers)
+        tag = f"{cfg}_l{layers}"
     dev = device if t.weight_bytes() > (1 << 28) else "cpu"
-    tp = s.cached(CACHE, f"{cfg}_seed0_{dev}.gguf", s.write_target, t, 0, dev)
-    hp = s.cached(CACHE, f"{cfg}_head_seed1_{dev}.gguf", s.write_head, h, t, 1, dev)
+    tp = s.cached(CACHE, f"{tag}_seed0_{dev}.gguf", s.write_target, t, 0, dev)
+    hp = s.cached(CACHE, f"{tag}_head_seed1_{dev}.gguf", s.write_head, h, t, 1, dev)
     return tp, hp
 
 
@@ -154,9 +159,17 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--profile-step", action="store_true",
                     help="short path for profilers: load, prefill, W warm-up rounds, K rounds, exit")
+    ap.add_argument("--profile-prefill", type=int, default=None, metavar="CLASSES",
+                    help="short path for profilers: load, model_prefill of 512 tokens, 3 wide prompt blocks of 256 tokens "
+                         "restricted to kernel classes (4 = gate/up matmul, 1023 = everything), exit")
+    ap.add_argument("--layers", type=int, default=0, help="cut the model to this many layers (small profiling cases)")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
     t_shape, h_shape, label = shapes(a.config)
+    if a.layers > 0:
+        import dataclasses
+        t_shape = dataclasses.replace(t_shape, n_layer=a.layers)
+        label += f" cut to {a.layers} layers"
     M = a.mtp_n
     workload = (f"{label}, batch 1, MTP K={M - 1} (verify width {M}), KV depth {a.depth}, "
                 f"oracle-replayed drafts p={a.p}, greedy")
@@ -170,7 +183,7 @@ def main():
             return
         import torch
         dev = "cuda" if torch.cuda.is_available() else "cpu"
-        tp, hp = ensure_files(a.config, dev)
+        tp, hp = ensure_files(a.config, dev, a.layers)
         n = max(1, min(a.steps, a.cpu_tokens))
         tps, info = cpu_reference_run(tp, n, warm=min(a.warmup, 1))
         line = dict(base, impl="reference", value=tps, ms_per_step=1e3 / tps, dtype="f32",
@@ -193,10 +206,10 @@ def main():
     build = importlib.import_module("little-gemma_b200.build")
     if RANK == 0:
         build.build()
-        ensure_files(a.config, "cuda")
+        ensure_files(a.config, "cuda", a.layers)
     if WORLD > 1:
         dist.barrier()
-    tp, hp = ensure_files(a.config, "cuda")
+    tp, hp = ensure_files(a.config, "cuda", a.layers)
     torch.cuda.empty_cache()
 
     V = t_shape.n_vocab
@@ -220,6 +233,16 @@ def main():
     def restart():
         sess.prefill(prompt[:-1], 0)
         return sess.next(int(prompt[-1]), a.depth - 1)
+
+    if a.profile_prefill is not None:
+        sess.prefill(synth.prompt_ids(min(512, max_seq - 8), V, seed=300), 0)
+        n_l = 0
+        for _ in range(3):
+            n_l = sess.prefill_pass(256, a.profile_prefill)
+        torch.cuda.synchronize()
+        print(json.dumps({"profile_prefill": a.profile_prefill, "launches_per_block": n_l, "config": base["config"]}), flush=True)
+        sess.close()
+        return
 
     first = restart()
     pos0 = a.depth
