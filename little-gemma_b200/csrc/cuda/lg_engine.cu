@@ -76,6 +76,8 @@ struct PrefillBuf {
     int *toks = nullptr, *pos = nullptr;                            // token ids; pos[g] = position of the g-th group of 8
     float2 *rope_local = nullptr, *rope_global = nullptr;
     __half *q_hi = nullptr, *q_lo = nullptr;                        // normed + rotated queries [LG_PF_MAXN][H][hd], f16 hi + lo
+    float *tokrow = nullptr, *pproj = nullptr, *ipl = nullptr, *pg = nullptr;   // per-layer-embedding rows [LG_PF_MAXN][ple * n_layer], gate rows
+    __half *a_ple = nullptr;
     int ld_attn = 0, ld_ff = 0;
 };
 
@@ -113,6 +115,7 @@ struct Engine {
     int pdl = 1;                              // programmatic dependent launch (LG_PDL=0 turns it off)
     long long round_launches = 0;
     PrefillBuf pf;
+    float *ssq1 = nullptr, *ssq2 = nullptr; int *gbar = nullptr;     // NORMTAIL scratch: partial sums of squares, grid barrier
     int mm_launches = 0;                      // kernels in the captured matmul-only pass             // kernels in one captured round (lg_rounds_enqueue)
 };
 
@@ -281,6 +284,10 @@ void set_kernel_attributes() {
     gemv_attr_r<1>(); gemv_attr_r<2>(); gemv_attr_r<4>();
     gemv_attr<4, 1, LG_FMT_Q4_0, LG_EPI_GEGLU>(); gemv_attr<4, 2, LG_FMT_Q4_0, LG_EPI_GEGLU>();
     gemv_attr<4, 1, LG_FMT_Q4_K, LG_EPI_GEGLU>(); gemv_attr<4, 2, LG_FMT_Q4_K, LG_EPI_GEGLU>();
+    gemv_attr<4, 1, LG_FMT_Q4_0, LG_EPI_GEGLU | LG_EPI_POST>(); gemv_attr<4, 2, LG_FMT_Q4_0, LG_EPI_GEGLU | LG_EPI_POST>();
+    gemv_attr<4, 1, LG_FMT_Q4_K, LG_EPI_GEGLU | LG_EPI_POST>(); gemv_attr<4, 2, LG_FMT_Q4_K, LG_EPI_GEGLU | LG_EPI_POST>();
+    gemv_attr<2, 1, LG_FMT_Q4_0, LG_EPI_NORMTAIL>(); gemv_attr<2, 2, LG_FMT_Q4_0, LG_EPI_NORMTAIL>();
+    gemv_attr<2, 1, LG_FMT_Q4_K, LG_EPI_NORMTAIL>(); gemv_attr<2, 2, LG_FMT_Q4_K, LG_EPI_NORMTAIL>();
     LG_CHECK(cudaFuncSetAttribute(lg_attn_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
     LG_CHECK(cudaFuncSetAttribute(lg_attn_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
     LG_CHECK(cudaFuncSetAttribute(lg_attn_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
@@ -327,6 +334,7 @@ GemvPlan plan_gemv(const Engine *e, const WMat &W, int np, int want_ks, bool hea
     p.gx = groups < ctas / p.ks ? groups : ctas / p.ks;
     if (head) p.gx = groups < ctas ? groups : ctas;
     if (p.gx < 1) p.gx = 1;
+
     return p;
 }
 
@@ -347,25 +355,62 @@ void launch_gemv_rn(Engine *e, const LgGemvArgs &a, const GemvPlan &p, int fmt, 
 
 struct GemvExtra {
     float softcap = 0.0f; float *logits = nullptr; float *amax_val = nullptr; int *amax_idx = nullptr;
-    const LgPanel *outp = nullptr;            // GeGLU epilogue target
+    const LgPanel *outp = nullptr;            // GeGLU / NORMTAIL epilogue target
     int *ks_out = nullptr, *gx_out = nullptr;
+    // NORMTAIL epilogue
+    float *xres = nullptr; int ldx = 0, n_cols = 0; const float *add_w = nullptr, *norm_w = nullptr; float out_scale = 1.0f, eps = 0.0f;
+    float *ssq1 = nullptr, *ssq2 = nullptr; int *gbar = nullptr;
+    // consumer of a deferred-norm panel
+    const float *post_ss = nullptr; int n_post = 0; float post_n = 1.0f, post_eps = 0.0f;
 };
+
+// Whether the o-projection can carry the residual update and the next norm in its epilogue: one item of 32 rows per
+// CTA, all items resident at once (they meet at a grid-wide barrier), the whole panel in one slice.
+bool normtail_ok(const Engine *e, const WMat &W, int np) {
+    static const int on = env_int("LG_NORMTAIL", 1);
+    const int groups = W.n_row_tiles / 2;
+    size_t smem = (size_t)np * (W.nkp + 1) * 2 * (256 + 32) + 128
+                + (size_t)LG_GEMV_STAGES * (W.fmt == LG_FMT_Q4_K ? gemv_stage_bytes<LG_FMT_Q4_K>() : gemv_stage_bytes<LG_FMT_Q4_0>())
+                + (size_t)LG_GEMV_CW * 2 * np * 64 * 4 + (size_t)np * 128 * 4 + (2 * LG_GEMV_STAGES + 1) * 8 + 16;
+    return on && W.n_row_tiles % 2 == 0 && groups <= 2 * e->sm_count && smem <= 100 * 1024;
+}
 
 // out[ks][tok][ldo] partial sums (EPI_STORE, optional tail), the GeGLU epilogue, or the head epilogue.
 void launch_gemv(Engine *e, const WMat &W, const LgPanel &X, int M, float *out, int epi, int force_ks,
                  const GemvExtra &x = GemvExtra()) {
     int np = M > 4 ? 2 : 1;
     GemvPlan p = plan_gemv(e, W, np, epi == LG_EPI_STORE ? force_ks : 1, epi == LG_EPI_HEAD, epi == LG_EPI_GEGLU);
+    if (epi == LG_EPI_NORMTAIL) {
+        p.r = 2; p.ks = 1; p.gx = W.n_row_tiles / 2;
+        int stage = W.fmt == LG_FMT_Q4_K ? gemv_stage_bytes<LG_FMT_Q4_K>() : gemv_stage_bytes<LG_FMT_Q4_0>();
+        p.smem = (size_t)np * (W.nkp + 1) * 2 * (256 + 32) + 128 + (size_t)LG_GEMV_STAGES * stage
+               + (size_t)LG_GEMV_CW * 2 * np * 64 * 4 + (size_t)np * 128 * 4 + (2 * LG_GEMV_STAGES + 1) * 8 + 16;
+    }
     LgGemvArgs a{};
     a.wq = W.wq; a.ws = W.ws; a.wd = W.wd; a.x = X; a.nkp = W.nkp; a.n_row_tiles = W.n_row_tiles; a.kslices = p.ks;
     a.out = out; a.ldo = W.ldo; a.M = M; a.softcap = x.softcap; a.logits = x.logits; a.n_valid_rows = W.m;
     a.amax_val = x.amax_val; a.amax_idx = x.amax_idx; a.err = e->err;
     if (x.outp) a.outp = *x.outp;
+    a.xres = x.xres; a.ldx = x.ldx; a.n_cols = x.n_cols; a.add_w = x.add_w; a.norm_w = x.norm_w; a.out_scale = x.out_scale; a.eps = x.eps;
+    a.ssq1 = x.ssq1; a.ssq2 = x.ssq2; a.gbar = x.gbar;
+    a.post_ss = x.post_ss; a.n_post = x.n_post; a.post_n = x.post_n; a.post_eps = x.post_eps;
     if (X.nsb * 32 != W.k) { fprintf(stderr, "lg_b200: panel width %d does not match matrix k %d\n", X.nsb * 32, W.k); exit(1); }
     if (x.ks_out) *x.ks_out = p.ks;
     if (x.gx_out) *x.gx_out = p.gx;
+    if (a.post_ss && epi != LG_EPI_GEGLU) { fprintf(stderr, "lg_b200: a deferred norm is only wired into the gate/up matmul\n"); exit(1); }
+    if (epi == LG_EPI_NORMTAIL) {
+        if (np == 1) { if (W.fmt == LG_FMT_Q4_0) launch_gemv_t<2, 1, LG_FMT_Q4_0, LG_EPI_NORMTAIL>(e, a, p); else launch_gemv_t<2, 1, LG_FMT_Q4_K, LG_EPI_NORMTAIL>(e, a, p); }
+        else         { if (W.fmt == LG_FMT_Q4_0) launch_gemv_t<2, 2, LG_FMT_Q4_0, LG_EPI_NORMTAIL>(e, a, p); else launch_gemv_t<2, 2, LG_FMT_Q4_K, LG_EPI_NORMTAIL>(e, a, p); }
+        return;
+    }
     if (epi == LG_EPI_GEGLU) {
         if (W.n_row_tiles % 4) { fprintf(stderr, "lg_b200: GeGLU matmul needs a multiple of 32 outputs\n"); exit(1); }
+        constexpr int GP = LG_EPI_GEGLU | LG_EPI_POST;
+        if (a.post_ss) {     // the panel's norm was deferred: the variant that rescales by 1/rms
+            if (np == 1) { if (W.fmt == LG_FMT_Q4_0) launch_gemv_t<4, 1, LG_FMT_Q4_0, GP>(e, a, p); else launch_gemv_t<4, 1, LG_FMT_Q4_K, GP>(e, a, p); }
+            else         { if (W.fmt == LG_FMT_Q4_0) launch_gemv_t<4, 2, LG_FMT_Q4_0, GP>(e, a, p); else launch_gemv_t<4, 2, LG_FMT_Q4_K, GP>(e, a, p); }
+            return;
+        }
         if (np == 1) { if (W.fmt == LG_FMT_Q4_0) launch_gemv_t<4, 1, LG_FMT_Q4_0, LG_EPI_GEGLU>(e, a, p); else launch_gemv_t<4, 1, LG_FMT_Q4_K, LG_EPI_GEGLU>(e, a, p); }
         else         { if (W.fmt == LG_FMT_Q4_0) launch_gemv_t<4, 2, LG_FMT_Q4_0, LG_EPI_GEGLU>(e, a, p); else launch_gemv_t<4, 2, LG_FMT_Q4_K, LG_EPI_GEGLU>(e, a, p); }
         return;
@@ -518,6 +563,8 @@ Engine *engine_for(const struct model *m) {
     e->pdl = env_int("LG_PDL", 1);
     e->err = dalloc<int>(1);
     e->tickets = dalloc<int>(MAX_KV_HEADS);
+    e->ssq1 = dalloc<float>((size_t)2 * e->sm_count * LG_MAXM); e->ssq2 = dalloc<float>((size_t)2 * e->sm_count * LG_MAXM);
+    e->gbar = dalloc<int>(2);
 
     const int ne = c->n_embd, H = c->n_head, ple = c->n_embd_per_layer;
     const struct gguf_tensor *emb = find_t(g, -1, "token_embd.weight");
@@ -720,17 +767,30 @@ void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags, int 
         aa.n_slots = e->part_slots; aa.part = e->part; aa.part_ml = e->part_ml; aa.out_f32 = nullptr;
         LgPanel pa = e->p_attn; pa.nsb = H * hd / 32;
         aa.out = pa;
+        static const int early_kv = env_int("LG_ATTN_EARLY_KV", 1);
+        aa.early_kv = early_kv && w.owns_kv;     // the target's position and this layer's older rows come from earlier graph launches
         if (only & C_ATTN) launch_attn(e, aa, tiles_for(aa.window, kv->max_seq, M, hd));
 
         // o-projection, then x += norm(o)*w_post_attn and the ffn_norm panel
         int ks_o = 1;
         GemvExtra xo; xo.ks_out = &ks_o;
-        if (only & C_O) launch_gemv(e, w.o, pa, M, e->oout, LG_EPI_STORE, 0, xo); else ks_o = plan_gemv(e, w.o, M > 4 ? 2 : 1, 0, false).ks;
-        if (only & C_NORM) launch_norm(e, M, e->x, ne, ne, c->rms_eps, e->oout, ks_o, (size_t)LG_MAXM * w.o.ldo, w.o.ldo, w.post_attn, 1.0f,
-                    w.ffn_norm, &e->p_ne, nullptr, 0);
+        // (class-isolated timing passes keep the o-projection a pure matmul followed by the norm kernel)
+        const bool tail_o = only == C_ALL && normtail_ok(e, w.o, M > 4 ? 2 : 1);
         // gate/up with the GeGLU epilogue writing the down-projection's panel
         LgPanel pf = e->p_ff; pf.nsb = w.nff / 32;
         GemvExtra xg; xg.outp = &pf;
+        if (tail_o) {
+            // the o-projection's epilogue does the residual update and writes the ffn_norm panel; that norm's 1/rms
+            // is applied by the gate/up matmul's epilogue
+            xo.xres = e->x; xo.ldx = ne; xo.n_cols = ne; xo.add_w = w.post_attn; xo.norm_w = w.ffn_norm; xo.out_scale = 1.0f;
+            xo.eps = c->rms_eps; xo.outp = &e->p_ne; xo.ssq1 = e->ssq1; xo.ssq2 = e->ssq2; xo.gbar = e->gbar;
+            if (only & C_O) launch_gemv(e, w.o, pa, M, nullptr, LG_EPI_NORMTAIL, 1, xo);
+            xg.post_ss = e->ssq2; xg.n_post = w.o.n_row_tiles / 2; xg.post_n = (float)ne; xg.post_eps = c->rms_eps;
+        } else {
+            if (only & C_O) launch_gemv(e, w.o, pa, M, e->oout, LG_EPI_STORE, 0, xo); else ks_o = plan_gemv(e, w.o, M > 4 ? 2 : 1, 0, false).ks;
+            if (only & C_NORM) launch_norm(e, M, e->x, ne, ne, c->rms_eps, e->oout, ks_o, (size_t)LG_MAXM * w.o.ldo, w.o.ldo, w.post_attn, 1.0f,
+                        w.ffn_norm, &e->p_ne, nullptr, 0);
+        }
         if (only & C_GATEUP) launch_gemv(e, w.gateup, e->p_ne, M, nullptr, LG_EPI_GEGLU, 1, xg);
 
         const bool last = l == nl - 1;
@@ -801,15 +861,24 @@ void prefill_alloc(Engine *e) {
     b.rope_global = dalloc<float2>((size_t)LG_PF_MAXN * max_hd / 2);
     b.q_hi = dalloc<__half>((size_t)LG_PF_MAXN * max_attn);
     b.q_lo = dalloc<__half>((size_t)LG_PF_MAXN * max_attn);
+    if (e->has_ple) {
+        const size_t total = e->pmp.ldo;
+        b.tokrow = dalloc<float>((size_t)LG_PF_MAXN * total); b.pproj = dalloc<float>((size_t)LG_PF_MAXN * total);
+        b.ipl = dalloc<float>((size_t)LG_PF_MAXN * total);
+        int max_g = 0;
+        for (auto &w : e->L) max_g = std::max(max_g, w.inp_gate.ldo);
+        b.pg = dalloc<float>((size_t)LG_PF_MAXN * max_g);
+        b.a_ple = dalloc<__half>((size_t)LG_PF_MAXN * c->n_embd_per_layer);
+    }
     b.ready = true;
 }
 
 // x += norm(add)*add_w (optional), x *= out_scale; yh = norm(x)*norm_w as f16 rows.  One CTA per token.
 void launch_norm_pf(Engine *e, int n_tok, float *x, int n, float eps, const float *add, int n_parts, int ld_add, const float *add_w,
-                    float out_scale, const float *norm_w, __half *yh) {
+                    float out_scale, const float *norm_w, __half *yh, bool row_itself = false) {
     LgNormArgs a{};
     a.x = x; a.ldx = n; a.add_src = add; a.n_parts = n_parts; a.part_stride = (size_t)LG_PF_MAXN * ld_add; a.ld_add = ld_add; a.add_w = add_w; a.out_scale = out_scale;
-    a.norm_w = norm_w; a.n = n; a.eps = eps; a.yh = norm_w ? yh : nullptr; a.ldyh = n;
+    a.norm_w = norm_w; a.n = n; a.eps = eps; a.yh = (norm_w || row_itself) ? yh : nullptr; a.ldyh = n;   // row_itself: the f16 row is x, not a norm of it
     int threads = n >= 2048 ? 1024 : (n >= 512 ? 512 : 256);
     launch_k(e, lg_norm_kernel, dim3(n_tok), dim3(threads), (size_t)(2 * n + 32) * 4, a);
 }
@@ -827,6 +896,18 @@ void enqueue_prefill_block(Engine *e, const struct kvcache *kv, int n, int only 
                  (const int *)b.toks, sqrtf((float)ne), b.x, ne);
         launch_k(e, lg_rope_table_kernel, dim3((n + 7) / 8), dim3(256), 0, (const int *)b.pos, n, e->hd_local, c->rope_freq_base_swa, (const float *)nullptr, b.rope_local);
         launch_k(e, lg_rope_table_kernel, dim3((n + 7) / 8), dim3(256), 0, (const int *)b.pos, n, e->hd_global, c->rope_freq_base, (const float *)e->rope_div, b.rope_global);
+    }
+    const int ple = c->n_embd_per_layer, total = ple * nl;
+    if (e->has_ple) {
+        // per-layer inputs of the block: table rows, projection of the embedding rows, their combination
+        if (only & C_MISC) {
+            launch_k(e, lg_dequant_rows, dim3(n), dim3(256), 0, e->ple_table, e->ple_table_type, total, (const int *)b.toks, c->n_vocab, 0,
+                     sqrtf((float)ple), b.tokrow, total);
+            launch_k(e, lg_f32_to_f16_rows, dim3((ne + 255) / 256, n), dim3(256), 0, (const float *)b.x, ne, b.a_ne, ne, ne);
+        }
+        if (only & C_PLE) launch_pf_gemm(e, e->pmp, b.a_ne, LG_PF_MAXN, n, b.pproj, nullptr, 0, LG_PF_STORE);
+        if (only & C_MISC) launch_k(e, lg_ple_build_kernel, dim3(nl, n), dim3(ple), 0, b.pproj, b.tokrow, e->ple_proj_norm, b.ipl, ple, e->pmp.ldo,
+                                    1.0f / sqrtf((float)ne), c->rms_eps);
     }
     if (only & C_NORM) launch_norm_pf(e, n, b.x, ne, c->rms_eps, nullptr, 0, 0, nullptr, 1.0f, e->L[0].attn_norm, b.a_ne);
     for (int l = 0; l < nl; l++) {
@@ -878,15 +959,27 @@ void enqueue_prefill_block(Engine *e, const struct kvcache *kv, int n, int only 
         if (only & C_GATEUP) launch_pf_gemm(e, w.gateup, b.a_ne, LG_PF_MAXN, n, nullptr, b.a_ff, w.nff, LG_PF_GEGLU);
         if (only & C_DOWN) launch_pf_gemm(e, w.down, b.a_ff, LG_PF_MAXN, n, b.o, nullptr, 0, LG_PF_STORE, ks_d);
         const float *next_w = l == nl - 1 ? nullptr : e->L[l + 1].attn_norm;
-        if (only & C_NORM) launch_norm_pf(e, n, b.x, ne, c->rms_eps, b.o, ks_d, w.down.ldo, w.post_ffw, w.out_scale, next_w, b.a_ne);
+        if (e->has_ple) {
+            // x += norm(down) * w_post_ffw; gate = inp_gate(x); x = (x + norm(proj(gelu(gate) * per-layer input)) * w_post_norm) * out_scale
+            if (only & C_NORM) launch_norm_pf(e, n, b.x, ne, c->rms_eps, b.o, ks_d, w.down.ldo, w.post_ffw, 1.0f, nullptr, b.a_ne, true);
+            if (only & C_PLE) launch_pf_gemm(e, w.inp_gate, b.a_ne, LG_PF_MAXN, n, b.pg, nullptr, 0, LG_PF_STORE);
+            if (only & C_MISC) launch_k(e, lg_pf_geglu_rows, dim3((ple + 255) / 256, n), dim3(256), 0, (const float *)b.pg, (const float *)(b.ipl + (size_t)l * ple),
+                                        w.inp_gate.ldo, e->pmp.ldo, ple, b.a_ple, ple);
+            if (only & C_PLE) launch_pf_gemm(e, w.proj, b.a_ple, LG_PF_MAXN, n, b.o, nullptr, 0, LG_PF_STORE);
+            if (only & C_NORM) launch_norm_pf(e, n, b.x, ne, c->rms_eps, b.o, 1, w.proj.ldo, w.post_norm, w.out_scale, next_w, b.a_ne);
+        } else {
+            if (only & C_NORM) launch_norm_pf(e, n, b.x, ne, c->rms_eps, b.o, ks_d, w.down.ldo, w.post_ffw, w.out_scale, next_w, b.a_ne);
+        }
     }
 }
 
 // Whether the wide pass can take this model (LG_PREFILL_WIDE=0 keeps every prompt on the narrow path).
 bool prefill_wide_ok(const Engine *e) {
     static const int on = env_int("LG_PREFILL_WIDE", 1);
-    if (!on || e->has_ple) return false;
+    if (!on) return false;
     for (auto &w : e->L) if (w.o.k != e->m->cfg.n_head * w.hd || w.down.k != w.nff) return false;
+    if (e->has_ple && (e->m->cfg.n_embd_per_layer % 64 || e->m->cfg.n_embd_per_layer > 1024 || e->pmp.ldo != e->m->cfg.n_embd_per_layer * e->m->cfg.n_layer))
+        return false;
     return true;
 }
 

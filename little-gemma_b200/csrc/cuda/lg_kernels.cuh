@@ -307,10 +307,22 @@ struct LgGemvArgs {
     // GeGLU epilogue: rows are interleaved (tile = 8 gate rows then the 8 matching up rows);
     // y = gelu_tanh(gate) * up goes straight into the next matmul's panel
     LgPanel outp;
+    // NORMTAIL epilogue (R = 2: an item's 32 rows are one panel group; one item per CTA, no k slices):
+    // after a grid-wide barrier, x[tok][rows] = (x + rmsnorm(out) * add_w) * out_scale and the next
+    // panel gets x * norm_w -- the 1/rms of that second norm is left to the consumer (post_ss below)
+    float *xres; int ldx;
+    const float *add_w, *norm_w; float out_scale, eps; int n_cols;
+    float *ssq1, *ssq2;        // [groups][LG_MAXM] partial sums of squares: of out, of the new x
+    int *gbar;                 // {arrived, left}, zero between launches
+    // consumer of a panel whose norm was deferred: results are multiplied by 1/rms from these partials
+    const float *post_ss; int n_post; float post_n, post_eps;
 };
 
 enum { LG_FMT_Q4_0 = 0, LG_FMT_Q4_K = 1 };
-enum { LG_EPI_STORE = 0, LG_EPI_HEAD = 1, LG_EPI_GEGLU = 2 };
+// bit 2 (LG_EPI_POST): the input panel's norm was deferred -- results are multiplied by 1/rms from post_ss.
+// A separate instantiation, so the plain epilogues carry none of that code.
+enum { LG_EPI_STORE = 0, LG_EPI_HEAD = 1, LG_EPI_GEGLU = 2, LG_EPI_NORMTAIL = 3, LG_EPI_POST = 4 };
+#define LG_ERR_GRID_BARRIER 256
 
 #define LG_GEMV_CW 8                    // consumer warps per CTA
 #define LG_GEMV_THREADS ((LG_GEMV_CW + 1) * 32)   // + one producer warp
@@ -343,13 +355,15 @@ template <int FMT> __host__ __device__ constexpr int gemv_stage_bytes() {
 //     shared load per lane, `mma.sync.m16n8k32.s8`, f32 scale-accumulate.  Partial sums of the
 //     warps are added in warp order.
 // Every wait is bounded; a timeout raises LG_ERR_MBAR_TIMEOUT and the kernel runs to its end.
-// Dynamic shared memory: panel q | panel s | ring | reduction | mbarriers
+// Dynamic shared memory: panel q | panel s | ring | reduction (| NORMTAIL: final sums) | mbarriers
 template <int R, int NP, int FMT, int EPI>
 __global__ void __launch_bounds__(LG_GEMV_THREADS)
 lg_gemv_kernel(LgGemvArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     constexpr int P = LG_GEMV_STAGE_TILES / R;               // tile positions per stage
     constexpr int NS = LG_GEMV_STAGES;
+    constexpr int EB = EPI & 3;                              // the epilogue proper
+    constexpr bool POST = (EPI & LG_EPI_POST) != 0;
     constexpr int STAGE = gemv_stage_bytes<FMT>();
     constexpr int SC_OFF = LG_GEMV_STAGE_TILES * 512;        // scales after the nibbles, {d,dmin} after the scales
     constexpr int DD_OFF = SC_OFF + LG_GEMV_STAGE_TILES * 64;
@@ -365,7 +379,7 @@ lg_gemv_kernel(LgGemvArgs a) {
     unsigned char *ring = (unsigned char *)(ss + (size_t)NP * nsb_s * 4);
     ring = (unsigned char *)(((uintptr_t)ring + 127) & ~(uintptr_t)127);
     float *red = (float *)(ring + (size_t)NS * STAGE);
-    uint64_t *full = (uint64_t *)(red + LG_GEMV_CW * R * NP * 64);
+    uint64_t *full = (uint64_t *)(red + LG_GEMV_CW * R * NP * 64 + (EB == LG_EPI_NORMTAIL ? NP * 128 : 0));   // NORMTAIL: + fin[tok][32]
     uint64_t *empty = full + NS, *pbar = empty + NS;
 
     pdl_launch();
@@ -422,6 +436,17 @@ lg_gemv_kernel(LgGemvArgs a) {
     for (int j = 0; j < SLOTS; j++) { best_v[j] = -INFINITY; best_i[j] = 0x7fffffff; }
 
     pdl_wait();
+    __shared__ float s_post[POST ? LG_MAXM : 1];
+    if (POST) {
+        // 1/rms of the deferred norm: partial sums of squares added in a fixed order (lane-strided, then the shuffle tree)
+        if (warp < a.M) {
+            float v = 0.0f;
+            for (int i = lane; i < a.n_post; i += 32) v += a.post_ss[(size_t)i * LG_MAXM + warp];
+            v = warp_sum(v);
+            if (lane == 0) s_post[warp] = 1.0f / sqrtf(v / a.post_n + a.post_eps);
+        }
+        consumer_sync();
+    }
     bool ok = mbar_wait(pbar, 0);
     if (!ok && threadIdx.x == 0) atomicOr(a.err, LG_ERR_MBAR_TIMEOUT);
     int stage = 0; uint32_t phase = 0;
@@ -499,7 +524,7 @@ lg_gemv_kernel(LgGemvArgs a) {
                 red[(warp * R * NP + r * NP + p) * 64 + t * 16 + g + 8] = acc[r][p][1];
             }
         consumer_sync();
-        if (EPI == LG_EPI_GEGLU) {
+        if (EB == LG_EPI_GEGLU) {
             // one warp per token: lane o = output (r, row8) of this item's 32 outputs
             for (int tok = warp; tok < NP * 4 && tok < a.M; tok += LG_GEMV_CW) {
                 const int p = tok >> 2, tl = tok & 3, r = lane >> 3, row8 = lane & 7;
@@ -507,9 +532,62 @@ lg_gemv_kernel(LgGemvArgs a) {
                 float gate = 0.0f, up = 0.0f;
                 #pragma unroll
                 for (int w2 = 0; w2 < LG_GEMV_CW; w2++) { gate += red[w2 * R * NP * 64 + ig]; up += red[w2 * R * NP * 64 + ig + 8]; }
-                float y = __fmul_rn(gelu_tanh(gate * 0.0625f), up * 0.0625f);
+                const float sc16 = POST ? 0.0625f * s_post[tok] : 0.0625f;
+                float y = __fmul_rn(gelu_tanh(gate * sc16), up * sc16);
                 quant_group_store(y, lane, tok, rt0 / R, a.outp);
             }
+        } else if (EB == LG_EPI_NORMTAIL) {
+            // (a) the item's final sums: fin[tok][32 rows]
+            float *fin = red + LG_GEMV_CW * R * NP * 64;
+            #pragma unroll
+            for (int j = 0; j < SLOTS; j++) {
+                int idx = threadIdx.x + j * CT;
+                if (idx < R * NP * 64) {
+                    int rp = idx >> 6, r = rp / NP, p = rp % NP, tok = p * 4 + ((idx >> 4) & 3);
+                    float sum = 0.0f;
+                    #pragma unroll
+                    for (int w2 = 0; w2 < LG_GEMV_CW; w2++) sum += red[w2 * R * NP * 64 + idx];
+                    fin[tok * 32 + r * 16 + (idx & 15)] = sum * 0.0625f;
+                }
+            }
+            consumer_sync();
+            // (b) warp tok: this item's sum of squares of token tok; its slice of x and of the two weight vectors
+            const int col = grp * 32 + lane;
+            const bool live = warp < a.M && col < a.n_cols;
+            float o_v = 0.0f, x_v = 0.0f, wa = 0.0f, wn = 0.0f;
+            if (warp < a.M) {
+                o_v = fin[warp * 32 + lane];
+                if (live) { x_v = a.xres[(size_t)warp * a.ldx + col]; wa = a.add_w[col]; wn = a.norm_w ? a.norm_w[col] : 1.0f; }
+                float ss = warp_sum(live ? o_v * o_v : 0.0f);
+                if (lane == 0) a.ssq1[(size_t)grp * LG_MAXM + warp] = ss;
+            }
+            // (c) grid-wide barrier: every item's partial is visible after it (bounded spin)
+            __threadfence();
+            consumer_sync();
+            if (threadIdx.x == 0) {
+                atomicAdd(a.gbar, 1);
+                int it = 0;
+                while (*(volatile int *)a.gbar < n_groups && ++it < (LG_SPIN_LIMIT << 2)) { }
+                if (it >= (LG_SPIN_LIMIT << 2)) atomicOr(a.err, LG_ERR_GRID_BARRIER);
+                __threadfence();
+            }
+            consumer_sync();
+            // (d) 1/rms of the whole row from all partials (fixed order), the residual update, the next panel
+            if (warp < a.M) {
+                float v = 0.0f;
+                for (int i = lane; i < n_groups; i += 32) v += __ldcg(a.ssq1 + (size_t)i * LG_MAXM + warp);
+                v = warp_sum(v);
+                const float s1 = 1.0f / sqrtf(v / (float)a.n_cols + a.eps);
+                float xn = __fadd_rn(x_v, __fmul_rn(__fmul_rn(o_v, s1), wa));
+                xn = __fmul_rn(xn, a.out_scale);
+                if (!live) xn = 0.0f;
+                if (live) a.xres[(size_t)warp * a.ldx + col] = xn;
+                float ss2 = warp_sum(xn * xn);
+                if (lane == 0) a.ssq2[(size_t)grp * LG_MAXM + warp] = ss2;
+                if (grp < a.outp.nsb) quant_group_store(__fmul_rn(xn, wn), lane, warp, grp, a.outp);
+            }
+            // (e) the last CTA to leave re-arms the barrier for the next launch
+            if (threadIdx.x == 0 && atomicAdd(a.gbar + 1, 1) == n_groups - 1) { a.gbar[0] = 0; a.gbar[1] = 0; }
         } else {
             #pragma unroll
             for (int j = 0; j < SLOTS; j++) {
@@ -519,10 +597,10 @@ lg_gemv_kernel(LgGemvArgs a) {
                     float sum = 0.0f;
                     #pragma unroll
                     for (int w2 = 0; w2 < LG_GEMV_CW; w2++) sum += red[w2 * R * NP * 64 + idx];
-                    sum *= 0.0625f;
+                    sum *= POST ? 0.0625f * s_post[tok & (LG_MAXM - 1)] : 0.0625f;
                     int row = (rt0 + r) * 16 + (idx & 15);
                     if (rt0 + r < a.n_row_tiles && tok < a.M) {
-                        if (EPI == LG_EPI_STORE) {
+                        if (EB == LG_EPI_STORE) {
                             a.out[((size_t)ks * LG_MAXM + tok) * a.ldo + row] = sum;
                         } else if (row < a.n_valid_rows) {
                             if (a.softcap > 0.0f) sum = a.softcap * tanhf(sum / a.softcap);
@@ -536,7 +614,7 @@ lg_gemv_kernel(LgGemvArgs a) {
         consumer_sync();
     }
 
-    if (EPI == LG_EPI_HEAD) {
+    if (EB == LG_EPI_HEAD) {
         // candidates of this CTA: one per (slot, thread); merge per token (larger value, lower index on ties)
         float *cv = red; int *ci = (int *)(red + R * NP * 64);
         #pragma unroll
@@ -793,6 +871,7 @@ struct LgAttnArgs {
     // raw projection rows [M][ld] = [q (H*hd) | k (Hkv*hd) | v (Hkv*hd)]; q_ready: q is [M][H][hd], final
     const float *qkv; int ld; int q_ready;
     int has_v, owns_kv;                  // v projection present; this layer writes K/V rows
+    int early_kv;                        // the tile's cached rows may be fetched before the dependency wait (see the kernel)
     const float *q_norm, *k_norm; float eps;
     const float2 *rope;                  // [M][hd/2] (cos, sin) of this layer kind at the block's positions
     __half *kc, *vc; int seq, kv_dim;
@@ -884,7 +963,9 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) 
     pdl_launch();
     if (!a.q_ready)
         for (int i = threadIdx.x; i < HD; i += LG_ATTN_THREADS) { s_qn[i] = a.q_norm[i]; s_kn[i] = a.k_norm ? a.k_norm[i] : 1.0f; }
-    pdl_wait();
+    // early_kv: the position and the cached rows below the block were written by earlier graph launches (this layer
+    // writes its own rows, and only here), so the tile may start streaming before the previous kernel has finished
+    if (!a.early_kv) pdl_wait();
     constexpr int S = lg_attn_tile(HD), LDH = HD + 8, LDP = S + 8, PER = HD / 64, HALF = HD / 2, NW = LG_ATTN_THREADS / 32;
     const int kvh = blockIdx.x, gqa = a.H / a.Hkv, nq = gqa * a.M, nq16 = (nq + 15) & ~15;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -919,6 +1000,7 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) 
             *(uint4 *)dv = make_uint4(0, 0, 0, 0);
         }
     }
+    if (a.early_kv) pdl_wait();
 
     // ---- 2. queries: per-head RMSNorm + RoPE, split into f16 hi + lo ----
     for (int qi = warp; qi < nq16; qi += NW) {

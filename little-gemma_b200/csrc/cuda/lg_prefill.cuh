@@ -316,6 +316,15 @@ __global__ void __launch_bounds__(LG_PF_THREADS) lg_pf_gemm_kernel(const __grid_
     }
 }
 
+// y = gelu_tanh(gate) * up as f16 rows (per-layer-embedding gate of a prompt block)
+__global__ void lg_pf_geglu_rows(const float *__restrict__ gate, const float *__restrict__ up, int ld_g, int ld_u, int n,
+                                 __half *__restrict__ out, int ld_out) {
+    pdl_launch(); pdl_wait();
+    const int tok = blockIdx.y;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+        out[(size_t)tok * ld_out + i] = __float2half_rn(__fmul_rn(gelu_tanh(gate[(size_t)tok * ld_g + i]), up[(size_t)tok * ld_u + i]));
+}
+
 // f32 rows -> f16 rows (the B operand of the wide matmul)
 __global__ void lg_f32_to_f16_rows(const float *__restrict__ src, int ld_src, __half *__restrict__ dst, int ld_dst, int n) {
     pdl_launch(); pdl_wait();
