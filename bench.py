@@ -385,7 +385,7 @@ def main():
     if prefill_rec and "matmul_block" in prefill_rec:
         tpeak = float(peaks.get("bf16_tflops_sustained", 1400.0))
         prefill_rec["matmul_block"].update(peak=tpeak, frac=prefill_rec["matmul_block"]["achieved"] / tpeak,
-                                           peak_source=("measured (MEASURED_PEAKS.json bf16_tflops_sustained: the pass is 192 "
+                                           peak_source=("measured (MEASURED_PEAKS.json bf16_tflops_sustained: the pass is a few ms of "
                                                         "back-to-back launches)" if peaks else "fallback 1400 TFLOP/s sustained"))
 
     # aggregate over replicas
