@@ -310,8 +310,20 @@ GemvPlan plan_gemv(const Engine *e, const WMat &W, int np, int want_ks, bool hea
     static const int force_r = env_int("LG_GEMV_R", 0), force_ks = env_int("LG_GEMV_KS", 0);
     p.r = 0; p.ks = want_ks;
     int ks_lo = want_ks > 0 ? want_ks : 1, ks_hi = want_ks > 0 ? want_ks : e->max_ks;
-    for (int ks = ks_lo; ks <= ks_hi && !p.r; ks *= 2) {
+    // First choice: a single wave -- as many items as fit the resident CTAs at once (one item per CTA, no second
+    // item's fill/drain behind the first), fewer k slices and fatter items on ties.
+    int best = 0;
+    for (int ks = ks_lo; ks <= ks_hi; ks *= 2) {
         if (W.nkp / ks > 80 && ks < ks_hi) continue;                      // keep a slice's panel below ~45 KB
+        if (ks > W.nkp) break;
+        for (int r = 4; r >= 1; r >>= 1) {
+            int items = ((W.n_row_tiles + r - 1) / r) * ks;
+            if (items <= ctas && items > best) { best = items; p.r = r; p.ks = ks; }
+        }
+    }
+    if (best * 2 < ctas) p.r = 0;                                         // too few items for one wave: several waves instead
+    for (int ks = ks_lo; ks <= ks_hi && !p.r; ks *= 2) {
+        if (W.nkp / ks > 80 && ks < ks_hi) continue;
         if (ks > W.nkp) break;
         for (int r = 4; r >= 1; r >>= 1)
             if (((W.n_row_tiles + r - 1) / r) * ks >= 3 * ctas / 2 || (ks == ks_hi && r == 1)) { p.r = r; p.ks = ks; break; }

@@ -527,14 +527,18 @@ lg_gemv_kernel(LgGemvArgs a) {
         if (EB == LG_EPI_GEGLU) {
             // one warp per token: lane o = output (r, row8) of this item's 32 outputs
             for (int tok = warp; tok < NP * 4 && tok < a.M; tok += LG_GEMV_CW) {
-                const int p = tok >> 2, tl = tok & 3, r = lane >> 3, row8 = lane & 7;
-                const int ig = ((r * NP + p) * 4 + tl) * 16 + row8;
-                float gate = 0.0f, up = 0.0f;
-                #pragma unroll
-                for (int w2 = 0; w2 < LG_GEMV_CW; w2++) { gate += red[w2 * R * NP * 64 + ig]; up += red[w2 * R * NP * 64 + ig + 8]; }
+                const int p = tok >> 2, tl = tok & 3, row8 = lane & 7;
                 const float sc16 = POST ? 0.0625f * s_post[tok] : 0.0625f;
-                float y = __fmul_rn(gelu_tanh(gate * sc16), up * sc16);
-                quant_group_store(y, lane, tok, rt0 / R, a.outp);
+                #pragma unroll
+                for (int rh = 0; rh < R / 4; rh++) {
+                    const int r = rh * 4 + (lane >> 3);
+                    const int ig = ((r * NP + p) * 4 + tl) * 16 + row8;
+                    float gate = 0.0f, up = 0.0f;
+                    #pragma unroll
+                    for (int w2 = 0; w2 < LG_GEMV_CW; w2++) { gate += red[w2 * R * NP * 64 + ig]; up += red[w2 * R * NP * 64 + ig + 8]; }
+                    float y = __fmul_rn(gelu_tanh(gate * sc16), up * sc16);
+                    quant_group_store(y, lane, tok, rt0 / 4 + rh, a.outp);
+                }
             }
         } else if (EB == LG_EPI_NORMTAIL) {
             // (a) the item's final sums: fin[tok][32 rows]
