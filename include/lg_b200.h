@@ -41,8 +41,10 @@ int  model_forward_next(struct model *m, struct kvcache *kv, int token, int pos)
 /* Fill the cache for tokens[0..n) at pos0.., no head.
  * Replaces: include/model.h:123 (src/cuda/prefill-kernel.cuh:631-675). */
 void model_prefill(struct model *m, struct kvcache *kv, const int *tokens, int n, int pos0);
-/* Media-row prefill forms: outside the speculative-decode path; _embd exits with a message,
- * _mixed accepts all-text spans.  Replaces: include/model.h:133,143 (prefill-kernel.cuh:678-810). */
+/* Media-row prefill forms: rows = f32 embedding rows [.][n_embd] that enter in place of token
+ * embeddings as they are (the per-layer table row of token 0 goes with them); _mixed: ids[i] >= 0
+ * is a token id, ids[i] < 0 names row -ids[i]-1.  Replaces: include/model.h:133,143
+ * (src/cuda/prefill-kernel.cuh:678-810; arithmetic: src/cpu/model-cpu.c:459-465,489-497). */
 void model_prefill_embd(struct model *m, struct kvcache *kv, const float *rows, int n, int pos0);
 void model_prefill_mixed(struct model *m, struct kvcache *kv, const float *rows, const int *ids, int n, int pos0);
 /* No-op here (buffers are sized at load).  Replaces: include/model.h:149. */

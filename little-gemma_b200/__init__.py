@@ -57,6 +57,8 @@ def load() -> C.CDLL:
     L.lgs_last_hidden.argtypes = [C.c_void_p, _f32p]
     L.lgs_next.argtypes = [C.c_void_p, C.c_int, C.c_int]; L.lgs_next.restype = C.c_int
     L.lgs_prefill.argtypes = [C.c_void_p, _i32p, C.c_int, C.c_int]
+    L.lgs_prefill_mixed.argtypes = [C.c_void_p, _f32p, _i32p, C.c_int, C.c_int]
+    L.lgs_prefill_embd.argtypes = [C.c_void_p, _f32p, C.c_int, C.c_int]
     L.lgs_spec.argtypes = [C.c_void_p, _i32p, C.c_int, _i32p]; L.lgs_spec.restype = C.c_int
     L.lgs_draft.argtypes = [C.c_void_p, C.c_int, C.c_int]; L.lgs_draft.restype = C.c_int
     L.lgs_draft_chain.argtypes = [C.c_void_p, C.c_int, C.c_int]; L.lgs_draft_chain.restype = C.c_int
@@ -201,6 +203,17 @@ class Session:
     def prefill(self, toks, pos0: int = 0):
         toks = np.ascontiguousarray(toks, dtype=np.int32)
         self.L.lgs_prefill(self.h, toks, len(toks), pos0)
+
+    def prefill_mixed(self, rows, ids, pos0: int = 0):
+        """model_prefill_mixed: ids[i] >= 0 is a token id, ids[i] < 0 names embedding row -ids[i]-1 of `rows` [n_rows, n_embd]."""
+        rows = np.ascontiguousarray(rows, dtype=np.float32).reshape(-1)
+        ids = np.ascontiguousarray(ids, dtype=np.int32)
+        self.L.lgs_prefill_mixed(self.h, rows, ids, len(ids), pos0)
+
+    def prefill_embd(self, rows, pos0: int = 0):
+        """model_prefill_embd: every position is an embedding row."""
+        rows = np.ascontiguousarray(rows, dtype=np.float32)
+        self.L.lgs_prefill_embd(self.h, rows.reshape(-1), rows.shape[0], pos0)
 
     def spec(self, toks, pos: int):
         toks = np.ascontiguousarray(toks, dtype=np.int32)

@@ -78,6 +78,7 @@ struct PrefillBuf {
     __half *q_hi = nullptr, *q_lo = nullptr;                        // normed + rotated queries [LG_PF_MAXN][H][hd], f16 hi + lo
     float *tokrow = nullptr, *pproj = nullptr, *ipl = nullptr, *pg = nullptr;   // per-layer-embedding rows [LG_PF_MAXN][ple * n_layer], gate rows
     __half *a_ple = nullptr;
+    float *rows = nullptr; int *ridx = nullptr;                     // media rows of the block and, per token, its row or -1
     int ld_attn = 0, ld_ff = 0;
 };
 
@@ -735,7 +736,7 @@ void bind_kv(Engine *e, const struct kvcache *kv) {
 // ------------------------------------------------------------------------------------------
 // the forward of M token rows (enqueue only; captured into graphs by the callers)
 // ------------------------------------------------------------------------------------------
-enum { F_HEAD = 1, F_LOGITS = 2, F_ACCEPT = 4, F_ADVANCE = 8 };
+enum { F_HEAD = 1, F_LOGITS = 2, F_ACCEPT = 4, F_ADVANCE = 8, F_NOEMBED = 16 };   // NOEMBED: x rows are already in place
 
 // `only` selects kernel classes (the benchmark times them in isolation); the default runs everything.
 enum { C_QKV = 1, C_O = 2, C_GATEUP = 4, C_DOWN = 8, C_HEAD = 16, C_PLE = 32, C_NORM = 64, C_ATTN = 256, C_MISC = 512,
@@ -748,8 +749,9 @@ void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags, int 
     cudaStream_t s = e->stream;
     const int *d_toks = e->st->toks, *d_pos = &e->st->pos;
 
-    if (only & C_MISC) launch_k(e, lg_embed_rows, dim3(M), dim3(256), 0, e->head.wq, e->head.ws, e->head.wd, e->head.fmt, e->head.nkp, e->head.m, d_toks,
-                                    sqrtf((float)ne), e->x, ne);
+    if ((only & C_MISC) && !(flags & F_NOEMBED))
+        launch_k(e, lg_embed_rows, dim3(M), dim3(256), 0, e->head.wq, e->head.ws, e->head.wd, e->head.fmt, e->head.nkp, e->head.m, d_toks,
+                 sqrtf((float)ne), e->x, ne);
     const int total = ple * nl;
     if (e->has_ple) {
         if (only & C_MISC) launch_k(e, lg_dequant_rows, dim3(M), dim3(256), 0, e->ple_table, e->ple_table_type, total, d_toks, c->n_vocab, 0, sqrtf((float)ple), e->tokrow, total);
@@ -873,6 +875,7 @@ void prefill_alloc(Engine *e) {
     b.rope_global = dalloc<float2>((size_t)LG_PF_MAXN * max_hd / 2);
     b.q_hi = dalloc<__half>((size_t)LG_PF_MAXN * max_attn);
     b.q_lo = dalloc<__half>((size_t)LG_PF_MAXN * max_attn);
+    b.rows = dalloc<float>((size_t)LG_PF_MAXN * ne); b.ridx = dalloc<int>(LG_PF_MAXN);
     if (e->has_ple) {
         const size_t total = e->pmp.ldo;
         b.tokrow = dalloc<float>((size_t)LG_PF_MAXN * total); b.pproj = dalloc<float>((size_t)LG_PF_MAXN * total);
@@ -899,13 +902,14 @@ void launch_norm_pf(Engine *e, int n_tok, float *x, int n, float eps, const floa
 // fills the KV rows of every layer.  The layer matmuls see all n tokens at once; attention walks the block in
 // groups of LG_MAXM query rows with the decode step's kernel, so a group's keys include the rows of the groups
 // before it.  Models with per-layer embeddings take the narrow path instead.
-void enqueue_prefill_block(Engine *e, const struct kvcache *kv, int n, int only = C_ALL) {
+void enqueue_prefill_block(Engine *e, const struct kvcache *kv, int n, int only = C_ALL, bool media = false) {
     const struct config *c = &e->m->cfg;
     const int ne = c->n_embd, H = c->n_head, nl = c->n_layer;
     PrefillBuf &b = e->pf;
     if (only & C_MISC) {
         launch_k(e, lg_embed_rows, dim3(n), dim3(256), 0, e->head.wq, e->head.ws, e->head.wd, e->head.fmt, e->head.nkp, e->head.m,
                  (const int *)b.toks, sqrtf((float)ne), b.x, ne);
+        if (media) launch_k(e, lg_inject_rows, dim3(n), dim3(256), 0, b.x, ne, (const float *)b.rows, (const int *)b.ridx, ne);
         launch_k(e, lg_rope_table_kernel, dim3((n + 7) / 8), dim3(256), 0, (const int *)b.pos, n, e->hd_local, c->rope_freq_base_swa, (const float *)nullptr, b.rope_local);
         launch_k(e, lg_rope_table_kernel, dim3((n + 7) / 8), dim3(256), 0, (const int *)b.pos, n, e->hd_global, c->rope_freq_base, (const float *)e->rope_div, b.rope_global);
     }
@@ -1282,41 +1286,81 @@ int model_forward_next(struct model *m, struct kvcache *kv, int token, int pos) 
     return out[0];
 }
 
-void model_prefill(struct model *m, struct kvcache *kv, const int *tokens, int n, int pos0) {
+// The prompt pass.  ids[i] >= 0: token id; ids[i] < 0 (only with rows): media position, embedding row -ids[i]-1 of
+// `rows` enters as it is and the per-layer table row of token 0 is used (src/cpu/model-cpu.c:459-465,489-497).
+static void prefill_impl(struct model *m, struct kvcache *kv, const float *rows, const int *ids, int n, int pos0) {
     Engine *e = engine_for(m);
+    const int ne = m->cfg.n_embd;
+    std::vector<int> toks(n), ridx(n, -1);
+    bool media = false;
+    for (int i = 0; i < n; i++) {
+        toks[i] = ids[i] >= 0 ? ids[i] : 0;
+        if (ids[i] < 0) { if (!rows) { fprintf(stderr, "lg_b200: a media position without embedding rows\n"); exit(1); } media = true; }
+    }
     int i = 0;
     if (prefill_wide_ok(e) && n >= 4 * LG_MAXM) {
         // whole blocks of up to LG_PF_MAXN tokens (a multiple of the attention group) on the wide pass
         bind_kv(e, kv);
         prefill_alloc(e);
         int gpos[LG_PF_MAXN / LG_MAXM];
+        std::vector<float> stage;
         while (n - i >= 4 * LG_MAXM) {
             const int b = std::min(LG_PF_MAXN, (n - i) / LG_MAXM * LG_MAXM);
             for (int g = 0; g < LG_PF_MAXN / LG_MAXM; g++) gpos[g] = pos0 + i + g * LG_MAXM;
-            LG_CHECK(cudaMemcpyAsync(e->pf.toks, tokens + i, sizeof(int) * b, cudaMemcpyHostToDevice, e->stream));
+            bool blk_media = false;
+            if (media) {                                 // this block's media rows, packed
+                stage.clear();
+                for (int j = 0; j < b; j++) {
+                    ridx[i + j] = -1;
+                    if (ids[i + j] < 0) {
+                        ridx[i + j] = (int)(stage.size() / ne);
+                        const float *r = rows + (size_t)(-ids[i + j] - 1) * ne;
+                        stage.insert(stage.end(), r, r + ne);
+                        blk_media = true;
+                    }
+                }
+                if (blk_media) {
+                    LG_CHECK(cudaMemcpyAsync(e->pf.rows, stage.data(), stage.size() * sizeof(float), cudaMemcpyHostToDevice, e->stream));
+                    LG_CHECK(cudaMemcpyAsync(e->pf.ridx, ridx.data() + i, sizeof(int) * b, cudaMemcpyHostToDevice, e->stream));
+                }
+            }
+            LG_CHECK(cudaMemcpyAsync(e->pf.toks, toks.data() + i, sizeof(int) * b, cudaMemcpyHostToDevice, e->stream));
             LG_CHECK(cudaMemcpyAsync(e->pf.pos, gpos, sizeof gpos, cudaMemcpyHostToDevice, e->stream));
-            enqueue_prefill_block(e, kv, b);
-            LG_CHECK(cudaStreamSynchronize(e->stream));  // gpos and the caller's ids are read by the copies above
+            enqueue_prefill_block(e, kv, b, C_ALL, blk_media);
+            LG_CHECK(cudaStreamSynchronize(e->stream));  // the host staging above is read by the copies
             i += b;
         }
         check_err(e);
     }
     for (; i < n; i += LG_MAXM) {
         int b = n - i < LG_MAXM ? n - i : LG_MAXM;
-        upload_round(e, tokens + i, b, pos0 + i);
-        run_forward(e, kv, b, 0);
+        upload_round(e, toks.data() + i, b, pos0 + i);
+        bool blk_media = false;
+        for (int j = 0; j < b; j++) blk_media |= ids[i + j] < 0;
+        if (blk_media) {
+            // token embeddings first, then the media rows over them; the forward then starts from x as it stands
+            launch_k(e, lg_embed_rows, dim3(b), dim3(256), 0, e->head.wq, e->head.ws, e->head.wd, e->head.fmt, e->head.nkp, e->head.m,
+                     (const int *)e->st->toks, sqrtf((float)ne), e->x, ne);
+            for (int j = 0; j < b; j++)
+                if (ids[i + j] < 0)
+                    LG_CHECK(cudaMemcpyAsync(e->x + (size_t)j * ne, rows + (size_t)(-ids[i + j] - 1) * ne, sizeof(float) * ne,
+                                             cudaMemcpyHostToDevice, e->stream));
+        }
+        run_forward(e, kv, b, blk_media ? F_NOEMBED : 0);
         LG_CHECK(cudaStreamSynchronize(e->stream));      // st_host is reused by the next upload
     }
 }
 
+void model_prefill(struct model *m, struct kvcache *kv, const int *tokens, int n, int pos0) {
+    prefill_impl(m, kv, nullptr, tokens, n, pos0);
+}
 void model_prefill_embd(struct model *m, struct kvcache *kv, const float *rows, int n, int pos0) {
-    (void)m; (void)kv; (void)rows; (void)n; (void)pos0;
-    fprintf(stderr, "lg_b200: model_prefill_embd (media rows) is outside the speculative-decode path and not built\n");
-    exit(1);
+    std::vector<int> ids(n);
+    for (int i = 0; i < n; i++) ids[i] = -(i + 1);
+    prefill_impl(m, kv, rows, ids.data(), n, pos0);
 }
 void model_prefill_mixed(struct model *m, struct kvcache *kv, const float *rows, const int *ids, int n, int pos0) {
-    for (int i = 0; i < n; i++) if (ids[i] < 0) { model_prefill_embd(m, kv, rows, n, pos0); return; }
-    model_prefill(m, kv, ids, n, pos0);
+    prefill_impl(m, kv, rows, ids, n, pos0);
 }
 void model_prefill_reserve(void) {}
 

@@ -325,6 +325,14 @@ __global__ void lg_pf_geglu_rows(const float *__restrict__ gate, const float *__
         out[(size_t)tok * ld_out + i] = __float2half_rn(__fmul_rn(gelu_tanh(gate[(size_t)tok * ld_g + i]), up[(size_t)tok * ld_u + i]));
 }
 
+// Media positions of a prompt block: x[tok] = rows[ridx[tok]] where ridx[tok] >= 0 (the row replaces the token embedding as it is)
+__global__ void lg_inject_rows(float *__restrict__ x, int ldx, const float *__restrict__ rows, const int *__restrict__ ridx, int n) {
+    pdl_launch(); pdl_wait();
+    const int tok = blockIdx.x, r = ridx[tok];
+    if (r < 0) return;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) x[(size_t)tok * ldx + i] = rows[(size_t)r * n + i];
+}
+
 // f32 rows -> f16 rows (the B operand of the wide matmul)
 __global__ void lg_f32_to_f16_rows(const float *__restrict__ src, int ld_src, __half *__restrict__ dst, int ld_dst, int n) {
     pdl_launch(); pdl_wait();

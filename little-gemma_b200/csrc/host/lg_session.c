@@ -61,6 +61,10 @@ void lgs_forward(void *p, int tok, int pos, float *logits) {
 void lgs_last_hidden(void *p, float *out) { lg_last_hidden(&((struct lg_session *)p)->m, out); }
 int  lgs_next(void *p, int tok, int pos) { struct lg_session *s = p; return model_forward_next(&s->m, &s->kv, tok, pos); }
 void lgs_prefill(void *p, const int *toks, int n, int pos0) { struct lg_session *s = p; model_prefill(&s->m, &s->kv, toks, n, pos0); }
+void lgs_prefill_mixed(void *p, const float *rows, const int *ids, int n, int pos0) {
+    struct lg_session *s = p; model_prefill_mixed(&s->m, &s->kv, rows, ids, n, pos0);
+}
+void lgs_prefill_embd(void *p, const float *rows, int n, int pos0) { struct lg_session *s = p; model_prefill_embd(&s->m, &s->kv, rows, n, pos0); }
 int  lgs_spec(void *p, const int *toks, int pos, int *out) {
     struct lg_session *s = p; return lg_forward_spec_n(&s->m, &s->kv, s->mtp_n, toks, pos, out);
 }

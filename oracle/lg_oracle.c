@@ -130,7 +130,9 @@ static void attend(float *out, const float *q, int n_head, int hd, int gqa, cons
 
 /* One position through the decoder (model-cpu.c:267-294 PLE inputs, :301-448 layers and head,
  * :450-457 embedding scale).  logits == NULL skips the head. */
-static void forward(struct orc *o, int tok, int pos, float *logits) {
+/* `row` != NULL: a media position -- the given embedding row enters as it is and the per-layer table row of
+ * token 0 (padding) is used (model-cpu.c:459-465, 489-497) */
+static void forward_row(struct orc *o, int tok, const float *row, int pos, float *logits) {
     struct model *m = &o->m;
     const struct config *c = &m->cfg;
     const struct gguf_context *g = o->g;
@@ -146,6 +148,7 @@ static void forward(struct orc *o, int tok, int pos, float *logits) {
     float *g1 = malloc(sizeof(float) * c->n_ff), *g2 = malloc(sizeof(float) * c->n_ff);
     float *att = malloc(sizeof(float) * (pos + 1)), *pg = malloc(sizeof(float) * (ple > 0 ? ple : 1));
     for (int i = 0; i < ne; i++) x[i] *= sqrtf((float)ne);
+    if (row) memcpy(x, row, sizeof(float) * ne);
 
     float *ipl = NULL;                                            /* per-layer inputs */
     const struct gguf_tensor *pte = ple > 0 ? T(g, -1, "per_layer_token_embd.weight") : NULL;
@@ -225,6 +228,8 @@ static void forward(struct orc *o, int tok, int pos, float *logits) {
     }
     free(x); free(h); free(q); free(xb); free(kb); free(vb); free(ob); free(g1); free(g2); free(att); free(pg); free(ipl);
 }
+
+static void forward(struct orc *o, int tok, int pos, float *logits) { forward_row(o, tok, NULL, pos, logits); }
 
 static int argmax_first(const float *v, int n) {                     /* model-cpu.c:476-478 */
     int b = 0;
@@ -341,6 +346,14 @@ int orc_next(void *p, int tok, int pos) {
 }
 void orc_prefill(void *p, const int *toks, int n, int pos0) {
     for (int i = 0; i < n; i++) forward(p, toks[i], pos0 + i, NULL);
+}
+/* ids[i] >= 0: token; ids[i] < 0: row -ids[i]-1 of `rows` (model-cpu.c:489-497) */
+void orc_prefill_mixed(void *p, const float *rows, const int *ids, int n, int pos0) {
+    struct orc *o = p;
+    for (int i = 0; i < n; i++) {
+        if (ids[i] >= 0) forward(o, ids[i], pos0 + i, NULL);
+        else forward_row(o, 0, rows + (size_t)(-ids[i] - 1) * o->m.cfg.n_embd, pos0 + i, NULL);
+    }
 }
 /* verify block, sequentially: forwards stop at the first draft that fails (model-cpu.c:51-58) */
 int orc_spec(void *p, const int *toks, int pos, int *out) {

@@ -53,6 +53,7 @@ class _Oracle:
         f("last_hidden").argtypes = [C.c_void_p, _f32p]; f("last_hidden").restype = None
         f("next").argtypes = [C.c_void_p, C.c_int, C.c_int]; f("next").restype = C.c_int
         f("prefill").argtypes = [C.c_void_p, _i32p, C.c_int, C.c_int]; f("prefill").restype = None
+        f("prefill_mixed").argtypes = [C.c_void_p, _f32p, _i32p, C.c_int, C.c_int]; f("prefill_mixed").restype = None
         f("spec").argtypes = [C.c_void_p, _i32p, C.c_int, _i32p]; f("spec").restype = C.c_int
         f("draft").argtypes = [C.c_void_p, C.c_int, C.c_int]; f("draft").restype = C.c_int
         f("kv_row").argtypes = [C.c_void_p, C.c_int, C.c_int, _f32p, _f32p]; f("kv_row").restype = C.c_int
@@ -89,6 +90,12 @@ class _Oracle:
     def prefill(self, toks, pos0: int = 0):
         toks = np.ascontiguousarray(toks, dtype=np.int32)
         self._f("prefill")(self.h, toks, len(toks), pos0)
+
+    def prefill_mixed(self, rows, ids, pos0: int = 0):
+        """ids[i] >= 0: token id; ids[i] < 0: embedding row -ids[i]-1 of `rows` [n_rows, n_embd] (a media position)."""
+        rows = np.ascontiguousarray(rows, dtype=np.float32).reshape(-1)
+        ids = np.ascontiguousarray(ids, dtype=np.int32)
+        self._f("prefill_mixed")(self.h, rows, ids, len(ids), pos0)
 
     def spec(self, toks, pos: int):
         toks = np.ascontiguousarray(toks, dtype=np.int32)

@@ -79,6 +79,10 @@ int ref_next(void *h, int tok, int pos) {
     struct ref_session *s = h;
     return model_forward_next(&s->m, &s->kv, tok, pos);
 }
+void ref_prefill_mixed(void *h, const float *rows, const int *ids, int n, int pos0) {
+    struct ref_session *s = h;
+    model_prefill_mixed(&s->m, &s->kv, rows, ids, n, pos0);
+}
 void ref_prefill(void *h, const int *toks, int n, int pos0) {
     struct ref_session *s = h;
     model_prefill(&s->m, &s->kv, toks, n, pos0);

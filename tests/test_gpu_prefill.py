@@ -123,3 +123,47 @@ def test_wide_prefill_then_mtp_equals_plain(lg):
         rp = s.replay_drafts(plain, g.n_vocab, 0.7)
         mtp, _ = g.generate_device(prompt, 96, 2, rp)
     assert np.array_equal(plain[:96], mtp[:96])
+
+
+@pytest.mark.parametrize("name,n", [("mid", 100), ("tiny", 70), ("mid", 13)])
+def test_mixed_prefill_matches_oracle(lg, port_built, name, n):
+    """model_prefill_mixed / model_prefill_embd: media positions take an embedding row as it is (wide blocks and the
+    narrow 8-token tail both), then the next steps' logits against the CPU oracle."""
+    from oracle.pyref import PortOracle
+    s = synth_module()
+    tp, _ = model_files(name)
+    o = PortOracle(tp, None, 256, True, 4)
+    rng = np.random.default_rng(41)
+    toks = s.prompt_ids(n + 3, o.n_vocab, seed=23)
+    n_rows = 9
+    rows = (rng.standard_normal((n_rows, o.n_embd)) * 2.0).astype(np.float32)
+    ids = toks[:n].astype(np.int32).copy()
+    where = rng.choice(n, size=n_rows, replace=False)
+    where[0] = n - 1                                     # one media position in the narrow tail
+    for r, w in enumerate(where):
+        ids[w] = -(r + 1)
+    o.prefill_mixed(rows, ids, 0)
+    with lg.Session(tp, None, 256) as g:
+        g.prefill_mixed(rows, ids, 0)
+        for i in range(n, n + 3):
+            want, got = o.forward(int(toks[i]), i), g.forward(int(toks[i]), i)
+            assert np.abs(got - want).max() / (want.max() - want.min()) <= 1e-2
+    o.close()
+
+
+def test_embd_prefill_matches_oracle(lg, port_built):
+    from oracle.pyref import PortOracle
+    s = synth_module()
+    tp, _ = model_files("mid")
+    o = PortOracle(tp, None, 256, True, 4)
+    rng = np.random.default_rng(42)
+    n = 45
+    rows = (rng.standard_normal((n, o.n_embd)) * 2.0).astype(np.float32)
+    o.prefill_mixed(rows, -(np.arange(n, dtype=np.int32) + 1), 0)
+    toks = s.prompt_ids(3, o.n_vocab, seed=24)
+    with lg.Session(tp, None, 256) as g:
+        g.prefill_embd(rows, 0)
+        for i in range(3):
+            want, got = o.forward(int(toks[i]), n + i), g.forward(int(toks[i]), n + i)
+            assert np.abs(got - want).max() / (want.max() - want.min()) <= 1e-2
+    o.close()

@@ -91,6 +91,25 @@ def test_port_bit_exact_vs_compiled_reference(port_built, name):
     assert np.array_equal(ga, gb)
 
 
+@pytest.mark.skipif(not has_ref(4), reason="compiled reference backend not present")
+@pytest.mark.parametrize("name", ["tiny", "mid"])
+def test_port_mixed_prefill_bit_exact_vs_compiled_reference(port_built, name):
+    """Media positions (embedding rows in place of token ids; token 0's per-layer row on models that have one)."""
+    from oracle.pyref import PortOracle, RefOracle
+    s = synth_module()
+    tp, _ = model_files(name)
+    a, b = RefOracle(tp, None, 128, True, 4), PortOracle(tp, None, 128, True, 4)
+    rng = np.random.default_rng(31)
+    toks = s.prompt_ids(14, a.n_vocab, seed=5)
+    rows = rng.standard_normal((3, a.n_embd)).astype(np.float32)
+    ids = toks.astype(np.int32).copy()
+    ids[[2, 3, 9]] = [-1, -3, -2]                       # rows 0, 2, 1
+    a.prefill_mixed(rows, ids[:13], 0); b.prefill_mixed(rows, ids[:13], 0)
+    la, lb = a.forward(int(toks[13]), 13), b.forward(int(toks[13]), 13)
+    a.close(); b.close()
+    assert np.array_equal(la.view(np.uint32), lb.view(np.uint32))
+
+
 def test_replay_rounds_equal_plain_on_oracle(port_built):
     """Oracle-replayed drafts at any acceptance rate never change the stream; adv counts follow p."""
     from oracle.pyref import PortOracle
