@@ -95,6 +95,11 @@ int   lg_bench_matmul_pass(struct model *m, int n, int classes);
 /* Enqueue the kernels of one wide prompt block of n <= 256 tokens restricted to kernel classes
  * (<= 0: the four layer matmuls); returns the number of launches or -1.  Timing utility. */
 int   lg_bench_prefill_pass(struct model *m, int n, int classes);
+/* Long-context attention: caches of at least min_seq rows run full-attention layers through the
+ * span kernel (G tiles of 64 keys per CTA, online softmax); force_g > 0 fixes G (tests), 0 derives it
+ * from the cache length.  Default: min_seq 4096 (LG_ATTN_DEEP_MIN), G derived.  Set before the
+ * session's first forward. */
+void  lg_set_attn_deep(int min_seq, int force_g);
 void  lg_engine_release(void);                       /* free all device state of the loaded model */
 
 /* Kernel-level entry points (host buffers in, host buffers out) used by the parity tests.

@@ -29,7 +29,7 @@ ABI_SYMBOLS = [
     "model_prefill_reserve", "model_forward_spec", "mtp_draft_device", "mtp_draft_chain_device", "mtp_free_device",
     "lg_forward_spec_n", "lg_set_replay", "lg_rounds_begin", "lg_rounds_enqueue", "lg_rounds_collect",
     "lg_weight_bytes", "lg_round_launches", "lg_last_hidden", "lg_kv_row", "lg_stream", "lg_engine_release",
-    "lg_bench_matmul_pass", "lg_bench_prefill_pass", "lg_flash_decode_noalloc",
+    "lg_bench_matmul_pass", "lg_bench_prefill_pass", "lg_set_attn_deep", "lg_flash_decode_noalloc",
     "lg_dequant_host", "lg_gemv_host", "lg_flash_decode_host", "lg_prefill_matmul_host",
 ]
 
@@ -88,6 +88,7 @@ def load() -> C.CDLL:
     L.lg_round_launches.argtypes = [C.c_void_p]; L.lg_round_launches.restype = C.c_longlong
     L.lg_stream.argtypes = [C.c_void_p]; L.lg_stream.restype = C.c_void_p
     L.lg_bench_matmul_pass.argtypes = [C.c_void_p, C.c_int, C.c_int]; L.lg_bench_matmul_pass.restype = C.c_int
+    L.lg_set_attn_deep.argtypes = [C.c_int, C.c_int]; L.lg_set_attn_deep.restype = None
     L.lg_bench_prefill_pass.argtypes = [C.c_void_p, C.c_int, C.c_int]; L.lg_bench_prefill_pass.restype = C.c_int
     L.lgs_rounds_host.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _i32p, C.c_int, C.c_void_p, _i32p]
     L.lgs_rounds_host.restype = C.c_int
@@ -135,6 +136,12 @@ def prefill_matmul(ggml_type: int, raw: np.ndarray, m: int, k: int, x: np.ndarra
     if rc:
         raise ValueError(f"lg_prefill_matmul_host failed ({rc})")
     return y
+
+
+def set_attn_deep(min_seq: int = 4096, force_g: int = 0) -> None:
+    """Caches of at least min_seq rows use the span attention kernel on full-attention layers (force_g > 0 fixes the
+    tiles per span).  Call before opening the Session it should apply to."""
+    load().lg_set_attn_deep(min_seq, force_g)
 
 
 def flash_decode(q: np.ndarray, k: np.ndarray, v: np.ndarray, n_head_kv: int, window: int, pos: int) -> np.ndarray:

@@ -1,0 +1,306 @@
+// lg_attn_deep.cuh -- split-KV flash-decode for full-attention layers of long-context sessions.
+//
+// The decode step's attention kernel (lg_attn_kernel) gives every tile of 128 keys its own CTA and
+// lets the last CTA of a KV head merge all tiles: right at a few thousand keys, but at 32K keys that
+// is 257 one-tile CTAs per head, one per SM at a time with its load and its math back to back, and a
+// 2 MB merge by a single CTA.  Here a CTA walks a SPAN of G consecutive tiles of 64 keys with an
+// online softmax (running max / sum per query, accumulators in registers), two CTAs fit an SM so one
+// CTA's tile load overlaps the other's math, and the merge runs over spans, G times fewer partials.
+//
+// Spans, like tiles, lie on ABSOLUTE position boundaries (span s = keys [s*G*64, (s+1)*G*64)), G is a
+// property of the session (the cache length), and a tile that is wholly outside a query's window is an
+// exact no-op for that query (weights 0, rescale 1).  So a query row's result depends on its own
+// position only -- not on the verify width or on which other rows share the launch -- which keeps the
+// speculative stream byte-identical to plain decoding.
+#pragma once
+#include "lg_kernels.cuh"
+
+#define LG_DEEP_S 64
+
+// dynamic smem: Qhi | Qlo [NQ16][HD+8] f16 | K [64][HD+8] | V [64][HD+8] | scores [NQ16][64] f32 | Phi | Plo [NQ16][72] f16 | m, l, alpha [NQ16][3]
+template <int HD, int MTM>      // MTM = 16-row query blocks the CTA carries accumulators for (>= nq16 / 16)
+__global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_deep_kernel(LgAttnArgs a) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ float s_qn[HD], s_kn[HD];
+    pdl_launch();
+    if (!a.q_ready)
+        for (int i = threadIdx.x; i < HD; i += LG_ATTN_THREADS) { s_qn[i] = a.q_norm[i]; s_kn[i] = a.k_norm ? a.k_norm[i] : 1.0f; }
+    if (!a.early_kv) pdl_wait();
+    constexpr int S = LG_DEEP_S, LDH = HD + 8, LDP = S + 8, PER = HD / 64, HALF = HD / 2, NW = LG_ATTN_THREADS / 32;
+    const int G = a.G;
+    const int kvh = blockIdx.x, gqa = a.H / a.Hkv, nq = gqa * a.M, nq16 = (nq + 15) & ~15, nmt = nq16 / 16;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int pos0 = *a.pos;
+    const int p_first = pos0 + a.qpos_off, p_last = pos0 + a.M - 1 + a.qpos_off;
+    if (p_last < 0) return;
+    const int lo_first = a.window > 0 ? max(0, p_first + a.win_shrink - a.window + 1) : 0;
+    const int t_lo = lo_first / S, t_hi = p_last / S;
+    const int s_lo = t_lo / G, s_hi = t_hi / G;                 // spans the block touches
+    const int SP = s_lo + blockIdx.y;
+    if (SP > s_hi) return;
+    const int slot = SP % a.n_slots;
+    const int T0 = max(SP * G, t_lo), T1 = min(SP * G + G - 1, t_hi);
+    const bool writes_kv = a.owns_kv && !a.q_ready;
+
+    __half *qhi = (__half *)smem, *qlo = qhi + (size_t)nq16 * LDH;
+    __half *sk = qlo + (size_t)nq16 * LDH, *sv = sk + (size_t)S * LDH;
+    float *sc = (float *)(sv + (size_t)S * LDH);
+    __half *phi = (__half *)(sc + (size_t)nq16 * S), *plo = phi + (size_t)nq16 * LDP;
+    float *row_m = (float *)(plo + (size_t)nq16 * LDP), *row_l = row_m + nq16, *row_a = row_l + nq16;
+
+    constexpr int CH = HD / 8;
+    auto load_tile = [&](int T) {
+        for (int i = threadIdx.x; i < S * CH; i += LG_ATTN_THREADS) {
+            const int key = i / CH, c = i % CH, p = T * S + key;
+            __half *dk = sk + (size_t)key * LDH + c * 8, *dv = sv + (size_t)key * LDH + c * 8;
+            if (p <= p_last && !(writes_kv && p >= pos0)) {
+                const size_t off = (size_t)(p % a.seq) * a.kv_dim + (size_t)kvh * HD + c * 8;
+                cp_async16(dk, a.kc + off);
+                cp_async16(dv, a.vc + off);
+            } else if (p > p_last) {
+                *(uint4 *)dk = make_uint4(0, 0, 0, 0);
+                *(uint4 *)dv = make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+    load_tile(T0);
+    if (a.early_kv) pdl_wait();
+
+    // queries: per-head RMSNorm + RoPE, split into f16 hi + lo
+    for (int qi = warp; qi < nq16; qi += NW) {
+        float v0[PER], v1[PER];
+        if (qi < nq) {
+            const int tok = qi / gqa, hq = kvh * gqa + qi % gqa;
+            if (a.q_ready) {
+                const float *src = a.qkv + ((size_t)tok * a.H + hq) * HD;
+                #pragma unroll
+                for (int e = 0; e < PER; e++) { v0[e] = src[lane * PER + e]; v1[e] = src[lane * PER + e + HALF]; }
+            } else {
+                head_norm_rope<HD>(a.qkv + (size_t)tok * a.ld + (size_t)hq * HD, s_qn, a.rope + (size_t)tok * HALF, a.eps, lane, v0, v1);
+            }
+        } else {
+            #pragma unroll
+            for (int e = 0; e < PER; e++) v0[e] = v1[e] = 0.0f;
+        }
+        #pragma unroll
+        for (int e = 0; e < PER; e++) {
+            int i = lane * PER + e;
+            __half h0 = __float2half_rn(v0[e]), h1 = __float2half_rn(v1[e]);
+            qhi[(size_t)qi * LDH + i] = h0; qhi[(size_t)qi * LDH + i + HALF] = h1;
+            qlo[(size_t)qi * LDH + i] = __float2half_rn(v0[e] - __half2float(h0));
+            qlo[(size_t)qi * LDH + i + HALF] = __float2half_rn(v1[e] - __half2float(h1));
+        }
+    }
+    for (int r = threadIdx.x; r < nq16; r += LG_ATTN_THREADS) { row_m[r] = -INFINITY; row_l[r] = 0.0f; }
+
+    const int g = lane >> 2, t = lane & 3;
+    constexpr int KPW = S / NW;                                  // 8 keys per warp: one 8-key n tile
+    constexpr int PVW = HD / 16 < NW ? HD / 16 : NW, DW = HD / PVW, NT = DW / 8;
+    float o[MTM][NT][4];
+    #pragma unroll
+    for (int mt = 0; mt < MTM; mt++)
+        #pragma unroll
+        for (int n = 0; n < NT; n++) o[mt][n][0] = o[mt][n][1] = o[mt][n][2] = o[mt][n][3] = 0.0f;
+
+    for (int T = T0; T <= T1; T++) {
+        if (T > T0) {
+            __syncthreads();                                     // the previous tile's K, V and P are no longer read
+            load_tile(T);
+        }
+        if (writes_kv) {
+            // rows of the new positions that fall into this tile: K (norm + rope) and V (plain norm), f16 RNE
+            for (int j = warp; j < 2 * a.M; j += NW) {
+                const int tok = j >> 1, isv = j & 1, p = pos0 + tok;
+                if (p / S != T) continue;
+                float v0[PER], v1[PER];
+                const float *src = a.qkv + (size_t)tok * a.ld + (size_t)(a.H + ((isv && a.has_v) ? a.Hkv : 0) + kvh) * HD;
+                head_norm_rope<HD>(src, isv ? nullptr : s_kn, isv ? nullptr : a.rope + (size_t)tok * HALF, a.eps, lane, v0, v1);
+                __half *dst = (isv ? a.vc : a.kc) + (size_t)(p % a.seq) * a.kv_dim + (size_t)kvh * HD;
+                __half *dsm = (isv ? sv : sk) + (size_t)(p - T * S) * LDH;
+                #pragma unroll
+                for (int e = 0; e < PER; e++) {
+                    const __half h0 = __float2half_rn(v0[e]), h1 = __float2half_rn(v1[e]);
+                    dst[lane * PER + e] = h0; dst[lane * PER + e + HALF] = h1;
+                    dsm[lane * PER + e] = h0; dsm[lane * PER + e + HALF] = h1;
+                }
+            }
+        }
+        cp_async_wait_all();
+        __syncthreads();
+
+        // scores: warp w takes keys [8w, 8w + 8)
+        #pragma unroll
+        for (int mt = 0; mt < MTM; mt++) {
+            if (mt >= nmt) break;
+            float c0[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            const __half *qa_hi = qhi + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + (lane >> 4) * 8;
+            const __half *qa_lo = qlo + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + (lane >> 4) * 8;
+            const __half *kb = sk + (size_t)(warp * KPW + (lane & 7)) * LDH + (lane >> 3) * 8;
+            #pragma unroll 2
+            for (int k0 = 0; k0 < HD; k0 += 32) {
+                uint32_t ah[4], al[4], ah2[4], al2[4], b[4];
+                ldsm_x4(ah, qa_hi + k0); ldsm_x4(al, qa_lo + k0);
+                ldsm_x4(ah2, qa_hi + k0 + 16); ldsm_x4(al2, qa_lo + k0 + 16);
+                ldsm_x4(b, kb + k0);
+                mma_f16(c0, ah, b[0], b[1]); mma_f16(c0, al, b[0], b[1]);
+                mma_f16(c0, ah2, b[2], b[3]); mma_f16(c0, al2, b[2], b[3]);
+            }
+            #pragma unroll
+            for (int h2 = 0; h2 < 2; h2++) {
+                const int qi = mt * 16 + g + h2 * 8;
+                const int pj = pos0 + qi / gqa + a.qpos_off;
+                const int lo = a.window > 0 ? max(0, pj + a.win_shrink - a.window + 1) : 0;
+                #pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const int key = warp * KPW + t * 2 + e, p = T * S + key;
+                    sc[(size_t)qi * S + key] = (qi < nq && p >= lo && p <= pj) ? c0[h2 * 2 + e] : -INFINITY;
+                }
+            }
+        }
+        __syncthreads();
+
+        // online softmax, one warp per query row: new running max, the tile's weights against it, the rescale
+        // of what was accumulated before (exactly 1 when the tile adds nothing for this row)
+        for (int qi = warp; qi < nq16; qi += NW) {
+            const float s0 = sc[(size_t)qi * S + lane], s1 = sc[(size_t)qi * S + lane + 32];
+            const float m_old = row_m[qi];
+            const float m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
+            const float e0 = s0 == -INFINITY ? 0.0f : expf(s0 - m_new), e1 = s1 == -INFINITY ? 0.0f : expf(s1 - m_new);
+            const __half h0 = __float2half_rn(e0), h1 = __float2half_rn(e1);
+            phi[(size_t)qi * LDP + lane] = h0; phi[(size_t)qi * LDP + lane + 32] = h1;
+            plo[(size_t)qi * LDP + lane] = __float2half_rn(e0 - __half2float(h0));
+            plo[(size_t)qi * LDP + lane + 32] = __float2half_rn(e1 - __half2float(h1));
+            const float sum = warp_sum(e0 + e1);
+            if (lane == 0) {
+                const float alpha = (m_old == m_new) ? 1.0f : expf(m_old - m_new);     // m_old = -inf < m_new: 0
+                row_a[qi] = alpha;
+                row_l[qi] = row_l[qi] * alpha + sum;
+                row_m[qi] = m_new;
+            }
+        }
+        __syncthreads();
+
+        // O = alpha O + P V: PVW warps split the head dims
+        if (warp < PVW) {
+            #pragma unroll
+            for (int mt = 0; mt < MTM; mt++) {
+                if (mt >= nmt) break;
+                const float a0 = row_a[mt * 16 + g], a1 = row_a[mt * 16 + g + 8];
+                #pragma unroll
+                for (int n = 0; n < NT; n++) { o[mt][n][0] *= a0; o[mt][n][1] *= a0; o[mt][n][2] *= a1; o[mt][n][3] *= a1; }
+                const __half *pa_hi = phi + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDP + (lane >> 4) * 8;
+                const __half *pa_lo = plo + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDP + (lane >> 4) * 8;
+                #pragma unroll
+                for (int k0 = 0; k0 < S; k0 += 16) {
+                    uint32_t ah[4], al[4];
+                    ldsm_x4(ah, pa_hi + k0); ldsm_x4(al, pa_lo + k0);
+                    const __half *vb = sv + (size_t)(k0 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + warp * DW + (lane >> 4) * 8;
+                    #pragma unroll
+                    for (int n = 0; n < NT; n += 2) {
+                        uint32_t b[4];
+                        ldsm_x4_t(b, vb + n * 8);
+                        mma_f16(o[mt][n], ah, b[0], b[1]); mma_f16(o[mt][n], al, b[0], b[1]);
+                        mma_f16(o[mt][n + 1], ah, b[2], b[3]); mma_f16(o[mt][n + 1], al, b[2], b[3]);
+                    }
+                }
+            }
+        }
+    }
+
+    // the span's partial (max, sum, accumulators) of every query row
+    if (warp < PVW) {
+        #pragma unroll
+        for (int mt = 0; mt < MTM; mt++) {
+            if (mt >= nmt) break;
+            #pragma unroll
+            for (int h2 = 0; h2 < 2; h2++) {
+                const int qi = mt * 16 + g + h2 * 8;
+                if (qi < nq) {
+                    const int tok = qi / gqa, hq = kvh * gqa + qi % gqa;
+                    float *pp = a.part + (((size_t)slot * a.M + tok) * a.H + hq) * HD;
+                    #pragma unroll
+                    for (int n = 0; n < NT; n++)
+                        *(float2 *)(pp + warp * DW + n * 8 + t * 2) = make_float2(o[mt][n][h2 * 2], o[mt][n][h2 * 2 + 1]);
+                    if (warp == 0 && t == 0)
+                        a.part_ml[((size_t)slot * a.M + tok) * a.H + hq] = make_float2(row_m[qi], row_l[qi]);
+                }
+            }
+        }
+    }
+
+    // the last CTA of this KV head merges the spans
+    __shared__ int s_last;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        s_last = atomicAdd(a.tickets + kvh, 1) == s_hi - s_lo;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const int ns_all = s_hi - s_lo + 1;
+    float2 *mls = (float2 *)sk;                               // [nq][ns_all]: (max, sum) then (weight, -); the K/V area is free now
+    float *invl = row_l;                                      // [nq]
+    for (int i = threadIdx.x; i < nq * ns_all; i += LG_ATTN_THREADS) {
+        const int qi = i / ns_all, S2 = s_lo + i % ns_all;
+        const int tok = qi / gqa, hq = kvh * gqa + qi % gqa;
+        mls[i] = __ldcg(a.part_ml + ((size_t)(S2 % a.n_slots) * a.M + tok) * a.H + hq);
+    }
+    __syncthreads();
+    for (int qi = warp; qi < nq; qi += NW) {
+        const int pj = pos0 + qi / gqa + a.qpos_off;
+        const int lo = a.window > 0 ? max(0, pj + a.win_shrink - a.window + 1) : 0;
+        const int i0 = pj >= 0 ? (lo / S) / G - s_lo : 0, i1 = pj >= 0 ? (pj / S) / G - s_lo : -1;
+        float mx = -INFINITY;
+        for (int i = i0 + lane; i <= i1; i += 32) { float2 v = mls[qi * ns_all + i]; if (v.y > 0.0f) mx = fmaxf(mx, v.x); }
+        mx = warp_max(mx);
+        float lsum = 0.0f;
+        for (int i = lane; i < ns_all; i += 32) {
+            float2 v = mls[qi * ns_all + i];
+            float w = (i >= i0 && i <= i1 && v.y > 0.0f) ? expf(v.x - mx) : 0.0f;
+            mls[qi * ns_all + i].x = w;
+            lsum += w * v.y;
+        }
+        lsum = warp_sum(lsum);
+        if (lane == 0) invl[qi] = lsum > 0.0f ? 1.0f / lsum : 0.0f;
+    }
+    __syncthreads();
+    float *ybuf = (float *)qhi;                                // [nq][HD] f32 (the query area is free now)
+    const size_t slot_stride = (size_t)a.M * a.H * HD;
+    for (int u = threadIdx.x; u < nq * (HD / 4); u += LG_ATTN_THREADS) {
+        const int qi = u / (HD / 4), d4 = (u % (HD / 4)) * 4;
+        const float *base = a.part + ((size_t)(qi / gqa) * a.H + kvh * gqa + qi % gqa) * HD + d4;
+        const float2 *wq = mls + (size_t)qi * ns_all;
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int i = 0; i < ns_all; i += 8) {                  // ascending span order, 8 loads in flight
+            float4 v[8];
+            #pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (i + j < ns_all) v[j] = __ldcg((const float4 *)(base + (size_t)((s_lo + i + j) % a.n_slots) * slot_stride));
+            #pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (i + j < ns_all) {
+                    const float w = wq[i + j].x;
+                    acc.x = fmaf(w, v[j].x, acc.x); acc.y = fmaf(w, v[j].y, acc.y);
+                    acc.z = fmaf(w, v[j].z, acc.z); acc.w = fmaf(w, v[j].w, acc.w);
+                }
+        }
+        const float il = invl[qi];
+        *(float4 *)(ybuf + (size_t)qi * HD + d4) = make_float4(acc.x * il, acc.y * il, acc.z * il, acc.w * il);
+    }
+    __syncthreads();
+    for (int u = warp; u < nq * (HD / 32); u += NW) {
+        const int qi = u / (HD / 32), d = (u % (HD / 32)) * 32 + lane;
+        const int tok = qi / gqa, hq = kvh * gqa + qi % gqa;
+        const float y = ybuf[(size_t)qi * HD + d];
+        if (a.out_f32) a.out_f32[((size_t)tok * a.H + hq) * HD + d] = y;
+        if (a.out_h) a.out_h[(size_t)tok * a.ld_h + hq * HD + d] = __float2half_rn(y);
+        if (a.out.q) quant_group_store(y, lane, tok, (hq * HD + d) >> 5, a.out);
+    }
+    if (threadIdx.x == 0) a.tickets[kvh] = 0;
+}
+
+inline size_t attn_deep_smem(int nq, int hd) {
+    size_t nq16 = (size_t)((nq + 15) & ~15), ldh = hd + 8, S = LG_DEEP_S;
+    return 2 * nq16 * ldh * 2 + 2 * S * ldh * 2 + nq16 * S * 4 + 2 * nq16 * (S + 8) * 2 + nq16 * 12 + 64;
+}

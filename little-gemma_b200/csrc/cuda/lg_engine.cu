@@ -17,6 +17,7 @@
 #include <string>
 #include "lg_kernels.cuh"
 #include "lg_prefill.cuh"
+#include "lg_attn_deep.cuh"
 #include "lg_host.h"
 #include "lg_b200.h"
 
@@ -294,6 +295,10 @@ void set_kernel_attributes() {
     LG_CHECK(cudaFuncSetAttribute(lg_attn_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
     LG_CHECK(cudaFuncSetAttribute(lg_attn_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
     pf_attr_n<64>(); pf_attr_n<128>(); pf_attr_n<256>();
+    LG_CHECK(cudaFuncSetAttribute(lg_attn_deep_kernel<128, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
+    LG_CHECK(cudaFuncSetAttribute(lg_attn_deep_kernel<128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
+    LG_CHECK(cudaFuncSetAttribute(lg_attn_deep_kernel<256, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
+    LG_CHECK(cudaFuncSetAttribute(lg_attn_deep_kernel<256, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
     LG_CHECK(cudaFuncSetAttribute(lg_pf_attn_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pf_attn_smem<64>()));
     LG_CHECK(cudaFuncSetAttribute(lg_pf_attn_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pf_attn_smem<128>()));
     LG_CHECK(cudaFuncSetAttribute(lg_pf_attn_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pf_attn_smem<256>()));
@@ -549,6 +554,34 @@ void launch_attn(Engine *e, LgAttnArgs a, int n_tiles_max) {
     }
 }
 
+// Long-context sessions: full-attention layers walk spans of G tiles of 64 keys per CTA (lg_attn_deep_kernel).
+// G is a property of the cache length alone, so every query position sees the same decomposition in plain and
+// in speculative decoding.  0 = the one-tile-per-CTA kernel.
+int g_deep_min = -1, g_deep_force = 0;
+int deep_span_tiles(const Engine *e, int max_seq, int n_kv_heads, int hd, int nq) {
+    if (g_deep_min < 0) g_deep_min = env_int("LG_ATTN_DEEP_MIN", 4096);
+    static const int on = env_int("LG_ATTN_DEEP", 1);
+    if (!on || max_seq < g_deep_min || (hd != 128 && hd != 256) || ((nq + 15) & ~15) > 32) return 0;
+    if (g_deep_force > 0) return g_deep_force;
+    const int tiles = (max_seq + LG_DEEP_S - 1) / LG_DEEP_S;
+    const int want = std::max(1, 2 * e->sm_count / std::max(1, n_kv_heads));     // spans per KV head that fill the GPU once
+    int G = (tiles + want - 1) / want;
+    return G < 2 ? 0 : std::min(G, 64);
+}
+
+void launch_attn_deep(Engine *e, LgAttnArgs a, int max_seq, int G) {
+    const int nq = (a.H / a.Hkv) * a.M, nmt = ((nq + 15) & ~15) / 16;
+    const size_t sm = attn_deep_smem(nq, a.hd);
+    const int n_spans = ((max_seq + LG_DEEP_S - 1) / LG_DEEP_S + G - 1) / G + 1;
+    if (n_spans > a.n_slots || (size_t)nq * n_spans * 8 > 2 * (size_t)LG_DEEP_S * (a.hd + 8) * 2 || sm > ATTN_SMEM_MAX || a.Hkv > MAX_KV_HEADS) {
+        fprintf(stderr, "lg_b200: %d key spans x %d queries do not fit the span attention kernel\n", n_spans, nq); exit(1);
+    }
+    a.tickets = e->tickets; a.G = G;
+    dim3 grid(a.Hkv, n_spans), block(LG_ATTN_THREADS);
+    if (a.hd == 256) { if (nmt <= 1) launch_k(e, lg_attn_deep_kernel<256, 1>, grid, block, sm, a); else launch_k(e, lg_attn_deep_kernel<256, 2>, grid, block, sm, a); }
+    else             { if (nmt <= 1) launch_k(e, lg_attn_deep_kernel<128, 1>, grid, block, sm, a); else launch_k(e, lg_attn_deep_kernel<128, 2>, grid, block, sm, a); }
+}
+
 int tiles_for(int window, int max_seq, int M, int hd) {
     const int S = lg_attn_tile(hd);
     if (window > 0 && window + M < max_seq) return (window + M + S - 1) / S + 1;
@@ -783,7 +816,11 @@ void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags, int 
         aa.out = pa;
         static const int early_kv = env_int("LG_ATTN_EARLY_KV", 1);
         aa.early_kv = early_kv && w.owns_kv;     // the target's position and this layer's older rows come from earlier graph launches
-        if (only & C_ATTN) launch_attn(e, aa, tiles_for(aa.window, kv->max_seq, M, hd));
+        const int deepG = w.local ? 0 : deep_span_tiles(e, kv->max_seq, w.nkv, hd, (H / w.nkv) * M);
+        if (only & C_ATTN) {
+            if (deepG) launch_attn_deep(e, aa, kv->max_seq, deepG);
+            else launch_attn(e, aa, tiles_for(aa.window, kv->max_seq, M, hd));
+        }
 
         // o-projection, then x += norm(o)*w_post_attn and the ffn_norm panel
         int ks_o = 1;
@@ -1557,6 +1594,11 @@ int lg_bench_prefill_pass(struct model *m, int n, int classes) {
     enqueue_prefill_block(e, e->kv_bound, n, classes);
     return (int)(e->launches - before);
 }
+
+// Session-wide choice of the span attention kernel: caches of at least min_seq rows use it on full-attention
+// layers; force_g > 0 fixes the tiles per span (tests), 0 derives it from the cache length.  Takes effect for
+// forwards captured afterwards (a new cache re-captures).
+void lg_set_attn_deep(int min_seq, int force_g) { g_deep_min = min_seq; g_deep_force = force_g; }
 
 void *lg_stream(struct model *m) { return (void *)engine_for(m)->stream; }
 long long lg_round_launches(struct model *m) { return engine_for(m)->round_launches; }

@@ -876,6 +876,7 @@ struct LgAttnArgs {
     const float *qkv; int ld; int q_ready;
     int has_v, owns_kv;                  // v projection present; this layer writes K/V rows
     int early_kv;                        // the tile's cached rows may be fetched before the dependency wait (see the kernel)
+    int G;                               // lg_attn_deep_kernel only: tiles of 64 keys per CTA span
     const float *q_norm, *k_norm; float eps;
     const float2 *rope;                  // [M][hd/2] (cos, sin) of this layer kind at the block's positions
     __half *kc, *vc; int seq, kv_dim;
