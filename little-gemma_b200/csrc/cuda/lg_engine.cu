@@ -559,7 +559,7 @@ void launch_attn(Engine *e, LgAttnArgs a, int n_tiles_max) {
 // in speculative decoding.  0 = the one-tile-per-CTA kernel.
 int g_deep_min = -1, g_deep_force = 0;
 int deep_span_tiles(const Engine *e, int max_seq, int n_kv_heads, int hd, int nq) {
-    if (g_deep_min < 0) g_deep_min = env_int("LG_ATTN_DEEP_MIN", 4096);
+    if (g_deep_min < 0) { g_deep_min = env_int("LG_ATTN_DEEP_MIN", 4096); g_deep_force = env_int("LG_ATTN_DEEP_G", 0); }
     static const int on = env_int("LG_ATTN_DEEP", 1);
     if (!on || max_seq < g_deep_min || (hd != 128 && hd != 256) || ((nq + 15) & ~15) > 32) return 0;
     if (g_deep_force > 0) return g_deep_force;
@@ -816,7 +816,8 @@ void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags, int 
         aa.out = pa;
         static const int early_kv = env_int("LG_ATTN_EARLY_KV", 1);
         aa.early_kv = early_kv && w.owns_kv;     // the target's position and this layer's older rows come from earlier graph launches
-        const int deepG = w.local ? 0 : deep_span_tiles(e, kv->max_seq, w.nkv, hd, (H / w.nkv) * M);
+        static const int deep_local = env_int("LG_ATTN_DEEP_LOCAL", 0);
+        const int deepG = (w.local && !deep_local) ? 0 : deep_span_tiles(e, kv->max_seq, w.nkv, hd, (H / w.nkv) * M);
         if (only & C_ATTN) {
             if (deepG) launch_attn_deep(e, aa, kv->max_seq, deepG);
             else launch_attn(e, aa, tiles_for(aa.window, kv->max_seq, M, hd));
