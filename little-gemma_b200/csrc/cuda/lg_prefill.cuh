@@ -69,6 +69,17 @@ template <int NT, int FMT> __host__ __device__ constexpr size_t pf_smem_bytes() 
          + (size_t)pf_raw_stages<NT, FMT>() * pf_raw_stage_bytes<FMT>() + 512;
 }
 
+// mbar_wait on a shared-space address that is already in a register
+__device__ __forceinline__ bool mbar_wait_u32(uint32_t bar, uint32_t parity) {
+    for (int it = 0; it < LG_SPIN_LIMIT; ++it) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  :: "r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
@@ -122,8 +133,9 @@ __global__ void __launch_bounds__(LG_PF_THREADS) lg_pf_gemm_kernel(const __grid_
     unsigned char *base = (unsigned char *)(((uintptr_t)pf_smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char *sA = base, *sB = sA + STA * A_BYTES, *sRaw = sB + STB * B_BYTES;
     uint64_t *bars = (uint64_t *)(sRaw + RS * RAW);
-    uint64_t *raw_full = bars, *raw_empty = raw_full + RS, *a_full = raw_empty + RS, *b_full = a_full + STA,
-             *a_empty = b_full + STB, *b_empty = a_empty + STA, *acc_full = b_empty + STB;
+    static_assert(STA == STB, "an operand stage is one A tile and one B tile behind the same pair of barriers");
+    // full[s]: the expand group's arrivals + the activation copy's bytes; empty[s]: one commit frees both tiles
+    uint64_t *raw_full = bars, *raw_empty = raw_full + RS, *full = raw_empty + RS, *empty = full + STA, *acc_full = empty + STA;
     uint32_t *tmem_slot = (uint32_t *)(acc_full + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -135,8 +147,7 @@ __global__ void __launch_bounds__(LG_PF_THREADS) lg_pf_gemm_kernel(const __grid_
     pdl_launch();
     if (threadIdx.x == 0) {
         for (int i = 0; i < RS; i++) { mbar_init(raw_full + i, 1); mbar_init(raw_empty + i, 2 * DQT / LG_PF_GROUPS); }
-        for (int i = 0; i < STA; i++) { mbar_init(a_full + i, DQT / LG_PF_GROUPS); mbar_init(a_empty + i, 1); }
-        for (int i = 0; i < STB; i++) { mbar_init(b_full + i, 1); mbar_init(b_empty + i, 1); }
+        for (int i = 0; i < STA; i++) { mbar_init(full + i, DQT / LG_PF_GROUPS + 1); mbar_init(empty + i, 1); }
         mbar_init(acc_full, 1);
     }
     if (warp == LG_PF_DQ_WARPS + 2) {        // tensor memory: NT f32 columns x 128 lanes
@@ -180,30 +191,40 @@ __global__ void __launch_bounds__(LG_PF_THREADS) lg_pf_gemm_kernel(const __grid_
             int issued = 0;
             for (int kb = 0; kb < nkb && ok; kb++) {
                 const int s = kb % STB;
-                if (kb >= STB && !mbar_wait(b_empty + s, ((kb / STB) & 1) ^ 1)) { atomicOr(a.err, LG_ERR_MBAR_TIMEOUT | 4); ok = false; break; }
-                mbar_expect_tx(b_full + s, B_BYTES);
-                tma_load_2d(sB + s * B_BYTES, &tmx, (kb_lo + kb) * LG_PF_BK, tok0, b_full + s);
+                if (kb >= STB && !mbar_wait(empty + s, ((kb / STB) & 1) ^ 1)) { atomicOr(a.err, LG_ERR_MBAR_TIMEOUT | 4); ok = false; break; }
+                mbar_expect_tx(full + s, B_BYTES);
+                tma_load_2d(sB + s * B_BYTES, &tmx, (kb_lo + kb) * LG_PF_BK, tok0, full + s);
                 issued = kb + 1;
             }
             if (!ok)
-                for (int kb = max(0, issued - STB); kb < issued; kb++) mbar_wait(b_full + kb % STB, (kb / STB) & 1);
+                for (int kb = max(0, issued - STB); kb < issued; kb++) mbar_wait(full + kb % STB, (kb / STB) & 1);
         }
     } else if (warp == LG_PF_DQ_WARPS + 2) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(LG_PF_BM >> 4) << 24);
+            // This one thread is the pipeline's pacemaker: everything it does per k block is a serial chain of dependent
+            // instructions, so the loop is unrolled over the stages (static stage index: descriptors and barrier
+            // addresses live in registers) and carries as little arithmetic as possible.
+            uint64_t adesc[STA], bdesc[STB];
+            uint32_t ufull[STA], uempty[STA];
+            #pragma unroll
+            for (int st = 0; st < STA; st++) {
+                adesc[st] = umma_desc_k128(smem_u32(sA + st * A_BYTES)); bdesc[st] = umma_desc_k128(smem_u32(sB + st * B_BYTES));
+                ufull[st] = smem_u32(full + st); uempty[st] = smem_u32(empty + st);
+            }
             bool ok = true;
-            for (int kb = 0; kb < nkb && ok; kb++) {
-                const int sa = kb % STA, sb = kb % STB;
-                if (!mbar_wait(a_full + sa, (kb / STA) & 1)) { atomicOr(a.err, LG_ERR_MBAR_TIMEOUT | 8); ok = false; break; }
-                if (!mbar_wait(b_full + sb, (kb / STB) & 1)) { atomicOr(a.err, LG_ERR_MBAR_TIMEOUT | 16); ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t ad = umma_desc_k128(smem_u32(sA + sa * A_BYTES)), bd = umma_desc_k128(smem_u32(sB + sb * B_BYTES));
+            uint32_t ph = 0, acc = 0;
+            for (int kb0 = 0; kb0 < nkb && ok; kb0 += STA, ph ^= 1) {
                 #pragma unroll
-                for (int j = 0; j < LG_PF_BK / 16; j++)
-                    umma_f16(tmem, ad + 2 * j, bd + 2 * j, idesc, (kb | j) ? 1u : 0u);
-                umma_commit(a_empty + sa);           // the stages are free once these MMAs have read them
-                umma_commit(b_empty + sb);
+                for (int st = 0; st < STA; st++) {
+                    if (kb0 + st >= nkb || !ok) break;
+                    if (!mbar_wait_u32(ufull[st], ph)) { atomicOr(a.err, LG_ERR_MBAR_TIMEOUT | 8); ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    #pragma unroll
+                    for (int j = 0; j < LG_PF_BK / 16; j++) { umma_f16(tmem, adesc[st] + 2 * j, bdesc[st] + 2 * j, idesc, acc); acc = 1u; }
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(uempty[st]) : "memory");
+                }
             }
             umma_commit(acc_full);                   // arrives when every MMA above has completed
         }
@@ -228,7 +249,7 @@ __global__ void __launch_bounds__(LG_PF_THREADS) lg_pf_gemm_kernel(const __grid_
         for (int kb = gi; kb < nkb; kb += NG) {
             const int s = kb % STA, r = kb >> 1, rs = r % RS, half = kb & 1;
             if (ok && !mbar_wait(raw_full + rs, (r / RS) & 1)) { ok = false; atomicOr(a.err, 32); }
-            if (ok && kb >= STA && !mbar_wait(a_empty + s, ((kb / STA) & 1) ^ 1)) { ok = false; atomicOr(a.err, 64); }
+            if (ok && kb >= STA && !mbar_wait(empty + s, ((kb / STA) & 1) ^ 1)) { ok = false; atomicOr(a.err, 64); }
             if (!ok) break;
             #pragma unroll
             for (int q = 0; q < TPW; q++) {
@@ -267,7 +288,7 @@ __global__ void __launch_bounds__(LG_PF_THREADS) lg_pf_gemm_kernel(const __grid_
                     }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");           // generic-proxy stores -> visible to the MMA
-            mbar_arrive(a_full + s);
+            mbar_arrive(full + s);
             mbar_arrive(raw_empty + rs);           // every expand thread arrives once per k block it takes
         }
         if (!ok && lane == 0) atomicOr(a.err, LG_ERR_MBAR_TIMEOUT);
