@@ -63,7 +63,7 @@ def load() -> C.CDLL:
     L.lgs_draft.argtypes = [C.c_void_p, C.c_int, C.c_int]; L.lgs_draft.restype = C.c_int
     L.lgs_draft_chain.argtypes = [C.c_void_p, C.c_int, C.c_int]; L.lgs_draft_chain.restype = C.c_int
     L.lgs_kv_row.argtypes = [C.c_void_p, C.c_int, C.c_int, _f32p, _f32p]; L.lgs_kv_row.restype = C.c_int
-    L.lgs_generate.argtypes = [C.c_void_p, _i32p, C.c_int, C.c_int, _i32p, C.c_int, C.c_void_p, _i32p]
+    L.lgs_generate.argtypes = [C.c_void_p, _i32p, C.c_int, C.c_int, _i32p, C.c_int, C.c_void_p, C.c_int, _i32p]
     L.lgs_generate.restype = C.c_int
     L.lgs_generate_device.argtypes = [C.c_void_p, _i32p, C.c_int, C.c_int, _i32p, C.c_int, C.c_void_p, C.c_int, _i32p]
     L.lgs_generate_device.restype = C.c_int
@@ -90,7 +90,7 @@ def load() -> C.CDLL:
     L.lg_bench_matmul_pass.argtypes = [C.c_void_p, C.c_int, C.c_int]; L.lg_bench_matmul_pass.restype = C.c_int
     L.lg_set_attn_deep.argtypes = [C.c_int, C.c_int]; L.lg_set_attn_deep.restype = None
     L.lg_bench_prefill_pass.argtypes = [C.c_void_p, C.c_int, C.c_int]; L.lg_bench_prefill_pass.restype = C.c_int
-    L.lgs_rounds_host.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _i32p, C.c_int, C.c_void_p, _i32p]
+    L.lgs_rounds_host.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _i32p, C.c_int, C.c_void_p, C.c_int, _i32p]
     L.lgs_rounds_host.restype = C.c_int
     _lib = L
     return L
@@ -244,11 +244,11 @@ class Session:
         """Host-driven generation through the reference-shaped blocking calls."""
         prompt = np.ascontiguousarray(prompt, dtype=np.int32)
         out = np.zeros(n_gen + 8, dtype=np.int32); stats = np.zeros(2, dtype=np.int32)
-        rp = None
+        rp, nr = None, 0
         if replay is not None:
-            replay = np.ascontiguousarray(np.concatenate([replay, np.zeros(8, np.int32)]), dtype=np.int32)
-            rp = replay.ctypes.data_as(C.c_void_p)
-        n = self.L.lgs_generate(self.h, prompt, len(prompt), n_gen, out, mode, rp, stats)
+            replay = np.ascontiguousarray(replay, dtype=np.int32)
+            rp, nr = replay.ctypes.data_as(C.c_void_p), len(replay)
+        n = self.L.lgs_generate(self.h, prompt, len(prompt), n_gen, out, mode, rp, nr, stats)
         return out[:n], (int(stats[0]), int(stats[1]))
 
     def generate_device(self, prompt, n_gen: int, mode: int = 0, replay=None):
@@ -267,11 +267,11 @@ class Session:
     def rounds_host(self, best: int, pos: int, n_emitted: int, n_gen: int, n_rounds: int, mode: int, replay=None):
         """Host-driven rounds from a given state; returns (tokens[n_emitted:], stats dict)."""
         out = np.zeros(n_gen + 8, dtype=np.int32); stats = np.zeros(4, dtype=np.int32)
-        rp = None
+        rp, nr = None, 0
         if replay is not None:
-            replay = np.ascontiguousarray(np.concatenate([replay, np.zeros(8, np.int32)]), dtype=np.int32)
-            rp = replay.ctypes.data_as(C.c_void_p)
-        g = self.L.lgs_rounds_host(self.h, best, pos, n_emitted, n_gen, n_rounds, out, mode, rp, stats)
+            replay = np.ascontiguousarray(replay, dtype=np.int32)
+            rp, nr = replay.ctypes.data_as(C.c_void_p), len(replay)
+        g = self.L.lgs_rounds_host(self.h, best, pos, n_emitted, n_gen, n_rounds, out, mode, rp, nr, stats)
         return out[n_emitted:g], dict(n_draft=int(stats[0]), n_accept=int(stats[1]), pos=int(stats[2]), best=int(stats[3]))
 
     def matmul_pass(self, n: int, classes: int = 0) -> int:

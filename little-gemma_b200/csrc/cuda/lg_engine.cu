@@ -118,6 +118,7 @@ struct Engine {
     long long round_launches = 0;
     PrefillBuf pf;
     float *ssq1 = nullptr, *ssq2 = nullptr; int *gbar = nullptr;     // NORMTAIL scratch: partial sums of squares, grid barrier
+    int pos_hi = 0;                           // host-side upper bound of the device position (device-resident rounds)
     int mm_launches = 0;                      // kernels in the captured matmul-only pass             // kernels in one captured round (lg_rounds_enqueue)
 };
 
@@ -186,25 +187,29 @@ float *upload_norm(const struct gguf_context *g, int L, const char *leaf) {
 // Upload file-format tensors and repack them into one tile-major matrix: stacked row-wise, or
 // (interleave) two equally shaped tensors woven 8 rows at a time -- gate rows then the matching
 // up rows in every 16-row tile.
+// While a draft head is being uploaded a tensor this backend cannot run must not end the process: the contract of the
+// reference is "drafting off, decoding goes on" (src/cuda/mtp-kernel.cuh:263-267,331-337).  With g_soft_build set,
+// build_wmat reports the problem, raises g_soft_failed and returns an empty matrix instead of exiting.
+bool g_soft_build = false, g_soft_failed = false;
+#define LG_BUILD_FAIL(...) do { fprintf(stderr, __VA_ARGS__); if (g_soft_build) { g_soft_failed = true; return WMat(); } exit(1); } while (0)
+
 WMat build_wmat(Engine *e, std::vector<const struct gguf_tensor *> parts, bool interleave = false) {
     WMat W;
-    for (auto t : parts) if (!t) { fprintf(stderr, "lg_b200: a weight tensor is missing from the file\n"); exit(1); }
+    if (g_soft_build && g_soft_failed) return W;
+    for (auto t : parts) if (!t) LG_BUILD_FAIL("lg_b200: a weight tensor is missing from the file\n");
     const struct gguf_tensor *t0 = parts[0];
-    if (t0->type != GGML_TYPE_Q4_0 && t0->type != GGML_TYPE_Q4_K) {
-        fprintf(stderr, "lg_b200: weight %s has ggml type %u; this backend runs q4_0 and q4_K matrices\n", t0->name, t0->type);
-        exit(1);
-    }
+    if (t0->type != GGML_TYPE_Q4_0 && t0->type != GGML_TYPE_Q4_K)
+        LG_BUILD_FAIL("lg_b200: weight %s has ggml type %u; this backend runs q4_0 and q4_K matrices\n", t0->name, t0->type);
     W.fmt = t0->type == GGML_TYPE_Q4_0 ? LG_FMT_Q4_0 : LG_FMT_Q4_K;
     W.k = (int)t0->dims[0];
-    if (W.k % 64) { fprintf(stderr, "lg_b200: %s: contraction length %d is not a multiple of 64\n", t0->name, W.k); exit(1); }
+    if (W.k % 64) LG_BUILD_FAIL("lg_b200: %s: contraction length %d is not a multiple of 64\n", t0->name, W.k);
     for (auto t : parts) {
-        if (t->type != t0->type || (int)t->dims[0] != W.k) { fprintf(stderr, "lg_b200: cannot stack %s onto %s\n", t->name, t0->name); exit(1); }
-        if (t != parts.back() && t->dims[1] % 16) { fprintf(stderr, "lg_b200: %s: %d rows is not a multiple of 16\n", t->name, (int)t->dims[1]); exit(1); }
+        if (t->type != t0->type || (int)t->dims[0] != W.k) LG_BUILD_FAIL("lg_b200: cannot stack %s onto %s\n", t->name, t0->name);
+        if (t != parts.back() && t->dims[1] % 16) LG_BUILD_FAIL("lg_b200: %s: %d rows is not a multiple of 16\n", t->name, (int)t->dims[1]);
         W.m += (int)t->dims[1];
     }
-    if (interleave && (parts.size() != 2 || parts[0]->dims[1] != parts[1]->dims[1] || parts[0]->dims[1] % 32)) {
-        fprintf(stderr, "lg_b200: %s / gate-up pair cannot be interleaved\n", t0->name); exit(1);
-    }
+    if (interleave && (parts.size() != 2 || parts[0]->dims[1] != parts[1]->dims[1] || parts[0]->dims[1] % 32))
+        LG_BUILD_FAIL("lg_b200: %s / gate-up pair cannot be interleaved\n", t0->name);
     W.nkp = W.k / 64;
     W.n_row_tiles = ((W.m + 15) / 16 + 3) / 4 * 4;          // padded with zero tiles: the kernels fetch groups of up to 4
     W.ldo = W.n_row_tiles * 16;
@@ -279,10 +284,14 @@ template <int NT> void pf_attr_n() {
     pf_attr<NT, LG_FMT_Q4_0, LG_PF_STORE>(); pf_attr<NT, LG_FMT_Q4_0, LG_PF_GEGLU>();
     pf_attr<NT, LG_FMT_Q4_K, LG_PF_STORE>(); pf_attr<NT, LG_FMT_Q4_K, LG_PF_GEGLU>();
 }
+// cudaFuncSetAttribute applies to the current device only, so the opt-in is tracked per device.
 void set_kernel_attributes() {
-    static bool done = false;
-    if (done) return;
-    done = true;
+    static bool done[64] = {false};
+    int dev = 0;
+    LG_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) { fprintf(stderr, "lg_b200: device ordinal %d out of range\n", dev); exit(1); }
+    if (done[dev]) return;
+    done[dev] = true;
     gemv_attr_r<1>(); gemv_attr_r<2>(); gemv_attr_r<4>();
     gemv_attr<4, 1, LG_FMT_Q4_0, LG_EPI_GEGLU>(); gemv_attr<4, 2, LG_FMT_Q4_0, LG_EPI_GEGLU>();
     gemv_attr<4, 1, LG_FMT_Q4_K, LG_EPI_GEGLU>(); gemv_attr<4, 2, LG_FMT_Q4_K, LG_EPI_GEGLU>();
@@ -772,14 +781,15 @@ void bind_kv(Engine *e, const struct kvcache *kv) {
 enum { F_HEAD = 1, F_LOGITS = 2, F_ACCEPT = 4, F_ADVANCE = 8, F_NOEMBED = 16 };   // NOEMBED: x rows are already in place
 
 // `only` selects kernel classes (the benchmark times them in isolation); the default runs everything.
+// C_FUSED: a class-restricted pass keeps the epilogue variants of the full step (the o-projection that carries the
+// residual update and the next norm, the gate/up matmul that applies the deferred 1/rms) instead of the plain ones.
 enum { C_QKV = 1, C_O = 2, C_GATEUP = 4, C_DOWN = 8, C_HEAD = 16, C_PLE = 32, C_NORM = 64, C_ATTN = 256, C_MISC = 512,
-       C_ALL = 1023 };
+       C_ALL = 1023, C_FUSED = 1024 };
 
-void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags, int only = C_ALL) {
+void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags, int only = C_ALL | C_FUSED) {
     const struct model *m = e->m;
     const struct config *c = &m->cfg;
     const int ne = c->n_embd, H = c->n_head, ple = c->n_embd_per_layer, nl = c->n_layer;
-    cudaStream_t s = e->stream;
     const int *d_toks = e->st->toks, *d_pos = &e->st->pos;
 
     if ((only & C_MISC) && !(flags & F_NOEMBED))
@@ -826,8 +836,9 @@ void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags, int 
         // o-projection, then x += norm(o)*w_post_attn and the ffn_norm panel
         int ks_o = 1;
         GemvExtra xo; xo.ks_out = &ks_o;
-        // (class-isolated timing passes keep the o-projection a pure matmul followed by the norm kernel)
-        const bool tail_o = only == C_ALL && normtail_ok(e, w.o, M > 4 ? 2 : 1);
+        // (class-isolated timing passes keep the o-projection a pure matmul followed by the norm kernel unless C_FUSED asks
+        // for the variants the full step runs)
+        const bool tail_o = ((only & C_ALL) == C_ALL || (only & C_FUSED)) && normtail_ok(e, w.o, M > 4 ? 2 : 1);
         // gate/up with the GeGLU epilogue writing the down-projection's panel
         LgPanel pf = e->p_ff; pf.nsb = w.nff / 32;
         GemvExtra xg; xg.outp = &pf;
@@ -1076,9 +1087,14 @@ void check_err(Engine *e) {
 // ------------------------------------------------------------------------------------------
 // draft head
 // ------------------------------------------------------------------------------------------
+void draft_free(DraftW *d);
+
+// Returns nullptr (after a message) when the head cannot run here: a tensor type this backend has no kernel for, or a
+// head count the target's KV heads do not divide.  The caller then disables drafting; decoding continues.
 DraftW *draft_build(Engine *e, struct mtp *t, const struct kvcache *kv) {
     const struct model *m = e->m;
     DraftW *d = new DraftW();
+    struct SoftScope { SoftScope() { g_soft_build = true; g_soft_failed = false; } ~SoftScope() { g_soft_build = false; } } soft_scope;
     d->ni = t->n_inner; d->nb = t->n_bb; d->nff = t->n_ff; d->n_head = t->n_head; d->n_vocab = t->n_vocab;
     d->eps = t->eps; d->base_full = t->base_full; d->base_swa = t->base_swa; d->softcap = t->softcap;
     d->pre = build_wmat(e, {t->pre});
@@ -1100,8 +1116,17 @@ DraftW *draft_build(Engine *e, struct mtp *t, const struct kvcache *kv) {
         if (d->n_head * s->hd > qmax) qmax = d->n_head * s->hd;
         if (s->hd > maxhd) maxhd = s->hd;
         if (s->local) d->hd_local = s->hd; else d->hd_global = s->hd;
-        if (d->n_head % m->n_head_kv[s->src]) { fprintf(stderr, "lg_b200: draft head count does not divide the target's KV heads\n"); exit(1); }
         d->blk.push_back(b);
+        if (d->n_head % m->n_head_kv[s->src]) {
+            fprintf(stderr, "lg_b200: the draft head's %d query heads are not a multiple of the target's %d KV heads\n", d->n_head, m->n_head_kv[s->src]);
+            g_soft_failed = true;
+        }
+        if (g_soft_failed) break;
+    }
+    if (g_soft_failed) {
+        fprintf(stderr, "lg_b200: draft head unusable on the device; drafting is off, decoding continues\n");
+        draft_free(d);
+        return nullptr;
     }
     d->cat = dalloc<float>(2 * d->nb); d->x = dalloc<float>(d->ni); d->hbuf = dalloc<float>(d->ni);
     d->qbuf = dalloc<float>((size_t)LG_MAXM * (qmax + 64)); d->qrot = dalloc<float>(qmax);
@@ -1126,7 +1151,6 @@ DraftW *draft_build(Engine *e, struct mtp *t, const struct kvcache *kv) {
 void enqueue_draft(Engine *e, DraftW *d, const struct kvcache *kv, int slot, bool chained) {
     const struct model *m = e->m;
     const struct config *c = &m->cfg;
-    cudaStream_t s = e->stream;
     const int ni = d->ni, nb = d->nb;
     launch_k(e, lg_embed_rows, dim3(1), dim3(256), 0, e->head.wq, e->head.ws, e->head.wd, e->head.fmt, e->head.nkp, e->head.m,
                                     e->st->toks + (slot - 1), sqrtf((float)nb), d->cat, 2 * nb);
@@ -1185,6 +1209,7 @@ DraftW *draft_for(Engine *e, struct mtp *t, const struct kvcache *kv) {
     if (e->draft && e->draft_owner == t) return e->draft;
     if (e->draft) { draft_free(e->draft); e->draft = nullptr; }
     e->draft = draft_build(e, t, kv);
+    if (!e->draft) { t->cuda = (void *)-1; e->draft_owner = nullptr; return nullptr; }     // permanently off for this head
     e->draft_owner = t;
     t->cuda = e->draft;
     return e->draft;
@@ -1208,8 +1233,18 @@ void run_draft(Engine *e, DraftW *d, const struct kvcache *kv, int slot, bool ch
     LG_CHECK(cudaGraphLaunch(it->second, e->stream));
 }
 
+// Positions [pos, pos + n) must lie inside the cache: past max_seq the full-attention layers would wrap over their
+// oldest rows and a block would touch more key tiles than the attention grid has.  The reference's callers guard this
+// themselves (src/run.c:752 falls back to plain decode near the end); a call that got through anyway is refused.
+bool pos_in_cache(const struct kvcache *kv, int pos, int n, const char *what) {
+    if (pos >= 0 && n >= 0 && (long long)pos + n <= kv->max_seq) return true;
+    fprintf(stderr, "lg_b200: %s at positions %d..%d lies outside the cache of %d rows\n", what, pos, pos + n - 1, kv->max_seq);
+    return false;
+}
+
 int spec_n(struct model *m, struct kvcache *kv, int n, const int *toks, int pos, int *out) {
     Engine *e = engine_for(m);
+    if (!pos_in_cache(kv, pos, n, "a forward")) exit(1);
     upload_round(e, toks, n, pos);
     int flags = F_HEAD | F_ACCEPT | (model_pick ? F_LOGITS : 0);
     run_forward(e, kv, n, flags);
@@ -1310,6 +1345,7 @@ void kvcache_restore_prefix(struct kvcache *kv, int n) {
 
 void model_forward(struct model *m, struct kvcache *kv, int token, int pos, float *logits) {
     Engine *e = engine_for(m);
+    if (!pos_in_cache(kv, pos, 1, "model_forward")) exit(1);
     upload_round(e, &token, 1, pos);
     run_forward(e, kv, 1, logits ? (F_HEAD | F_LOGITS | F_ACCEPT) : 0);
     if (logits) LG_CHECK(cudaMemcpyAsync(logits, e->logits, (size_t)m->cfg.n_vocab * 4, cudaMemcpyDeviceToHost, e->stream));
@@ -1329,6 +1365,8 @@ int model_forward_next(struct model *m, struct kvcache *kv, int token, int pos) 
 static void prefill_impl(struct model *m, struct kvcache *kv, const float *rows, const int *ids, int n, int pos0) {
     Engine *e = engine_for(m);
     const int ne = m->cfg.n_embd;
+    if (n <= 0) return;
+    if (!pos_in_cache(kv, pos0, n, "a prompt pass")) exit(1);
     std::vector<int> toks(n), ridx(n, -1);
     bool media = false;
     for (int i = 0; i < n; i++) {
@@ -1408,6 +1446,7 @@ int model_forward_spec(struct model *m, struct kvcache *kv, const int *toks, int
 
 int lg_forward_spec_n(struct model *m, struct kvcache *kv, int n, const int *toks, int pos, int *out) {
     if (n < 1 || n > LG_MAXM) return -1;
+    if (!pos_in_cache(kv, pos, n, "lg_forward_spec_n")) return -2;
     return spec_n(m, kv, n, toks, pos, out);
 }
 
@@ -1499,6 +1538,7 @@ int lg_rounds_begin(struct model *m, int first, int pos, int n_emitted) {
     h->pos = pos; h->toks[0] = first; h->n_emitted = n_emitted;
     LG_CHECK(cudaMemcpyAsync(e->st, h, sizeof *h, cudaMemcpyHostToDevice, e->stream));
     LG_CHECK(cudaStreamSynchronize(e->stream));
+    e->pos_hi = pos;
     return 0;
 }
 
@@ -1507,6 +1547,13 @@ int lg_rounds_enqueue(struct model *m, struct kvcache *kv, struct mtp *t, int n,
     if (n < 1 || n > LG_MAXM) return -1;
     DraftW *d = (t && n > 1) ? draft_for(e, t, kv) : nullptr;
     if (mode == 1 && n > 1 && !d) return -1;
+    // The position advances on the device; the host only knows an upper bound (every round accepts everything).  Rounds
+    // that could step outside the cache are refused before anything is enqueued; lg_rounds_collect tightens the bound.
+    if (n_rounds < 0 || (long long)e->pos_hi + (long long)n_rounds * n > kv->max_seq) {
+        fprintf(stderr, "lg_b200: %d rounds of width %d from position <= %d could leave the cache of %d rows\n", n_rounds, n, e->pos_hi, kv->max_seq);
+        return -2;
+    }
+    e->pos_hi += n_rounds * n;
     bind_kv(e, kv);
     char key[48];
     snprintf(key, sizeof key, "r%d_%d_%d", n, mode, d ? 1 : 0);
@@ -1549,6 +1596,7 @@ int lg_rounds_collect(struct model *m, int *tokens, int from, int cap, int *stat
     LG_CHECK(cudaMemcpyAsync(e->st_host, e->st, sizeof(LgRoundState), cudaMemcpyDeviceToHost, e->stream));
     check_err(e);
     LgRoundState *h = e->st_host;
+    e->pos_hi = h->pos;
     int n = h->n_emitted - from;
     if (n > cap) n = cap;
     if (n > 0 && tokens) LG_CHECK(cudaMemcpy(tokens, e->log + from, (size_t)n * 4, cudaMemcpyDeviceToHost));
@@ -1564,7 +1612,7 @@ int lg_bench_matmul_pass(struct model *m, int n, int classes) {
     Engine *e = engine_for(m);
     if (n < 1 || n > LG_MAXM || !e->kv_bound) return -1;
     char key[32];
-    if (classes <= 0) classes = C_QKV | C_O | C_GATEUP | C_DOWN | C_HEAD | C_PLE;
+    if (classes <= 0) classes = C_QKV | C_O | C_GATEUP | C_DOWN | C_HEAD | C_PLE | C_FUSED;
     snprintf(key, sizeof key, "mm%d_%d", n, classes);
     auto it = e->graphs.find(key);
     if (it == e->graphs.end()) {
@@ -1633,6 +1681,12 @@ extern "C" int lg_flash_decode_noalloc(const float *d_q, const void *d_k_f16, co
     if (M < 1 || M > LG_MAXM || (hd != 64 && hd != 128 && hd != 256 && hd != 512) || Hkv < 1 || H % Hkv || Hkv > MAX_KV_HEADS ||
         seq < 1 || pos < 0 || !d_q || !d_k_f16 || !d_v_f16 || !d_out) {
         fprintf(stderr, "lg_flash_decode_noalloc: bad arguments\n");
+        return -1;
+    }
+    // K and V rows are fetched with 16-byte asynchronous copies and q / out with 4-byte accesses: a pointer into the
+    // middle of a tensor (an odd element offset) would fault on the device, so it is turned away here
+    if ((((uintptr_t)d_k_f16 | (uintptr_t)d_v_f16) & 15) || (((uintptr_t)d_q | (uintptr_t)d_out) & 3)) {
+        fprintf(stderr, "lg_flash_decode_noalloc: k and v must be 16-byte aligned, q and out 4-byte aligned\n");
         return -1;
     }
     int dev = 0;

@@ -66,6 +66,8 @@ static void parse_value(struct cursor *c, struct gguf_meta *kv) {
         if (!kv->value.arr.data) { c->bad = 1; return; }
         take(c, kv->value.arr.data, n * esz);
     } else if (kv->value.arr.type == GGUF_TYPE_STRING) {
+        /* every string costs at least its 8-byte length word: more entries than that cannot be in the file */
+        if (n > (uint64_t)(c->end - c->p) / 8) { c->bad = 1; return; }
         char **v = calloc(n ? n : 1, sizeof(char *));
         kv->value.arr.data = v;
         if (!v) { c->bad = 1; return; }
@@ -144,10 +146,16 @@ struct gguf_context *load_gguf(const char *path) {
     g->data_size = g->map_len - g->data_offset;
     for (uint64_t i = 0; i < g->header.num_tensors; i++) {
         struct gguf_tensor *t = &g->tensors[i];
+        /* element count with overflow caught: no format packs more than 32 elements into a byte-sized unit
+         * smaller than 1/32 byte per element, so a count beyond 32 x the data section cannot be real */
         int64_t n = 1;
-        for (uint32_t d = 0; d < t->n_dims; d++) n *= (int64_t)t->dims[d];
-        size_t bytes = ggml_nbytes(t->type, n);
-        if (t->offset > g->data_size || bytes > g->data_size - t->offset) {
+        int wrapped = 0;
+        for (uint32_t d = 0; d < t->n_dims; d++) {
+            if (t->dims[d] > (uint64_t)INT64_MAX || __builtin_mul_overflow(n, (int64_t)t->dims[d], &n)) { wrapped = 1; break; }
+            if ((uint64_t)n > (uint64_t)g->data_size * 32u + 32u) { wrapped = 1; break; }
+        }
+        size_t bytes = wrapped ? 0 : ggml_nbytes(t->type, n);
+        if (wrapped || t->offset > g->data_size || bytes > g->data_size - t->offset) {
             fprintf(stderr, "gguf: tensor %s lies outside the file\n", t->name);
             free_gguf(g);
             return NULL;

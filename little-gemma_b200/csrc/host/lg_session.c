@@ -50,7 +50,8 @@ int  lgs_n_vocab(void *p) { return ((struct lg_session *)p)->m.cfg.n_vocab; }
 int  lgs_n_embd(void *p) { return ((struct lg_session *)p)->m.cfg.n_embd; }
 int  lgs_n_layer(void *p) { return ((struct lg_session *)p)->m.cfg.n_layer; }
 int  lgs_mtp_n(void) { return LG_MTP_N; }
-void lgs_set_mtp_n(void *p, int n) { ((struct lg_session *)p)->mtp_n = n; }
+/* verify width of the session's rounds, clamped to what the backend runs (1..8) */
+void lgs_set_mtp_n(void *p, int n) { ((struct lg_session *)p)->mtp_n = n < 1 ? 1 : (n > 8 ? 8 : n); }
 void *lgs_model(void *p) { return &((struct lg_session *)p)->m; }
 void *lgs_kv(void *p) { return &((struct lg_session *)p)->kv; }
 void *lgs_head(void *p) { return ((struct lg_session *)p)->head; }
@@ -87,10 +88,13 @@ int  lgs_dequant(unsigned type, const void *src, float *out, long long n) {
  * mode 0 plain decode, 1 head drafts, 2 replayed drafts (replay[i] = draft for stream index i),
  * 3 head drafts computed through the API but replaced by the replayed ones (the acceptance
  * rate is then the table's while the head's cost is still paid). */
+static int replay_at(const int *replay, int n_replay, int i) { return replay && i >= 0 && i < n_replay ? replay[i] : 0; }
+
 int lgs_rounds_host(void *p, int best, int pos, int g, int n_gen, int n_rounds, int *out_toks, int mode,
-                    const int *replay, int *stats) {
+                    const int *replay, int n_replay, int *stats) {
     struct lg_session *s = p;
     int nd = 0, na = 0, N = s->mtp_n, rounds = 0;
+    if (N < 1 || N > 8) return -1;
     while (g < n_gen && (n_rounds <= 0 || rounds < n_rounds)) {
         rounds++;
         if (!mode) { best = model_forward_next(&s->m, &s->kv, best, pos++); out_toks[g++] = best; continue; }
@@ -99,14 +103,14 @@ int lgs_rounds_host(void *p, int best, int pos, int g, int n_gen, int n_rounds, 
         if (mode == 1 || mode == 3) {
             int d = mtp_draft(s->head, &s->m, &s->kv, best, pos);
             toks[1] = d >= 0 ? d : best;
-            if (mode == 3) toks[1] = replay[g];
+            if (mode == 3) toks[1] = replay_at(replay, n_replay, g);
             for (int j = 2; j < N; j++) {
                 int dj = mtp_draft_chain(s->head, &s->m, &s->kv, toks[j - 1], pos + j - 1);
                 toks[j] = dj >= 0 ? dj : toks[j - 1];
-                if (mode == 3) toks[j] = replay[g + j - 1];
+                if (mode == 3) toks[j] = replay_at(replay, n_replay, g + j - 1);
             }
         } else {
-            for (int j = 1; j < N; j++) toks[j] = replay[g + j - 1];
+            for (int j = 1; j < N; j++) toks[j] = replay_at(replay, n_replay, g + j - 1);
         }
         int adv = lg_forward_spec_n(&s->m, &s->kv, N, toks, pos, out);
         nd += N - 1; na += adv - 1;
@@ -121,14 +125,14 @@ int lgs_rounds_host(void *p, int best, int pos, int g, int n_gen, int n_rounds, 
 
 /* Prompt then host-driven rounds: the generate loop of src/run.c:697-785. */
 int lgs_generate(void *p, const int *prompt, int n_prompt, int n_gen, int *out_toks, int mode,
-                 const int *replay, int *stats) {
+                 const int *replay, int n_replay, int *stats) {
     struct lg_session *s = p;
     int st[4];
     if (n_prompt > 1) model_prefill(&s->m, &s->kv, prompt, n_prompt - 1, 0);
     int pos = n_prompt - 1;
     int best = model_forward_next(&s->m, &s->kv, prompt[n_prompt - 1], pos++);
     out_toks[0] = best;
-    int g = lgs_rounds_host(p, best, pos, 1, n_gen, 0, out_toks, mode, replay, st);
+    int g = lgs_rounds_host(p, best, pos, 1, n_gen, 0, out_toks, mode, replay, n_replay, st);
     if (stats) { stats[0] = st[0]; stats[1] = st[1]; }
     return g;
 }

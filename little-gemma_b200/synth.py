@@ -204,6 +204,10 @@ class TargetShape:
     q_norm_scale: Optional[float] = None   # "conditioned twin": attn_q_norm.weight = this constant
     wtype: int = Q4_0
     sigma: float = 0.02
+    head_dim_global: Optional[int] = None  # head size of the full-attention layers when it differs (Gemma-4: 512 vs 256)
+
+    def hd(self, l: int) -> int:
+        return self.head_dim if (self.is_local(l) or self.head_dim_global is None) else self.head_dim_global
 
     def is_local(self, l: int) -> bool:
         return (self.n_layer - 1 - l) % (self.local_per_global + 1) != 0
@@ -211,8 +215,10 @@ class TargetShape:
     def weight_bytes(self) -> int:
         """Algorithmic bytes of quantized weights one decode/verify step streams."""
         ne, H, Hkv, hd, L = self.n_embd, self.n_head, self.n_head_kv, self.head_dim, self.n_layer
-        per_layer = ne * H * hd + 2 * ne * Hkv * hd + H * hd * ne + 3 * ne * self.n_ff + 2 * ne * self.ple
-        total = L * per_layer + self.n_vocab * ne + ne * self.ple * L
+        total = self.n_vocab * ne + ne * self.ple * L
+        for l in range(L):
+            hd = self.hd(l)
+            total += ne * H * hd + 2 * ne * Hkv * hd + H * hd * ne + 3 * ne * self.n_ff + 2 * ne * self.ple
         return int(total * 0.5625)
 
 
@@ -290,7 +296,7 @@ def write_target(path: str, s: TargetShape, seed: int = 0, device: str = "cpu") 
     w.add_f32(f"{a}.rope.freq_base", s.rope_base)
     w.add_f32(f"{a}.rope.freq_base_swa", s.rope_base_swa)
     w.add_f32(f"{a}.final_logit_softcapping", s.softcap)
-    w.add_u32(f"{a}.attention.key_length", s.head_dim)
+    w.add_u32(f"{a}.attention.key_length", s.head_dim_global or s.head_dim)
     w.add_u32(f"{a}.attention.key_length_swa", s.head_dim)
     w.add_u32(f"{a}.attention.shared_kv_layers", s.shared_kv_layers)
     w.add_arr_bool(f"{a}.attention.sliding_window_pattern", [s.is_local(l) for l in range(s.n_layer)])
@@ -302,13 +308,14 @@ def write_target(path: str, s: TargetShape, seed: int = 0, device: str = "cpu") 
             wt = Q4_0                           # super-blocks need k % 256 == 0
         w.declare(name, [k, m], wt, lambda: g.weight(k * m, s.sigma, wt))
 
-    ne, H, Hkv, hd, L = s.n_embd, s.n_head, s.n_head_kv, s.head_dim, s.n_layer
+    ne, H, Hkv, L = s.n_embd, s.n_head, s.n_head_kv, s.n_layer
     n_own = L - s.shared_kv_layers
     qw("token_embd.weight", ne, s.n_vocab)
     w.declare("output_norm.weight", [ne], F32, _ones(ne))
     if s.rope_freqs:
-        rf = np.linspace(1.0, 8.0, hd // 2, dtype=np.float32)
-        w.declare("rope_freqs.weight", [hd // 2], F32, lambda: rf.view(np.uint8))
+        hg = s.head_dim_global or s.head_dim
+        rf = np.linspace(1.0, 8.0, hg // 2, dtype=np.float32)
+        w.declare("rope_freqs.weight", [hg // 2], F32, lambda: rf.view(np.uint8))
     if s.ple:
         # gather-only table: always q4_0 so its row length need not be a multiple of 256
         qw("per_layer_token_embd.weight", s.ple * L, s.n_vocab, Q4_0)
@@ -316,14 +323,15 @@ def write_target(path: str, s: TargetShape, seed: int = 0, device: str = "cpu") 
         w.declare("per_layer_proj_norm.weight", [s.ple], F32, _ones(s.ple))
     for l in range(L):
         p = f"blk.{l}."
+        hd = s.hd(l)
         w.declare(p + "attn_norm.weight", [ne], F32, _ones(ne))
         qw(p + "attn_q.weight", ne, H * hd)
         if l < n_own:
             qw(p + "attn_k.weight", ne, Hkv * hd)
             if not s.drop_attn_v:
                 qw(p + "attn_v.weight", ne, Hkv * hd)
-        w.declare(p + "attn_q_norm.weight", [hd], F32,
-                  _ones(hd, 1.0 if s.q_norm_scale is None else s.q_norm_scale))
+        qs = 1.0 if s.q_norm_scale is None else s.q_norm_scale * (s.head_dim / hd) ** 0.5   # hd^-0.5 per layer kind
+        w.declare(p + "attn_q_norm.weight", [hd], F32, _ones(hd, qs))
         w.declare(p + "attn_k_norm.weight", [hd], F32, _ones(hd))
         qw(p + "attn_output.weight", H * hd, ne)
         w.declare(p + "post_attention_norm.weight", [ne], F32, _ones(ne))

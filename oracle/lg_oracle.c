@@ -6,6 +6,9 @@
  * backend (oracle/_ref) on seeded models and by golden vectors generated from that backend
  * (tests/golden).  Each routine names the reference lines whose arithmetic it restates.
  */
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -331,6 +334,15 @@ int  orc_n_vocab(void *p) { return ((struct orc *)p)->m.cfg.n_vocab; }
 int  orc_n_embd(void *p) { return ((struct orc *)p)->m.cfg.n_embd; }
 int  orc_n_layer(void *p) { return ((struct orc *)p)->m.cfg.n_layer; }
 int  orc_mtp_n(void) { return LG_MTP_N; }
+/* thread count of the OpenMP runtime (set it explicitly: a launcher may have exported OMP_NUM_THREADS=1) */
+int  orc_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n; return 1;
+#endif
+}
 void orc_set_mtp_n(void *p, int n) { ((struct orc *)p)->mtp_n = n; }
 void orc_forward(void *p, int tok, int pos, float *logits) { forward(p, tok, pos, logits); }
 void orc_last_hidden(void *p, float *out) {

@@ -61,6 +61,7 @@ class _Oracle:
         f("generate").argtypes = [C.c_void_p, _i32p, C.c_int, C.c_int, _i32p, C.c_int, C.c_void_p, _i32p]
         f("generate").restype = C.c_int
         f("mtp_n").restype = C.c_int
+        f("set_threads").argtypes = [C.c_int]; f("set_threads").restype = C.c_int
         self._f = f
         self.h = f("open")(target.encode(), (head or "").encode(), max_seq, int(kv_f16_all))
         if not self.h:
@@ -73,6 +74,10 @@ class _Oracle:
         if self.h:
             self._f("close")(self.h)
             self.h = None
+
+    def set_threads(self, n: int) -> int:
+        """Ask the checker's OpenMP runtime for n threads (0: leave as is); returns the count it will use."""
+        return int(self._f("set_threads")(n))
 
     def forward(self, tok: int, pos: int) -> np.ndarray:
         out = np.empty(self.n_vocab, dtype=np.float32)

@@ -15,7 +15,23 @@
 #include "quant.h"
 #include "model.h"
 
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
 int (*model_pick)(const float *logits, int n) = NULL;
+
+/* Thread count of the OpenMP runtime this image is linked against.  A launcher may have exported
+ * OMP_NUM_THREADS=1 for its workers (torchrun does) before this library was loaded; the timed CPU
+ * baseline sets the count it wants here and reports what the runtime then says. */
+int ref_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n; return 1;
+#endif
+}
 
 struct ref_session {
     struct gguf_context *ctx;

@@ -25,6 +25,28 @@ def shapes():
         "mid_k": (s.TargetShape(n_layer=3, n_embd=512, n_head=8, n_head_kv=2, head_dim=256, n_ff=2048, n_vocab=8192,
                                 window=64, local_per_global=2, ple=0, q_norm_scale=256 ** -0.5, wtype=s.Q4_K),
                   None, 7, 8),
+        # --- layer cuts of the benchmark shapes (2 layers: one sliding-window, one full-attention; vocab cut to 32768) ---
+        # 12B-class shape, q4_0, norms = 1 as the benchmark files have them
+        "b12_cut": (dataclasses.replace(s.B12, n_layer=2, n_vocab=32768), None, 20, 21),
+        # its well-conditioned twin (q-norm weight hd^-0.5) with a 1-block head of the benchmark head's width
+        "b12_cut_cond": (dataclasses.replace(s.B12, n_layer=2, n_vocab=32768, q_norm_scale=256 ** -0.5),
+                         dataclasses.replace(s.B12_HEAD, n_layer=1), 20, 21),
+        # the same shape in q4_K
+        "b12k_cut": (dataclasses.replace(s.B12, n_layer=2, n_vocab=32768, wtype=s.Q4_K), None, 22, 23),
+        "b12k_cut_cond": (dataclasses.replace(s.B12, n_layer=2, n_vocab=32768, wtype=s.Q4_K, q_norm_scale=256 ** -0.5),
+                          None, 22, 23),
+        # E4B-class shape: per-layer embeddings of width 256 together with head size 256, 8 / 2 heads
+        "e4b_cut": (dataclasses.replace(s.E4B, n_layer=2, n_vocab=32768), None, 24, 25),
+        "e4b_cut_cond": (dataclasses.replace(s.E4B, n_layer=2, n_vocab=32768, q_norm_scale=256 ** -0.5),
+                         dataclasses.replace(s.E4B_HEAD, n_layer=1), 24, 25),
+        # full-attention layers with head size 512 beside sliding-window layers of 256 (real Gemma-4 geometry)
+        "hd512": (s.TargetShape(n_layer=4, n_embd=512, n_head=4, n_head_kv=2, head_dim=256, head_dim_global=512, n_ff=1024,
+                                n_vocab=4096, window=64, local_per_global=1, ple=0, q_norm_scale=256 ** -0.5),
+                  None, 26, 27),
+        # a head whose 3 query heads the target's 2 KV heads do not divide: the device must turn drafting off, not exit
+        "mid_oddhead": (s.TargetShape(n_layer=6, n_embd=512, n_head=8, n_head_kv=2, head_dim=256, n_ff=2048, n_vocab=8192,
+                                      window=64, local_per_global=2, ple=0, q_norm_scale=256 ** -0.5),
+                        s.HeadShape(n_layer=1, n_inner=256, n_head=3, n_ff=512), 5, 11),
         # all-zero weights: every logit ties at 0, the argmax must be index 0
         "zero": (dataclasses.replace(tiny, sigma=0.0, ple=0), None, 9, 10),
     }

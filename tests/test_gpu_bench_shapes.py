@@ -1,0 +1,139 @@
+"""GPU parity tests on layer cuts of the benchmark's own shapes.
+
+The full 12B-class / E4B-class files take the CPU oracle minutes per token, so each shape is cut to
+two layers (one sliding-window, one full-attention) with the vocabulary cut to 32768; everything
+else -- widths, head counts, head size 256, FFN width, per-layer embeddings of width 256, window,
+q4_0 and q4_K super-blocks -- is the benchmark's.  Two files per shape:
+
+* the "conditioned twin" (q-norm weight hd^-0.5) carries the end-to-end gates: teacher-forced logits
+  within 1e-2 of the step's logit range, argmax equality outside the error margin, speculative
+  stream == plain stream;
+* the file with every norm weight = 1 (what the benchmark runs) is compared layer-locally: with two
+  layers the chain oracle-embedding -> layer (window) -> layer (full) -> head is one layer of each kind fed
+  by bit-identical inputs, so the same bound applies before the model's own noise amplification
+  (which grows with depth) takes over.
+
+A third model has full-attention layers of head size 512 beside sliding-window layers of 256.
+"""
+import numpy as np
+import pytest
+
+from tests.conftest import model_files, synth_module
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-2          # max-abs logit error allowed, as a fraction of that step's logit range
+
+
+def _random_stream_logits(lg, name, n_steps, n_prefill=0, max_seq=1024, seed=31):
+    """Feed one seeded uniform-random token stream to the oracle and to the CUDA backend, token by token (after an
+    optional prompt pass of n_prefill tokens on both sides); returns rows of (err/range, oracle margin/range, argmax equal)."""
+    from oracle.pyref import PortOracle
+    s = synth_module()
+    tp, _ = model_files(name)
+    o = PortOracle(tp, None, max_seq, True, 4)
+    stream = s.prompt_ids(n_prefill + n_steps, o.n_vocab, seed=seed)
+    rows = []
+    with lg.Session(tp, None, max_seq) as g:
+        if n_prefill:
+            o.prefill(stream[:n_prefill], 0)
+            g.prefill(stream[:n_prefill], 0)
+        for i in range(n_prefill, n_prefill + n_steps):
+            want = o.forward(int(stream[i]), i)
+            got = g.forward(int(stream[i]), i)
+            rng_ = float(want.max() - want.min())
+            top2 = np.partition(want, -2)[-2:]
+            rows.append((float(np.abs(got - want).max()) / rng_, float(top2[1] - top2[0]) / rng_,
+                         int(got.argmax() == want.argmax())))
+    o.close()
+    return np.array(rows)
+
+
+def _gate(name, r, what):
+    err, margin, same = r[:, 0], r[:, 1], r[:, 2]
+    print(f"{name} {what}: max err/range {err.max():.2e}, mean {err.mean():.2e}, argmax equal {int(same.sum())}/{len(same)}")
+    assert err.max() <= TOL, (name, what, err.max())
+    clear = margin > 2 * err.max()
+    assert np.all(same[clear] == 1), (name, what)
+
+
+@pytest.mark.parametrize("name", ["b12_cut_cond", "b12k_cut_cond", "e4b_cut_cond", "hd512"])
+def test_conditioned_twin_logits_token_by_token(lg, port_built, name):
+    _gate(name, _random_stream_logits(lg, name, 28), "decode steps")
+
+
+@pytest.mark.parametrize("name", ["b12_cut", "b12k_cut", "e4b_cut"])
+def test_norms_one_file_layer_local_logits(lg, port_built, name):
+    _gate(name, _random_stream_logits(lg, name, 20), "norms = 1, one layer of each kind")
+
+
+@pytest.mark.parametrize("name", ["b12_cut_cond", "b12k_cut_cond", "e4b_cut_cond", "hd512"])
+def test_prompt_pass_then_logits(lg, port_built, name):
+    """The wide prompt pass (a block of 40 tokens, then a ragged tail) fills the cache; the following steps are compared."""
+    _gate(name, _random_stream_logits(lg, name, 6, n_prefill=45), "after a 45-token prompt pass")
+
+
+@pytest.mark.parametrize("name", ["b12_cut_cond", "e4b_cut_cond", "hd512"])
+def test_verify_rows_equal_plain_steps(lg, name):
+    """Every row of a verify block carries the bits of the plain decode step at its position (random drafts, so rows
+    past the first rejected draft are checked as well through the returned successors)."""
+    s = synth_module()
+    tp, _ = model_files(name)
+    with lg.Session(tp, None, 512, mtp_n=4) as g:
+        V = g.n_vocab
+        stream = s.prompt_ids(40, V, seed=33)
+        g.prefill(stream[:16], 0)
+        plain = [g.next(int(stream[i]), i) for i in range(16, 40)]          # greedy successor of every position
+    for n in (2, 4, 5, 8):
+        with lg.Session(tp, None, 512, mtp_n=n) as g:
+            g.prefill(stream[:16], 0)
+            for p in range(16, 40 - n, n):
+                adv, out = g.spec(stream[p:p + n], p)
+                assert list(out) == plain[p - 16:p - 16 + n], (name, n, p)
+                want_adv = 1
+                while want_adv < n and plain[p - 16 + want_adv - 1] == stream[p + want_adv]:
+                    want_adv += 1
+                assert adv == want_adv
+
+
+@pytest.mark.parametrize("name", ["b12_cut_cond", "e4b_cut_cond"])
+def test_mtp_stream_equals_plain_stream_with_head(lg, name):
+    """Replayed drafts at several acceptance rates and the real (random-init) head, host-driven and device-resident."""
+    s = synth_module()
+    tp, hp = model_files(name)
+    with lg.Session(tp, hp, 1024) as g:
+        V = g.n_vocab
+        prompt = s.prompt_ids(24, V, seed=34)
+        plain, _ = g.generate_device(prompt, 64, 0)
+    for p in (0.0, 0.5, 1.0):
+        rp = s.replay_drafts(plain, V, p)
+        with lg.Session(tp, hp, 1024) as g:
+            a, _ = g.generate_device(prompt, 64, 2, rp)
+            assert np.array_equal(a[:64], plain[:64]), (name, p, "device")
+        with lg.Session(tp, hp, 1024) as g:
+            b, _ = g.generate(prompt, 64, 2, rp)
+            assert np.array_equal(b[:64], plain[:64]), (name, p, "host")
+    with lg.Session(tp, hp, 1024) as g:
+        c, st = g.generate_device(prompt, 64, 1)
+        assert np.array_equal(c[:64], plain[:64]), (name, "head")
+        assert st[0] > 0
+
+
+def test_bench_head_drafts_match_oracle(lg, port_built):
+    """The 12B-class draft head's width (inner 1024, 16 heads of 256): device drafts against the oracle's host draft."""
+    from oracle.pyref import PortOracle
+    s = synth_module()
+    tp, hp = model_files("b12_cut_cond")
+    o = PortOracle(tp, hp, 256, True, 4)
+    stream = s.prompt_ids(28, o.n_vocab, seed=35)
+    same = total = 0
+    with lg.Session(tp, hp, 256) as g:
+        for i in range(len(stream) - 1):
+            o.forward(int(stream[i]), i)
+            g.forward(int(stream[i]), i)
+            if i >= 4:
+                total += 1
+                same += int(g.draft(int(stream[i + 1]), i + 1) == o.draft(int(stream[i + 1]), i + 1))
+    o.close()
+    print(f"12B-class head: draft tokens equal to the oracle's {same}/{total}")
+    assert same >= total * 0.8

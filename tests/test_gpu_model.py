@@ -177,8 +177,11 @@ def test_draft_tokens_match_oracle_where_margin_allows(lg, port_built):
     same = 0
     with lg.Session(tp, hp, 512) as g:
         for i in range(len(stream) - 1):
-            o.forward(int(stream[i]), i)
-            assert g.next(int(stream[i]), i) == int(o.forward(int(stream[i]), i).argmax()) or True
+            want = o.forward(int(stream[i]), i)
+            got = g.next(int(stream[i]), i)
+            top2 = np.partition(want, -2)[-2:]
+            if top2[1] - top2[0] > 2e-2 * (want.max() - want.min()):      # a clear margin: the greedy successor must agree
+                assert got == int(want.argmax()), i
             if i >= 8:
                 same += int(g.draft(int(stream[i + 1]), i + 1) == o.draft(int(stream[i + 1]), i + 1))
     o.close()

@@ -1,0 +1,135 @@
+"""GPU tests of how the serving loop of the reference uses the backend around the speculative step:
+the sampling hook (`model_pick`, src/run.c:83, src/cuda/mtp-kernel.cuh:103-111), plain and speculative
+steps mixed in one session (the `-think` interleave, src/run.c:549-553), a head the device cannot run
+(drafting off, decoding on: src/cuda/mtp-kernel.cuh:263-267,331-337) and the position guard."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from tests.conftest import model_files, synth_module
+
+pytestmark = pytest.mark.gpu
+
+PICK_T = C.CFUNCTYPE(C.c_int, C.POINTER(C.c_float), C.c_int)
+
+
+class _Hook:
+    """Installs a Python function as the library's `model_pick` for the duration of a with-block."""
+
+    def __init__(self, lib, fn):
+        self.slot = C.c_void_p.in_dll(lib, "model_pick")
+        self.rows = []
+
+        def cb(ptr, n):
+            row = np.ctypeslib.as_array(ptr, shape=(n,)).copy()
+            self.rows.append(row)
+            return int(fn(row))
+        self.cb = PICK_T(cb)
+
+    def __enter__(self):
+        self.slot.value = C.cast(self.cb, C.c_void_p).value
+        return self
+
+    def __exit__(self, *a):
+        self.slot.value = None
+
+
+def test_model_pick_rows_are_the_logits_and_its_choice_is_returned(lg, port_built):
+    from oracle.pyref import PortOracle
+    s = synth_module()
+    tp, _ = model_files("tiny_cond")
+    prompt = s.prompt_ids(12, 4096, seed=41)
+    second = lambda row: int(np.argsort(row, kind="stable")[-2])
+    with lg.Session(tp, None, 256, mtp_n=4) as g:
+        g.prefill(prompt[:-1], 0)
+        greedy = g.next(int(prompt[-1]), 11)
+        with _Hook(g.L, second) as h:
+            picked = g.next(int(prompt[-1]), 11)
+            assert len(h.rows) == 1
+        o = PortOracle(tp, None, 256, True, 4)
+        o.prefill(prompt[:-1], 0)
+        want = o.forward(int(prompt[-1]), 11)
+        o.close()
+        row = h.rows[0]
+        # the hook saw the soft-capped logits row of that step, and the call returned the hook's token
+        assert np.abs(row - want).max() <= 1e-2 * (want.max() - want.min())
+        assert int(row.argmax()) == greedy and picked == second(row) and picked != greedy
+        # a verify block: out[j] is the hook's choice on row j, adv counts the run of out[j-1] == toks[j]
+        toks = np.array([int(prompt[-1]), picked, 7, 9], dtype=np.int32)
+        with _Hook(g.L, second) as h:
+            adv, out = g.spec(toks, 11)
+            assert len(h.rows) == 4
+        assert out[0] == picked and [int(x) for x in out] == [second(r) for r in h.rows]
+        want_adv = 1
+        while want_adv < 4 and out[want_adv - 1] == toks[want_adv]:
+            want_adv += 1
+        assert adv == want_adv and adv >= 2
+        # with the hook gone the greedy path is back
+        assert g.next(int(prompt[-1]), 11) == greedy
+
+
+def test_plain_and_speculative_steps_interleave_in_one_session(lg):
+    s = synth_module()
+    tp, _ = model_files("mid")
+    with lg.Session(tp, None, 1024, mtp_n=4) as g:
+        V = g.n_vocab
+        prompt = s.prompt_ids(20, V, seed=42)
+        plain, _ = g.generate(prompt, 80, 0)
+    rp = s.replay_drafts(plain, V, 0.6)
+    with lg.Session(tp, None, 1024, mtp_n=4) as g:
+        g.prefill(prompt[:-1], 0)
+        best, pos, got = g.next(int(prompt[-1]), 19), 20, []
+        got.append(best)
+        n_done = 1
+        for seg, (mode, rounds) in enumerate([(2, 3), (0, 5), (2, 4), (0, 2), (2, 50)]):
+            toks, st = g.rounds_host(best, pos, n_done, 80, rounds, mode, rp)
+            got.extend(int(t) for t in toks)
+            n_done += len(toks)
+            best, pos = st["best"], st["pos"]
+            if n_done >= 80:
+                break
+        assert got[:80] == [int(t) for t in plain[:80]]
+
+
+def test_head_the_device_cannot_run_turns_drafting_off(lg):
+    s = synth_module()
+    tp, hp = model_files("mid_oddhead")
+    with lg.Session(tp, hp, 512, mtp_n=4) as g:
+        assert g.head                                   # the host accepted the file
+        prompt = s.prompt_ids(16, g.n_vocab, seed=43)
+        plain, _ = g.generate(prompt, 24, 0)
+    with lg.Session(tp, hp, 512, mtp_n=4) as g:
+        g.prefill(prompt[:-1], 0)
+        first = g.next(int(prompt[-1]), 15)
+        assert g.draft(first, 16) == -1                 # unusable on the device: -1, no exit
+        assert g.draft(first, 16) == -1                 # and it stays off
+        assert g.draft_chain(first, 17) == -1
+    with lg.Session(tp, hp, 512, mtp_n=4) as g:
+        out, st = g.generate(prompt, 24, 1)             # the caller pads the slots; the stream is unchanged
+        assert np.array_equal(out, plain)
+    with lg.Session(tp, hp, 512, mtp_n=4) as g:
+        with pytest.raises(RuntimeError):
+            g.generate_device(prompt, 24, 1)            # device-resident rounds need a head: refused, not crashed
+        assert g.next(int(prompt[-1]), 15) == first
+
+
+def test_rounds_that_could_leave_the_cache_are_refused(lg):
+    s = synth_module()
+    tp, _ = model_files("tiny")
+    with lg.Session(tp, None, 64, mtp_n=4) as g:
+        prompt = s.prompt_ids(8, 4096, seed=44)
+        g.prefill(prompt[:-1], 0)
+        first = g.next(int(prompt[-1]), 7)
+        g.set_replay(np.zeros(256, dtype=np.int32))
+        g.rounds_begin(first, 8, 1)
+        assert g.rounds_enqueue(4, 2, 14, use_head=False) == 0        # 8 + 14 * 4 = 64 rows: fits
+        _, st = g.rounds_collect(1, 0)
+        assert st["pos"] <= 64
+        left = (64 - st["pos"]) // 4
+        assert g.rounds_enqueue(4, 2, left + 1, use_head=False) == -2  # one round too many
+        assert g.rounds_enqueue(4, 2, left, use_head=False) == 0
+        g.rounds_collect(1, 0)
+        out = np.zeros(8, dtype=np.int32)
+        toks = np.zeros(4, dtype=np.int32)
+        assert g.L.lgs_spec(g.h, toks, 62, out) == -2                   # rows 62..65 of a 64-row cache

@@ -1,4 +1,4 @@
-"""The allocation-free flash-decode entry point against the regular one.
+"""The allocation-free flash-decode entry point against the regular one and against an f64 reference.
 
 Collected last on purpose (file name): if it fails, a run that stops at the first failure has
 already run everything else.  It must pass alone in a fresh process and after the other tests.
@@ -41,6 +41,10 @@ def test_no_alloc_flash_decode_matches_regular_entry_point_twice(lg):
         torch.cuda.synchronize()
         got = out.cpu().numpy()
         assert np.abs(got - want).max() < 2e-4 * max(1.0, np.abs(want).max())
+        # and against plain f64 attention over the f16-rounded cache, so a fault shared by both entry points shows
+        from tests.test_gpu_kernels import _attn_ref
+        ref = _attn_ref(q, k, v, Hkv, window, pos)
+        assert np.abs(got - ref).max() < 2e-4 * max(1.0, np.abs(ref).max())
 
 
 def test_no_alloc_rejects_oversized_requests(lg):
@@ -51,3 +55,19 @@ def test_no_alloc_rejects_oversized_requests(lg):
                                  buf.data_ptr(), 0)
     assert rc == -4
     assert lg.flash_decode_noalloc(0, 0, 0, 1, 1, 1, 64, 16, 0, 0, 0, 0) == -1
+
+
+def test_no_alloc_rejects_misaligned_pointers_without_launching(lg):
+    import torch
+    # K / V rows are fetched 16 bytes at a time: a view that starts at an odd element must be turned away on the host
+    q = torch.zeros((1, 1, 64), dtype=torch.float32, device="cuda")
+    kv = torch.zeros(16 * 64 + 8, dtype=torch.float16, device="cuda")
+    out = torch.zeros((1, 1, 64), dtype=torch.float32, device="cuda")
+    ok = lg.flash_decode_noalloc(q.data_ptr(), kv.data_ptr(), kv.data_ptr(), 1, 1, 1, 64, 16, 0, 3, out.data_ptr(), 0)
+    assert ok == 0
+    torch.cuda.synchronize()
+    off = kv[1:].data_ptr()                              # 2 bytes into the buffer
+    assert lg.flash_decode_noalloc(q.data_ptr(), off, kv.data_ptr(), 1, 1, 1, 64, 16, 0, 3, out.data_ptr(), 0) == -1
+    assert lg.flash_decode_noalloc(q.data_ptr(), kv.data_ptr(), off, 1, 1, 1, 64, 16, 0, 3, out.data_ptr(), 0) == -1
+    assert lg.flash_decode_noalloc(q.data_ptr() + 2, kv.data_ptr(), kv.data_ptr(), 1, 1, 1, 64, 16, 0, 3, out.data_ptr(), 0) == -1
+    torch.cuda.synchronize()
