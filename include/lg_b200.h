@@ -120,6 +120,11 @@ int  lg_prefill_matmul_host(int type, const void *blocks, const void *blocks_up,
  * (rounded to f16 on upload): q [M][H][hd], k/v [seq][Hkv*hd], positions pos..pos+M-1. */
 int  lg_flash_decode_host(const float *q, const float *k, const float *v, int M, int H, int Hkv, int hd,
                           int seq, int window, int pos, float *out);
+/* The same attention through the kernel the decode step prefers when a KV head's key tiles fit one thread-block
+ * cluster (at most 16 tiles of 128 keys): one CTA per tile, partials merged through distributed shared memory
+ * instead of global scratch.  -3: the case does not fit a cluster. */
+int  lg_flash_decode_cluster_host(const float *q, const float *k, const float *v, int M, int H, int Hkv, int hd,
+                                  int seq, int window, int pos, float *out);
 
 /* Split-KV flash-decode for callers that cannot allocate device memory (a captured stream, a
  * serving loop whose memory was fixed at start-up, a process whose allocator owns the device).

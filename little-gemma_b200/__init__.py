@@ -30,7 +30,7 @@ ABI_SYMBOLS = [
     "lg_forward_spec_n", "lg_set_replay", "lg_rounds_begin", "lg_rounds_enqueue", "lg_rounds_collect",
     "lg_weight_bytes", "lg_round_launches", "lg_last_hidden", "lg_kv_row", "lg_stream", "lg_engine_release",
     "lg_bench_matmul_pass", "lg_bench_prefill_pass", "lg_set_attn_deep", "lg_flash_decode_noalloc",
-    "lg_dequant_host", "lg_gemv_host", "lg_flash_decode_host", "lg_prefill_matmul_host",
+    "lg_dequant_host", "lg_gemv_host", "lg_flash_decode_host", "lg_flash_decode_cluster_host", "lg_prefill_matmul_host",
 ]
 
 _lib = None
@@ -75,6 +75,8 @@ def load() -> C.CDLL:
     L.lg_flash_decode_host.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                        C.c_int, _f32p]
     L.lg_flash_decode_host.restype = C.c_int
+    L.lg_flash_decode_cluster_host.argtypes = L.lg_flash_decode_host.argtypes
+    L.lg_flash_decode_cluster_host.restype = C.c_int
     L.lg_flash_decode_noalloc.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                           C.c_int, C.c_int, C.c_void_p, C.c_void_p]
     L.lg_flash_decode_noalloc.restype = C.c_int
@@ -144,15 +146,17 @@ def set_attn_deep(min_seq: int = 4096, force_g: int = 0) -> None:
     load().lg_set_attn_deep(min_seq, force_g)
 
 
-def flash_decode(q: np.ndarray, k: np.ndarray, v: np.ndarray, n_head_kv: int, window: int, pos: int) -> np.ndarray:
-    """q [M, H, hd]; k, v [seq, Hkv*hd] (rounded to f16 on upload); query j sits at pos + j."""
+def flash_decode(q: np.ndarray, k: np.ndarray, v: np.ndarray, n_head_kv: int, window: int, pos: int,
+                 cluster: bool = False) -> np.ndarray:
+    """q [M, H, hd]; k, v [seq, Hkv*hd] (rounded to f16 on upload); query j sits at pos + j.
+    cluster=True runs the cluster-merged kernel (raises if the case has more key tiles than a cluster holds)."""
     L = load()
     q = np.ascontiguousarray(q, dtype=np.float32); k = np.ascontiguousarray(k, dtype=np.float32)
     v = np.ascontiguousarray(v, dtype=np.float32)
     M, H, hd = q.shape
     out = np.empty_like(q)
-    rc = L.lg_flash_decode_host(q.reshape(-1), k.reshape(-1), v.reshape(-1), M, H, n_head_kv, hd, k.shape[0], window,
-                                pos, out.reshape(-1))
+    fn = L.lg_flash_decode_cluster_host if cluster else L.lg_flash_decode_host
+    rc = fn(q.reshape(-1), k.reshape(-1), v.reshape(-1), M, H, n_head_kv, hd, k.shape[0], window, pos, out.reshape(-1))
     if rc:
         raise ValueError(f"lg_flash_decode_host failed ({rc})")
     return out

@@ -22,7 +22,7 @@ NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 HOST_SRC = ["lg_gguf.c", "lg_quant.c", "lg_setup.c", "lg_session.c"]
 CUDA_SRC = ["lg_engine.cu"]
 DEPS = [os.path.join(HOST, f) for f in HOST_SRC + ["lg_host.h"]] + \
-       [os.path.join(CUDA, f) for f in CUDA_SRC + ["lg_kernels.cuh", "lg_capi.cuh", "lg_prefill.cuh", "lg_attn_deep.cuh"]] + \
+       [os.path.join(CUDA, f) for f in CUDA_SRC + ["lg_kernels.cuh", "lg_capi.cuh", "lg_prefill.cuh", "lg_attn_deep.cuh", "lg_attn_cluster.cuh"]] + \
        [os.path.join(INC, "lg_abi.h"), os.path.join(INC, "lg_b200.h"), os.path.abspath(__file__)]
 
 

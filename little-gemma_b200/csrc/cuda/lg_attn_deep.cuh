@@ -254,8 +254,12 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_deep_kernel(LgAttnArg
         float mx = -INFINITY;
         for (int i = i0 + lane; i <= i1; i += 32) { float2 v = mls[qi * ns_all + i]; if (v.y > 0.0f) mx = fmaxf(mx, v.x); }
         mx = warp_max(mx);
+        // a span always lands in lane (absolute span index % 32): the order of this sum is the same wherever the block's
+        // first span lies (spans outside the query's window add exact zeros)
         float lsum = 0.0f;
-        for (int i = lane; i < ns_all; i += 32) {
+        for (int S2 = (s_lo & ~31) + lane; S2 <= s_hi; S2 += 32) {
+            if (S2 < s_lo) continue;
+            const int i = S2 - s_lo;
             float2 v = mls[qi * ns_all + i];
             float w = (i >= i0 && i <= i1 && v.y > 0.0f) ? expf(v.x - mx) : 0.0f;
             mls[qi * ns_all + i].x = w;

@@ -108,8 +108,8 @@ extern "C" int lg_prefill_matmul_host(int type, const void *blocks, const void *
     return 0;
 }
 
-extern "C" int lg_flash_decode_host(const float *q, const float *k, const float *v, int M, int H, int Hkv, int hd,
-                                    int seq, int window, int pos, float *out) {
+static int flash_decode_host_impl(const float *q, const float *k, const float *v, int M, int H, int Hkv, int hd,
+                                 int seq, int window, int pos, float *out, int cluster) {
     if (M < 1 || M > LG_MAXM || (hd != 64 && hd != 128 && hd != 256 && hd != 512) || H % Hkv) return -1;
     Engine *e = scratch_engine();
     const int kv_dim = Hkv * hd;
@@ -131,9 +131,24 @@ extern "C" int lg_flash_decode_host(const float *q, const float *k, const float 
     a.kc = d_k; a.vc = d_v; a.seq = seq; a.kv_dim = kv_dim; a.H = H; a.Hkv = Hkv; a.hd = hd; a.M = M;
     a.n_slots = slots; a.window = window; a.qpos_off = 0; a.win_shrink = 0; a.pos = d_pos;
     a.part = d_part; a.part_ml = d_ml; a.out.q = nullptr; a.out_f32 = d_o;
-    launch_attn(e, a, slots);
-    LG_CHECK(cudaMemcpyAsync(out, d_o, (size_t)M * H * hd * 4, cudaMemcpyDeviceToHost, e->stream));
+    int rc = 0;
+    if (cluster) {
+        const int C = attn_cluster_size(e, window, max_seq, hd, H, Hkv);
+        if (C) launch_attn_cluster(e, a, C); else rc = -3;         // more tiles than a cluster holds (or no cluster support)
+    } else {
+        launch_attn(e, a, slots);
+    }
+    if (!rc) LG_CHECK(cudaMemcpyAsync(out, d_o, (size_t)M * H * hd * 4, cudaMemcpyDeviceToHost, e->stream));
     LG_CHECK(cudaStreamSynchronize(e->stream));
     cudaFree(d_k); cudaFree(d_v); cudaFree(d_q); cudaFree(d_o); cudaFree(d_pos); cudaFree(d_part); cudaFree(d_ml);
-    return 0;
+    return rc;
+}
+
+extern "C" int lg_flash_decode_host(const float *q, const float *k, const float *v, int M, int H, int Hkv, int hd,
+                                    int seq, int window, int pos, float *out) {
+    return flash_decode_host_impl(q, k, v, M, H, Hkv, hd, seq, window, pos, out, 0);
+}
+extern "C" int lg_flash_decode_cluster_host(const float *q, const float *k, const float *v, int M, int H, int Hkv, int hd,
+                                            int seq, int window, int pos, float *out) {
+    return flash_decode_host_impl(q, k, v, M, H, Hkv, hd, seq, window, pos, out, 1);
 }

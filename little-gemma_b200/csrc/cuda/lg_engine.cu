@@ -18,6 +18,7 @@
 #include "lg_kernels.cuh"
 #include "lg_prefill.cuh"
 #include "lg_attn_deep.cuh"
+#include "lg_attn_cluster.cuh"
 #include "lg_host.h"
 #include "lg_b200.h"
 
@@ -285,6 +286,10 @@ template <int NT> void pf_attr_n() {
     pf_attr<NT, LG_FMT_Q4_K, LG_PF_STORE>(); pf_attr<NT, LG_FMT_Q4_K, LG_PF_GEGLU>();
 }
 // cudaFuncSetAttribute applies to the current device only, so the opt-in is tracked per device.
+template <int HD> void attn_cluster_attr() {
+    LG_CHECK(cudaFuncSetAttribute(lg_attn_cluster_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
+    LG_CHECK(cudaFuncSetAttribute(lg_attn_cluster_kernel<HD>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+}
 void set_kernel_attributes() {
     static bool done[64] = {false};
     int dev = 0;
@@ -303,6 +308,7 @@ void set_kernel_attributes() {
     LG_CHECK(cudaFuncSetAttribute(lg_attn_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
     LG_CHECK(cudaFuncSetAttribute(lg_attn_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
     LG_CHECK(cudaFuncSetAttribute(lg_attn_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
+    attn_cluster_attr<64>(); attn_cluster_attr<128>(); attn_cluster_attr<256>(); attn_cluster_attr<512>();
     pf_attr_n<64>(); pf_attr_n<128>(); pf_attr_n<256>();
     LG_CHECK(cudaFuncSetAttribute(lg_attn_deep_kernel<128, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
     LG_CHECK(cudaFuncSetAttribute(lg_attn_deep_kernel<128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
@@ -591,6 +597,71 @@ void launch_attn_deep(Engine *e, LgAttnArgs a, int max_seq, int G) {
     else             { if (nmt <= 1) launch_k(e, lg_attn_deep_kernel<128, 1>, grid, block, sm, a); else launch_k(e, lg_attn_deep_kernel<128, 2>, grid, block, sm, a); }
 }
 
+int tiles_for(int window, int max_seq, int M, int hd);
+
+const void *attn_cluster_fn(int hd) {
+    switch (hd) {
+    case 64: return (const void *)lg_attn_cluster_kernel<64>;
+    case 128: return (const void *)lg_attn_cluster_kernel<128>;
+    case 256: return (const void *)lg_attn_cluster_kernel<256>;
+    case 512: return (const void *)lg_attn_cluster_kernel<512>;
+    default: return nullptr;
+    }
+}
+
+void attn_cluster_config(cudaLaunchConfig_t &cfg, cudaLaunchAttribute *at, int Hkv, int C, size_t smem, cudaStream_t stream, bool pdl) {
+    cfg = {};
+    cfg.gridDim = dim3(Hkv, C); cfg.blockDim = dim3(LG_ATTN_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 1; at[0].val.clusterDim.y = C; at[0].val.clusterDim.z = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = pdl ? 2 : 1;
+}
+
+// Cluster size for the attention of a layer whose blocks touch at most tiles_for(...) key tiles: the CTAs of one KV head
+// form one cluster, one CTA per tile, and merge through distributed shared memory (lg_attn_cluster_kernel).  The choice
+// is a property of the layer and the cache (never of the block width), so plain and speculative steps of a session run
+// the same kernel.  0 = no cluster (too many tiles, or the device cannot co-schedule such a cluster): the ticket kernel.
+int attn_cluster_size(const Engine *e, int window, int max_seq, int hd, int H, int Hkv) {
+    static const int on = env_int("LG_ATTN_CLUSTER", 1);
+    if (!on || Hkv < 1 || Hkv > MAX_KV_HEADS) return 0;
+    const int tiles = tiles_for(window, max_seq, LG_MAXM, hd);
+    if (tiles > LG_ATTN_CL_MAX) return 0;
+    int C = 1;
+    while (C < tiles) C *= 2;
+    const int nq_max = (H / Hkv) * LG_MAXM;
+    const size_t sm = attn_cluster_smem(nq_max, hd);
+    const void *fn = attn_cluster_fn(hd);
+    if (!fn || sm > ATTN_SMEM_MAX || ((nq_max + 15) & ~15) > 32) return 0;
+    if ((size_t)((nq_max + 15) & ~15) * hd * 4 > (size_t)lg_attn_tile(hd) * (hd + 8) * 2) return 0;   // accumulators reuse the K tile
+    static std::map<long long, int> cache;        // (hd, C, smem) -> clusters the device can hold at once
+    const long long key = ((long long)hd << 40) | ((long long)C << 32) | (long long)sm;
+    auto it = cache.find(key);
+    if (it == cache.end()) {
+        cudaLaunchConfig_t cfg; cudaLaunchAttribute at[2];
+        attn_cluster_config(cfg, at, Hkv, C, sm, e->stream, false);
+        int n = 0;
+        cudaError_t rc = cudaOccupancyMaxActiveClusters(&n, fn, &cfg);
+        if (rc != cudaSuccess) { cudaGetLastError(); n = 0; }
+        it = cache.emplace(key, n).first;
+    }
+    return it->second >= 1 ? C : 0;
+}
+
+void launch_attn_cluster(Engine *e, LgAttnArgs a, int C) {
+    const int nq = (a.H / a.Hkv) * a.M;
+    cudaLaunchConfig_t cfg; cudaLaunchAttribute at[2];
+    attn_cluster_config(cfg, at, a.Hkv, C, attn_cluster_smem(nq, a.hd), e->stream, e->pdl != 0);
+    switch (a.hd) {
+    case 64:  LG_CHECK(cudaLaunchKernelEx(&cfg, lg_attn_cluster_kernel<64>, a)); break;
+    case 128: LG_CHECK(cudaLaunchKernelEx(&cfg, lg_attn_cluster_kernel<128>, a)); break;
+    case 256: LG_CHECK(cudaLaunchKernelEx(&cfg, lg_attn_cluster_kernel<256>, a)); break;
+    default:  LG_CHECK(cudaLaunchKernelEx(&cfg, lg_attn_cluster_kernel<512>, a)); break;
+    }
+    e->launches++;
+}
+
 int tiles_for(int window, int max_seq, int M, int hd) {
     const int S = lg_attn_tile(hd);
     if (window > 0 && window + M < max_seq) return (window + M + S - 1) / S + 1;
@@ -829,7 +900,9 @@ void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags, int 
         static const int deep_local = env_int("LG_ATTN_DEEP_LOCAL", 0);
         const int deepG = (w.local && !deep_local) ? 0 : deep_span_tiles(e, kv->max_seq, w.nkv, hd, (H / w.nkv) * M);
         if (only & C_ATTN) {
+            const int cl = deepG ? 0 : attn_cluster_size(e, aa.window, kv->max_seq, hd, H, w.nkv);
             if (deepG) launch_attn_deep(e, aa, kv->max_seq, deepG);
+            else if (cl) launch_attn_cluster(e, aa, cl);
             else launch_attn(e, aa, tiles_for(aa.window, kv->max_seq, M, hd));
         }
 
@@ -1182,7 +1255,9 @@ void enqueue_draft(Engine *e, DraftW *d, const struct kvcache *kv, int slot, boo
         aa.n_slots = d->n_slots_global; aa.part = d->part; aa.part_ml = d->part_ml;
         LgPanel pa = d->p_attn; pa.nsb = d->n_head * hd / 32;
         aa.out = pa; aa.out_f32 = nullptr;
-        launch_attn(e, aa, tiles_for(aa.window, kv->max_seq, 1, hd));
+        const int cl = attn_cluster_size(e, aa.window, kv->max_seq, hd, d->n_head, Hkv);
+        if (cl) launch_attn_cluster(e, aa, cl);
+        else launch_attn(e, aa, tiles_for(aa.window, kv->max_seq, 1, hd));
         int ks_o = 1;
         GemvExtra xo; xo.ks_out = &ks_o;
         launch_gemv(e, b.o, pa, 1, d->obuf, LG_EPI_STORE, 0, xo);

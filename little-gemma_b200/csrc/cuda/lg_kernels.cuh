@@ -1180,8 +1180,12 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) 
         float mx = -INFINITY;
         for (int i = i0 + lane; i <= i1; i += 32) { float2 v = mls[qi * nt_all + i]; if (v.y > 0.0f) mx = fmaxf(mx, v.x); }
         mx = warp_max(mx);
+        // a tile always lands in lane (absolute tile index % 32), so the order of this sum does not depend on where the
+        // block's first tile lies (tiles outside the query's window add exact zeros)
         float lsum = 0.0f;
-        for (int i = lane; i < nt_all; i += 32) {
+        for (int T2 = (t_lo & ~31) + lane; T2 <= t_hi; T2 += 32) {
+            if (T2 < t_lo) continue;
+            const int i = T2 - t_lo;
             float2 v = mls[qi * nt_all + i];
             float w = (i >= i0 && i <= i1 && v.y > 0.0f) ? expf(v.x - mx) : 0.0f;
             mls[qi * nt_all + i].x = w;
