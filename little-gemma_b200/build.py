@@ -33,13 +33,13 @@ def stale() -> bool:
     return any(os.path.getmtime(d) > t for d in DEPS)
 
 
-def build(mtp_n: int = 4, force: bool = False, ptxas_v: bool = False) -> str:
+def build(mtp_n: int = 4, force: bool = False, ptxas_v: bool = False, stamps: bool = False) -> str:
     if not force and not stale():
         return LIB
     objdir = os.path.join(HERE, "build")
     os.makedirs(objdir, exist_ok=True)
     objs = []
-    defs = [f"-DLG_MTP_N={mtp_n}"]
+    defs = [f"-DLG_MTP_N={mtp_n}"] + (["-DLG_STAMPS"] if stamps else [])     # stamps: profiling build with phase time stamps
     for f in HOST_SRC:
         o = os.path.join(objdir, f + ".o")
         subprocess.check_call(["gcc", "-O2", "-fPIC", "-std=gnu11", "-Wall", "-Wextra", *defs, f"-I{INC}", f"-I{HOST}",
@@ -62,5 +62,6 @@ if __name__ == "__main__":
     ap.add_argument("--mtp-n", type=int, default=4)
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--ptxas-v", action="store_true")
+    ap.add_argument("--stamps", action="store_true", help="profiling build: kernels record phase time stamps (lg_debug_stamps)")
     a = ap.parse_args()
-    print(build(a.mtp_n, a.force, a.ptxas_v))
+    print(build(a.mtp_n, a.force or a.stamps, a.ptxas_v, a.stamps))

@@ -1,21 +1,30 @@
 // lg_attn_cluster.cuh -- the decode step's attention with the tile merge inside a thread-block cluster.
 //
 // lg_attn_kernel sends every (query, tile) partial through global memory, takes a ticket, and lets the last CTA of
-// a KV head read all partials back and merge them alone: a serial tail of several microseconds per layer.  Here
-// the CTAs of one KV head form ONE cluster (one CTA per tile of 128 keys, up to 16 tiles).  A CTA keeps its
-// partial (max, sum, accumulators) in its own shared memory; after a cluster barrier every CTA merges a share of
-// the output -- one warp per (query, 32 output dims) -- reading the tiles' partials straight out of the peers'
+// a KV head read all partials back and merge them alone: a serial tail of ~9 us per layer.  Here the CTAs of one
+// KV head form ONE cluster.  Cluster rank r works on key tiles t_lo + r, t_lo + r + C, ... (one tile per CTA for a
+// sliding-window layer; a few for a full-attention layer whose cache is longer than C tiles), keeps the running
+// (max, sum, accumulators) of its tiles in registers / shared memory, and after a cluster barrier every CTA merges
+// a share of the output -- one warp per (query, 32 output dims) -- reading the partials straight out of the peers'
 // shared memory (ld.shared::cluster), and writes that share of the o-projection's panel.  No scratch in global
 // memory, no atomics, no fence, and the merge is spread over the whole cluster instead of one CTA.
 //
-// Tile arithmetic (norm + rope of q/k/v, QK^T, softmax, PV) is that of lg_attn_kernel.  Tiles lie on absolute
-// position boundaries; the merge walks a query's tiles in ascending order with exact zero weights for tiles
-// outside its window, so a row's bits depend on its own position only -- not on the verify width or on the rows
-// that share the launch.  Only plain distributed-shared-memory loads are used: no multicast, no remote stores.
+// A tile's K and V rows arrive by tiled TMA copies (cp.async.bulk.tensor.2d over a tensor map of the layer's cache,
+// 128-byte swizzle, one elected thread issues HD/64 boxes per matrix): issuing 2 x 128 row copies per CTA one by
+// one cost ~8 us, 16-byte cp.async loops ~3 us; the tiled copies cost one instruction per 64 columns.
+//
+// Bit-stability.  Tiles lie on absolute position boundaries.  A sliding-window layer always has one tile per CTA
+// (the host picks C >= the tiles a block can touch), and the merge walks a query's tiles in ascending order with
+// exact zero weights outside its window.  A full-attention layer has t_lo = 0, so the tiles a CTA folds together
+// (T = r mod C) and their order are fixed by the absolute tile index; a tile past a query's position is an exact
+// no-op for that query (weights 0, rescale 1).  So a row's bits depend on its own position only -- not on the
+// verify width or on the rows that share the launch.  Only the CTA's own memory and plain loads from the peers'
+// shared memory are used.
 #pragma once
 #include "lg_kernels.cuh"
+#include "lg_prefill.cuh"            // tma_load_2d
 
-#define LG_ATTN_CL_MAX 16            // CTAs per cluster (non-portable size; 8 where 8 tiles are enough)
+#define LG_ATTN_CL_MAX 16            // CTAs per cluster (sizes above 8 are "non-portable": the host asks the device first)
 
 __device__ __forceinline__ uint32_t dsmem_addr(const void *local_addr, uint32_t rank) {
     uint32_t la = smem_u32(local_addr), ra;
@@ -33,58 +42,80 @@ __device__ __forceinline__ float2 dsmem_ld_f32x2(uint32_t ra) {
     return v;
 }
 
-// grid (Hkv, C), cluster (1, C, 1): cluster rank r works on tile t_lo + r.
-// dynamic smem: Qhi | Qlo [NQ16][HD+8] f16 | K [S][HD+8] (later: the tile's accumulators [NQ16][HD] f32) | V [S][HD+8]
-//               | scores [NQ16][S] f32 | Phi | Plo [NQ16][S+8] f16 | ml [NQ16] float2
+// Element (row, col) of a K or V tile as the tiled copies leave it: blocks of 64 columns, each [S rows][128 bytes],
+// the 16-byte chunk j of row r stored at chunk j ^ (r % 8) (128-byte swizzle; tile base 1024-byte aligned).
+template <int S>
+__device__ __forceinline__ __half *kv_at(__half *tile, int row, int col) {
+    return tile + (col >> 6) * (S * 64) + row * 64 + ((((col & 63) >> 3) ^ (row & 7)) << 3) + (col & 7);
+}
+
+// grid (Hkv, C), cluster (1, C, 1).
+// dynamic smem (1024-byte aligned): K tile | V tile [HD/64][S][64] f16 swizzled (K later: the CTA's accumulators [NQ16][HD] f32)
+//               | Qhi | Qlo [NQ16][HD+8] f16 | scores [NQ16][S] f32 | Phi | Plo [NQ16][S+8] f16 | ml [NQ16] float2 | alpha [NQ16]
 template <int HD>
-__global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_cluster_kernel(LgAttnArgs a) {
-    extern __shared__ __align__(128) unsigned char smem[];
+__global__ void __launch_bounds__(LG_ATTN_THREADS)
+lg_attn_cluster_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_constant__ CUtensorMap tmv, LgAttnArgs a) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ float s_qn[HD], s_kn[HD];
+    __shared__ __align__(8) uint64_t kv_bar;
     pdl_launch();
-    if (!a.q_ready)
-        for (int i = threadIdx.x; i < HD; i += LG_ATTN_THREADS) { s_qn[i] = a.q_norm[i]; s_kn[i] = a.k_norm ? a.k_norm[i] : 1.0f; }
-    if (!a.early_kv) pdl_wait();
+    LG_STAMP(a.tag, 0);
+    LG_STAMP_KIND(a.tag, 6);
     constexpr int S = lg_attn_tile(HD), LDH = HD + 8, LDP = S + 8, PER = HD / 64, HALF = HD / 2, NW = LG_ATTN_THREADS / 32;
+    constexpr uint32_t TILE_BYTES = (uint32_t)S * HD * 2;
+    unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int C = gridDim.y;
-    const int kvh = blockIdx.x, gqa = a.H / a.Hkv, nq = gqa * a.M, nq16 = (nq + 15) & ~15;
+    const int kvh = blockIdx.x, gqa = a.H / a.Hkv, nq = gqa * a.M, nq16 = (nq + 15) & ~15, nmt = nq16 / 16;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int rank = (int)cluster_rank();
+
+    __half *sk = (__half *)smem, *sv = sk + (size_t)S * HD;
+    __half *qhi = sv + (size_t)S * HD, *qlo = qhi + (size_t)nq16 * LDH;
+    float *sc = (float *)(qlo + (size_t)nq16 * LDH);
+    __half *phi = (__half *)(sc + (size_t)nq16 * S), *plo = phi + (size_t)nq16 * LDP;
+    float2 *ml = (float2 *)(plo + (size_t)nq16 * LDP);        // running (max, sum) of this CTA's tiles, per query
+    float *row_a = (float *)(ml + nq16);
+    float *opart = (float *)sk;                               // [nq16][HD] f32, written once the last K tile has been consumed
+
+    if (threadIdx.x == 0) mbar_init(&kv_bar, 1);
+    if (!a.q_ready)
+        for (int i = threadIdx.x; i < HD; i += LG_ATTN_THREADS) { s_qn[i] = a.q_norm[i]; s_kn[i] = a.k_norm ? a.k_norm[i] : 1.0f; }
+    for (int qi = threadIdx.x; qi < nq16; qi += LG_ATTN_THREADS) ml[qi] = make_float2(-INFINITY, 0.0f);
+    // early_kv: the position and the cached rows below the block were written by earlier graph launches (this layer
+    // writes its own rows, and only here), so the first tile may start streaming before the previous kernel has finished
+    if (!a.early_kv) pdl_wait();
     const int pos0 = *a.pos;
     const int p_first = pos0 + a.qpos_off, p_last = pos0 + a.M - 1 + a.qpos_off;
     const int lo_first = a.window > 0 ? max(0, p_first + a.win_shrink - a.window + 1) : 0;
     const int t_lo = lo_first / S, t_hi = p_last >= 0 ? p_last / S : -1;
-    const int T = t_lo + rank;
-    const bool live = p_last >= 0 && T <= t_hi;               // this CTA has a tile; the others only help with the merge
+    const int T_first = t_lo + rank;
+    const bool live = T_first <= t_hi;                        // this CTA has at least one tile; the others only help with the merge
     const bool writes_kv = a.owns_kv && !a.q_ready;
 
-    __half *qhi = (__half *)smem, *qlo = qhi + (size_t)nq16 * LDH;
-    __half *sk = qlo + (size_t)nq16 * LDH, *sv = sk + (size_t)S * LDH;
-    float *sc = (float *)(sv + (size_t)S * LDH);
-    __half *phi = (__half *)(sc + (size_t)nq16 * S), *plo = phi + (size_t)nq16 * LDP;
-    float2 *ml = (float2 *)(plo + (size_t)nq16 * LDP);
-    float *opart = (float *)sk;                               // [nq16][HD] f32, written once the K tile has been consumed
+    // one elected thread sends a tile's K and V boxes; the copies complete on kv_bar
+    auto load_tile = [&](int T) {
+        mbar_expect_tx(&kv_bar, 2u * TILE_BYTES);
+        const int y = (int)(((long long)T * S) % a.seq);
+        #pragma unroll
+        for (int c = 0; c < HD / 64; c++) {
+            tma_load_2d(sk + (size_t)c * S * 64, &tmk, kvh * HD + c * 64, y, &kv_bar);
+            tma_load_2d(sv + (size_t)c * S * 64, &tmv, kvh * HD + c * 64, y, &kv_bar);
+        }
+    };
+    if (live && threadIdx.x == 0) load_tile(T_first);
+    if (a.early_kv) pdl_wait();
+    LG_STAMP(a.tag, 1);
 
     const int g = lane >> 2, t = lane & 3;
-    if (live) {
-        // ---- 1. cached K and V rows of the tile start streaming into shared memory at once ----
-        constexpr int CH = HD / 8;
-        for (int i = threadIdx.x; i < S * CH; i += LG_ATTN_THREADS) {
-            const int key = i / CH, c = i % CH, p = T * S + key;
-            __half *dk = sk + (size_t)key * LDH + c * 8, *dv = sv + (size_t)key * LDH + c * 8;
-            if (p <= p_last && !(writes_kv && p >= pos0)) {
-                const size_t off = (size_t)(p % a.seq) * a.kv_dim + (size_t)kvh * HD + c * 8;
-                cp_async16(dk, a.kc + off);
-                cp_async16(dv, a.vc + off);
-            } else if (p > p_last) {
-                *(uint4 *)dk = make_uint4(0, 0, 0, 0);
-                *(uint4 *)dv = make_uint4(0, 0, 0, 0);
-            }
-        }
-    }
-    if (a.early_kv) pdl_wait();
+    constexpr int PVW = HD / 16 < NW ? HD / 16 : NW, DW = HD / PVW, NT = DW / 8;
+    float o[2][NT][4];                                        // accumulators of up to 32 query rows, kept across this CTA's tiles
+    #pragma unroll
+    for (int mt = 0; mt < 2; mt++)
+        #pragma unroll
+        for (int n = 0; n < NT; n++) o[mt][n][0] = o[mt][n][1] = o[mt][n][2] = o[mt][n][3] = 0.0f;
 
     if (live) {
-        // ---- 2. queries: per-head RMSNorm + RoPE, split into f16 hi + lo ----
+        // ---- queries: per-head RMSNorm + RoPE, split into f16 hi + lo (once per CTA) ----
         for (int qi = warp; qi < nq16; qi += NW) {
             float v0[PER], v1[PER];
             if (qi < nq) {
@@ -109,123 +140,153 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_cluster_kernel(LgAttn
                 qlo[(size_t)qi * LDH + i + HALF] = __float2half_rn(v1[e] - __half2float(h1));
             }
         }
-        if (writes_kv) {
-            // rows of the new positions that fall into this tile: K (norm + rope) and V (plain norm), f16 RNE
-            for (int j = warp; j < 2 * a.M; j += NW) {
-                const int tok = j >> 1, isv = j & 1, p = pos0 + tok;
-                if (p / S != T) continue;
-                float v0[PER], v1[PER];
-                const float *src = a.qkv + (size_t)tok * a.ld + (size_t)(a.H + ((isv && a.has_v) ? a.Hkv : 0) + kvh) * HD;
-                head_norm_rope<HD>(src, isv ? nullptr : s_kn, isv ? nullptr : a.rope + (size_t)tok * HALF, a.eps, lane, v0, v1);
-                __half *dst = (isv ? a.vc : a.kc) + (size_t)(p % a.seq) * a.kv_dim + (size_t)kvh * HD;
-                __half *dsm = (isv ? sv : sk) + (size_t)(p - T * S) * LDH;
-                #pragma unroll
-                for (int e = 0; e < PER; e++) {
-                    const __half h0 = __float2half_rn(v0[e]), h1 = __float2half_rn(v1[e]);
-                    dst[lane * PER + e] = h0; dst[lane * PER + e + HALF] = h1;
-                    dsm[lane * PER + e] = h0; dsm[lane * PER + e + HALF] = h1;
-                }
-            }
-        }
-        cp_async_wait_all();
-        __syncthreads();
+        LG_STAMP(a.tag, 2);
 
-        // ---- 3. scores: warp w takes keys [w*S/8, (w+1)*S/8) ----
-        constexpr int KPW = S / NW, NKT = KPW / 8;
-        for (int mt = 0; mt < nq16 / 16; mt++) {
-            float c0[NKT][4];
-            #pragma unroll
-            for (int n = 0; n < NKT; n++) c0[n][0] = c0[n][1] = c0[n][2] = c0[n][3] = 0.0f;
-            const __half *qa_hi = qhi + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + (lane >> 4) * 8;
-            const __half *qa_lo = qlo + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + (lane >> 4) * 8;
-            const __half *kb = sk + (size_t)(warp * KPW + (lane & 7)) * LDH + (lane >> 3) * 8;
-            #pragma unroll 2
-            for (int k0 = 0; k0 < HD; k0 += 32) {
-                uint32_t ah[4], al[4], ah2[4], al2[4];
-                ldsm_x4(ah, qa_hi + k0); ldsm_x4(al, qa_lo + k0);
-                ldsm_x4(ah2, qa_hi + k0 + 16); ldsm_x4(al2, qa_lo + k0 + 16);
-                #pragma unroll
-                for (int n = 0; n < NKT; n++) {
-                    uint32_t b[4];
-                    ldsm_x4(b, kb + (size_t)n * 8 * LDH + k0);
-                    mma_f16(c0[n], ah, b[0], b[1]); mma_f16(c0[n], al, b[0], b[1]);
-                    mma_f16(c0[n], ah2, b[2], b[3]); mma_f16(c0[n], al2, b[2], b[3]);
-                }
+        uint32_t parity = 0;
+        for (int T = T_first; T <= t_hi; T += C) {
+            __syncthreads();                                    // first pass: barrier init and Q are visible; later: the previous tile is no longer read
+            if (T > T_first && threadIdx.x == 0) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the tile was last touched through ordinary loads and stores
+                load_tile(T);
             }
-            #pragma unroll
-            for (int h2 = 0; h2 < 2; h2++) {
-                const int qi = mt * 16 + g + h2 * 8;
-                const int pj = pos0 + qi / gqa + a.qpos_off;
-                const int lo = a.window > 0 ? max(0, pj + a.win_shrink - a.window + 1) : 0;
-                #pragma unroll
-                for (int n = 0; n < NKT; n++)
+            // the tile has landed (bounded wait)
+            if (!mbar_wait(&kv_bar, parity) && a.err && lane == 0) atomicOr(a.err, LG_ERR_MBAR_TIMEOUT);
+            parity ^= 1;
+            if (writes_kv) {
+                // rows of the new positions that fall into this tile: K (norm + rope) and V (plain norm), f16 RNE, to the
+                // cache and -- over whatever the copy brought for those rows -- into the tile
+                for (int j = warp; j < 2 * a.M; j += NW) {
+                    const int tok = j >> 1, isv = j & 1, p = pos0 + tok;
+                    if (p / S != T) continue;
+                    float v0[PER], v1[PER];
+                    const float *src = a.qkv + (size_t)tok * a.ld + (size_t)(a.H + ((isv && a.has_v) ? a.Hkv : 0) + kvh) * HD;
+                    head_norm_rope<HD>(src, isv ? nullptr : s_kn, isv ? nullptr : a.rope + (size_t)tok * HALF, a.eps, lane, v0, v1);
+                    __half *dst = (isv ? a.vc : a.kc) + (size_t)(p % a.seq) * a.kv_dim + (size_t)kvh * HD;
+                    __half *tile = isv ? sv : sk;
+                    const int row = p - T * S;
                     #pragma unroll
-                    for (int e = 0; e < 2; e++) {
-                        const int key = warp * KPW + n * 8 + t * 2 + e, p = T * S + key;
-                        sc[(size_t)qi * S + key] = (qi < nq && p >= lo && p <= pj) ? c0[n][h2 * 2 + e] : -INFINITY;
+                    for (int e = 0; e < PER; e++) {
+                        const __half h0 = __float2half_rn(v0[e]), h1 = __float2half_rn(v1[e]);
+                        dst[lane * PER + e] = h0; dst[lane * PER + e + HALF] = h1;
+                        *kv_at<S>(tile, row, lane * PER + e) = h0; *kv_at<S>(tile, row, lane * PER + e + HALF) = h1;
                     }
+                }
+                __syncthreads();
             }
-        }
-        __syncthreads();
+            if (T == T_first) LG_STAMP(a.tag, 3);
 
-        // ---- 4. per-query softmax over the tile ----
-        for (int qi = warp; qi < nq16; qi += NW) {
-            float sv_[S / 32], mx = -INFINITY;
-            #pragma unroll
-            for (int j = 0; j < S / 32; j++) { sv_[j] = sc[(size_t)qi * S + lane + 32 * j]; mx = fmaxf(mx, sv_[j]); }
-            mx = warp_max(mx);
-            float sum = 0.0f;
-            #pragma unroll
-            for (int j = 0; j < S / 32; j++) {
-                const float e = (sv_[j] == -INFINITY) ? 0.0f : expf(sv_[j] - mx);
-                const __half h = __float2half_rn(e);
-                phi[(size_t)qi * LDP + lane + 32 * j] = h;
-                plo[(size_t)qi * LDP + lane + 32 * j] = __float2half_rn(e - __half2float(h));
-                sum += e;
-            }
-            sum = warp_sum(sum);
-            if (lane == 0) ml[qi] = make_float2(mx, sum);
-        }
-        __syncthreads();
-
-        // ---- 5. O = P V: PVW warps split the head dims; the tile's accumulators go where the K tile was ----
-        constexpr int PVW = HD / 16 < NW ? HD / 16 : NW, DW = HD / PVW, NT = DW / 8;
-        if (warp < PVW) {
-            for (int mt = 0; mt < nq16 / 16; mt++) {
-                float o[NT][4];
+            // ---- scores: warp w takes keys [w*S/8, (w+1)*S/8); keys past a query's position or before its window: -inf ----
+            constexpr int KPW = S / NW, NKT = KPW / 8;
+            for (int mt = 0; mt < nmt; mt++) {
+                float c0[NKT][4];
                 #pragma unroll
-                for (int n = 0; n < NT; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
-                const __half *pa_hi = phi + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDP + (lane >> 4) * 8;
-                const __half *pa_lo = plo + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDP + (lane >> 4) * 8;
-                #pragma unroll
-                for (int k0 = 0; k0 < S; k0 += 16) {
-                    uint32_t ah[4], al[4];
-                    ldsm_x4(ah, pa_hi + k0); ldsm_x4(al, pa_lo + k0);
-                    const __half *vb = sv + (size_t)(k0 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + warp * DW + (lane >> 4) * 8;
+                for (int n = 0; n < NKT; n++) c0[n][0] = c0[n][1] = c0[n][2] = c0[n][3] = 0.0f;
+                const __half *qa_hi = qhi + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + (lane >> 4) * 8;
+                const __half *qa_lo = qlo + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + (lane >> 4) * 8;
+                #pragma unroll 2
+                for (int k0 = 0; k0 < HD; k0 += 32) {
+                    uint32_t ah[4], al[4], ah2[4], al2[4];
+                    ldsm_x4(ah, qa_hi + k0); ldsm_x4(al, qa_lo + k0);
+                    ldsm_x4(ah2, qa_hi + k0 + 16); ldsm_x4(al2, qa_lo + k0 + 16);
                     #pragma unroll
-                    for (int n = 0; n < NT; n += 2) {
-                        uint32_t b[4];
-                        ldsm_x4_t(b, vb + n * 8);
-                        mma_f16(o[n], ah, b[0], b[1]); mma_f16(o[n], al, b[0], b[1]);
-                        mma_f16(o[n + 1], ah, b[2], b[3]); mma_f16(o[n + 1], al, b[2], b[3]);
+                    for (int n = 0; n < NKT; n++) {
+                        uint32_t b[4];                          // 4 matrices: key rows n*8.., dims k0, +8, +16, +24
+                        ldsm_x4(b, kv_at<S>(sk, warp * KPW + n * 8 + (lane & 7), k0 + (lane >> 3) * 8));
+                        mma_f16(c0[n], ah, b[0], b[1]); mma_f16(c0[n], al, b[0], b[1]);
+                        mma_f16(c0[n], ah2, b[2], b[3]); mma_f16(c0[n], al2, b[2], b[3]);
                     }
                 }
                 #pragma unroll
                 for (int h2 = 0; h2 < 2; h2++) {
                     const int qi = mt * 16 + g + h2 * 8;
+                    const int pj = pos0 + qi / gqa + a.qpos_off;
+                    const int lo = a.window > 0 ? max(0, pj + a.win_shrink - a.window + 1) : 0;
                     #pragma unroll
-                    for (int n = 0; n < NT; n++)
-                        *(float2 *)(opart + (size_t)qi * HD + warp * DW + n * 8 + t * 2) = make_float2(o[n][h2 * 2], o[n][h2 * 2 + 1]);
+                    for (int n = 0; n < NKT; n++)
+                        #pragma unroll
+                        for (int e = 0; e < 2; e++) {
+                            const int key = warp * KPW + n * 8 + t * 2 + e, p = T * S + key;
+                            sc[(size_t)qi * S + key] = (qi < nq && p >= lo && p <= pj) ? c0[n][h2 * 2 + e] : -INFINITY;
+                        }
+                }
+            }
+            __syncthreads();
+
+            // ---- online softmax, one warp per query row: new running max, the tile's weights against it, the rescale of
+            //      what was accumulated before (exactly 1 when the tile adds nothing for this row) ----
+            for (int qi = warp; qi < nq16; qi += NW) {
+                float sv_[S / 32], mx = -INFINITY;
+                #pragma unroll
+                for (int j = 0; j < S / 32; j++) { sv_[j] = sc[(size_t)qi * S + lane + 32 * j]; mx = fmaxf(mx, sv_[j]); }
+                const float2 old = ml[qi];
+                const float m_new = fmaxf(old.x, warp_max(mx));
+                float sum = 0.0f;
+                #pragma unroll
+                for (int j = 0; j < S / 32; j++) {
+                    const float e = (sv_[j] == -INFINITY) ? 0.0f : expf(sv_[j] - m_new);
+                    const __half h = __float2half_rn(e);
+                    phi[(size_t)qi * LDP + lane + 32 * j] = h;
+                    plo[(size_t)qi * LDP + lane + 32 * j] = __float2half_rn(e - __half2float(h));
+                    sum += e;
+                }
+                sum = warp_sum(sum);
+                __syncwarp();
+                if (lane == 0) {
+                    const float alpha = (old.x == m_new) ? 1.0f : expf(old.x - m_new);      // old max -inf < new max: 0
+                    row_a[qi] = alpha;
+                    ml[qi] = make_float2(m_new, old.y * alpha + sum);
+                }
+            }
+            __syncthreads();
+
+            // ---- O = alpha O + P V: PVW warps split the head dims ----
+            if (warp < PVW) {
+                #pragma unroll
+                for (int mt = 0; mt < 2; mt++) {
+                    if (mt >= nmt) break;
+                    const float a0 = row_a[mt * 16 + g], a1 = row_a[mt * 16 + g + 8];
+                    #pragma unroll
+                    for (int n = 0; n < NT; n++) { o[mt][n][0] *= a0; o[mt][n][1] *= a0; o[mt][n][2] *= a1; o[mt][n][3] *= a1; }
+                    const __half *pa_hi = phi + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDP + (lane >> 4) * 8;
+                    const __half *pa_lo = plo + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDP + (lane >> 4) * 8;
+                    #pragma unroll
+                    for (int k0 = 0; k0 < S; k0 += 16) {
+                        uint32_t ah[4], al[4];
+                        ldsm_x4(ah, pa_hi + k0); ldsm_x4(al, pa_lo + k0);
+                        #pragma unroll
+                        for (int n = 0; n < NT; n += 2) {
+                            uint32_t b[4];                      // key rows k0.. (two halves of 8), dims warp*DW + n*8, +8
+                            ldsm_x4_t(b, kv_at<S>(sv, k0 + (lane & 7) + ((lane >> 3) & 1) * 8, warp * DW + n * 8 + (lane >> 4) * 8));
+                            mma_f16(o[mt][n], ah, b[0], b[1]); mma_f16(o[mt][n], al, b[0], b[1]);
+                            mma_f16(o[mt][n + 1], ah, b[2], b[3]); mma_f16(o[mt][n + 1], al, b[2], b[3]);
+                        }
+                    }
                 }
             }
         }
-    } else {
-        for (int qi = threadIdx.x; qi < nq16; qi += LG_ATTN_THREADS) ml[qi] = make_float2(-INFINITY, 0.0f);
+        // ---- this CTA's accumulators go where the K tile was (every warp is past its last use of K) ----
+        __syncthreads();
+        if (warp < PVW) {
+            #pragma unroll
+            for (int mt = 0; mt < 2; mt++) {
+                if (mt >= nmt) break;
+                #pragma unroll
+                for (int h2 = 0; h2 < 2; h2++) {
+                    const int qi = mt * 16 + g + h2 * 8;
+                    #pragma unroll
+                    for (int n = 0; n < NT; n++)
+                        *(float2 *)(opart + (size_t)qi * HD + warp * DW + n * 8 + t * 2) = make_float2(o[mt][n][h2 * 2], o[mt][n][h2 * 2 + 1]);
+                }
+            }
+        }
     }
 
-    // ---- 6. every tile's partial is in place: merge across the cluster ----
+    // ---- every CTA's partial is in place: merge across the cluster ----
+    LG_STAMP(a.tag, 4);
     cluster_sync_all();
-    // one warp per (query, group of 32 output dims), spread over all warps of the cluster
+    LG_STAMP(a.tag, 5);
+    // one warp per (query, group of 32 output dims), spread over all warps of the cluster; rank i holds the query's
+    // tiles t_lo + i, t_lo + i + C, ...: weights are exact zeros for ranks without a tile of this query
     const int n_items = nq * (HD / 32);
     for (int u = rank * NW + warp; u < n_items; u += C * NW) {
         const int qi = u / (HD / 32), d = (u % (HD / 32)) * 32 + lane;
@@ -234,14 +295,13 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_cluster_kernel(LgAttn
         float y = 0.0f;
         if (pj >= 0) {
             const int lo = a.window > 0 ? max(0, pj + a.win_shrink - a.window + 1) : 0;
-            const int i0 = lo / S - t_lo, i1 = pj / S - t_lo;            // this query's tiles, as cluster ranks
-            // lane i holds tile i's (max, sum) of this query
+            const int i0 = lo / S - t_lo, i1 = min(pj / S - t_lo, i0 + C - 1);      // ranks that hold tiles of this query
             float2 v = make_float2(-INFINITY, 0.0f);
             if (lane < C && lane >= i0 && lane <= i1) v = dsmem_ld_f32x2(dsmem_addr(ml + qi, (uint32_t)lane));
             const bool ok = v.y > 0.0f;
             const float mx = warp_max(ok ? v.x : -INFINITY);
             const float w = ok ? expf(v.x - mx) : 0.0f;
-            // the tiles' accumulators of this lane's dim: all loads first, then the sums in ascending tile order
+            // the ranks' accumulators of this lane's dim: all loads first, then the sums in ascending rank order
             float ov[LG_ATTN_CL_MAX];
             #pragma unroll
             for (int i = 0; i < LG_ATTN_CL_MAX; i++)
@@ -260,10 +320,12 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_cluster_kernel(LgAttn
         if (a.out.q) quant_group_store(y, lane, tok, (hq * HD + d) >> 5, a.out);
     }
     // nobody may leave while a peer can still read its shared memory
+    LG_STAMP(a.tag, 6);
     cluster_sync_all();
+    LG_STAMP(a.tag, 7);
 }
 
 inline size_t attn_cluster_smem(int nq, int hd) {
     size_t nq16 = (size_t)((nq + 15) & ~15), ldh = hd + 8, S = lg_attn_tile(hd);
-    return 2 * nq16 * ldh * 2 + 2 * S * ldh * 2 + nq16 * S * 4 + 2 * nq16 * (S + 8) * 2 + nq16 * 8 + 64;
+    return 1024 + 2 * S * hd * 2 + 2 * nq16 * ldh * 2 + nq16 * S * 4 + 2 * nq16 * (S + 8) * 2 + nq16 * 12 + 64;
 }

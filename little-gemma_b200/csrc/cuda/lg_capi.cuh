@@ -130,10 +130,10 @@ static int flash_decode_host_impl(const float *q, const float *k, const float *v
     a.qkv = d_q; a.ld = 0; a.q_ready = 1; a.has_v = 1; a.owns_kv = 0; a.eps = 0.0f; a.rope = nullptr;
     a.kc = d_k; a.vc = d_v; a.seq = seq; a.kv_dim = kv_dim; a.H = H; a.Hkv = Hkv; a.hd = hd; a.M = M;
     a.n_slots = slots; a.window = window; a.qpos_off = 0; a.win_shrink = 0; a.pos = d_pos;
-    a.part = d_part; a.part_ml = d_ml; a.out.q = nullptr; a.out_f32 = d_o;
+    a.part = d_part; a.part_ml = d_ml; a.out.q = nullptr; a.out_f32 = d_o; a.err = e->err;
     int rc = 0;
     if (cluster) {
-        const int C = attn_cluster_size(e, window, max_seq, hd, H, Hkv);
+        const int C = attn_cluster_size(e, window, max_seq, seq, hd, H, Hkv);
         if (C) launch_attn_cluster(e, a, C); else rc = -3;         // more tiles than a cluster holds (or no cluster support)
     } else {
         launch_attn(e, a, slots);

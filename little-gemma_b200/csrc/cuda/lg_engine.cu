@@ -264,7 +264,29 @@ void free_wmat(WMat &W) { cudaFree(W.wq); cudaFree(W.ws); cudaFree(W.wd); W = WM
 // ------------------------------------------------------------------------------------------
 // launch helpers
 // ------------------------------------------------------------------------------------------
-struct GemvPlan { int r, ks, gx; size_t smem; };
+int env_int(const char *name, int fb) { const char *v = getenv(name); return v && v[0] ? atoi(v) : fb; }
+
+struct GemvPlan { int r, ks, gx, ns; size_t smem; };
+// dynamic shared memory of the small-M matmul: panel slice | ring | warp partials (| norm-tail sums) | mbarriers
+size_t gemv_smem_bytes(int np, int nkp_slice, int r, int fmt, int ns, bool normtail) {
+    const int stage = fmt == LG_FMT_Q4_K ? gemv_stage_bytes<LG_FMT_Q4_K>() : gemv_stage_bytes<LG_FMT_Q4_0>();
+    return (size_t)np * nkp_slice * 2 * (256 + 32) + 128 + (size_t)ns * stage + (size_t)LG_GEMV_CW * r * np * 64 * 4
+         + (normtail ? (size_t)np * 128 * 4 : 0) + (2 * LG_GEMV_STAGES_MAX + 1) * 8 + 16;
+}
+// most dynamic shared memory a CTA may take while two CTAs still share an SM (228 KB per SM, 1 KB reserved per CTA), less
+// the kernel's few static bytes
+constexpr size_t GEMV_SMEM_2CTA = (233472 - 2 * 1024) / 2 - 256;
+// One more ring stage where two CTAs per SM still fit: a short kernel (an item or two per CTA) then has its whole share of
+// the weights in flight before the activations arrive instead of refilling a stage behind a full memory latency.
+void gemv_pick_stages(GemvPlan &p, int np, int nkp_slice, int fmt, bool normtail) {
+    static const int max_ns = env_int("LG_GEMV_STAGES", LG_GEMV_STAGES_MAX);
+    p.ns = LG_GEMV_STAGES;
+    p.smem = gemv_smem_bytes(np, nkp_slice, p.r, fmt, p.ns, normtail);
+    if (max_ns >= 4 && p.smem <= GEMV_SMEM_2CTA) {
+        const size_t s4 = gemv_smem_bytes(np, nkp_slice, p.r, fmt, 4, normtail);
+        if (s4 <= GEMV_SMEM_2CTA) { p.ns = 4; p.smem = s4; }
+    }
+}
 constexpr size_t GEMV_SMEM_MAX = 200 * 1024, ATTN_SMEM_MAX = 220 * 1024;
 constexpr int MAX_KV_HEADS = 64;
 
@@ -319,7 +341,6 @@ void set_kernel_attributes() {
     LG_CHECK(cudaFuncSetAttribute(lg_pf_attn_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pf_attn_smem<256>()));
 }
 
-int env_int(const char *name, int fb) { const char *v = getenv(name); return v && v[0] ? atoi(v) : fb; }
 
 // Decomposition of one matmul into CTA work items: R row tiles x one of ks column slices, walked
 // by a persistent grid of about two CTAs per SM.  Few slices (each slice's partial costs an extra
@@ -355,17 +376,19 @@ GemvPlan plan_gemv(const Engine *e, const WMat &W, int np, int want_ks, bool hea
     if (force_ks && want_ks <= 0 && !head && !geglu) p.ks = force_ks;
     if (p.ks > e->max_ks) p.ks = e->max_ks;
     if (p.ks > W.nkp) p.ks = W.nkp;
-    int stage = W.fmt == LG_FMT_Q4_K ? gemv_stage_bytes<LG_FMT_Q4_K>() : gemv_stage_bytes<LG_FMT_Q4_0>();
     for (;;) {
         int nkp_s = (W.nkp + p.ks - 1) / p.ks + 1;
-        p.smem = (size_t)np * nkp_s * 2 * (256 + 32) + 128 + (size_t)LG_GEMV_STAGES * stage
-               + (size_t)LG_GEMV_CW * p.r * np * 64 * 4 + (2 * LG_GEMV_STAGES + 1) * 8 + 16;
+        gemv_pick_stages(p, np, nkp_s, W.fmt, false);
         if (p.smem <= GEMV_SMEM_MAX || p.ks >= e->max_ks || p.ks * 2 > W.nkp || head || geglu) break;
         p.ks *= 2;                                   // the slice's panel does not fit: cut k finer
     }
+    // items beyond one wave: spread them evenly -- every CTA walks the same number of items (or one fewer), so no CTA
+    // is still on its second item while the others have left
     int groups = (W.n_row_tiles + p.r - 1) / p.r;
-    p.gx = groups < ctas / p.ks ? groups : ctas / p.ks;
-    if (head) p.gx = groups < ctas ? groups : ctas;
+    int cap = head ? ctas : ctas / p.ks;
+    if (cap < 1) cap = 1;
+    const int waves = (groups + cap - 1) / cap;
+    p.gx = (groups + waves - 1) / waves;
     if (p.gx < 1) p.gx = 1;
 
     return p;
@@ -402,9 +425,7 @@ struct GemvExtra {
 bool normtail_ok(const Engine *e, const WMat &W, int np) {
     static const int on = env_int("LG_NORMTAIL", 1);
     const int groups = W.n_row_tiles / 2;
-    size_t smem = (size_t)np * (W.nkp + 1) * 2 * (256 + 32) + 128
-                + (size_t)LG_GEMV_STAGES * (W.fmt == LG_FMT_Q4_K ? gemv_stage_bytes<LG_FMT_Q4_K>() : gemv_stage_bytes<LG_FMT_Q4_0>())
-                + (size_t)LG_GEMV_CW * 2 * np * 64 * 4 + (size_t)np * 128 * 4 + (2 * LG_GEMV_STAGES + 1) * 8 + 16;
+    size_t smem = gemv_smem_bytes(np, W.nkp + 1, 2, W.fmt, LG_GEMV_STAGES, true);
     return on && W.n_row_tiles % 2 == 0 && groups <= 2 * e->sm_count && smem <= 100 * 1024;
 }
 
@@ -415,9 +436,7 @@ void launch_gemv(Engine *e, const WMat &W, const LgPanel &X, int M, float *out, 
     GemvPlan p = plan_gemv(e, W, np, epi == LG_EPI_STORE ? force_ks : 1, epi == LG_EPI_HEAD, epi == LG_EPI_GEGLU);
     if (epi == LG_EPI_NORMTAIL) {
         p.r = 2; p.ks = 1; p.gx = W.n_row_tiles / 2;
-        int stage = W.fmt == LG_FMT_Q4_K ? gemv_stage_bytes<LG_FMT_Q4_K>() : gemv_stage_bytes<LG_FMT_Q4_0>();
-        p.smem = (size_t)np * (W.nkp + 1) * 2 * (256 + 32) + 128 + (size_t)LG_GEMV_STAGES * stage
-               + (size_t)LG_GEMV_CW * 2 * np * 64 * 4 + (size_t)np * 128 * 4 + (2 * LG_GEMV_STAGES + 1) * 8 + 16;
+        gemv_pick_stages(p, np, W.nkp + 1, W.fmt, true);
     }
     LgGemvArgs a{};
     a.wq = W.wq; a.ws = W.ws; a.wd = W.wd; a.x = X; a.nkp = W.nkp; a.n_row_tiles = W.n_row_tiles; a.kslices = p.ks;
@@ -427,6 +446,7 @@ void launch_gemv(Engine *e, const WMat &W, const LgPanel &X, int M, float *out, 
     a.xres = x.xres; a.ldx = x.ldx; a.n_cols = x.n_cols; a.add_w = x.add_w; a.norm_w = x.norm_w; a.out_scale = x.out_scale; a.eps = x.eps;
     a.ssq1 = x.ssq1; a.ssq2 = x.ssq2; a.gbar = x.gbar;
     a.post_ss = x.post_ss; a.n_post = x.n_post; a.post_n = x.post_n; a.post_eps = x.post_eps;
+    a.tag = (int)e->launches; a.ns = p.ns;
     if (X.nsb * 32 != W.k) { fprintf(stderr, "lg_b200: panel width %d does not match matrix k %d\n", X.nsb * 32, W.k); exit(1); }
     if (x.ks_out) *x.ks_out = p.ks;
     if (x.gx_out) *x.gx_out = p.gx;
@@ -463,6 +483,7 @@ void launch_norm(Engine *e, int M, float *x, int ldx, int n, float eps,
     a.add_w = add_w; a.out_scale = out_scale; a.norm_w = norm_w;
     if (panel) { a.panel = *panel; a.want_panel = 1; }
     a.y = y; a.ldy = ldy; a.n = n; a.eps = eps;
+    a.tag = (int)e->launches;
     static const int use_cluster = env_int("LG_NORM_CLUSTER", 1);
     if (use_cluster && n >= 32 * LG_NORM_CL) {
         // one cluster of LG_NORM_CL CTAs per token row
@@ -515,6 +536,26 @@ CUtensorMap act_tensor_map(const __half *ptr, int k, int rows, int nt) {
     return map;
 }
 
+CUtensorMap kv_tensor_map(const __half *ptr, int kv_dim, int seq, int S) {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        LG_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr));
+        if (!p || qr != cudaDriverEntryPointSuccess) { fprintf(stderr, "lg_b200: the driver has no cuTensorMapEncodeTiled\n"); exit(1); }
+        fn = (EncodeTiledFn)p;
+    }
+    CUtensorMap map;
+    cuuint64_t dims[2] = {(cuuint64_t)kv_dim, (cuuint64_t)seq};
+    cuuint64_t strides[1] = {(cuuint64_t)kv_dim * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)S};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { fprintf(stderr, "lg_b200: cuTensorMapEncodeTiled failed (%d) for a cache of %d rows x %d\n", (int)r, seq, kv_dim); exit(1); }
+    return map;
+}
+
 template <int NT, int FMT> void launch_pf_nt(Engine *e, const CUtensorMap &tm, const LgPfGemmArgs &a, int epi, dim3 grid) {
     const size_t sm = pf_smem_bytes<NT, FMT>();
     if (epi == LG_PF_GEGLU) launch_k(e, (lg_pf_gemm_kernel<NT, FMT, LG_PF_GEGLU>), grid, dim3(LG_PF_THREADS), sm, tm, a);
@@ -558,7 +599,7 @@ void launch_attn(Engine *e, LgAttnArgs a, int n_tiles_max) {
     if ((size_t)nq * n_tiles_max * 8 > 2 * (size_t)lg_attn_tile(a.hd) * (a.hd + 8) * 2) {
         fprintf(stderr, "lg_b200: %d key tiles x %d queries exceed the merge buffer of the attention kernel\n", n_tiles_max, nq); exit(1);
     }
-    a.tickets = e->tickets;
+    a.tickets = e->tickets; a.tag = (int)e->launches;
     dim3 grid(a.Hkv, n_tiles_max), block(LG_ATTN_THREADS);
     switch (a.hd) {
     case 64:  launch_k(e, lg_attn_kernel<64>, grid, block, sm, a); break;
@@ -619,45 +660,81 @@ void attn_cluster_config(cudaLaunchConfig_t &cfg, cudaLaunchAttribute *at, int H
     cfg.attrs = at; cfg.numAttrs = pdl ? 2 : 1;
 }
 
-// Cluster size for the attention of a layer whose blocks touch at most tiles_for(...) key tiles: the CTAs of one KV head
-// form one cluster, one CTA per tile, and merge through distributed shared memory (lg_attn_cluster_kernel).  The choice
-// is a property of the layer and the cache (never of the block width), so plain and speculative steps of a session run
-// the same kernel.  0 = no cluster (too many tiles, or the device cannot co-schedule such a cluster): the ticket kernel.
-int attn_cluster_size(const Engine *e, int window, int max_seq, int hd, int H, int Hkv) {
+// Tiled-copy descriptor of one layer's K (or V) cache [seq rows][kv_dim] f16: boxes of 64 columns x S rows, 128-byte swizzle.
+CUtensorMap kv_tensor_map(const __half *ptr, int kv_dim, int seq, int S);
+
+// Cluster size for the attention of a layer: the CTAs of one KV head form one cluster and merge through distributed
+// shared memory (lg_attn_cluster_kernel).  A sliding-window layer gets one CTA per key tile a block can touch; a
+// full-attention layer (first tile always 0) may give a CTA up to 4 tiles.  The choice is a property of the layer and
+// the cache (never of the block width), so plain and speculative steps of a session run the same kernel.
+// 0 = no cluster (too many tiles, a ring whose length is not a whole number of tiles, or the device cannot hold such
+// clusters): the ticket kernel.
+int attn_cluster_size(const Engine *e, int window, int max_seq, int seq, int hd, int H, int Hkv) {
     static const int on = env_int("LG_ATTN_CLUSTER", 1);
     if (!on || Hkv < 1 || Hkv > MAX_KV_HEADS) return 0;
+    const int S = lg_attn_tile(hd);
+    if (seq < max_seq && seq % S) return 0;                    // a tile must not straddle the ring's wrap
+    const bool from_zero = window <= 0 || window + LG_MAXM >= max_seq;      // every block's first tile is tile 0
     const int tiles = tiles_for(window, max_seq, LG_MAXM, hd);
-    if (tiles > LG_ATTN_CL_MAX) return 0;
-    int C = 1;
-    while (C < tiles) C *= 2;
+    if (tiles > (from_zero ? 4 * LG_ATTN_CL_MAX : LG_ATTN_CL_MAX)) return 0;
     const int nq_max = (H / Hkv) * LG_MAXM;
     const size_t sm = attn_cluster_smem(nq_max, hd);
     const void *fn = attn_cluster_fn(hd);
     if (!fn || sm > ATTN_SMEM_MAX || ((nq_max + 15) & ~15) > 32) return 0;
-    if ((size_t)((nq_max + 15) & ~15) * hd * 4 > (size_t)lg_attn_tile(hd) * (hd + 8) * 2) return 0;   // accumulators reuse the K tile
-    static std::map<long long, int> cache;        // (hd, C, smem) -> clusters the device can hold at once
-    const long long key = ((long long)hd << 40) | ((long long)C << 32) | (long long)sm;
+    if ((size_t)((nq_max + 15) & ~15) * hd * 4 > (size_t)S * hd * 2) return 0;          // accumulators reuse the K tile
+    // What matters is that the clusters of ALL KV heads are resident at once (a cluster that has to wait for another one
+    // to finish doubles the kernel's latency).  Ask the device how many clusters of each size it can hold.
+    static std::map<long long, int> cache;        // (hd, tiles, from_zero, Hkv, smem) -> chosen size
+    const long long key = ((long long)hd << 48) | ((long long)tiles << 40) | ((long long)from_zero << 39) | ((long long)Hkv << 32) | (long long)sm;
     auto it = cache.find(key);
     if (it == cache.end()) {
-        cudaLaunchConfig_t cfg; cudaLaunchAttribute at[2];
-        attn_cluster_config(cfg, at, Hkv, C, sm, e->stream, false);
-        int n = 0;
-        cudaError_t rc = cudaOccupancyMaxActiveClusters(&n, fn, &cfg);
-        if (rc != cudaSuccess) { cudaGetLastError(); n = 0; }
-        it = cache.emplace(key, n).first;
+        static const int verbose = env_int("LG_VERBOSE", 0), force = env_int("LG_ATTN_CLUSTER_SIZE", 0);
+        int fit[LG_ATTN_CL_MAX + 1] = {0};
+        for (int C = 1; C <= LG_ATTN_CL_MAX; C++) {
+            cudaLaunchConfig_t cfg; cudaLaunchAttribute at[2];
+            attn_cluster_config(cfg, at, Hkv, C, sm, e->stream, false);
+            int n = 0;
+            cudaError_t rc = cudaOccupancyMaxActiveClusters(&n, fn, &cfg);
+            if (rc != cudaSuccess) { cudaGetLastError(); n = 0; }
+            fit[C] = n;
+        }
+        int best_c = 0;
+        if (!from_zero) {
+            // one tile per CTA: the smallest size >= tiles that holds every head at once, else the one that holds most
+            int best_n = 0;
+            for (int C = tiles; C <= LG_ATTN_CL_MAX; C++) {
+                const int useful = fit[C] < Hkv ? fit[C] : Hkv;
+                if (useful > best_n) { best_n = useful; best_c = C; }
+            }
+        } else {
+            // tiles are dealt round-robin: the largest size (fewest tiles per CTA) that still holds every head at once
+            for (int C = std::min(tiles, LG_ATTN_CL_MAX); C >= 1; C--)
+                if (fit[C] >= Hkv && (tiles + C - 1) / C <= 4) { best_c = C; break; }
+        }
+        if (force && force <= LG_ATTN_CL_MAX && fit[force] > 0 && (from_zero || force >= tiles)) best_c = force;
+        if (verbose) {
+            fprintf(stderr, "lg_b200: attention clusters (head size %d, %zu bytes of shared memory, %d KV heads, %d tiles%s): fit per size",
+                    hd, sm, Hkv, tiles, from_zero ? " from tile 0" : "");
+            for (int C = 1; C <= LG_ATTN_CL_MAX; C++) fprintf(stderr, " %d:%d", C, fit[C]);
+            fprintf(stderr, " -> %d\n", best_c);
+        }
+        it = cache.emplace(key, best_c).first;
     }
-    return it->second >= 1 ? C : 0;
+    return it->second;
 }
 
 void launch_attn_cluster(Engine *e, LgAttnArgs a, int C) {
     const int nq = (a.H / a.Hkv) * a.M;
+    a.tag = (int)e->launches;
+    const int S = lg_attn_tile(a.hd);
+    const CUtensorMap tmk = kv_tensor_map(a.kc, a.kv_dim, a.seq, S), tmv = kv_tensor_map(a.vc, a.kv_dim, a.seq, S);
     cudaLaunchConfig_t cfg; cudaLaunchAttribute at[2];
     attn_cluster_config(cfg, at, a.Hkv, C, attn_cluster_smem(nq, a.hd), e->stream, e->pdl != 0);
     switch (a.hd) {
-    case 64:  LG_CHECK(cudaLaunchKernelEx(&cfg, lg_attn_cluster_kernel<64>, a)); break;
-    case 128: LG_CHECK(cudaLaunchKernelEx(&cfg, lg_attn_cluster_kernel<128>, a)); break;
-    case 256: LG_CHECK(cudaLaunchKernelEx(&cfg, lg_attn_cluster_kernel<256>, a)); break;
-    default:  LG_CHECK(cudaLaunchKernelEx(&cfg, lg_attn_cluster_kernel<512>, a)); break;
+    case 64:  LG_CHECK(cudaLaunchKernelEx(&cfg, lg_attn_cluster_kernel<64>, tmk, tmv, a)); break;
+    case 128: LG_CHECK(cudaLaunchKernelEx(&cfg, lg_attn_cluster_kernel<128>, tmk, tmv, a)); break;
+    case 256: LG_CHECK(cudaLaunchKernelEx(&cfg, lg_attn_cluster_kernel<256>, tmk, tmv, a)); break;
+    default:  LG_CHECK(cudaLaunchKernelEx(&cfg, lg_attn_cluster_kernel<512>, tmk, tmv, a)); break;
     }
     e->launches++;
 }
@@ -892,7 +969,7 @@ void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags, int 
         aa.kc = (__half *)kv->k[src]; aa.vc = (__half *)kv->v[src]; aa.seq = kv->seq[src]; aa.kv_dim = kv->kv_dim[src];
         aa.H = H; aa.Hkv = w.nkv; aa.hd = hd; aa.M = M;
         aa.window = w.local ? c->sliding_window : 0; aa.qpos_off = 0; aa.win_shrink = 0; aa.pos = d_pos;
-        aa.n_slots = e->part_slots; aa.part = e->part; aa.part_ml = e->part_ml; aa.out_f32 = nullptr;
+        aa.n_slots = e->part_slots; aa.part = e->part; aa.part_ml = e->part_ml; aa.out_f32 = nullptr; aa.err = e->err;
         LgPanel pa = e->p_attn; pa.nsb = H * hd / 32;
         aa.out = pa;
         static const int early_kv = env_int("LG_ATTN_EARLY_KV", 1);
@@ -900,7 +977,7 @@ void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags, int 
         static const int deep_local = env_int("LG_ATTN_DEEP_LOCAL", 0);
         const int deepG = (w.local && !deep_local) ? 0 : deep_span_tiles(e, kv->max_seq, w.nkv, hd, (H / w.nkv) * M);
         if (only & C_ATTN) {
-            const int cl = deepG ? 0 : attn_cluster_size(e, aa.window, kv->max_seq, hd, H, w.nkv);
+            const int cl = deepG ? 0 : attn_cluster_size(e, aa.window, kv->max_seq, aa.seq, hd, H, w.nkv);
             if (deepG) launch_attn_deep(e, aa, kv->max_seq, deepG);
             else if (cl) launch_attn_cluster(e, aa, cl);
             else launch_attn(e, aa, tiles_for(aa.window, kv->max_seq, M, hd));
@@ -1252,10 +1329,10 @@ void enqueue_draft(Engine *e, DraftW *d, const struct kvcache *kv, int slot, boo
         aa.H = d->n_head; aa.Hkv = Hkv; aa.hd = hd; aa.M = 1;
         aa.window = (b.local && c->sliding_window > 0) ? c->sliding_window : 0;
         aa.qpos_off = -1; aa.win_shrink = aa.window > 0 ? 1 : 0; aa.pos = &e->st->dpos;
-        aa.n_slots = d->n_slots_global; aa.part = d->part; aa.part_ml = d->part_ml;
+        aa.n_slots = d->n_slots_global; aa.part = d->part; aa.part_ml = d->part_ml; aa.err = e->err;
         LgPanel pa = d->p_attn; pa.nsb = d->n_head * hd / 32;
         aa.out = pa; aa.out_f32 = nullptr;
-        const int cl = attn_cluster_size(e, aa.window, kv->max_seq, hd, d->n_head, Hkv);
+        const int cl = attn_cluster_size(e, aa.window, kv->max_seq, aa.seq, hd, d->n_head, Hkv);
         if (cl) launch_attn_cluster(e, aa, cl);
         else launch_attn(e, aa, tiles_for(aa.window, kv->max_seq, 1, hd));
         int ks_o = 1;
@@ -1363,8 +1440,9 @@ int kvcache_init(struct kvcache *kv, const struct model *m, int max_seq) {
         kv->kv_dim[L] = m->n_head_kv[L] * m->head_dim[L];
         if (L >= c->n_kv_start) continue;
         int seq = max_seq;
-        if (m->is_local[L] && c->sliding_window > 0 && c->sliding_window + RING_SPARE < max_seq)
-            seq = c->sliding_window + RING_SPARE;
+        // a ring holds the window plus the spare, rounded up to whole key tiles of 128 so that a tile never straddles the wrap
+        if (m->is_local[L] && c->sliding_window > 0 && ((c->sliding_window + RING_SPARE + 127) & ~127) < max_seq)
+            seq = (c->sliding_window + RING_SPARE + 127) & ~127;
         kv->seq[L] = seq;
         kv->f16[L] = 1;
         size_t bytes = (size_t)seq * kv->kv_dim[L] * 2;
@@ -1723,6 +1801,29 @@ int lg_bench_prefill_pass(struct model *m, int n, int classes) {
 // layers; force_g > 0 fixes the tiles per span (tests), 0 derives it from the cache length.  Takes effect for
 // forwards captured afterwards (a new cache re-captures).
 void lg_set_attn_deep(int min_seq, int force_g) { g_deep_min = min_seq; g_deep_force = force_g; }
+
+// Profiling builds (-DLG_STAMPS): copy the phase time stamps of the most recent launches to the host;
+// out is [96 launches][320 CTAs][10 slots] of nanosecond timer values (0 = not written; slot 9 of CTA 0 = kernel kind).  -1 in the product build.
+int lg_debug_stamps(long long *out) {
+#ifdef LG_STAMPS
+    LG_CHECK(cudaDeviceSynchronize());
+    LG_CHECK(cudaMemcpyFromSymbol(out, lg_stamps, sizeof(long long) * LG_STAMP_LAUNCHES * LG_STAMP_CTAS * LG_STAMP_SLOTS));
+    return 0;
+#else
+    (void)out; return -1;
+#endif
+}
+int lg_debug_clear_stamps(void) {
+#ifdef LG_STAMPS
+    void *p = nullptr;
+    LG_CHECK(cudaGetSymbolAddress(&p, lg_stamps));
+    LG_CHECK(cudaMemset(p, 0, sizeof(long long) * LG_STAMP_LAUNCHES * LG_STAMP_CTAS * LG_STAMP_SLOTS));
+    LG_CHECK(cudaDeviceSynchronize());
+    return 0;
+#else
+    return -1;
+#endif
+}
 
 void *lg_stream(struct model *m) { return (void *)engine_for(m)->stream; }
 long long lg_round_launches(struct model *m) { return engine_for(m)->round_launches; }

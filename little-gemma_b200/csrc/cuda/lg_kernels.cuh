@@ -101,6 +101,33 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
+// ---- phase time stamps (profiling builds only: -DLG_STAMPS) ------------------------------------
+// Thread 0 of a CTA records the global nanosecond timer at named points of a kernel into
+// lg_stamps[launch tag][CTA][slot]; the host reads the array back after a forward and lays the launches of a
+// layer on one time axis (lg_debug_stamps).  Compiled out of the product build.
+#define LG_STAMP_LAUNCHES 96
+#define LG_STAMP_CTAS 320
+#define LG_STAMP_SLOTS 10
+#ifdef LG_STAMPS
+__device__ long long lg_stamps[LG_STAMP_LAUNCHES][LG_STAMP_CTAS][LG_STAMP_SLOTS];
+__device__ __forceinline__ void lg_stamp(int tag, int slot) {
+    if (threadIdx.x == 0 && tag >= 0 && tag < LG_STAMP_LAUNCHES) {
+        const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+        if (cta < LG_STAMP_CTAS) {
+            long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            lg_stamps[tag][cta][slot] = t;
+        }
+    }
+}
+#define LG_STAMP(tag, slot) lg_stamp(tag, slot)
+// slot 9 of CTA 0 names the kernel (1 matmul store, 2 head, 3 GeGLU, 4 norm tail, 5 attention/ticket, 6 attention/cluster, 7 norm)
+#define LG_STAMP_KIND(tag, kind) do { if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && (tag) >= 0 && (tag) < LG_STAMP_LAUNCHES) lg_stamps[tag][0][9] = (kind); } while (0)
+#else
+#define LG_STAMP(tag, slot) do { } while (0)
+#define LG_STAMP_KIND(tag, kind) do { } while (0)
+#endif
+
 // streaming 16-byte weight load: read-only path, do not keep in L1
 __device__ __forceinline__ uint4 ldg_stream16(const uint4 *p) {
     uint4 v;
@@ -284,6 +311,7 @@ struct LgNormArgs {
     float *y; int ldy;                   // optional f32 copy of the normed row
     int n; float eps;
     __half *yh; int ldyh;                // optional f16 copy (input of the wide prompt matmul; single-CTA kernel only)
+    int tag;                             // launch index for LG_STAMP (profiling builds)
 };
 
 struct LgGemvArgs {
@@ -316,6 +344,8 @@ struct LgGemvArgs {
     int *gbar;                 // {arrived, left}, zero between launches
     // consumer of a panel whose norm was deferred: results are multiplied by 1/rms from these partials
     const float *post_ss; int n_post; float post_n, post_eps;
+    int tag;                   // launch index for LG_STAMP (profiling builds)
+    int ns;                    // ring stages (LG_GEMV_STAGES .. LG_GEMV_STAGES_MAX)
 };
 
 enum { LG_FMT_Q4_0 = 0, LG_FMT_Q4_K = 1 };
@@ -323,10 +353,14 @@ enum { LG_FMT_Q4_0 = 0, LG_FMT_Q4_K = 1 };
 // A separate instantiation, so the plain epilogues carry none of that code.
 enum { LG_EPI_STORE = 0, LG_EPI_HEAD = 1, LG_EPI_GEGLU = 2, LG_EPI_NORMTAIL = 3, LG_EPI_POST = 4 };
 #define LG_ERR_GRID_BARRIER 256
+// partial sums of squares one lane adds when a row's norm is assembled from per-CTA partials: 32 lanes x 10 cover the
+// 296 CTAs of a grid of two per SM (the planner keeps such grids at or below 320 CTAs)
+#define LG_SS_PER_LANE 10
 
 #define LG_GEMV_CW 8                    // consumer warps per CTA
 #define LG_GEMV_THREADS ((LG_GEMV_CW + 1) * 32)   // + one producer warp
-#define LG_GEMV_STAGES 3               // ring depth
+#define LG_GEMV_STAGES 3               // ring depth: 3 stages, 4 (LG_GEMV_STAGES_MAX) where two CTAs per SM still fit
+#define LG_GEMV_STAGES_MAX 4
 #define LG_GEMV_STAGE_TILES 32         // 16x64 weight tiles per stage (R row tiles x 32/R positions)
 
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
@@ -361,7 +395,7 @@ __global__ void __launch_bounds__(LG_GEMV_THREADS)
 lg_gemv_kernel(LgGemvArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     constexpr int P = LG_GEMV_STAGE_TILES / R;               // tile positions per stage
-    constexpr int NS = LG_GEMV_STAGES;
+    const int NS = a.ns;                                     // ring depth chosen by the host (3 or 4)
     constexpr int EB = EPI & 3;                              // the epilogue proper
     constexpr bool POST = (EPI & LG_EPI_POST) != 0;
     constexpr int STAGE = gemv_stage_bytes<FMT>();
@@ -383,6 +417,8 @@ lg_gemv_kernel(LgGemvArgs a) {
     uint64_t *empty = full + NS, *pbar = empty + NS;
 
     pdl_launch();
+    LG_STAMP(a.tag, 0);
+    LG_STAMP_KIND(a.tag, 1 + EB);
     if (threadIdx.x == 0) {
         for (int i = 0; i < NS; i++) { mbar_init(full + i, 1); mbar_init(empty + i, LG_GEMV_CW); }
         mbar_init(pbar, 1);
@@ -393,6 +429,10 @@ lg_gemv_kernel(LgGemvArgs a) {
         // ---------------- producer ----------------
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0; bool panel_sent = false, ok = true;
+            // stages this CTA will stream in all, and how many of them go out before the dependency wait: a full ring
+            const int my_groups = blockIdx.x < n_groups ? (n_groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+            const int total_stages = my_groups * n_chunks, early = min(NS, total_stages);
+            int issued = 0;
             for (int grp = blockIdx.x; grp < n_groups && ok; grp += gridDim.x) {
                 const size_t tile_base = (size_t)grp * R * a.nkp + kp0;
                 for (int c = 0; c < n_chunks && ok; c++) {
@@ -410,8 +450,8 @@ lg_gemv_kernel(LgGemvArgs a) {
                             bulk_g2s(st + DD_OFF + (size_t)r * P * 64, a.wd + tile * 8, (uint32_t)np * 64, full + stage);
                     }
                     if (++stage == NS) { stage = 0; phase ^= 1; }
-                    if (!panel_sent && (stage == NS - 1 || c == n_chunks - 1)) {
-                        // weights are in flight; now the activations, which the previous kernel produced
+                    if (!panel_sent && ++issued == early) {
+                        // a ring of weights is in flight; now the activations, which the previous kernel produced
                         pdl_wait();
                         uint32_t qb = (uint32_t)nsb_s * 256, sb = (uint32_t)nsb_s * 32;
                         mbar_expect_tx(pbar, NP * (qb + sb));
@@ -436,19 +476,22 @@ lg_gemv_kernel(LgGemvArgs a) {
     for (int j = 0; j < SLOTS; j++) { best_v[j] = -INFINITY; best_i[j] = 0x7fffffff; }
 
     pdl_wait();
+    LG_STAMP(a.tag, 1);
     __shared__ float s_post[POST ? LG_MAXM : 1];
-    if (POST) {
-        // 1/rms of the deferred norm: partial sums of squares added in a fixed order (lane-strided, then the shuffle tree)
-        if (warp < a.M) {
-            float v = 0.0f;
-            for (int i = lane; i < a.n_post; i += 32) v += a.post_ss[(size_t)i * LG_MAXM + warp];
-            v = warp_sum(v);
-            if (lane == 0) s_post[warp] = 1.0f / sqrtf(v / a.post_n + a.post_eps);
+    // 1/rms of the deferred norm: a lane's partial sums of squares are all fetched here, before the first use (one memory
+    // latency, hidden under the panel wait and the main loop); they are added in a fixed order just before the epilogue
+    float post_pv[POST ? LG_SS_PER_LANE : 1];
+    if (POST && warp < a.M) {
+        #pragma unroll
+        for (int j = 0; j < LG_SS_PER_LANE; j++) {
+            const int i = lane + 32 * j;
+            post_pv[j] = i < a.n_post ? __ldcg(a.post_ss + (size_t)i * LG_MAXM + warp) : 0.0f;
         }
-        consumer_sync();
     }
+    bool post_done = false;
     bool ok = mbar_wait(pbar, 0);
     if (!ok && threadIdx.x == 0) atomicOr(a.err, LG_ERR_MBAR_TIMEOUT);
+    LG_STAMP(a.tag, 2);
     int stage = 0; uint32_t phase = 0;
 
     for (int grp = blockIdx.x; grp < n_groups; grp += gridDim.x) {
@@ -515,6 +558,17 @@ lg_gemv_kernel(LgGemvArgs a) {
             if (++stage == NS) { stage = 0; phase ^= 1; }
         }
 
+        LG_STAMP(a.tag, 3);
+        if (POST && !post_done) {
+            if (warp < a.M) {
+                float v = 0.0f;
+                #pragma unroll
+                for (int j = 0; j < LG_SS_PER_LANE; j++) v += post_pv[j];       // lane-strided, then the shuffle tree: a fixed order
+                v = warp_sum(v);
+                if (lane == 0) s_post[warp] = 1.0f / sqrtf(v / a.post_n + a.post_eps);
+            }
+            post_done = true;                                  // the consumer_sync below orders s_post before its readers
+        }
         // fixed-order sum over the consumer warps
         #pragma unroll
         for (int r = 0; r < R; r++)
@@ -566,6 +620,7 @@ lg_gemv_kernel(LgGemvArgs a) {
                 if (lane == 0) a.ssq1[(size_t)grp * LG_MAXM + warp] = ss;
             }
             // (c) grid-wide barrier: every item's partial is visible after it (bounded spin)
+            LG_STAMP(a.tag, 4);
             __threadfence();
             consumer_sync();
             if (threadIdx.x == 0) {
@@ -576,10 +631,18 @@ lg_gemv_kernel(LgGemvArgs a) {
                 __threadfence();
             }
             consumer_sync();
+            LG_STAMP(a.tag, 5);
             // (d) 1/rms of the whole row from all partials (fixed order), the residual update, the next panel
             if (warp < a.M) {
+                float pv[LG_SS_PER_LANE];
+                #pragma unroll
+                for (int j = 0; j < LG_SS_PER_LANE; j++) {
+                    const int i = lane + 32 * j;
+                    pv[j] = i < n_groups ? __ldcg(a.ssq1 + (size_t)i * LG_MAXM + warp) : 0.0f;
+                }
                 float v = 0.0f;
-                for (int i = lane; i < n_groups; i += 32) v += __ldcg(a.ssq1 + (size_t)i * LG_MAXM + warp);
+                #pragma unroll
+                for (int j = 0; j < LG_SS_PER_LANE; j++) v += pv[j];
                 v = warp_sum(v);
                 const float s1 = 1.0f / sqrtf(v / (float)a.n_cols + a.eps);
                 float xn = __fadd_rn(x_v, __fmul_rn(__fmul_rn(o_v, s1), wa));
@@ -616,6 +679,7 @@ lg_gemv_kernel(LgGemvArgs a) {
             }
         }
         consumer_sync();
+        LG_STAMP(a.tag, 6);
     }
 
     if (EB == LG_EPI_HEAD) {
@@ -766,6 +830,7 @@ __global__ void lg_norm_kernel(LgNormArgs a) {
 // touches 1/8 of the row and the whole row is in flight at once.
 #define LG_NORM_CL 8
 #define LG_NORM_CL_THREADS 128
+#define LG_NORM_CL_EPT 4               // row elements per thread the batched-load path holds in registers (rows up to 4096)
 
 __device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
 __device__ __forceinline__ void cluster_sync_all() {
@@ -792,10 +857,52 @@ __global__ void __launch_bounds__(LG_NORM_CL_THREADS) lg_norm_cluster_kernel(LgN
         if (a.add_src) wa[j] = a.add_w[i0 + j];
         if (a.norm_w) wn[j] = a.norm_w[i0 + j];
     }
+    LG_STAMP(a.tag, 0);
+    LG_STAMP_KIND(a.tag, 7);
     pdl_wait();
+    LG_STAMP(a.tag, 1);
     float *x = a.x + (size_t)tok * a.ldx;
     float ss2 = 0.0f;
-    if (a.add_src) {
+    if (a.add_src && cnt <= LG_NORM_CL_EPT * LG_NORM_CL_THREADS && a.n_parts <= 4) {
+        // every load of this thread -- the k-slice partials and the residual elements -- is issued before the first use,
+        // so the chain after the dependency wait holds ONE memory latency instead of one per partial and one for x
+        float pv[LG_NORM_CL_EPT][4], xv[LG_NORM_CL_EPT];
+        #pragma unroll
+        for (int u = 0; u < LG_NORM_CL_EPT; u++) {
+            const int j = threadIdx.x + u * LG_NORM_CL_THREADS;
+            #pragma unroll
+            for (int p = 0; p < 4; p++)
+                pv[u][p] = (j < cnt && p < a.n_parts) ? __ldcg(a.add_src + (size_t)p * a.part_stride + (size_t)tok * a.ld_add + i0 + j) : 0.0f;
+            xv[u] = j < cnt ? __ldcg(x + i0 + j) : 0.0f;
+        }
+        float ss = 0.0f, sv[LG_NORM_CL_EPT];
+        #pragma unroll
+        for (int u = 0; u < LG_NORM_CL_EPT; u++) {
+            float v = 0.0f;
+            #pragma unroll
+            for (int p = 0; p < 4; p++) v += pv[u][p];           // p >= n_parts adds an exact zero: the order of the sum is that of the loop form
+            sv[u] = v;
+            ss += v * v;
+        }
+        ss = block_sum(ss, red);
+        if (threadIdx.x < LG_NORM_CL) dsmem_store(&slots[0][rank], threadIdx.x, ss);
+        cluster_sync_all();
+        float tot = 0.0f;
+        #pragma unroll
+        for (int r = 0; r < LG_NORM_CL; r++) tot += slots[0][r];
+        const float s = 1.0f / sqrtf(tot / (float)a.n + a.eps);
+        #pragma unroll
+        for (int u = 0; u < LG_NORM_CL_EPT; u++) {
+            const int j = threadIdx.x + u * LG_NORM_CL_THREADS;
+            if (j < cnt) {
+                float v = __fadd_rn(xv[u], __fmul_rn(__fmul_rn(sv[u], s), wa[j]));
+                v = __fmul_rn(v, a.out_scale);
+                x[i0 + j] = v;
+                row[j] = v;
+                ss2 += v * v;
+            }
+        }
+    } else if (a.add_src) {
         float ss = 0.0f;
         for (int j = threadIdx.x; j < cnt; j += LG_NORM_CL_THREADS) {
             const int i = i0 + j;
@@ -841,6 +948,7 @@ __global__ void __launch_bounds__(LG_NORM_CL_THREADS) lg_norm_cluster_kernel(LgN
         if (a.y) a.y[(size_t)tok * a.ldy + i] = yv;
         if (a.want_panel) quant_group_store(yv, lane, tok, gq, a.panel);
     }
+    LG_STAMP(a.tag, 6);
     // every remote write into this CTA's slots precedes a cluster barrier this CTA has passed: safe to exit
 }
 
@@ -891,6 +999,8 @@ struct LgAttnArgs {
     int *tickets;              // [Hkv], zero between launches
     LgPanel out; float *out_f32;   // merged output: panel of [M][H*hd] and/or f32 [M][H][hd]
     __half *out_h; int ld_h;       // and/or f16 rows [M][ld_h] (input of the wide prompt matmul)
+    int tag;                       // launch index for LG_STAMP (profiling builds)
+    int *err;                      // status word for bounded waits that gave up (may be null)
 };
 
 #define LG_ATTN_THREADS 256
@@ -966,6 +1076,8 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) 
     // the per-head norm weights are cold in HBM and do not depend on the previous kernel: fetch them first
     __shared__ float s_qn[HD], s_kn[HD];
     pdl_launch();
+    LG_STAMP(a.tag, 0);
+    LG_STAMP_KIND(a.tag, 5);
     if (!a.q_ready)
         for (int i = threadIdx.x; i < HD; i += LG_ATTN_THREADS) { s_qn[i] = a.q_norm[i]; s_kn[i] = a.k_norm ? a.k_norm[i] : 1.0f; }
     // early_kv: the position and the cached rows below the block were written by earlier graph launches (this layer
@@ -1006,6 +1118,7 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) 
         }
     }
     if (a.early_kv) pdl_wait();
+    LG_STAMP(a.tag, 1);
 
     // ---- 2. queries: per-head RMSNorm + RoPE, split into f16 hi + lo ----
     for (int qi = warp; qi < nq16; qi += NW) {
@@ -1050,8 +1163,10 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) 
             }
         }
     }
+    LG_STAMP(a.tag, 2);
     cp_async_wait_all();
     __syncthreads();
+    LG_STAMP(a.tag, 3);
 
     // ---- 3. scores: warp w takes keys [w*S/8, (w+1)*S/8) ----
     const int g = lane >> 2, t = lane & 3;
@@ -1155,11 +1270,13 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) 
     // ---- 6. the last CTA of this KV head merges ----
     __shared__ int s_last;
     __syncthreads();
+    LG_STAMP(a.tag, 4);
     if (threadIdx.x == 0) {
         __threadfence();
         s_last = atomicAdd(a.tickets + kvh, 1) == t_hi - t_lo;
     }
     __syncthreads();
+    LG_STAMP(a.tag, 5);
     if (!s_last) return;
     __threadfence();
     // (a) every (query, tile) max and sum -> shared memory (the K/V tile area is free now)
@@ -1242,6 +1359,7 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) 
         if (a.out.q) quant_group_store(y, lane, tok, (hq * HD + d) >> 5, a.out);
     }
     if (threadIdx.x == 0) a.tickets[kvh] = 0;
+    LG_STAMP(a.tag, 6);
 }
 
 // ---------------------------------------------------------------------------------------------
