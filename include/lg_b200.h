@@ -81,6 +81,17 @@ int  lg_rounds_begin(struct model *m, int first_token, int pos, int n_emitted);
 int  lg_rounds_enqueue(struct model *m, struct kvcache *kv, struct mtp *t, int n, int mode, int n_rounds);
 int  lg_rounds_collect(struct model *m, int *tokens, int from, int cap, int *stats);
 
+/* One host wait per round behind the blocking calls.  mtp_draft_device runs the whole round on the stream (every draft,
+ * the verify of the tokens they turned out to be, the acceptance) and waits once for its record; mtp_draft_chain_device
+ * and model_forward_spec / lg_forward_spec_n answer from that record when they are asked about exactly those tokens, and
+ * fall back to running synchronously otherwise (the results are the same either way).  The round is run at the width set
+ * here (default LG_MTP_N).  LG_LAZY_ROUND=0 in the environment keeps every call synchronous. */
+void lg_set_round_width(int n);
+/* With a replay table set (lg_set_replay), that whole-round path overrides the head's drafts as the device-resident rounds
+ * do: the draft offered for position p is replay[p + offset].  enable = 0 turns the override off. */
+void lg_set_replay_origin(struct model *m, int offset, int enable);
+long long lg_host_syncs(struct model *m);            /* blocking device-to-host waits made by the blocking calls so far */
+
 /* Introspection for tests and the benchmark. */
 long long lg_weight_bytes(struct model *m);          /* file bytes of all matrices uploaded so far */
 long long lg_round_launches(struct model *m);        /* kernels in one captured round */

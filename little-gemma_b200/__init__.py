@@ -28,7 +28,7 @@ ABI_SYMBOLS = [
     "model_forward", "model_forward_next", "model_prefill", "model_prefill_embd", "model_prefill_mixed",
     "model_prefill_reserve", "model_forward_spec", "mtp_draft_device", "mtp_draft_chain_device", "mtp_free_device",
     "lg_forward_spec_n", "lg_set_replay", "lg_rounds_begin", "lg_rounds_enqueue", "lg_rounds_collect",
-    "lg_weight_bytes", "lg_round_launches", "lg_last_hidden", "lg_kv_row", "lg_stream", "lg_engine_release",
+    "lg_set_round_width", "lg_set_replay_origin", "lg_host_syncs", "lg_weight_bytes", "lg_round_launches", "lg_last_hidden", "lg_kv_row", "lg_stream", "lg_engine_release",
     "lg_bench_matmul_pass", "lg_bench_prefill_pass", "lg_set_attn_deep", "lg_flash_decode_noalloc",
     "lg_dequant_host", "lg_gemv_host", "lg_flash_decode_host", "lg_flash_decode_cluster_host", "lg_prefill_matmul_host",
 ]
@@ -94,6 +94,9 @@ def load() -> C.CDLL:
     L.lg_bench_prefill_pass.argtypes = [C.c_void_p, C.c_int, C.c_int]; L.lg_bench_prefill_pass.restype = C.c_int
     L.lgs_rounds_host.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _i32p, C.c_int, C.c_void_p, C.c_int, _i32p]
     L.lgs_rounds_host.restype = C.c_int
+    L.lgs_host_syncs.argtypes = [C.c_void_p]; L.lgs_host_syncs.restype = C.c_longlong
+    L.lg_set_round_width.argtypes = [C.c_int]; L.lg_set_round_width.restype = None
+    L.lg_set_replay_origin.argtypes = [C.c_void_p, C.c_int, C.c_int]; L.lg_set_replay_origin.restype = None
     _lib = L
     return L
 
@@ -302,6 +305,10 @@ class Session:
         toks = np.zeros(max(cap, 1), dtype=np.int32)
         n = self.L.lg_rounds_collect(self.model, toks.ctypes.data_as(C.c_void_p), from_, cap, stats)
         return toks[:n], dict(pos=int(stats[0]), n_emitted=int(stats[1]), n_draft=int(stats[2]), n_accept=int(stats[3]))
+
+    def host_syncs(self) -> int:
+        """Blocking device-to-host waits the reference-shaped calls of this session have made so far."""
+        return int(self.L.lgs_host_syncs(self.h))
 
     def weight_bytes(self) -> int:
         return int(self.L.lg_weight_bytes(self.model))

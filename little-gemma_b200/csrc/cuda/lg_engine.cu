@@ -108,7 +108,7 @@ struct Engine {
     // session
     LgRoundState *st = nullptr;               // device
     LgRoundState *st_host = nullptr;          // pinned mirror for uploads / downloads
-    int *log = nullptr, *replay = nullptr; int n_replay = 0;
+    int *log = nullptr, *replay = nullptr, *d_n_replay = nullptr; int n_replay = 0, replay_cap = 0;   // replay table (capacity grows; its length lives on the device)
     int *err = nullptr, *tickets = nullptr;
     std::map<std::string, cudaGraphExec_t> graphs;
     const struct kvcache *kv_bound = nullptr;
@@ -120,6 +120,11 @@ struct Engine {
     PrefillBuf pf;
     float *ssq1 = nullptr, *ssq2 = nullptr; int *gbar = nullptr;     // NORMTAIL scratch: partial sums of squares, grid barrier
     int pos_hi = 0;                           // host-side upper bound of the device position (device-resident rounds)
+    // One host synchronisation per round behind the blocking calls: mtp_draft_device runs the WHOLE round and keeps its
+    // outcome here; the chained-draft and verify calls that follow are answered from it when they ask what was computed.
+    struct { bool valid = false; int n = 0, pos = 0, adv = 0, toks[LG_MAXM] = {0}, out[LG_MAXM] = {0}; bool chained = false; } lazy;
+    int replay_off = 0; bool lazy_replay = false;   // replay table index of a draft = its position + replay_off (lg_set_replay_origin)
+    long long host_syncs = 0;                 // blocking device-to-host waits made by the reference-shaped calls
     int mm_launches = 0;                      // kernels in the captured matmul-only pass             // kernels in one captured round (lg_rounds_enqueue)
 };
 
@@ -896,7 +901,7 @@ void engine_free(Engine *e) {
     cudaFree(e->hidden); cudaFree(e->h_prev); cudaFree(e->part); cudaFree(e->tokrow); cudaFree(e->pproj); cudaFree(e->ipl);
     cudaFree(e->pg); cudaFree(e->logits); cudaFree(e->amax_val); cudaFree(e->amax_idx);
     panel_free(e->p_ne); panel_free(e->p_attn); panel_free(e->p_ff); panel_free(e->p_ple);
-    cudaFree(e->st); cudaFreeHost(e->st_host); cudaFree(e->log); cudaFree(e->replay); cudaFree(e->err); cudaFree(e->tickets);
+    cudaFree(e->st); cudaFreeHost(e->st_host); cudaFree(e->log); cudaFree(e->replay); cudaFree(e->d_n_replay); cudaFree(e->err); cudaFree(e->tickets);
     free(e->pick_rows);
     cudaStreamDestroy(e->stream);
     delete e;
@@ -1397,6 +1402,18 @@ bool pos_in_cache(const struct kvcache *kv, int pos, int n, const char *what) {
 int spec_n(struct model *m, struct kvcache *kv, int n, const int *toks, int pos, int *out) {
     Engine *e = engine_for(m);
     if (!pos_in_cache(kv, pos, n, "a forward")) exit(1);
+    if (e->lazy.valid) {
+        // the round this verify belongs to has already run (mtp_draft_device): if the caller verifies exactly the tokens it
+        // was handed, the outcome is on the host already -- no launch, no wait
+        bool same = e->lazy.n == n && e->lazy.pos == pos && !model_pick;
+        for (int j = 0; same && j < n; j++) same = toks[j] == e->lazy.toks[j];
+        e->lazy.valid = false;
+        if (same) {
+            for (int j = 0; j < n; j++) out[j] = e->lazy.out[j];
+            return e->lazy.adv;
+        }
+        // other tokens than predicted (or a sampling hook): run the verify now; it overwrites the same cache rows
+    }
     upload_round(e, toks, n, pos);
     int flags = F_HEAD | F_ACCEPT | (model_pick ? F_LOGITS : 0);
     run_forward(e, kv, n, flags);
@@ -1407,6 +1424,7 @@ int spec_n(struct model *m, struct kvcache *kv, int n, const int *toks, int pos,
             LG_CHECK(cudaMemcpyAsync(e->pick_rows + (size_t)j * c->n_vocab, e->logits + (size_t)j * e->head.ldo,
                                      (size_t)c->n_vocab * 4, cudaMemcpyDeviceToHost, e->stream));
         LG_CHECK(cudaStreamSynchronize(e->stream));
+        e->host_syncs++;
         for (int j = 0; j < n; j++) out[j] = model_pick(e->pick_rows + (size_t)j * c->n_vocab, c->n_vocab);
         int adv = 1;
         while (adv < n && out[adv - 1] == toks[adv]) adv++;
@@ -1416,9 +1434,45 @@ int spec_n(struct model *m, struct kvcache *kv, int n, const int *toks, int pos,
     }
     LG_CHECK(cudaMemcpyAsync(e->st_host->out, e->st->out, sizeof(int) * (LG_MAXM + 1), cudaMemcpyDeviceToHost, e->stream));
     LG_CHECK(cudaStreamSynchronize(e->stream));
+    e->host_syncs++;
     for (int j = 0; j < n; j++) out[j] = e->st_host->out[j];
     return e->st_host->adv;
 }
+
+// One whole round as a graph: drafts of head d (if any) into toks[1..n-1], the replay override, the verify forward of
+// width n, greedy acceptance; `advance` also moves the device state on to the next round (device-resident rounds).
+cudaGraphExec_t round_graph(Engine *e, const struct kvcache *kv, DraftW *d, int n, bool replay, bool advance) {
+    bind_kv(e, kv);
+    char key[48];
+    snprintf(key, sizeof key, "r%d_%d_%d_%d", n, replay ? 1 : 0, d ? 1 : 0, advance ? 1 : 0);
+    auto it = e->graphs.find(key);
+    if (it == e->graphs.end()) {
+        cudaGraph_t graph;
+        e->launches = 0;
+        LG_CHECK(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeRelaxed));
+        if (d) {
+            for (int j = 1; j < n; j++) {
+                if (j >= 2 && !d->has_post) {           // no chaining: pad like the reference caller does
+                    launch_k(e, lg_pad_drafts, dim3(1), dim3(1), 0, e->st, j, n);
+                    break;
+                }
+                launch_k(e, lg_set_draft_pos, dim3(1), dim3(1), 0, e->st, j - 1);
+                enqueue_draft(e, d, kv, j, j >= 2);
+            }
+        }
+        if (replay && n > 1) launch_k(e, lg_replay_drafts_kernel, dim3(1), dim3(32), 0, e->st, n, (const int *)e->replay, (const int *)e->d_n_replay);
+        enqueue_forward(e, kv, n, F_HEAD | F_ACCEPT | (advance ? F_ADVANCE : 0));
+        LG_CHECK(cudaStreamEndCapture(e->stream, &graph));
+        cudaGraphExec_t exec;
+        LG_CHECK(cudaGraphInstantiate(&exec, graph, 0));
+        LG_CHECK(cudaGraphDestroy(graph));
+        it = e->graphs.emplace(key, exec).first;
+        e->round_launches = e->launches;
+    }
+    return it->second;
+}
+
+int g_round_width = LG_MTP_N;                 // verify width the blocking calls' whole-round path assumes (lg_set_round_width)
 
 }  // namespace
 
@@ -1498,6 +1552,7 @@ void kvcache_restore_prefix(struct kvcache *kv, int n) {
 
 void model_forward(struct model *m, struct kvcache *kv, int token, int pos, float *logits) {
     Engine *e = engine_for(m);
+    e->lazy.valid = false;
     if (!pos_in_cache(kv, pos, 1, "model_forward")) exit(1);
     upload_round(e, &token, 1, pos);
     run_forward(e, kv, 1, logits ? (F_HEAD | F_LOGITS | F_ACCEPT) : 0);
@@ -1519,6 +1574,7 @@ static void prefill_impl(struct model *m, struct kvcache *kv, const float *rows,
     Engine *e = engine_for(m);
     const int ne = m->cfg.n_embd;
     if (n <= 0) return;
+    e->lazy.valid = false;
     if (!pos_in_cache(kv, pos0, n, "a prompt pass")) exit(1);
     std::vector<int> toks(n), ridx(n, -1);
     bool media = false;
@@ -1608,12 +1664,34 @@ int mtp_draft_device(struct mtp *t, const struct model *m, const struct kvcache 
     DraftW *d = draft_for(e, t, kv);
     if (!d) return -1;
     LgRoundState *h = e->st_host;
+    static const int lazy_on = env_int("LG_LAZY_ROUND", 1);
+    const int n = g_round_width;
+    e->lazy.valid = false;
+    if (lazy_on && n >= 2 && n <= LG_MAXM && !model_pick && pos >= 0 && (long long)pos + n <= kv->max_seq) {
+        // The reference's caller asks for the drafts one by one and then for the verify, blocking on each answer
+        // (src/run.c:54-71).  Here the first call runs the whole round on the stream -- every draft, the verify of the
+        // tokens the drafts turned out to be, the acceptance -- and waits ONCE for its record; the calls that follow
+        // find their answers in it.
+        memset(h, 0, sizeof *h);
+        h->pos = pos; h->toks[0] = token; h->n_emitted = pos + e->replay_off;
+        LG_CHECK(cudaMemcpyAsync(e->st, h, sizeof *h, cudaMemcpyHostToDevice, e->stream));
+        const bool replay = e->lazy_replay && e->replay != nullptr && e->n_replay > 0;
+        LG_CHECK(cudaGraphLaunch(round_graph(e, kv, d, n, replay, false), e->stream));
+        LG_CHECK(cudaMemcpyAsync(h, e->st, sizeof *h, cudaMemcpyDeviceToHost, e->stream));
+        check_err(e);                                    // the one wait of this round
+        e->host_syncs++;
+        e->lazy.valid = true; e->lazy.n = n; e->lazy.pos = pos; e->lazy.adv = h->adv; e->lazy.chained = d->has_post != 0;
+        for (int j = 0; j < n; j++) { e->lazy.toks[j] = h->toks[j]; e->lazy.out[j] = h->out[j]; }
+        h->pos = pos;                                    // what the chained-draft call derives its slot from
+        return e->lazy.toks[1];
+    }
     h->pos = pos; h->toks[0] = token;
     LG_CHECK(cudaMemcpyAsync(e->st, h, sizeof(int) * 2, cudaMemcpyHostToDevice, e->stream));
     LG_CHECK(cudaMemcpyAsync(&e->st->dpos, &h->pos, sizeof(int), cudaMemcpyHostToDevice, e->stream));
     run_draft(e, d, kv, 1, false);
     LG_CHECK(cudaMemcpyAsync(&h->toks[1], &e->st->toks[1], sizeof(int), cudaMemcpyDeviceToHost, e->stream));
     LG_CHECK(cudaStreamSynchronize(e->stream));
+    e->host_syncs++;
     return h->toks[1];
 }
 
@@ -1625,12 +1703,21 @@ int mtp_draft_chain_device(struct mtp *t, const struct model *m, const struct kv
     LgRoundState *h = e->st_host;
     int slot = pos - h->pos + 1;                         // chained draft j lands in toks[j], drafted at pos + j - 1
     if (slot < 2 || slot >= LG_MAXM) return -1;
+    if (e->lazy.valid) {
+        // asked to extend exactly the draft the round produced: that draft's successor is known
+        if (slot < e->lazy.n && pos == e->lazy.pos + slot - 1 && token == e->lazy.toks[slot - 1]) return e->lazy.toks[slot];
+        // anything else leaves the recorded round behind: draft synchronously from the device state as it stands
+        e->lazy.valid = false;
+        for (int j = 0; j < slot - 1 && j < LG_MAXM; j++) h->toks[j] = e->lazy.toks[j];
+        LG_CHECK(cudaMemcpyAsync(&e->st->pos, &h->pos, sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    }
     h->toks[slot - 1] = token; h->dpos = pos;
     LG_CHECK(cudaMemcpyAsync(&e->st->toks[slot - 1], &h->toks[slot - 1], sizeof(int), cudaMemcpyHostToDevice, e->stream));
     LG_CHECK(cudaMemcpyAsync(&e->st->dpos, &h->dpos, sizeof(int), cudaMemcpyHostToDevice, e->stream));
     run_draft(e, d, kv, slot, true);
     LG_CHECK(cudaMemcpyAsync(&h->toks[slot], &e->st->toks[slot], sizeof(int), cudaMemcpyDeviceToHost, e->stream));
     LG_CHECK(cudaStreamSynchronize(e->stream));
+    e->host_syncs++;
     return h->toks[slot];
 }
 
@@ -1675,18 +1762,41 @@ int lg_kv_row(struct model *m, struct kvcache *kv, int layer, int pos, float *k,
 int lg_set_replay(struct model *m, const int *replay, int n) {
     Engine *e = engine_for(m);
     LG_CHECK(cudaStreamSynchronize(e->stream));
-    cudaFree(e->replay); e->replay = nullptr; e->n_replay = 0;
-    if (n > 0) {
-        e->replay = dalloc<int>(n);
-        h2d_sync(e->replay, replay, (size_t)n * 4);
-        e->n_replay = n;
+    e->lazy.valid = false;
+    if (n < 0) n = 0;
+    if (!e->d_n_replay) e->d_n_replay = dalloc<int>(1);
+    if (n > e->replay_cap || !e->replay) {
+        // the table moves: graphs that hold its address are rebuilt on their next use
+        for (auto it = e->graphs.begin(); it != e->graphs.end();)
+            if (it->first[0] == 'r') { cudaGraphExecDestroy(it->second); it = e->graphs.erase(it); } else ++it;
+        cudaFree(e->replay);
+        e->replay_cap = n > 2 * e->replay_cap ? n : 2 * e->replay_cap;
+        if (e->replay_cap < 1024) e->replay_cap = 1024;
+        e->replay = dalloc<int>(e->replay_cap);
     }
+    if (n > 0) h2d_sync(e->replay, replay, (size_t)n * 4);
+    h2d_sync(e->d_n_replay, &n, 4);
+    e->n_replay = n;
+    if (n == 0) e->lazy_replay = false;
     return 0;
 }
+
+// Verify width the blocking calls assume when mtp_draft_device runs a whole round ahead (default: LG_MTP_N, the width
+// model_forward_spec is compiled for); callers of lg_forward_spec_n with another width set it here.
+void lg_set_round_width(int n) { g_round_width = n; }
+// With a replay table set, the whole-round path behind the blocking calls overrides the head's drafts too: the draft
+// for position p is replay[p + offset].  enable = 0 turns the override off again.
+void lg_set_replay_origin(struct model *m, int offset, int enable) {
+    Engine *e = engine_for(m);
+    e->replay_off = offset; e->lazy_replay = enable != 0; e->lazy.valid = false;
+}
+// Blocking device-to-host waits the reference-shaped calls have made so far (the benchmark reports waits per round).
+long long lg_host_syncs(struct model *m) { return engine_for(m)->host_syncs; }
 
 int lg_rounds_begin(struct model *m, int first, int pos, int n_emitted) {
     Engine *e = engine_for(m);
     LgRoundState *h = e->st_host;
+    e->lazy.valid = false;
     memset(h, 0, sizeof *h);
     h->pos = pos; h->toks[0] = first; h->n_emitted = n_emitted;
     LG_CHECK(cudaMemcpyAsync(e->st, h, sizeof *h, cudaMemcpyHostToDevice, e->stream));
@@ -1707,39 +1817,8 @@ int lg_rounds_enqueue(struct model *m, struct kvcache *kv, struct mtp *t, int n,
         return -2;
     }
     e->pos_hi += n_rounds * n;
-    bind_kv(e, kv);
-    char key[48];
-    snprintf(key, sizeof key, "r%d_%d_%d", n, mode, d ? 1 : 0);
-    auto it = e->graphs.find(key);
-    if (it == e->graphs.end()) {
-        cudaGraph_t graph;
-        e->launches = 0;
-        LG_CHECK(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeRelaxed));
-        if (d) {
-            for (int j = 1; j < n; j++) {
-                if (j >= 2 && !d->has_post) {           // no chaining: pad like the reference caller does
-                    launch_k(e, lg_pad_drafts, dim3(1), dim3(1), 0, e->st, j, n);
-                   
-                    break;
-                }
-                launch_k(e, lg_set_draft_pos, dim3(1), dim3(1), 0, e->st, j - 1);
-               
-                enqueue_draft(e, d, kv, j, j >= 2);
-            }
-        }
-        if (mode == 2 && n > 1) {
-            launch_k(e, lg_replay_drafts_kernel, dim3(1), dim3(32), 0, e->st, n, e->replay, e->n_replay);
-           
-        }
-        enqueue_forward(e, kv, n, F_HEAD | F_ACCEPT | F_ADVANCE);
-        LG_CHECK(cudaStreamEndCapture(e->stream, &graph));
-        cudaGraphExec_t exec;
-        LG_CHECK(cudaGraphInstantiate(&exec, graph, 0));
-        LG_CHECK(cudaGraphDestroy(graph));
-        it = e->graphs.emplace(key, exec).first;
-        e->round_launches = e->launches;
-    }
-    for (int r = 0; r < n_rounds; r++) LG_CHECK(cudaGraphLaunch(it->second, e->stream));
+    cudaGraphExec_t g = round_graph(e, kv, d, n, mode == 2, true);
+    for (int r = 0; r < n_rounds; r++) LG_CHECK(cudaGraphLaunch(g, e->stream));
     return 0;
 }
 

@@ -1436,10 +1436,10 @@ __global__ void lg_accept_kernel(LgRoundState *st, int M, const float *__restric
 }
 
 // drafts for the coming round: slot j <- replay[n_emitted + j - 1] (oracle-replayed drafts)
-__global__ void lg_replay_drafts_kernel(LgRoundState *st, int M, const int *__restrict__ replay, int n_replay) {
+__global__ void lg_replay_drafts_kernel(LgRoundState *st, int M, const int *__restrict__ replay, const int *__restrict__ n_replay) {
     pdl_launch(); pdl_wait();
     int j = threadIdx.x + 1;
-    if (j < M) { int i = st->n_emitted + j - 1; st->toks[j] = i < n_replay ? replay[i] : 0; }
+    if (j < M) { int i = st->n_emitted + j - 1; st->toks[j] = (i >= 0 && i < *n_replay) ? replay[i] : 0; }
 }
 
 // draft-head input: cat = [ embed(tok)*sqrt(nb) , h_prev ] is assembled by lg_embed_rows + this copy

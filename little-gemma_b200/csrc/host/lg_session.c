@@ -23,6 +23,8 @@ struct lg_session {
     int mtp_n;
 };
 
+long long lgs_host_syncs(void *p) { return lg_host_syncs(&((struct lg_session *)p)->m); }
+
 void *lgs_open(const char *target, const char *head, int max_seq, int kv_f16_all_ignored) {
     (void)kv_f16_all_ignored;                       /* the device cache is always f16 */
     struct lg_session *s = calloc(1, sizeof *s);
@@ -33,6 +35,7 @@ void *lgs_open(const char *target, const char *head, int max_seq, int kv_f16_all
     if (kvcache_init(&s->kv, &s->m, max_seq) != 0) { model_free(&s->m); free_gguf(s->g); free(s); return NULL; }
     if (head && head[0]) s->head = mtp_open(head, &s->m);
     s->mtp_n = LG_MTP_N;
+    lg_set_round_width(LG_MTP_N);
     return s;
 }
 void lgs_close(void *p) {
@@ -51,7 +54,11 @@ int  lgs_n_embd(void *p) { return ((struct lg_session *)p)->m.cfg.n_embd; }
 int  lgs_n_layer(void *p) { return ((struct lg_session *)p)->m.cfg.n_layer; }
 int  lgs_mtp_n(void) { return LG_MTP_N; }
 /* verify width of the session's rounds, clamped to what the backend runs (1..8) */
-void lgs_set_mtp_n(void *p, int n) { ((struct lg_session *)p)->mtp_n = n < 1 ? 1 : (n > 8 ? 8 : n); }
+void lgs_set_mtp_n(void *p, int n) {
+    struct lg_session *s = p;
+    s->mtp_n = n < 1 ? 1 : (n > 8 ? 8 : n);
+    lg_set_round_width(s->mtp_n);
+}
 void *lgs_model(void *p) { return &((struct lg_session *)p)->m; }
 void *lgs_kv(void *p) { return &((struct lg_session *)p)->kv; }
 void *lgs_head(void *p) { return ((struct lg_session *)p)->head; }
@@ -95,6 +102,15 @@ int lgs_rounds_host(void *p, int best, int pos, int g, int n_gen, int n_rounds, 
     struct lg_session *s = p;
     int nd = 0, na = 0, N = s->mtp_n, rounds = 0;
     if (N < 1 || N > 8) return -1;
+    lg_set_round_width(N);
+    if (mode == 3 && replay) {
+        /* the device applies the same override when it runs a round ahead of the calls below: draft for stream index i
+         * is replay[i], and the index of the first draft of a round is g = (its position) + (g - pos) */
+        lg_set_replay(&s->m, replay, n_replay);
+        lg_set_replay_origin(&s->m, g - pos, 1);
+    } else {
+        lg_set_replay_origin(&s->m, 0, 0);
+    }
     while (g < n_gen && (n_rounds <= 0 || rounds < n_rounds)) {
         rounds++;
         if (!mode) { best = model_forward_next(&s->m, &s->kv, best, pos++); out_toks[g++] = best; continue; }

@@ -133,3 +133,54 @@ def test_rounds_that_could_leave_the_cache_are_refused(lg):
         out = np.zeros(8, dtype=np.int32)
         toks = np.zeros(4, dtype=np.int32)
         assert g.L.lgs_spec(g.h, toks, 62, out) == -2                   # rows 62..65 of a 64-row cache
+
+
+def test_blocking_calls_wait_once_per_round(lg):
+    """mtp_draft runs the whole round ahead; the chained drafts and the verify that follow are answered from its record."""
+    s = synth_module()
+    tp, hp = model_files("mid")
+    with lg.Session(tp, hp, 1024, mtp_n=4) as g:
+        V = g.n_vocab
+        prompt = s.prompt_ids(20, V, seed=45)
+        plain, _ = g.generate(prompt, 60, 0)
+    rp = s.replay_drafts(plain, V, 0.7)
+    for mode in (1, 3):                                   # the head's own drafts; the head's cost with replayed drafts
+        with lg.Session(tp, hp, 1024, mtp_n=4) as g:
+            g.prefill(prompt[:-1], 0)
+            best = g.next(int(prompt[-1]), 19)
+            before = g.host_syncs()
+            toks, st = g.rounds_host(best, 20, 1, 60, 12, mode, rp if mode == 3 else None)
+            waits = g.host_syncs() - before
+            assert waits == 12, (mode, waits)              # one wait per round, not one per call (4 per round)
+            got = [best] + [int(t) for t in toks]
+            assert got == [int(t) for t in plain[:len(got)]], mode
+            if mode == 3:
+                assert st["n_accept"] > 0                   # the replayed drafts, not the random head's, were verified
+
+
+def test_caller_that_verifies_other_tokens_than_drafted_gets_its_own_answer(lg):
+    s = synth_module()
+    tp, hp = model_files("mid")
+    with lg.Session(tp, hp, 512, mtp_n=4) as g:
+        V = g.n_vocab
+        prompt = s.prompt_ids(16, V, seed=46)
+        plain, _ = g.generate(prompt, 24, 0)
+    with lg.Session(tp, hp, 512, mtp_n=4) as g:
+        g.prefill(prompt[:-1], 0)
+        best = g.next(int(prompt[-1]), 15)
+        assert best == plain[0]
+        d1 = g.draft(best, 16)                              # the whole round ran on the head's drafts
+        assert d1 >= 0
+        # the caller ignores them and verifies the true continuation with one wrong token in slot 2
+        toks = np.array([best, plain[1], (plain[2] + 1) % V, plain[3]], dtype=np.int32)
+        adv, out = g.spec(toks, 16)
+        assert adv == 2 and out[0] == plain[1] and out[1] == plain[2]
+        # a chained draft asked for another token than the recorded one still answers (synchronously), and the verify of
+        # the true continuation after it is right
+        best2, pos2 = int(out[1]), 18
+        d = g.draft(best2, pos2)
+        other = (d + 1) % V
+        assert g.draft_chain(other, pos2 + 1) >= 0
+        toks = np.array([best2, plain[3], plain[4], plain[5]], dtype=np.int32)
+        adv, out = g.spec(toks, pos2)
+        assert adv == 4 and [int(x) for x in out] == [int(x) for x in plain[3:7]]
