@@ -112,13 +112,21 @@ int   lg_bench_prefill_pass(struct model *m, int n, int classes);
  * session's first forward. */
 void  lg_set_attn_deep(int min_seq, int force_g);
 void  lg_engine_release(void);                       /* free all device state of the loaded model */
+/* Test entry: one CTA waits on a barrier nothing completes, gives up after `polls` polls (1 .. 2^20) and raises the status
+ * bit a production kernel's bounded wait would raise; returns the status word read back (1 = the wait ran out, as it must)
+ * and clears it.  The device context stays usable: no trap, no fault, no endless loop. */
+int   lg_debug_bounded_wait(struct model *m, int polls);
+/* Profiling builds only (-DLG_STAMPS): phase time stamps of the latest launches / clear them; -1 in the product build. */
+int   lg_debug_stamps(long long *out);
+int   lg_debug_clear_stamps(void);
 
 /* Kernel-level entry points (host buffers in, host buffers out) used by the parity tests.
  * Each returns 0 or a negative error. */
-/* Decode n_rows rows of k elements of ggml type (2 = q4_0, 12 = q4_K) on the device. */
+/* Decode n_rows rows of k elements of a ggml type (0 f32, 1 f16, 30 bf16, 2 q4_0, 8 q8_0, 11 q3_K, 12 q4_K, 13 q5_K,
+ * 14 q6_K) on the device; replaces dequantize_row / dequantize_into (src/quant.c:287-343) bit for bit. */
 int  lg_dequant_host(int type, const void *blocks, int n_rows, int k, float *out);
 /* y[tok][row] = W x[tok] for tok < M <= 8 through the tile-major repack, the 16-bit activation
- * panel and the tensor-core kernel; W is m rows of file-format blocks. */
+ * panel and the tensor-core kernel; W is m rows of file-format blocks (q4_0, q4_K, q8_0, q6_K, q5_K, q3_K). */
 int  lg_gemv_host(int type, const void *blocks, int m, int k, const float *x, int M, int kslices, float *y);
 /* The wide (prompt) matmul: out[tok][row] = W x[tok] for tok < n <= 256 at once, x rounded to f16,
  * weights expanded q4 -> f16 inside the kernel, tcgen05.mma with f32 accumulation.  With blocks_up

@@ -30,6 +30,7 @@ ABI_SYMBOLS = [
     "lg_forward_spec_n", "lg_set_replay", "lg_rounds_begin", "lg_rounds_enqueue", "lg_rounds_collect",
     "lg_set_round_width", "lg_set_replay_origin", "lg_host_syncs", "lg_weight_bytes", "lg_round_launches", "lg_last_hidden", "lg_kv_row", "lg_stream", "lg_engine_release",
     "lg_bench_matmul_pass", "lg_bench_prefill_pass", "lg_set_attn_deep", "lg_flash_decode_noalloc",
+    "lg_debug_bounded_wait", "lg_debug_stamps", "lg_debug_clear_stamps",
     "lg_dequant_host", "lg_gemv_host", "lg_flash_decode_host", "lg_flash_decode_cluster_host", "lg_prefill_matmul_host",
 ]
 
@@ -94,6 +95,7 @@ def load() -> C.CDLL:
     L.lg_bench_prefill_pass.argtypes = [C.c_void_p, C.c_int, C.c_int]; L.lg_bench_prefill_pass.restype = C.c_int
     L.lgs_rounds_host.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _i32p, C.c_int, C.c_void_p, C.c_int, _i32p]
     L.lgs_rounds_host.restype = C.c_int
+    L.lg_debug_bounded_wait.argtypes = [C.c_void_p, C.c_int]; L.lg_debug_bounded_wait.restype = C.c_int
     L.lgs_host_syncs.argtypes = [C.c_void_p]; L.lgs_host_syncs.restype = C.c_longlong
     L.lg_set_round_width.argtypes = [C.c_int]; L.lg_set_round_width.restype = None
     L.lg_set_replay_origin.argtypes = [C.c_void_p, C.c_int, C.c_int]; L.lg_set_replay_origin.restype = None

@@ -39,8 +39,8 @@ extern "C" int lg_dequant_host(int type, const void *blocks, int n_rows, int k, 
 }
 
 extern "C" int lg_gemv_host(int type, const void *blocks, int m, int k, const float *x, int M, int kslices, float *y) {
-    if (M < 1 || M > LG_MAXM || k % 64 || (type != GGML_TYPE_Q4_0 && type != GGML_TYPE_Q4_K)) return -1;
-    if (type == GGML_TYPE_Q4_K && k % 256) return -1;
+    if (M < 1 || M > LG_MAXM || k % 64 || (type != GGML_TYPE_Q4_0 && type != GGML_TYPE_Q4_K && !lg_fmt_is_i8(type))) return -1;
+    if (ggml_blck_size((uint32_t)type) == 256 && k % 256) return -1;
     Engine *e = scratch_engine();
     struct gguf_tensor t;
     memset(&t, 0, sizeof t);

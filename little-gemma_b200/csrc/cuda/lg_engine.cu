@@ -34,7 +34,7 @@ constexpr int RING_SPARE = 1024;             // ring rows beyond the window (cov
 constexpr int LOG_CAP = 1 << 20;
 
 struct WMat {
-    uint4 *wq = nullptr; uint2 *ws = nullptr; uint2 *wd = nullptr;
+    uint4 *wq = nullptr; uint2 *ws = nullptr; uint2 *wd = nullptr; uint4 *wm = nullptr;      // tiles, scales (see lg_kernels.cuh)
     int fmt = 0, m = 0, k = 0, nkp = 0, n_row_tiles = 0, ldo = 0;
     size_t file_bytes = 0;
 };
@@ -43,6 +43,9 @@ struct Panel { LgPanel p{}; };
 
 struct LayerW {
     WMat qkv, o, gateup, down, inp_gate, proj;
+    // q / k / v tensors of different formats cannot share one stacked matrix: they are kept apart, each multiplied on its
+    // own into its rows of the projection buffer (qkv then only carries the row stride)
+    std::vector<WMat> qkv_parts; std::vector<int> qkv_row0;
     float *attn_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr, *post_attn = nullptr, *ffn_norm = nullptr,
           *post_ffw = nullptr, *post_norm = nullptr;
     float out_scale = 1.0f;
@@ -125,6 +128,7 @@ struct Engine {
     struct { bool valid = false; int n = 0, pos = 0, adv = 0, toks[LG_MAXM] = {0}, out[LG_MAXM] = {0}; bool chained = false; } lazy;
     int replay_off = 0; bool lazy_replay = false;   // replay table index of a draft = its position + replay_off (lg_set_replay_origin)
     long long host_syncs = 0;                 // blocking device-to-host waits made by the reference-shaped calls
+    cudaEvent_t mid_event = nullptr;          // LG_MTP_PROFILE: recorded between the layers and the head of a forward
     int mm_launches = 0;                      // kernels in the captured matmul-only pass             // kernels in one captured round (lg_rounds_enqueue)
 };
 
@@ -204,11 +208,22 @@ WMat build_wmat(Engine *e, std::vector<const struct gguf_tensor *> parts, bool i
     if (g_soft_build && g_soft_failed) return W;
     for (auto t : parts) if (!t) LG_BUILD_FAIL("lg_b200: a weight tensor is missing from the file\n");
     const struct gguf_tensor *t0 = parts[0];
-    if (t0->type != GGML_TYPE_Q4_0 && t0->type != GGML_TYPE_Q4_K)
-        LG_BUILD_FAIL("lg_b200: weight %s has ggml type %u; this backend runs q4_0 and q4_K matrices\n", t0->name, t0->type);
-    W.fmt = t0->type == GGML_TYPE_Q4_0 ? LG_FMT_Q4_0 : LG_FMT_Q4_K;
+    // q4_0 / q4_K keep their 4 bits; q8_0, q6_K, q5_K, q3_K become i8 tiles.  Dense f32 / f16 / bf16 matrices are
+    // accepted for a DRAFT HEAD only (g_soft_build): there they are re-encoded as q8_0 blocks on the host -- a draft never
+    // changes the output, only how often it is accepted -- while a dense matrix in the target model is refused, because a
+    // lossy re-encoding there would move the logits.
+    uint32_t type = t0->type;
+    const bool dense = type == GGML_TYPE_F32 || type == GGML_TYPE_F16 || type == GGML_TYPE_BF16;
+    if (dense && !g_soft_build)
+        LG_BUILD_FAIL("lg_b200: weight %s is a dense %s matrix; this backend multiplies block-quantised matrices only\n", t0->name,
+                      type == GGML_TYPE_F32 ? "f32" : type == GGML_TYPE_F16 ? "f16" : "bf16");
+    if (!dense && type != GGML_TYPE_Q4_0 && type != GGML_TYPE_Q4_K && !lg_fmt_is_i8((int)type))
+        LG_BUILD_FAIL("lg_b200: weight %s has ggml type %u, which this backend has no kernel for\n", t0->name, type);
+    if (dense) type = GGML_TYPE_Q8_0;
+    W.fmt = type == GGML_TYPE_Q4_0 ? LG_FMT_Q4_0 : type == GGML_TYPE_Q4_K ? LG_FMT_Q4_K : type == GGML_TYPE_Q5_K ? LG_FMT_I8M : LG_FMT_I8;
     W.k = (int)t0->dims[0];
     if (W.k % 64) LG_BUILD_FAIL("lg_b200: %s: contraction length %d is not a multiple of 64\n", t0->name, W.k);
+    if (ggml_blck_size(type) == 256 && W.k % 256) LG_BUILD_FAIL("lg_b200: %s: contraction length %d is not a multiple of 256\n", t0->name, W.k);
     for (auto t : parts) {
         if (t->type != t0->type || (int)t->dims[0] != W.k) LG_BUILD_FAIL("lg_b200: cannot stack %s onto %s\n", t->name, t0->name);
         if (t != parts.back() && t->dims[1] % 16) LG_BUILD_FAIL("lg_b200: %s: %d rows is not a multiple of 16\n", t->name, (int)t->dims[1]);
@@ -219,23 +234,61 @@ WMat build_wmat(Engine *e, std::vector<const struct gguf_tensor *> parts, bool i
     W.nkp = W.k / 64;
     W.n_row_tiles = ((W.m + 15) / 16 + 3) / 4 * 4;          // padded with zero tiles: the kernels fetch groups of up to 4
     W.ldo = W.n_row_tiles * 16;
-    size_t tiles = (size_t)W.n_row_tiles * W.nkp;
-    W.wq = dalloc<uint4>(tiles * 32);
+    const size_t tiles = (size_t)W.n_row_tiles * W.nkp;
+    const size_t tq = lg_tile_bytes(W.fmt) / 16;             // uint4 per tile
+    W.wq = dalloc<uint4>(tiles * tq);
     W.ws = dalloc<uint2>(tiles * 8);
-    if (W.fmt == LG_FMT_Q4_K) W.wd = dalloc<uint2>(tiles * 8);
+    if (W.fmt != LG_FMT_Q4_0) W.wd = dalloc<uint2>(tiles * 8);
+    if (W.fmt == LG_FMT_I8M) W.wm = dalloc<uint4>(tiles * 8);
     const int nsb = W.k / 32;
+
+    // file bytes of one part on the device (dense parts: re-encoded as q8_0 first)
+    auto stage_part = [&](const struct gguf_tensor *t, uint8_t *dst, size_t bytes) {
+        if (!dense) { h2d_sync(dst, t->data, bytes); return; }
+        const int64_t n = (int64_t)t->dims[1] * W.k;
+        std::vector<float> f((size_t)W.k);
+        std::vector<uint8_t> enc(bytes);
+        const size_t esz = t->type == GGML_TYPE_F32 ? 4 : 2;
+        for (int64_t r = 0; r < (int64_t)t->dims[1]; r++) {
+            dequantize_into(t->type, (const uint8_t *)t->data + (size_t)r * W.k * esz, f.data(), W.k);
+            for (int b = 0; b < W.k / 32; b++) {
+                float amax = 0.0f;
+                for (int j = 0; j < 32; j++) amax = fmaxf(amax, fabsf(f[(size_t)b * 32 + j]));
+                const __half dh = __float2half_rn(amax / 127.0f);
+                const float d = __half2float(dh), inv = d > 0.0f ? 1.0f / d : 0.0f;
+                uint8_t *o = enc.data() + ((size_t)r * (W.k / 32) + b) * 34;
+                memcpy(o, &dh, 2);
+                for (int j = 0; j < 32; j++) {
+                    int q = (int)lrintf(f[(size_t)b * 32 + j] * inv);
+                    o[2 + j] = (uint8_t)(int8_t)(q < -127 ? -127 : q > 127 ? 127 : q);
+                }
+            }
+        }
+        (void)n;
+        h2d_sync(dst, enc.data(), bytes);
+    };
+    auto repack = [&](const uint8_t *a, const uint8_t *b, size_t toff, int rows, int rts) {
+        if (W.fmt >= LG_FMT_I8) {
+            const size_t threads = (size_t)rts * W.nkp * 64;
+            lg_repack_i8<<<(unsigned)((threads + 255) / 256), 256, 0, e->stream>>>(a, b, (int)type, W.wq + toff * tq, W.ws + toff * 8, W.wd + toff * 8,
+                                                                                  W.wm ? W.wm + toff * 8 : nullptr, rows, nsb, rts);
+        } else {
+            const size_t threads = (size_t)rts * W.nkp * 32;
+            const unsigned blocks = (unsigned)((threads + 255) / 256);
+            if (W.fmt == LG_FMT_Q4_0) lg_repack_q4_0<<<blocks, 256, 0, e->stream>>>(a, b, W.wq + toff * 32, W.ws + toff * 8, rows, nsb, rts);
+            else lg_repack_q4_K<<<blocks, 256, 0, e->stream>>>(a, b, W.wq + toff * 32, W.ws + toff * 8, W.wd + toff * 8, rows, nsb, rts);
+        }
+        LG_CHECK(cudaGetLastError());
+        LG_CHECK(cudaStreamSynchronize(e->stream));
+    };
     if (interleave) {
-        int rows = (int)parts[0]->dims[1];
-        size_t bytes = ggml_nbytes(t0->type, (int64_t)rows * W.k);
+        const int rows = (int)parts[0]->dims[1];
+        const size_t bytes = ggml_nbytes(type, (int64_t)rows * W.k);
         uint8_t *stage = nullptr;
         LG_CHECK(cudaMalloc(&stage, 2 * bytes));
-        h2d_sync(stage, parts[0]->data, bytes);
-        h2d_sync(stage + bytes, parts[1]->data, bytes);
-        size_t threads = (size_t)W.n_row_tiles * W.nkp * 32;
-        unsigned blocks = (unsigned)((threads + 255) / 256);
-        if (W.fmt == LG_FMT_Q4_0) lg_repack_q4_0<<<blocks, 256, 0, e->stream>>>(stage, stage + bytes, W.wq, W.ws, rows, nsb, W.n_row_tiles);
-        else lg_repack_q4_K<<<blocks, 256, 0, e->stream>>>(stage, stage + bytes, W.wq, W.ws, W.wd, rows, nsb, W.n_row_tiles);
-        LG_CHECK(cudaStreamSynchronize(e->stream));
+        stage_part(parts[0], stage, bytes);
+        stage_part(parts[1], stage + bytes, bytes);
+        repack(stage, stage + bytes, 0, rows, W.n_row_tiles);
         cudaFree(stage);
         W.file_bytes = 2 * bytes;
         e->weight_bytes += W.file_bytes;
@@ -243,20 +296,12 @@ WMat build_wmat(Engine *e, std::vector<const struct gguf_tensor *> parts, bool i
     }
     int row_off = 0;
     for (auto t : parts) {
-        int rows = (int)t->dims[1];
-        size_t bytes = ggml_nbytes(t->type, (int64_t)rows * W.k);
+        const int rows = (int)t->dims[1];
+        const size_t bytes = ggml_nbytes(type, (int64_t)rows * W.k);
         uint8_t *stage = nullptr;
         LG_CHECK(cudaMalloc(&stage, bytes));
-        h2d_sync(stage, t->data, bytes);
-        int rts = (rows + 15) / 16;
-        size_t threads = (size_t)rts * W.nkp * 32;
-        size_t toff = (size_t)(row_off / 16) * W.nkp;
-        unsigned blocks = (unsigned)((threads + 255) / 256);
-        if (W.fmt == LG_FMT_Q4_0)
-            lg_repack_q4_0<<<blocks, 256, 0, e->stream>>>(stage, nullptr, W.wq + toff * 32, W.ws + toff * 8, rows, nsb, rts);
-        else
-            lg_repack_q4_K<<<blocks, 256, 0, e->stream>>>(stage, nullptr, W.wq + toff * 32, W.ws + toff * 8, W.wd + toff * 8, rows, nsb, rts);
-        LG_CHECK(cudaStreamSynchronize(e->stream));
+        stage_part(t, stage, bytes);
+        repack(stage, nullptr, (size_t)(row_off / 16) * W.nkp, rows, (rows + 15) / 16);
         cudaFree(stage);
         row_off += rows;
         W.file_bytes += bytes;
@@ -264,7 +309,7 @@ WMat build_wmat(Engine *e, std::vector<const struct gguf_tensor *> parts, bool i
     e->weight_bytes += W.file_bytes;
     return W;
 }
-void free_wmat(WMat &W) { cudaFree(W.wq); cudaFree(W.ws); cudaFree(W.wd); W = WMat(); }
+void free_wmat(WMat &W) { cudaFree(W.wq); cudaFree(W.ws); cudaFree(W.wd); cudaFree(W.wm); W = WMat(); }
 
 // ------------------------------------------------------------------------------------------
 // launch helpers
@@ -274,7 +319,8 @@ int env_int(const char *name, int fb) { const char *v = getenv(name); return v &
 struct GemvPlan { int r, ks, gx, ns; size_t smem; };
 // dynamic shared memory of the small-M matmul: panel slice | ring | warp partials (| norm-tail sums) | mbarriers
 size_t gemv_smem_bytes(int np, int nkp_slice, int r, int fmt, int ns, bool normtail) {
-    const int stage = fmt == LG_FMT_Q4_K ? gemv_stage_bytes<LG_FMT_Q4_K>() : gemv_stage_bytes<LG_FMT_Q4_0>();
+    const int stage = fmt == LG_FMT_Q4_0 ? gemv_stage_bytes<LG_FMT_Q4_0>() : fmt == LG_FMT_Q4_K ? gemv_stage_bytes<LG_FMT_Q4_K>()
+                    : fmt == LG_FMT_I8 ? gemv_stage_bytes<LG_FMT_I8>() : gemv_stage_bytes<LG_FMT_I8M>();
     return (size_t)np * nkp_slice * 2 * (256 + 32) + 128 + (size_t)ns * stage + (size_t)LG_GEMV_CW * r * np * 64 * 4
          + (normtail ? (size_t)np * 128 * 4 : 0) + (2 * LG_GEMV_STAGES_MAX + 1) * 8 + 16;
 }
@@ -298,11 +344,14 @@ constexpr int MAX_KV_HEADS = 64;
 template <int R, int NP, int FMT, int EPI> void gemv_attr() {
     LG_CHECK(cudaFuncSetAttribute(lg_gemv_kernel<R, NP, FMT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMV_SMEM_MAX));
 }
-template <int R> void gemv_attr_r() {
-    gemv_attr<R, 1, LG_FMT_Q4_0, LG_EPI_STORE>(); gemv_attr<R, 1, LG_FMT_Q4_0, LG_EPI_HEAD>();
-    gemv_attr<R, 2, LG_FMT_Q4_0, LG_EPI_STORE>(); gemv_attr<R, 2, LG_FMT_Q4_0, LG_EPI_HEAD>();
-    gemv_attr<R, 1, LG_FMT_Q4_K, LG_EPI_STORE>(); gemv_attr<R, 1, LG_FMT_Q4_K, LG_EPI_HEAD>();
-    gemv_attr<R, 2, LG_FMT_Q4_K, LG_EPI_STORE>(); gemv_attr<R, 2, LG_FMT_Q4_K, LG_EPI_HEAD>();
+template <int R, int FMT> void gemv_attr_rf() {
+    gemv_attr<R, 1, FMT, LG_EPI_STORE>(); gemv_attr<R, 2, FMT, LG_EPI_STORE>();
+}
+template <int FMT> void gemv_attr_f() {
+    gemv_attr_rf<1, FMT>(); gemv_attr_rf<2, FMT>(); gemv_attr_rf<4, FMT>();
+    gemv_attr<4, 1, FMT, LG_EPI_HEAD>(); gemv_attr<4, 2, FMT, LG_EPI_HEAD>();
+    gemv_attr<4, 1, FMT, LG_EPI_GEGLU>(); gemv_attr<4, 2, FMT, LG_EPI_GEGLU>();
+    gemv_attr<4, 1, FMT, LG_EPI_GEGLU | LG_EPI_POST>(); gemv_attr<4, 2, FMT, LG_EPI_GEGLU | LG_EPI_POST>();
 }
 // Opt every kernel into large dynamic shared memory once, outside any stream capture.
 template <int NT, int FMT, int EPI> void pf_attr() {
@@ -324,11 +373,7 @@ void set_kernel_attributes() {
     if (dev < 0 || dev >= 64) { fprintf(stderr, "lg_b200: device ordinal %d out of range\n", dev); exit(1); }
     if (done[dev]) return;
     done[dev] = true;
-    gemv_attr_r<1>(); gemv_attr_r<2>(); gemv_attr_r<4>();
-    gemv_attr<4, 1, LG_FMT_Q4_0, LG_EPI_GEGLU>(); gemv_attr<4, 2, LG_FMT_Q4_0, LG_EPI_GEGLU>();
-    gemv_attr<4, 1, LG_FMT_Q4_K, LG_EPI_GEGLU>(); gemv_attr<4, 2, LG_FMT_Q4_K, LG_EPI_GEGLU>();
-    gemv_attr<4, 1, LG_FMT_Q4_0, LG_EPI_GEGLU | LG_EPI_POST>(); gemv_attr<4, 2, LG_FMT_Q4_0, LG_EPI_GEGLU | LG_EPI_POST>();
-    gemv_attr<4, 1, LG_FMT_Q4_K, LG_EPI_GEGLU | LG_EPI_POST>(); gemv_attr<4, 2, LG_FMT_Q4_K, LG_EPI_GEGLU | LG_EPI_POST>();
+    gemv_attr_f<LG_FMT_Q4_0>(); gemv_attr_f<LG_FMT_Q4_K>(); gemv_attr_f<LG_FMT_I8>(); gemv_attr_f<LG_FMT_I8M>();
     gemv_attr<2, 1, LG_FMT_Q4_0, LG_EPI_NORMTAIL>(); gemv_attr<2, 2, LG_FMT_Q4_0, LG_EPI_NORMTAIL>();
     gemv_attr<2, 1, LG_FMT_Q4_K, LG_EPI_NORMTAIL>(); gemv_attr<2, 2, LG_FMT_Q4_K, LG_EPI_NORMTAIL>();
     LG_CHECK(cudaFuncSetAttribute(lg_attn_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
@@ -405,12 +450,14 @@ void launch_gemv_t(Engine *e, const LgGemvArgs &a, const GemvPlan &p) {
     dim3 grid(p.gx, p.ks);
     launch_k(e, (lg_gemv_kernel<R, NP, FMT, EPI>), dim3(grid), dim3(LG_GEMV_THREADS), p.smem, a);
 }
-template <int R, int NP>
-void launch_gemv_rn(Engine *e, const LgGemvArgs &a, const GemvPlan &p, int fmt, int epi) {
-    if (fmt == LG_FMT_Q4_0) {
-        if (epi == LG_EPI_HEAD) launch_gemv_t<R, NP, LG_FMT_Q4_0, LG_EPI_HEAD>(e, a, p); else launch_gemv_t<R, NP, LG_FMT_Q4_0, LG_EPI_STORE>(e, a, p);
-    } else {
-        if (epi == LG_EPI_HEAD) launch_gemv_t<R, NP, LG_FMT_Q4_K, LG_EPI_HEAD>(e, a, p); else launch_gemv_t<R, NP, LG_FMT_Q4_K, LG_EPI_STORE>(e, a, p);
+// dispatch on the weight format (a template parameter of the kernel)
+template <int R, int NP, int EPI>
+void launch_gemv_f(Engine *e, const LgGemvArgs &a, const GemvPlan &p, int fmt) {
+    switch (fmt) {
+    case LG_FMT_Q4_0: launch_gemv_t<R, NP, LG_FMT_Q4_0, EPI>(e, a, p); break;
+    case LG_FMT_Q4_K: launch_gemv_t<R, NP, LG_FMT_Q4_K, EPI>(e, a, p); break;
+    case LG_FMT_I8:   launch_gemv_t<R, NP, LG_FMT_I8, EPI>(e, a, p); break;
+    default:          launch_gemv_t<R, NP, LG_FMT_I8M, EPI>(e, a, p); break;
     }
 }
 
@@ -418,6 +465,7 @@ struct GemvExtra {
     float softcap = 0.0f; float *logits = nullptr; float *amax_val = nullptr; int *amax_idx = nullptr;
     const LgPanel *outp = nullptr;            // GeGLU / NORMTAIL epilogue target
     int *ks_out = nullptr, *gx_out = nullptr;
+    int ldo = 0;                              // row stride of the output when it is not the matrix's own padded row count
     // NORMTAIL epilogue
     float *xres = nullptr; int ldx = 0, n_cols = 0; const float *add_w = nullptr, *norm_w = nullptr; float out_scale = 1.0f, eps = 0.0f;
     float *ssq1 = nullptr, *ssq2 = nullptr; int *gbar = nullptr;
@@ -431,7 +479,23 @@ bool normtail_ok(const Engine *e, const WMat &W, int np) {
     static const int on = env_int("LG_NORMTAIL", 1);
     const int groups = W.n_row_tiles / 2;
     size_t smem = gemv_smem_bytes(np, W.nkp + 1, 2, W.fmt, LG_GEMV_STAGES, true);
-    return on && W.n_row_tiles % 2 == 0 && groups <= 2 * e->sm_count && smem <= 100 * 1024;
+    if (!on || W.fmt > LG_FMT_Q4_K || W.n_row_tiles % 2 || smem > 100 * 1024) return false;
+    // The epilogue's grid-wide barrier needs every CTA of the grid resident at once: ask the device how many CTAs of this
+    // kernel (with its registers and this much shared memory) an SM holds instead of trusting the shared-memory estimate.
+    static std::map<long long, int> per_sm;
+    const long long key = ((long long)np << 40) | ((long long)W.fmt << 32) | (long long)smem;
+    auto it = per_sm.find(key);
+    if (it == per_sm.end()) {
+        int n = 0;
+        cudaError_t rc;
+        if (np == 1) rc = W.fmt == LG_FMT_Q4_0 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, lg_gemv_kernel<2, 1, LG_FMT_Q4_0, LG_EPI_NORMTAIL>, LG_GEMV_THREADS, smem)
+                                                : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, lg_gemv_kernel<2, 1, LG_FMT_Q4_K, LG_EPI_NORMTAIL>, LG_GEMV_THREADS, smem);
+        else         rc = W.fmt == LG_FMT_Q4_0 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, lg_gemv_kernel<2, 2, LG_FMT_Q4_0, LG_EPI_NORMTAIL>, LG_GEMV_THREADS, smem)
+                                                : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, lg_gemv_kernel<2, 2, LG_FMT_Q4_K, LG_EPI_NORMTAIL>, LG_GEMV_THREADS, smem);
+        if (rc != cudaSuccess) { cudaGetLastError(); n = 0; }
+        it = per_sm.emplace(key, n).first;
+    }
+    return groups <= it->second * e->sm_count;
 }
 
 // out[ks][tok][ldo] partial sums (EPI_STORE, optional tail), the GeGLU epilogue, or the head epilogue.
@@ -444,8 +508,8 @@ void launch_gemv(Engine *e, const WMat &W, const LgPanel &X, int M, float *out, 
         gemv_pick_stages(p, np, W.nkp + 1, W.fmt, true);
     }
     LgGemvArgs a{};
-    a.wq = W.wq; a.ws = W.ws; a.wd = W.wd; a.x = X; a.nkp = W.nkp; a.n_row_tiles = W.n_row_tiles; a.kslices = p.ks;
-    a.out = out; a.ldo = W.ldo; a.M = M; a.softcap = x.softcap; a.logits = x.logits; a.n_valid_rows = W.m;
+    a.wq = W.wq; a.ws = W.ws; a.wd = W.wd; a.wm = W.wm; a.x = X; a.nkp = W.nkp; a.n_row_tiles = W.n_row_tiles; a.kslices = p.ks;
+    a.out = out; a.ldo = x.ldo ? x.ldo : W.ldo; a.M = M; a.softcap = x.softcap; a.logits = x.logits; a.n_valid_rows = W.m;
     a.amax_val = x.amax_val; a.amax_idx = x.amax_idx; a.err = e->err;
     if (x.outp) a.outp = *x.outp;
     a.xres = x.xres; a.ldx = x.ldx; a.n_cols = x.n_cols; a.add_w = x.add_w; a.norm_w = x.norm_w; a.out_scale = x.out_scale; a.eps = x.eps;
@@ -465,18 +529,20 @@ void launch_gemv(Engine *e, const WMat &W, const LgPanel &X, int M, float *out, 
         if (W.n_row_tiles % 4) { fprintf(stderr, "lg_b200: GeGLU matmul needs a multiple of 32 outputs\n"); exit(1); }
         constexpr int GP = LG_EPI_GEGLU | LG_EPI_POST;
         if (a.post_ss) {     // the panel's norm was deferred: the variant that rescales by 1/rms
-            if (np == 1) { if (W.fmt == LG_FMT_Q4_0) launch_gemv_t<4, 1, LG_FMT_Q4_0, GP>(e, a, p); else launch_gemv_t<4, 1, LG_FMT_Q4_K, GP>(e, a, p); }
-            else         { if (W.fmt == LG_FMT_Q4_0) launch_gemv_t<4, 2, LG_FMT_Q4_0, GP>(e, a, p); else launch_gemv_t<4, 2, LG_FMT_Q4_K, GP>(e, a, p); }
+            if (np == 1) launch_gemv_f<4, 1, GP>(e, a, p, W.fmt); else launch_gemv_f<4, 2, GP>(e, a, p, W.fmt);
             return;
         }
-        if (np == 1) { if (W.fmt == LG_FMT_Q4_0) launch_gemv_t<4, 1, LG_FMT_Q4_0, LG_EPI_GEGLU>(e, a, p); else launch_gemv_t<4, 1, LG_FMT_Q4_K, LG_EPI_GEGLU>(e, a, p); }
-        else         { if (W.fmt == LG_FMT_Q4_0) launch_gemv_t<4, 2, LG_FMT_Q4_0, LG_EPI_GEGLU>(e, a, p); else launch_gemv_t<4, 2, LG_FMT_Q4_K, LG_EPI_GEGLU>(e, a, p); }
+        if (np == 1) launch_gemv_f<4, 1, LG_EPI_GEGLU>(e, a, p, W.fmt); else launch_gemv_f<4, 2, LG_EPI_GEGLU>(e, a, p, W.fmt);
+        return;
+    }
+    if (epi == LG_EPI_HEAD) {
+        if (np == 1) launch_gemv_f<4, 1, LG_EPI_HEAD>(e, a, p, W.fmt); else launch_gemv_f<4, 2, LG_EPI_HEAD>(e, a, p, W.fmt);
         return;
     }
     if (np == 1) {
-        if (p.r == 4) launch_gemv_rn<4, 1>(e, a, p, W.fmt, epi); else if (p.r == 2) launch_gemv_rn<2, 1>(e, a, p, W.fmt, epi); else launch_gemv_rn<1, 1>(e, a, p, W.fmt, epi);
+        if (p.r == 4) launch_gemv_f<4, 1, LG_EPI_STORE>(e, a, p, W.fmt); else if (p.r == 2) launch_gemv_f<2, 1, LG_EPI_STORE>(e, a, p, W.fmt); else launch_gemv_f<1, 1, LG_EPI_STORE>(e, a, p, W.fmt);
     } else {
-        if (p.r == 4) launch_gemv_rn<4, 2>(e, a, p, W.fmt, epi); else if (p.r == 2) launch_gemv_rn<2, 2>(e, a, p, W.fmt, epi); else launch_gemv_rn<1, 2>(e, a, p, W.fmt, epi);
+        if (p.r == 4) launch_gemv_f<4, 2, LG_EPI_STORE>(e, a, p, W.fmt); else if (p.r == 2) launch_gemv_f<2, 2, LG_EPI_STORE>(e, a, p, W.fmt); else launch_gemv_f<1, 2, LG_EPI_STORE>(e, a, p, W.fmt);
     }
 }
 
@@ -806,7 +872,19 @@ Engine *engine_for(const struct model *m) {
             w.has_v = v != nullptr;
             if (v) parts.push_back(v);
         }
-        w.qkv = build_wmat(e, parts);
+        bool one_type = true;
+        for (auto t : parts) one_type = one_type && t && parts[0] && t->type == parts[0]->type;
+        if (one_type) {
+            w.qkv = build_wmat(e, parts);
+        } else {
+            int row0 = 0;
+            for (auto t : parts) {
+                w.qkv_parts.push_back(build_wmat(e, {t}));
+                w.qkv_row0.push_back(row0);
+                row0 += t ? (int)t->dims[1] : 0;
+            }
+            w.qkv.ldo = (row0 + 63) / 64 * 64 + 64;          // room for the last part's zero padding rows
+        }
         w.o = build_wmat(e, {find_t(g, l, "attn_output.weight")});
         w.gateup = build_wmat(e, {find_t(g, l, "ffn_gate.weight"), find_t(g, l, "ffn_up.weight")}, true);
         w.down = build_wmat(e, {find_t(g, l, "ffn_down.weight")});
@@ -891,6 +969,7 @@ void engine_free(Engine *e) {
     draft_free(e->draft);
     for (auto &w : e->L) {
         free_wmat(w.qkv); free_wmat(w.o); free_wmat(w.gateup); free_wmat(w.down); free_wmat(w.inp_gate); free_wmat(w.proj);
+        for (auto &pw : w.qkv_parts) free_wmat(pw);
         cudaFree(w.attn_norm); cudaFree(w.q_norm); cudaFree(w.k_norm); cudaFree(w.post_attn); cudaFree(w.ffn_norm);
         cudaFree(w.post_ffw); cudaFree(w.post_norm);
     }
@@ -946,7 +1025,7 @@ void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags, int 
     const int *d_toks = e->st->toks, *d_pos = &e->st->pos;
 
     if ((only & C_MISC) && !(flags & F_NOEMBED))
-        launch_k(e, lg_embed_rows, dim3(M), dim3(256), 0, e->head.wq, e->head.ws, e->head.wd, e->head.fmt, e->head.nkp, e->head.m, d_toks,
+        launch_k(e, lg_embed_rows, dim3(M), dim3(256), 0, e->head.wq, e->head.ws, e->head.wd, e->head.wm, e->head.fmt, e->head.nkp, e->head.m, d_toks,
                  sqrtf((float)ne), e->x, ne);
     const int total = ple * nl;
     if (e->has_ple) {
@@ -966,7 +1045,12 @@ void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags, int 
     for (int l = 0; l < nl; l++) {
         LayerW &w = e->L[l];
         const int hd = w.hd, src = w.src;
-        if (only & C_QKV) launch_gemv(e, w.qkv, e->p_ne, M, e->qkv, LG_EPI_STORE, 1);
+        if ((only & C_QKV) && w.qkv_parts.empty()) launch_gemv(e, w.qkv, e->p_ne, M, e->qkv, LG_EPI_STORE, 1);
+        if ((only & C_QKV) && !w.qkv_parts.empty())
+            for (size_t i = 0; i < w.qkv_parts.size(); i++) {     // in row order: a part's zero padding rows are overwritten by the next part
+                GemvExtra xp; xp.ldo = w.qkv.ldo;
+                launch_gemv(e, w.qkv_parts[i], e->p_ne, M, e->qkv + w.qkv_row0[i], LG_EPI_STORE, 1, xp);
+            }
         LgAttnArgs aa{};
         aa.qkv = e->qkv; aa.ld = w.qkv.ldo; aa.q_ready = 0; aa.has_v = w.has_v; aa.owns_kv = w.owns_kv;
         aa.q_norm = w.q_norm; aa.k_norm = w.k_norm; aa.eps = c->rms_eps;
@@ -1034,6 +1118,7 @@ void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags, int 
                         next_w, next_p, y, ne);
         }
     }
+    if (e->mid_event) LG_CHECK(cudaEventRecord(e->mid_event, e->stream));
     if (flags & F_HEAD) {
         float *lg = nullptr;
         if (flags & F_LOGITS) {
@@ -1111,7 +1196,7 @@ void enqueue_prefill_block(Engine *e, const struct kvcache *kv, int n, int only 
     const int ne = c->n_embd, H = c->n_head, nl = c->n_layer;
     PrefillBuf &b = e->pf;
     if (only & C_MISC) {
-        launch_k(e, lg_embed_rows, dim3(n), dim3(256), 0, e->head.wq, e->head.ws, e->head.wd, e->head.fmt, e->head.nkp, e->head.m,
+        launch_k(e, lg_embed_rows, dim3(n), dim3(256), 0, e->head.wq, e->head.ws, e->head.wd, e->head.wm, e->head.fmt, e->head.nkp, e->head.m,
                  (const int *)b.toks, sqrtf((float)ne), b.x, ne);
         if (media) launch_k(e, lg_inject_rows, dim3(n), dim3(256), 0, b.x, ne, (const float *)b.rows, (const int *)b.ridx, ne);
         launch_k(e, lg_rope_table_kernel, dim3((n + 7) / 8), dim3(256), 0, (const int *)b.pos, n, e->hd_local, c->rope_freq_base_swa, (const float *)nullptr, b.rope_local);
@@ -1197,7 +1282,12 @@ void enqueue_prefill_block(Engine *e, const struct kvcache *kv, int n, int only 
 bool prefill_wide_ok(const Engine *e) {
     static const int on = env_int("LG_PREFILL_WIDE", 1);
     if (!on) return false;
-    for (auto &w : e->L) if (w.o.k != e->m->cfg.n_head * w.hd || w.down.k != w.nff) return false;
+    for (auto &w : e->L) {
+        if (w.o.k != e->m->cfg.n_head * w.hd || w.down.k != w.nff || !w.qkv_parts.empty()) return false;
+        // the wide matmul expands q4 tiles; layers in another format take the 8-token path
+        for (const WMat *W : {&w.qkv, &w.o, &w.gateup, &w.down, &w.inp_gate, &w.proj}) if (W->wq && W->fmt > LG_FMT_Q4_K) return false;
+    }
+    if (e->has_ple && e->pmp.fmt > LG_FMT_Q4_K) return false;
     if (e->has_ple && (e->m->cfg.n_embd_per_layer % 64 || e->m->cfg.n_embd_per_layer > 1024 || e->pmp.ldo != e->m->cfg.n_embd_per_layer * e->m->cfg.n_layer))
         return false;
     return true;
@@ -1222,6 +1312,30 @@ void run_forward(Engine *e, const struct kvcache *kv, int M, int flags) {
         it = e->graphs.emplace(key, exec).first;
     }
     LG_CHECK(cudaGraphLaunch(it->second, e->stream));
+}
+
+// LG_MTP_PROFILE (any value, as in the reference: src/cuda/mtp-kernel.cuh:44-61,99-101): the verify forward runs
+// un-captured with an event between its two halves, and every 50 calls the mean time of the layers and of the head is
+// printed in the reference's words.  The whole-round path behind mtp_draft_device is bypassed (each call synchronous).
+void run_forward_profiled(Engine *e, const struct kvcache *kv, int M, int flags) {
+    static cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
+    static double tl = 0, th = 0;
+    static int calls = 0;
+    bind_kv(e, kv);
+    if (!ev[0]) for (auto &x : ev) LG_CHECK(cudaEventCreate(&x));
+    if ((flags & F_LOGITS) && !e->logits) e->logits = dalloc<float>((size_t)LG_MAXM * e->head.ldo);
+    e->mid_event = ev[1];
+    LG_CHECK(cudaEventRecord(ev[0], e->stream));
+    enqueue_forward(e, kv, M, flags);
+    e->mid_event = nullptr;
+    LG_CHECK(cudaEventRecord(ev[2], e->stream));
+    LG_CHECK(cudaEventSynchronize(ev[2]));
+    float a = 0, b = 0;
+    LG_CHECK(cudaEventElapsedTime(&a, ev[0], ev[1]));
+    LG_CHECK(cudaEventElapsedTime(&b, ev[1], ev[2]));
+    tl += a; th += b;
+    if (++calls % 50 == 0)
+        fprintf(stderr, "verify profile over %d: layers %.3fms ea, head %.3fms ea\n", calls, tl / calls, th / calls);
 }
 
 void upload_round(Engine *e, const int *toks, int n, int pos) {
@@ -1307,7 +1421,7 @@ void enqueue_draft(Engine *e, DraftW *d, const struct kvcache *kv, int slot, boo
     const struct model *m = e->m;
     const struct config *c = &m->cfg;
     const int ni = d->ni, nb = d->nb;
-    launch_k(e, lg_embed_rows, dim3(1), dim3(256), 0, e->head.wq, e->head.ws, e->head.wd, e->head.fmt, e->head.nkp, e->head.m,
+    launch_k(e, lg_embed_rows, dim3(1), dim3(256), 0, e->head.wq, e->head.ws, e->head.wd, e->head.wm, e->head.fmt, e->head.nkp, e->head.m,
                                     e->st->toks + (slot - 1), sqrtf((float)nb), d->cat, 2 * nb);
     if (chained) {
         // h_prev = post(x): x still holds the previous draft's normed hidden, p_ni its panel
@@ -1416,7 +1530,9 @@ int spec_n(struct model *m, struct kvcache *kv, int n, const int *toks, int pos,
     }
     upload_round(e, toks, n, pos);
     int flags = F_HEAD | F_ACCEPT | (model_pick ? F_LOGITS : 0);
-    run_forward(e, kv, n, flags);
+    static const int profile = getenv("LG_MTP_PROFILE") != nullptr;
+    if (profile && n > 1) run_forward_profiled(e, kv, n, flags);
+    else run_forward(e, kv, n, flags);
     const struct config *c = &m->cfg;
     if (model_pick) {
         if (!e->pick_rows) e->pick_rows = (float *)malloc((size_t)LG_MAXM * c->n_vocab * sizeof(float));
@@ -1624,7 +1740,7 @@ static void prefill_impl(struct model *m, struct kvcache *kv, const float *rows,
         for (int j = 0; j < b; j++) blk_media |= ids[i + j] < 0;
         if (blk_media) {
             // token embeddings first, then the media rows over them; the forward then starts from x as it stands
-            launch_k(e, lg_embed_rows, dim3(b), dim3(256), 0, e->head.wq, e->head.ws, e->head.wd, e->head.fmt, e->head.nkp, e->head.m,
+            launch_k(e, lg_embed_rows, dim3(b), dim3(256), 0, e->head.wq, e->head.ws, e->head.wd, e->head.wm, e->head.fmt, e->head.nkp, e->head.m,
                      (const int *)e->st->toks, sqrtf((float)ne), e->x, ne);
             for (int j = 0; j < b; j++)
                 if (ids[i + j] < 0)
@@ -1664,7 +1780,7 @@ int mtp_draft_device(struct mtp *t, const struct model *m, const struct kvcache 
     DraftW *d = draft_for(e, t, kv);
     if (!d) return -1;
     LgRoundState *h = e->st_host;
-    static const int lazy_on = env_int("LG_LAZY_ROUND", 1);
+    static const int lazy_on = env_int("LG_LAZY_ROUND", 1) && getenv("LG_MTP_PROFILE") == nullptr;
     const int n = g_round_width;
     e->lazy.valid = false;
     if (lazy_on && n >= 2 && n <= LG_MAXM && !model_pick && pos >= 0 && (long long)pos + n <= kv->max_seq) {
@@ -1902,6 +2018,20 @@ int lg_debug_clear_stamps(void) {
 #else
     return -1;
 #endif
+}
+
+// Test entry for the bounded waits: one CTA waits on an mbarrier that nothing will ever complete, with a limit of
+// `polls` polls, gives up, raises the status bit a real kernel would raise, and returns.  The call hands back the status
+// word it read (LG_ERR_MBAR_TIMEOUT = 1 expected) and clears it, so the engine stays usable.
+int lg_debug_bounded_wait(struct model *m, int polls) {
+    Engine *e = engine_for(m);
+    if (polls < 1 || polls > (1 << 20)) return -1;
+    lg_wait_probe_kernel<<<1, 32, 0, e->stream>>>(e->err, polls);
+    int err = 0;
+    LG_CHECK(cudaMemcpyAsync(&err, e->err, sizeof(int), cudaMemcpyDeviceToHost, e->stream));
+    LG_CHECK(cudaMemsetAsync(e->err, 0, sizeof(int), e->stream));
+    LG_CHECK(cudaStreamSynchronize(e->stream));
+    return err;
 }
 
 void *lg_stream(struct model *m) { return (void *)engine_for(m)->stream; }

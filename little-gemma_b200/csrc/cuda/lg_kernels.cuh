@@ -26,6 +26,7 @@
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
 #include <stdint.h>
+#include "lg_formats.h"
 
 #define LG_MAXM 8              // widest verify block
 #define LG_QMAX 32639.0f       // 127*256 + 127: keeps both bytes of the split in [-128,127]
@@ -172,6 +173,22 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
     return false;
 }
 
+// Bounded-wait probe: waits on an mbarrier nobody completes, for at most `polls` polls, then reports like the kernels do.
+__global__ void lg_wait_probe_kernel(int *err, int polls) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        bool done = false;
+        for (int it = 0; it < polls && !done; ++it) {
+            uint32_t ok;
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                         : "=r"(ok) : "r"(smem_u32(&bar)), "r"(0u) : "memory");
+            done = ok != 0;
+        }
+        if (!done) atomicOr(err, LG_ERR_MBAR_TIMEOUT);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // weight repack (runs once per tensor at load)
 // ---------------------------------------------------------------------------------------------
@@ -254,6 +271,59 @@ __global__ void lg_repack_q4_K(const uint8_t *__restrict__ src, const uint8_t *_
     }
 }
 
+// File blocks of q8_0 / q6_K / q5_K / q3_K [m][k/blk][bytes] -> i8 tiles.  One thread per (tile, lane, sub-block): its 16
+// bytes are {row g, row g+8} x {columns 4t..4t+3, 16+4t..16+4t+3} of that sub-block = the A operands of the two k16 MMAs.
+// wq: [tile][2 sub-blocks][32 lanes] uint4;  ws: f16 d {row g sb0, row g+8 sb0, row g sb1, row g+8 sb1} per (tile, g);
+// wd: integer scales, .x = row g {sb0 cols 0-15, sb0 16-31, sb1 0-15, sb1 16-31}, .y = row g+8;  wm: f32 dmin*m (q5_K).
+// With src_b: the two tensors woven 8 rows at a time, as in lg_repack_q4_0.
+__global__ void lg_repack_i8(const uint8_t *__restrict__ src, const uint8_t *__restrict__ src_b, int type,
+                             uint4 *__restrict__ wq, uint2 *__restrict__ ws, uint2 *__restrict__ wd, uint4 *__restrict__ wm,
+                             int m, int nsb, int n_row_tiles) {
+    const int nkp = nsb >> 1;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t total = (size_t)n_row_tiles * nkp * 64;
+    if (idx >= total) return;
+    const int lane = idx & 31, sb_in = (idx >> 5) & 1;
+    const size_t tile = idx >> 6;
+    const int kp = (int)(tile % nkp), rt = (int)(tile / nkp);
+    const int g = lane >> 2, t = lane & 3;
+    const int blk = lg_fmt_block(type), bytes = lg_fmt_bytes(type), k = nsb * 32;
+    uint32_t w[4] = {0, 0, 0, 0};
+    uint32_t dsc[2] = {0, 0}, isc[2] = {0, 0}; float mo[2] = {0.0f, 0.0f};
+    #pragma unroll
+    for (int hi8 = 0; hi8 < 2; hi8++) {
+        const int row = src_b ? rt * 8 + g : rt * 16 + g + hi8 * 8;
+        if (row >= m) continue;
+        const uint8_t *base = ((src_b && hi8) ? src_b : src) + (size_t)row * (k / blk) * bytes;
+        #pragma unroll
+        for (int half = 0; half < 2; half++) {
+            uint32_t word = 0;
+            #pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int col = kp * 64 + sb_in * 32 + half * 16 + 4 * t + i;
+                int q, sc, mi; uint16_t db, mb;
+                lg_fmt_elem(type, base + (size_t)(col / blk) * bytes, col % blk, &q, &sc, &db, &mb, &mi);
+                word |= (uint32_t)(uint8_t)(int8_t)q << (8 * i);
+                if (t == 0 && i == 0) {
+                    dsc[hi8] = db;
+                    isc[hi8] |= (uint32_t)(uint8_t)(int8_t)sc << (8 * half);
+                    mo[hi8] = __fmul_rn(__half2float(__ushort_as_half(mb)), (float)mi);
+                }
+            }
+            w[half * 2 + hi8] = word;
+        }
+    }
+    wq[idx] = make_uint4(w[0], w[1], w[2], w[3]);
+    if (t == 0) {
+        // two threads (sub-block 0 and 1) share each scale record: each writes its half
+        uint16_t *dp = (uint16_t *)(ws + tile * 8 + g);
+        dp[sb_in * 2 + 0] = (uint16_t)dsc[0]; dp[sb_in * 2 + 1] = (uint16_t)dsc[1];
+        uint16_t *ip = (uint16_t *)(wd + tile * 8 + g);
+        ip[0 * 2 + sb_in] = (uint16_t)isc[0]; ip[1 * 2 + sb_in] = (uint16_t)isc[1];
+        if (wm) { float *mp = (float *)(wm + tile * 8 + g); mp[sb_in * 2 + 0] = mo[0]; mp[sb_in * 2 + 1] = mo[1]; }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // exact dequantisation of file-format rows (embedding gather; also the bit-exactness gate)
 // ---------------------------------------------------------------------------------------------
@@ -286,6 +356,19 @@ __global__ void lg_dequant_rows(const uint8_t *__restrict__ src, int type, int k
             float v = __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)nib), __fmul_rn(dmin, (float)mn));
             o[e] = __fmul_rn(v, scale);
         }
+    } else if (lg_fmt_is_i8(type)) {
+        const int blk = lg_fmt_block(type), bytes = lg_fmt_bytes(type);
+        const uint8_t *base = src + (size_t)row * (k / blk) * bytes;
+        for (int e = threadIdx.x; e < k; e += blockDim.x) {
+            int q, sc, mi; uint16_t db, mb;
+            lg_fmt_elem(type, base + (size_t)(e / blk) * bytes, e % blk, &q, &sc, &db, &mb, &mi);
+            float v = __fmul_rn(__fmul_rn(__half2float(__ushort_as_half(db)), (float)sc), (float)q);
+            if (type == LG_T_Q5_K) v = __fsub_rn(v, __fmul_rn(__half2float(__ushort_as_half(mb)), (float)mi));
+            o[e] = __fmul_rn(v, scale);
+        }
+    } else if (type == 30) {
+        const unsigned short *h = (const unsigned short *)src + (size_t)row * k;      // bf16: the upper half of an f32
+        for (int e = threadIdx.x; e < k; e += blockDim.x) o[e] = __fmul_rn(__uint_as_float((uint32_t)h[e] << 16), scale);
     } else if (type == 1) {
         const __half *h = (const __half *)src + (size_t)row * k;
         for (int e = threadIdx.x; e < k; e += blockDim.x) o[e] = __fmul_rn(__half2float(h[e]), scale);
@@ -317,7 +400,8 @@ struct LgNormArgs {
 struct LgGemvArgs {
     const uint4 *wq;           // tile-major nibbles
     const uint2 *ws;           // q4_0: 4 f16 scales per (tile, g); q4_K: 4 x (sc|mn<<8)
-    const uint2 *wd;           // q4_K only: {d,dmin} for rows g and g+8 per (tile, g)
+    const uint2 *wd;           // q4_K: {d,dmin} for rows g and g+8 per (tile, g); i8 tiles: 2 x 4 integer scales (rows g, g+8; 16-column groups)
+    const uint4 *wm;           // LG_FMT_I8M: f32 offsets {row g sb0, row g+8 sb0, row g sb1, row g+8 sb1} per (tile, g)
     LgPanel x;
     int nkp;                   // 64-column tile count along k (whole matrix)
     int n_row_tiles;
@@ -348,7 +432,15 @@ struct LgGemvArgs {
     int ns;                    // ring stages (LG_GEMV_STAGES .. LG_GEMV_STAGES_MAX)
 };
 
-enum { LG_FMT_Q4_0 = 0, LG_FMT_Q4_K = 1 };
+// Weight formats of the tile-major copies.  The two q4 formats keep 4 bits per weight.  Every other block format the
+// reference reads (q8_0, q6_K, q5_K, q3_K) is expanded at load to "i8 tiles": one signed byte per weight (q8_0: the file's;
+// the K formats: q - 32, q, q - 4.. as their decode defines them), the block scale d as f16 per (row, 32 columns), an
+// integer scale per (row, 16 columns), and for q5_K (LG_FMT_I8M) the f32 offset dmin * m per (row, 32 columns); the decode
+// (d * s) * q - m is the file's, bit for bit.  More bytes than the file for the K formats (1.125 B per weight against
+// 0.82 for q6_K): the price of one kernel for all of them.
+enum { LG_FMT_Q4_0 = 0, LG_FMT_Q4_K = 1, LG_FMT_I8 = 2, LG_FMT_I8M = 3 };
+__host__ __device__ constexpr int lg_tile_bytes(int fmt) { return fmt >= LG_FMT_I8 ? 1024 : 512; }              // weights of one 16x64 tile
+__host__ __device__ constexpr int lg_tile_extra(int fmt) { return fmt == LG_FMT_Q4_0 ? 64 : fmt == LG_FMT_I8M ? 256 : 128; }   // its scale bytes
 // bit 2 (LG_EPI_POST): the input panel's norm was deferred -- results are multiplied by 1/rms from post_ss.
 // A separate instantiation, so the plain epilogues carry none of that code.
 enum { LG_EPI_STORE = 0, LG_EPI_HEAD = 1, LG_EPI_GEGLU = 2, LG_EPI_NORMTAIL = 3, LG_EPI_POST = 4 };
@@ -361,7 +453,8 @@ enum { LG_EPI_STORE = 0, LG_EPI_HEAD = 1, LG_EPI_GEGLU = 2, LG_EPI_NORMTAIL = 3,
 #define LG_GEMV_THREADS ((LG_GEMV_CW + 1) * 32)   // + one producer warp
 #define LG_GEMV_STAGES 3               // ring depth: 3 stages, 4 (LG_GEMV_STAGES_MAX) where two CTAs per SM still fit
 #define LG_GEMV_STAGES_MAX 4
-#define LG_GEMV_STAGE_TILES 32         // 16x64 weight tiles per stage (R row tiles x 32/R positions)
+#define LG_GEMV_STAGE_TILES 32         // 16x64 q4 weight tiles per stage (R row tiles x 32/R positions); i8 tiles: 16
+template <int FMT> __host__ __device__ constexpr int gemv_stage_tiles() { return FMT >= LG_FMT_I8 ? 16 : LG_GEMV_STAGE_TILES; }
 
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_u32(bar)) : "memory");
@@ -372,7 +465,11 @@ __device__ __forceinline__ void consumer_sync() {       // the consumer warps on
 
 // Bytes of one ring stage: nibbles, scales (and the {d,dmin} pairs of q4_K)
 template <int FMT> __host__ __device__ constexpr int gemv_stage_bytes() {
-    return LG_GEMV_STAGE_TILES * (512 + 64 + (FMT == LG_FMT_Q4_K ? 64 : 0));
+    return gemv_stage_tiles<FMT>() * (lg_tile_bytes(FMT) + lg_tile_extra(FMT));
+}
+__device__ __forceinline__ void mma_s8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(b0));
 }
 
 // The small-M matmul.  A CTA walks items = (group of R consecutive row tiles) x (its k slice,
@@ -394,13 +491,18 @@ template <int R, int NP, int FMT, int EPI>
 __global__ void __launch_bounds__(LG_GEMV_THREADS)
 lg_gemv_kernel(LgGemvArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
-    constexpr int P = LG_GEMV_STAGE_TILES / R;               // tile positions per stage
+    constexpr int ST = gemv_stage_tiles<FMT>();
+    constexpr int P = ST / R;                                // tile positions per stage
+    constexpr int TB = lg_tile_bytes(FMT);
+    // fewer positions than consumer warps (i8 tiles with R = 4): the warps also split the row tiles of a position
+    constexpr int PW = P < LG_GEMV_CW ? P : LG_GEMV_CW, RS = LG_GEMV_CW / PW;
     const int NS = a.ns;                                     // ring depth chosen by the host (3 or 4)
     constexpr int EB = EPI & 3;                              // the epilogue proper
     constexpr bool POST = (EPI & LG_EPI_POST) != 0;
     constexpr int STAGE = gemv_stage_bytes<FMT>();
-    constexpr int SC_OFF = LG_GEMV_STAGE_TILES * 512;        // scales after the nibbles, {d,dmin} after the scales
-    constexpr int DD_OFF = SC_OFF + LG_GEMV_STAGE_TILES * 64;
+    constexpr int SC_OFF = ST * TB;                          // scales after the weights, {d,dmin} / integer scales after them, offsets last
+    constexpr int DD_OFF = SC_OFF + ST * 64;
+    constexpr int MM_OFF = DD_OFF + ST * 64;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int ks = blockIdx.y;
     const int kp0 = (int)((long long)a.nkp * ks / a.kslices), kp1 = (int)((long long)a.nkp * (ks + 1) / a.kslices);
@@ -438,16 +540,18 @@ lg_gemv_kernel(LgGemvArgs a) {
                 for (int c = 0; c < n_chunks && ok; c++) {
                     if (!mbar_wait(empty + stage, phase ^ 1)) { atomicOr(a.err, LG_ERR_MBAR_TIMEOUT); ok = false; break; }
                     const int np = min(P, nkp_s - c * P);
-                    const uint32_t tile_bytes = (uint32_t)np * (512 + 64 + (FMT == LG_FMT_Q4_K ? 64 : 0));
+                    const uint32_t tile_bytes = (uint32_t)np * (TB + lg_tile_extra(FMT));
                     unsigned char *st = ring + (size_t)stage * STAGE;
                     mbar_expect_tx(full + stage, R * tile_bytes);
                     #pragma unroll
                     for (int r = 0; r < R; r++) {
                         const size_t tile = tile_base + (size_t)r * a.nkp + (size_t)c * P;
-                        bulk_g2s(st + (size_t)r * P * 512, a.wq + tile * 32, (uint32_t)np * 512, full + stage);
+                        bulk_g2s(st + (size_t)r * P * TB, a.wq + tile * (TB / 16), (uint32_t)np * TB, full + stage);
                         bulk_g2s(st + SC_OFF + (size_t)r * P * 64, a.ws + tile * 8, (uint32_t)np * 64, full + stage);
-                        if (FMT == LG_FMT_Q4_K)
+                        if (FMT != LG_FMT_Q4_0)
                             bulk_g2s(st + DD_OFF + (size_t)r * P * 64, a.wd + tile * 8, (uint32_t)np * 64, full + stage);
+                        if (FMT == LG_FMT_I8M)
+                            bulk_g2s(st + MM_OFF + (size_t)r * P * 128, a.wm + tile * 8, (uint32_t)np * 128, full + stage);
                     }
                     if (++stage == NS) { stage = 0; phase ^= 1; }
                     if (!panel_sent && ++issued == early) {
@@ -506,7 +610,7 @@ lg_gemv_kernel(LgGemvArgs a) {
             if (ok && !mbar_wait(full + stage, phase)) { ok = false; if (lane == 0) atomicOr(a.err, LG_ERR_MBAR_TIMEOUT); }
             const int np = min(P, nkp_s - c * P);
             const unsigned char *st = ring + (size_t)stage * STAGE;
-            for (int pp = warp; pp < np; pp += LG_GEMV_CW) {
+            for (int pp = warp % PW; pp < np; pp += PW) {
                 uint2 b[2][NP]; float2 xs[2][NP];
                 #pragma unroll
                 for (int s = 0; s < 2; s++)
@@ -518,6 +622,45 @@ lg_gemv_kernel(LgGemvArgs a) {
                     }
                 #pragma unroll
                 for (int r = 0; r < R; r++) {
+                    if (RS > 1 && (r % RS) != warp / PW) continue;          // another warp's row tile
+                    if (FMT >= LG_FMT_I8) {
+                        // i8 tile: per sub-block this lane's 16 bytes are {row g, row g+8} x {columns 4t.., 16+4t..}; one
+                        // k16 MMA per 16-column group, whose integer scale joins the block's f16 d (x16: the common
+                        // epilogue divides by the 16 the q4 tiles carry)
+                        const unsigned char *tp = st + (size_t)(r * P + pp) * TB;
+                        const uint2 sw2 = *(const uint2 *)(st + SC_OFF + (size_t)(r * P + pp) * 64 + g * 8);
+                        const uint2 is2 = *(const uint2 *)(st + DD_OFF + (size_t)(r * P + pp) * 64 + g * 8);
+                        uint4 mm = make_uint4(0, 0, 0, 0);
+                        if (FMT == LG_FMT_I8M) mm = *(const uint4 *)(st + MM_OFF + (size_t)(r * P + pp) * 128 + g * 16);
+                        #pragma unroll
+                        for (int s = 0; s < 2; s++) {
+                            const uint4 w = *(const uint4 *)(tp + s * 512 + lane * 16);
+                            const float2 fd = __half22float2(*(const __half2 *)(s ? &sw2.y : &sw2.x));
+                            #pragma unroll
+                            for (int h = 0; h < 2; h++) {
+                                const int i0 = (int)(int8_t)((is2.x >> (8 * (2 * s + h))) & 0xff), i1 = (int)(int8_t)((is2.y >> (8 * (2 * s + h))) & 0xff);
+                                const float e0 = 16.0f * __fmul_rn(fd.x, (float)i0), e1 = 16.0f * __fmul_rn(fd.y, (float)i1);
+                                #pragma unroll
+                                for (int p = 0; p < NP; p++) {
+                                    int cc[4] = {0, 0, 0, 0};
+                                    mma_s8_k16(cc, h ? w.z : w.x, h ? w.w : w.y, h ? b[s][p].y : b[s][p].x);
+                                    const float v0 = (float)((cc[0] << 8) + cc[1]) * xs[s][p].x;
+                                    const float v1 = (float)((cc[2] << 8) + cc[3]) * xs[s][p].x;
+                                    acc[r][p][0] = fmaf(v0, e0, acc[r][p][0]);
+                                    acc[r][p][1] = fmaf(v1, e1, acc[r][p][1]);
+                                }
+                            }
+                            if (FMT == LG_FMT_I8M) {
+                                const float m0 = -16.0f * __uint_as_float(s ? mm.z : mm.x), m1 = -16.0f * __uint_as_float(s ? mm.w : mm.y);
+                                #pragma unroll
+                                for (int p = 0; p < NP; p++) {
+                                    acc[r][p][0] = fmaf(m0, xs[s][p].y, acc[r][p][0]);
+                                    acc[r][p][1] = fmaf(m1, xs[s][p].y, acc[r][p][1]);
+                                }
+                            }
+                        }
+                        continue;
+                    }
                     // this lane's 16 bytes: {row g, row g+8} words of sub-block 0, then of sub-block 1
                     const uint4 w = *(const uint4 *)(st + (size_t)(r * P + pp) * 512 + lane * 16);
                     const uint2 sw2 = *(const uint2 *)(st + SC_OFF + (size_t)(r * P + pp) * 64 + g * 8);
@@ -741,13 +884,28 @@ __global__ void lg_argmax_final(const float *__restrict__ val, const int *__rest
 // x[tok][0..ne) = decode(token_embd row toks[tok]) * sqrt(ne) from the TILE-MAJOR copy (the same
 // matrix is the output head).  Bit-identical to decoding the file row: value = d * (nibble-8).
 __global__ void lg_embed_rows(const uint4 *__restrict__ wq, const uint2 *__restrict__ ws, const uint2 *__restrict__ wd,
-                              int fmt, int nkp, int n_rows, const int *__restrict__ toks, float scale,
+                              const uint4 *__restrict__ wm, int fmt, int nkp, int n_rows, const int *__restrict__ toks, float scale,
                               float *__restrict__ out, int ldo) {
     pdl_launch(); pdl_wait();
     int tok = blockIdx.x;
     int row = min(max(toks[tok], 0), n_rows - 1);               // an out-of-range id must not read outside the table
     int rt = row >> 4, r = row & 15, g = r & 7, hi8 = r >> 3;
     const uint32_t *wq32 = (const uint32_t *)wq;
+    if (fmt >= LG_FMT_I8) {
+        // i8 tiles: value = (d * s) * q - m, the file's decode
+        const int8_t *wq8 = (const int8_t *)wq;
+        for (int e = threadIdx.x; e < nkp * 64; e += blockDim.x) {
+            const int kp = e >> 6, s = (e >> 5) & 1, kk = e & 31, half = kk >> 4, t = (kk & 15) >> 2, i = kk & 3;
+            const size_t tile = (size_t)rt * nkp + kp;
+            const int q = wq8[tile * 1024 + (size_t)s * 512 + (g * 4 + t) * 16 + (half * 2 + hi8) * 4 + i];
+            const uint16_t db = ((const uint16_t *)(ws + tile * 8 + g))[s * 2 + hi8];
+            const int sc = ((const int8_t *)(wd + tile * 8 + g))[hi8 * 4 + s * 2 + half];
+            float v = __fmul_rn(__fmul_rn(__half2float(__ushort_as_half(db)), (float)sc), (float)q);
+            if (fmt == LG_FMT_I8M) v = __fsub_rn(v, ((const float *)(wm + tile * 8 + g))[s * 2 + hi8]);
+            out[(size_t)tok * ldo + e] = __fmul_rn(v, scale);
+        }
+        return;
+    }
     for (int e = threadIdx.x; e < nkp * 64; e += blockDim.x) {
         int kp = e >> 6, s = (e >> 5) & 1, kk = e & 31;
         int t = (kk & 15) >> 2, i = kk & 3;

@@ -7,6 +7,7 @@
 #include <stdlib.h>
 #include <string.h>
 #include "lg_host.h"
+#include "lg_formats.h"
 
 float lg_half_to_float(uint16_t h) {
     uint32_t s = (uint32_t)(h >> 15) << 31, e = (h >> 10) & 31, f = h & 1023, bits;
@@ -27,7 +28,7 @@ int ggml_blck_size(uint32_t t) {
     switch (t) {
     case GGML_TYPE_F32: case GGML_TYPE_F16: case GGML_TYPE_BF16: return 1;
     case GGML_TYPE_Q4_0: case GGML_TYPE_Q8_0: return 32;
-    case GGML_TYPE_Q4_K: return 256;
+    case GGML_TYPE_Q4_K: case GGML_TYPE_Q3_K: case GGML_TYPE_Q5_K: case GGML_TYPE_Q6_K: return 256;
     default: return 0;
     }
 }
@@ -38,6 +39,9 @@ size_t ggml_type_size(uint32_t t) {
     case GGML_TYPE_Q4_0: return 18;
     case GGML_TYPE_Q8_0: return 34;
     case GGML_TYPE_Q4_K: return 144;
+    case GGML_TYPE_Q3_K: return 110;
+    case GGML_TYPE_Q5_K: return 176;
+    case GGML_TYPE_Q6_K: return 210;
     default: return 0;
     }
 }
@@ -78,13 +82,20 @@ bool dequantize_into(uint32_t type, const void *src, float *y, int64_t n) {
             }
         }
         return true;
-    case GGML_TYPE_Q8_0:
-        for (int64_t b = 0; b < nb; b++, p += 34, y += 32) {
-            uint16_t h; memcpy(&h, p, 2);
-            float d = lg_half_to_float(h);
-            for (int j = 0; j < 32; j++) y[j] = d * (float)(int8_t)p[2 + j];
-        }
+    case GGML_TYPE_Q8_0: case GGML_TYPE_Q6_K: case GGML_TYPE_Q5_K: case GGML_TYPE_Q3_K: {
+        /* y = (d * s) * q - (dmin * m), element by element (src/quant.c:184-274 evaluates the same products in the same order) */
+        const int bytes = lg_fmt_bytes((int)type);
+        for (int64_t b = 0; b < nb; b++, p += bytes, y += blk)
+            for (int e = 0; e < blk; e++) {
+                int q, sc, mi; uint16_t db, mb;
+                lg_fmt_elem((int)type, p, e, &q, &sc, &db, &mb, &mi);
+                float ds = lg_half_to_float(db) * (float)sc;
+                float v = ds * (float)q;
+                if (type == GGML_TYPE_Q5_K) { float off = lg_half_to_float(mb) * (float)mi; v = v - off; }
+                y[e] = v;
+            }
         return true;
+    }
     case GGML_TYPE_Q4_K:
         for (int64_t b = 0; b < nb; b++, p += 144) {
             uint16_t h0, h1; memcpy(&h0, p, 2); memcpy(&h1, p + 2, 2);

@@ -30,7 +30,8 @@ from typing import Dict, List, Optional
 import numpy as np
 
 # ggml tensor type ids (reference: include/quant.h:13-24)
-F32, F16, Q4_0, Q4_K = 0, 1, 2, 12
+F32, F16, Q4_0, Q8_0, Q3_K, Q4_K, Q5_K, Q6_K, BF16 = 0, 1, 2, 8, 11, 12, 13, 14, 30
+BLOCK_BYTES = {Q4_0: (32, 18), Q8_0: (32, 34), Q3_K: (256, 110), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210)}
 # gguf metadata value types (reference: include/gguf.h:17-32)
 T_U32, T_I32, T_F32, T_BOOL, T_STR, T_ARR = 4, 5, 6, 7, 8, 9
 
@@ -82,6 +83,43 @@ def random_q4_K(rng: np.random.Generator, n_elems: int) -> np.ndarray:
     out[:, 0:2] = d.astype(np.float16).view(np.uint8).reshape(-1, 2)
     out[:, 2:4] = dmin.astype(np.float16).view(np.uint8).reshape(-1, 2)
     out[:, 4:] = rng.integers(0, 256, size=(nb, 140), dtype=np.uint8)
+    return out.reshape(-1)
+
+
+def quantize_q8_0(x: np.ndarray) -> np.ndarray:
+    """Encode float32 values as q8_0 blocks: per 32 values d = f16(amax/127), q = rint(x/d) as int8 (layout: reference
+    src/quant.c:78-81)."""
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, 32)
+    d16 = (np.abs(x).max(axis=1) / np.float32(127.0)).astype(np.float16)
+    d = d16.astype(np.float32)
+    inv = np.where(d > 0, np.float32(1.0) / np.where(d > 0, d, 1), np.float32(0.0)).astype(np.float32)
+    q = np.clip(np.rint(x * inv[:, None]), -127, 127).astype(np.int8)
+    out = np.empty((x.shape[0], 34), dtype=np.uint8)
+    out[:, 0:2] = d16.view(np.uint8).reshape(-1, 2)
+    out[:, 2:] = q.view(np.uint8)
+    return out.reshape(-1)
+
+
+def random_k_blocks(rng: np.random.Generator, n_elems: int, wtype: int) -> np.ndarray:
+    """Random q6_K / q5_K / q3_K super-blocks with weights of magnitude <~ 0.1: every packed byte uniform, the f16
+    super-block scales drawn so that d * (largest integer scale) * (largest q) stays small (layouts: reference
+    src/quant.c:48-78; decode :184-274)."""
+    blk, nbytes = BLOCK_BYTES[wtype]
+    nb = n_elems // blk
+    out = rng.integers(0, 256, size=(nb, nbytes), dtype=np.uint8)
+    if wtype == Q6_K:        # |q| <= 32, |scale| <= 128
+        d = rng.uniform(1.0e-5, 2.5e-5, nb).astype(np.float16)
+        out[:, 208:210] = d.view(np.uint8).reshape(-1, 2)
+    elif wtype == Q3_K:      # |q| <= 4, |scale| <= 32
+        d = rng.uniform(4.0e-4, 8.0e-4, nb).astype(np.float16)
+        out[:, 108:110] = d.view(np.uint8).reshape(-1, 2)
+    elif wtype == Q5_K:      # q <= 31, scale <= 63; dmin ~ 15.5 d centres the weights
+        d = rng.uniform(2.5e-5, 7.5e-5, nb).astype(np.float32)
+        dmin = (d * 15.5 * rng.uniform(0.9, 1.1, nb)).astype(np.float32)
+        out[:, 0:2] = d.astype(np.float16).view(np.uint8).reshape(-1, 2)
+        out[:, 2:4] = dmin.astype(np.float16).view(np.uint8).reshape(-1, 2)
+    else:
+        raise ValueError(wtype)
     return out.reshape(-1)
 
 
@@ -141,7 +179,9 @@ class GGUFWriter:
     @staticmethod
     def nbytes(ttype: int, dims) -> int:
         n = int(np.prod(dims))
-        return {F32: 4 * n, F16: 2 * n, Q4_0: n // 32 * 18, Q4_K: n // 256 * 144}[ttype]
+        if ttype in BLOCK_BYTES:
+            return n // BLOCK_BYTES[ttype][0] * BLOCK_BYTES[ttype][1]
+        return {F32: 4 * n, F16: 2 * n, BF16: 2 * n}[ttype]
 
     def declare(self, name: str, dims, ttype: int, producer):
         """producer() -> bytes-like (numpy uint8 array or bytes) of exactly nbytes."""
@@ -205,6 +245,8 @@ class TargetShape:
     wtype: int = Q4_0
     sigma: float = 0.02
     head_dim_global: Optional[int] = None  # head size of the full-attention layers when it differs (Gemma-4: 512 vs 256)
+    # per-tensor formats: tensor-name suffix (e.g. "ffn_down.weight", "token_embd.weight") -> ggml type, overriding wtype
+    wtypes: Dict[str, int] = field(default_factory=dict)
 
     def hd(self, l: int) -> int:
         return self.head_dim if (self.is_local(l) or self.head_dim_global is None) else self.head_dim_global
@@ -233,6 +275,7 @@ class HeadShape:
     layer_output_scale: bool = False
     with_post: bool = True
     sigma: float = 0.02
+    wtypes: Dict[str, int] = field(default_factory=dict)    # tensor-name suffix -> ggml type (default q4_0)
 
 
 # Shapes of the benchmark configurations.
@@ -261,8 +304,16 @@ class _Gen:
     def weight(self, n: int, sigma: float, wtype: int):
         if wtype == Q4_K:
             return random_q4_K(self.rng, n)
-        if self.device == "cpu":
+        if wtype in (Q6_K, Q5_K, Q3_K):
+            return random_k_blocks(self.rng, n, wtype)
+        if self.device == "cpu" or wtype in (Q8_0, F16, BF16):
             x = self.rng.standard_normal(n, dtype=np.float32) * np.float32(sigma)
+            if wtype == Q8_0:
+                return quantize_q8_0(x)
+            if wtype == F16:
+                return x.astype(np.float16).view(np.uint8)
+            if wtype == BF16:
+                return (x.view(np.uint32) >> 16).astype(np.uint16).view(np.uint8)
             return quantize_q4_0(x) if wtype == Q4_0 else x.view(np.uint8)
         import torch
         out = []
@@ -304,7 +355,10 @@ def write_target(path: str, s: TargetShape, seed: int = 0, device: str = "cpu") 
 
     def qw(name, k, m, wtype=None):
         wt = s.wtype if wtype is None else wtype
-        if wt == Q4_K and k % 256:
+        for suffix, t in s.wtypes.items():
+            if name.endswith(suffix):
+                wt = t
+        if wt in (Q4_K, Q6_K, Q5_K, Q3_K) and k % 256:
             wt = Q4_0                           # super-blocks need k % 256 == 0
         w.declare(name, [k, m], wt, lambda: g.weight(k * m, s.sigma, wt))
 
@@ -367,7 +421,11 @@ def write_head(path: str, h: HeadShape, t: TargetShape, seed: int = 1, device: s
     w.add_f32(f"{arch}.final_logit_softcapping", h.softcap)
 
     def qw(name, k, m):
-        w.declare(name, [k, m], Q4_0, lambda: g.weight(k * m, h.sigma, Q4_0))
+        wt = Q4_0
+        for suffix, t in h.wtypes.items():
+            if name.endswith(suffix):
+                wt = t
+        w.declare(name, [k, m], wt, lambda: g.weight(k * m, h.sigma, wt))
 
     ni, hd = h.n_inner, t.head_dim
     qw("nextn.pre_projection.weight", 2 * t.n_embd, ni)

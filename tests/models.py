@@ -47,6 +47,16 @@ def shapes():
         "mid_oddhead": (s.TargetShape(n_layer=6, n_embd=512, n_head=8, n_head_kv=2, head_dim=256, n_ff=2048, n_vocab=8192,
                                       window=64, local_per_global=2, ple=0, q_norm_scale=256 ** -0.5),
                         s.HeadShape(n_layer=1, n_inner=256, n_head=3, n_ff=512), 5, 11),
+        # every block format the reference reads in one model: q6_K embeddings / head and o-projection, q8_0 queries, q5_K
+        # keys, values, gate and up, q3_K down-projection, a q6_K per-layer table; the head file carries an f16 and a bf16
+        # matrix beside q8_0 ones (dense matrices are accepted in a draft head only)
+        "mixed": (dataclasses.replace(tiny, q_norm_scale=64 ** -0.5,
+                                      wtypes={"token_embd.weight": s.Q6_K, "attn_q.weight": s.Q8_0, "attn_k.weight": s.Q5_K,
+                                              "attn_v.weight": s.Q5_K, "attn_output.weight": s.Q6_K, "ffn_gate.weight": s.Q5_K,
+                                              "ffn_up.weight": s.Q5_K, "ffn_down.weight": s.Q3_K, "inp_gate.weight": s.Q8_0,
+                                              "per_layer_token_embd.weight": s.Q6_K, "per_layer_model_proj.weight": s.Q6_K}),
+                  dataclasses.replace(s.TINY_HEAD, wtypes={"pre_projection.weight": s.F16, "post_projection.weight": s.BF16,
+                                                           "attn_q.weight": s.Q8_0, "ffn_down.weight": s.Q8_0}), 30, 31),
         # all-zero weights: every logit ties at 0, the argmax must be index 0
         "zero": (dataclasses.replace(tiny, sigma=0.0, ple=0), None, 9, 10),
     }

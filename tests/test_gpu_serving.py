@@ -184,3 +184,15 @@ def test_caller_that_verifies_other_tokens_than_drafted_gets_its_own_answer(lg):
         toks = np.array([best2, plain[3], plain[4], plain[5]], dtype=np.int32)
         adv, out = g.spec(toks, pos2)
         assert adv == 4 and [int(x) for x in out] == [int(x) for x in plain[3:7]]
+
+
+def test_a_wait_that_runs_out_reports_and_returns(lg):
+    """Every device-side wait in this library is bounded: when nothing completes the barrier, the kernel gives up after its
+    limit, raises a status bit the host reads, and returns -- the context stays usable (no trap, no hang)."""
+    s = synth_module()
+    tp, _ = model_files("tiny")
+    with lg.Session(tp, None, 64) as g:
+        before = g.next(5, 0)
+        assert g.L.lg_debug_bounded_wait(g.model, 1024) == 1      # LG_ERR_MBAR_TIMEOUT: the wait ran out and said so
+        assert g.L.lg_debug_bounded_wait(g.model, 0) == -1        # bad argument, no launch
+        assert g.next(5, 0) == before                              # the engine and the context still work

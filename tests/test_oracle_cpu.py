@@ -19,6 +19,25 @@ def test_generator_is_reproducible(golden):
     assert _sha(hp) == str(golden["sha_head"])
 
 
+@pytest.mark.skipif(not has_ref(4), reason="compiled reference backend not present")
+@pytest.mark.parametrize("tname", ["Q8_0", "Q6_K", "Q5_K", "Q3_K", "Q4_K", "Q4_0"])
+def test_port_decode_bit_exact_vs_compiled_reference_on_random_blocks(port_built, tname):
+    """All byte patterns (f16 scale fields kept finite): the host decode this repository ships equals the reference's."""
+    from oracle.pyref import PortOracle, RefOracle
+    s = synth_module()
+    t = getattr(s, tname)
+    tp, _ = model_files("tiny")
+    blk, nbytes = s.BLOCK_BYTES[t]
+    rng = np.random.default_rng(80 + t)
+    raw = rng.integers(0, 256, size=(3000, nbytes), dtype=np.uint8)
+    for col in {s.Q8_0: [0], s.Q6_K: [208], s.Q5_K: [0, 2], s.Q3_K: [108], s.Q4_K: [0, 2], s.Q4_0: [0]}[t]:
+        raw[:, col + 1] &= 0xBF                              # clear one exponent bit: no inf / nan scales
+    a, b = RefOracle(tp, None, 64), PortOracle(tp, None, 64)
+    ya, yb = a.dequant(t, raw.reshape(-1), 3000 * blk), b.dequant(t, raw.reshape(-1), 3000 * blk)
+    a.close(); b.close()
+    assert np.array_equal(ya.view(np.uint32), yb.view(np.uint32))
+
+
 def test_port_dequant_matches_reference_kat(golden, port_built):
     from oracle.pyref import PortOracle
     s = synth_module()
@@ -72,9 +91,10 @@ def test_port_teacher_forced_logits_and_drafts_bit_exact(golden, port_built):
 
 
 @pytest.mark.skipif(not has_ref(4), reason="compiled reference backend not present")
-@pytest.mark.parametrize("name", ["var", "mid", "mid_k"])
+@pytest.mark.parametrize("name", ["var", "mid", "mid_k", "mixed", "hd512"])
 def test_port_bit_exact_vs_compiled_reference(port_built, name):
-    """Every optional branch (softcap, output scale, rope divisors, V=K, KV sharing, q4_K, hd 256)."""
+    """Every optional branch (softcap, output scale, rope divisors, V=K, KV sharing, q4_K, hd 256; q8_0 / q6_K / q5_K / q3_K
+    matrices with f16 / bf16 head tensors; full-attention layers of head size 512)."""
     from oracle.pyref import PortOracle, RefOracle
     s = synth_module()
     tp, hp = model_files(name)
