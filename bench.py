@@ -534,10 +534,10 @@ def main():
     dt_h = time.perf_counter() - t0
     syncs_per_round = (sess.host_syncs() - syncs0) / e2e_rounds
     identical = identical and bool(np.array_equal(toks_h, greedy[1:1 + len(toks_h)]))
-    # per round the blocking calls upload the round state once and download its record once (both sizeof(LgRoundState) = 88 B)
+    # per round the blocking calls upload the round state once and download its record once (both sizeof(LgRoundState) = 96 B)
     # plus the 4-byte status word; the per-call form (LG_LAZY_ROUND=0) moves (M-1)*12 + (1+M)*4 up and (M-1)*4 + 40 down
-    h2d = 88 if syncs_per_round < 1.5 else (M - 1) * 12 + (1 + M) * 4
-    d2h = 92 if syncs_per_round < 1.5 else (M - 1) * 4 + 36 + 4
+    h2d = 96 if syncs_per_round < 1.5 else (M - 1) * 12 + (1 + M) * 4
+    d2h = 100 if syncs_per_round < 1.5 else (M - 1) * 4 + 36 + 4
 
     peak = float(peaks.get("hbm_gbs", 6650.0))
     peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "fallback 6650 GB/s"

@@ -91,6 +91,11 @@ void lg_set_round_width(int n);
  * do: the draft offered for position p is replay[p + offset].  enable = 0 turns the override off. */
 void lg_set_replay_origin(struct model *m, int offset, int enable);
 long long lg_host_syncs(struct model *m);            /* blocking device-to-host waits made by the blocking calls so far */
+/* Variable draft length: a draft whose best logit leads the runner-up by less than `margin` calls off the round's remaining
+ * drafts (forwards skipped on the device, slots padded with the previous token as for a head that cannot chain).  0 = off.
+ * The idea is the reference's own open lever (docs/upstream-llama-study.md:306-311); the output never changes. */
+void lg_set_draft_margin(struct model *m, float margin);
+long long lg_drafts_skipped(struct model *m);        /* drafts called off, as of the latest lg_rounds_collect */
 
 /* Introspection for tests and the benchmark. */
 long long lg_weight_bytes(struct model *m);          /* file bytes of all matrices uploaded so far */

@@ -28,7 +28,7 @@ ABI_SYMBOLS = [
     "model_forward", "model_forward_next", "model_prefill", "model_prefill_embd", "model_prefill_mixed",
     "model_prefill_reserve", "model_forward_spec", "mtp_draft_device", "mtp_draft_chain_device", "mtp_free_device",
     "lg_forward_spec_n", "lg_set_replay", "lg_rounds_begin", "lg_rounds_enqueue", "lg_rounds_collect",
-    "lg_set_round_width", "lg_set_replay_origin", "lg_host_syncs", "lg_weight_bytes", "lg_round_launches", "lg_last_hidden", "lg_kv_row", "lg_stream", "lg_engine_release",
+    "lg_set_round_width", "lg_set_replay_origin", "lg_host_syncs", "lg_set_draft_margin", "lg_drafts_skipped", "lg_weight_bytes", "lg_round_launches", "lg_last_hidden", "lg_kv_row", "lg_stream", "lg_engine_release",
     "lg_bench_matmul_pass", "lg_bench_prefill_pass", "lg_set_attn_deep", "lg_flash_decode_noalloc",
     "lg_debug_bounded_wait", "lg_debug_stamps", "lg_debug_clear_stamps",
     "lg_dequant_host", "lg_gemv_host", "lg_flash_decode_host", "lg_flash_decode_cluster_host", "lg_prefill_matmul_host",
@@ -95,6 +95,8 @@ def load() -> C.CDLL:
     L.lg_bench_prefill_pass.argtypes = [C.c_void_p, C.c_int, C.c_int]; L.lg_bench_prefill_pass.restype = C.c_int
     L.lgs_rounds_host.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _i32p, C.c_int, C.c_void_p, C.c_int, _i32p]
     L.lgs_rounds_host.restype = C.c_int
+    L.lg_set_draft_margin.argtypes = [C.c_void_p, C.c_float]; L.lg_set_draft_margin.restype = None
+    L.lg_drafts_skipped.argtypes = [C.c_void_p]; L.lg_drafts_skipped.restype = C.c_longlong
     L.lg_debug_bounded_wait.argtypes = [C.c_void_p, C.c_int]; L.lg_debug_bounded_wait.restype = C.c_int
     L.lgs_host_syncs.argtypes = [C.c_void_p]; L.lgs_host_syncs.restype = C.c_longlong
     L.lg_set_round_width.argtypes = [C.c_int]; L.lg_set_round_width.restype = None
@@ -307,6 +309,13 @@ class Session:
         toks = np.zeros(max(cap, 1), dtype=np.int32)
         n = self.L.lg_rounds_collect(self.model, toks.ctypes.data_as(C.c_void_p), from_, cap, stats)
         return toks[:n], dict(pos=int(stats[0]), n_emitted=int(stats[1]), n_draft=int(stats[2]), n_accept=int(stats[3]))
+
+    def set_draft_margin(self, margin: float) -> None:
+        """Call off a round's remaining drafts when a draft's best logit leads the runner-up by less than `margin` (0 = off)."""
+        self.L.lg_set_draft_margin(self.model, float(margin))
+
+    def drafts_skipped(self) -> int:
+        return int(self.L.lg_drafts_skipped(self.model))
 
     def host_syncs(self) -> int:
         """Blocking device-to-host waits the reference-shaped calls of this session have made so far."""

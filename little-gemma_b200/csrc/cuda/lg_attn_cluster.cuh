@@ -83,7 +83,7 @@ lg_attn_cluster_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_con
     for (int qi = threadIdx.x; qi < nq16; qi += LG_ATTN_THREADS) ml[qi] = make_float2(-INFINITY, 0.0f);
     // early_kv: the position and the cached rows below the block were written by earlier graph launches (this layer
     // writes its own rows, and only here), so the first tile may start streaming before the previous kernel has finished
-    if (!a.early_kv) pdl_wait();
+    if (!a.early_kv) { pdl_wait(); if (a.skip && *a.skip) return; }     // called off: the whole cluster leaves before any copy or barrier
     const int pos0 = *a.pos;
     const int p_first = pos0 + a.qpos_off, p_last = pos0 + a.M - 1 + a.qpos_off;
     const int lo_first = a.window > 0 ? max(0, p_first + a.win_shrink - a.window + 1) : 0;

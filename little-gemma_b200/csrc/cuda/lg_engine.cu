@@ -66,6 +66,7 @@ struct DraftW {
     // activations (one token)
     float *cat = nullptr, *x = nullptr, *hbuf = nullptr, *qbuf = nullptr, *qrot = nullptr, *obuf = nullptr, *gu = nullptr, *part = nullptr;
     float *amax_val = nullptr; int *amax_idx = nullptr, *best = nullptr;
+    float *amax_val2 = nullptr, *margin = nullptr;      // runner-up logits per CTA; best - second best of the latest draft
     float2 *part_ml = nullptr;
     LgPanel p_cat{}, p_ni{}, p_attn{}, p_ff{};
     float2 *rope_local = nullptr, *rope_global = nullptr; int hd_local = 0, hd_global = 0;
@@ -128,6 +129,7 @@ struct Engine {
     struct { bool valid = false; int n = 0, pos = 0, adv = 0, toks[LG_MAXM] = {0}, out[LG_MAXM] = {0}; bool chained = false; } lazy;
     int replay_off = 0; bool lazy_replay = false;   // replay table index of a draft = its position + replay_off (lg_set_replay_origin)
     long long host_syncs = 0;                 // blocking device-to-host waits made by the reference-shaped calls
+    float *d_margin_thr = nullptr;            // confidence margin below which a draft calls off the drafts after it (0: never)
     cudaEvent_t mid_event = nullptr;          // LG_MTP_PROFILE: recorded between the layers and the head of a forward
     int mm_launches = 0;                      // kernels in the captured matmul-only pass             // kernels in one captured round (lg_rounds_enqueue)
 };
@@ -466,6 +468,8 @@ struct GemvExtra {
     const LgPanel *outp = nullptr;            // GeGLU / NORMTAIL epilogue target
     int *ks_out = nullptr, *gx_out = nullptr;
     int ldo = 0;                              // row stride of the output when it is not the matrix's own padded row count
+    const int *skip = nullptr;                // the launch does nothing when this device word is non-zero
+    float *amax_val2 = nullptr;               // head epilogue: runner-up logits
     // NORMTAIL epilogue
     float *xres = nullptr; int ldx = 0, n_cols = 0; const float *add_w = nullptr, *norm_w = nullptr; float out_scale = 1.0f, eps = 0.0f;
     float *ssq1 = nullptr, *ssq2 = nullptr; int *gbar = nullptr;
@@ -510,7 +514,7 @@ void launch_gemv(Engine *e, const WMat &W, const LgPanel &X, int M, float *out, 
     LgGemvArgs a{};
     a.wq = W.wq; a.ws = W.ws; a.wd = W.wd; a.wm = W.wm; a.x = X; a.nkp = W.nkp; a.n_row_tiles = W.n_row_tiles; a.kslices = p.ks;
     a.out = out; a.ldo = x.ldo ? x.ldo : W.ldo; a.M = M; a.softcap = x.softcap; a.logits = x.logits; a.n_valid_rows = W.m;
-    a.amax_val = x.amax_val; a.amax_idx = x.amax_idx; a.err = e->err;
+    a.amax_val = x.amax_val; a.amax_idx = x.amax_idx; a.amax_val2 = x.amax_val2; a.skip = x.skip; a.err = e->err;
     if (x.outp) a.outp = *x.outp;
     a.xres = x.xres; a.ldx = x.ldx; a.n_cols = x.n_cols; a.add_w = x.add_w; a.norm_w = x.norm_w; a.out_scale = x.out_scale; a.eps = x.eps;
     a.ssq1 = x.ssq1; a.ssq2 = x.ssq2; a.gbar = x.gbar;
@@ -548,8 +552,9 @@ void launch_gemv(Engine *e, const WMat &W, const LgPanel &X, int M, float *out, 
 
 void launch_norm(Engine *e, int M, float *x, int ldx, int n, float eps,
                  const float *add_src, int n_parts, size_t part_stride, int ld_add, const float *add_w, float out_scale,
-                 const float *norm_w, const LgPanel *panel, float *y, int ldy) {
+                 const float *norm_w, const LgPanel *panel, float *y, int ldy, const int *skip = nullptr) {
     LgNormArgs a{};
+    a.skip = skip;
     a.x = x; a.ldx = ldx; a.add_src = add_src; a.n_parts = n_parts; a.part_stride = part_stride; a.ld_add = ld_add;
     a.add_w = add_w; a.out_scale = out_scale; a.norm_w = norm_w;
     if (panel) { a.panel = *panel; a.want_panel = 1; }
@@ -839,6 +844,8 @@ Engine *engine_for(const struct model *m) {
     e->tickets = dalloc<int>(MAX_KV_HEADS);
     e->ssq1 = dalloc<float>((size_t)2 * e->sm_count * LG_MAXM); e->ssq2 = dalloc<float>((size_t)2 * e->sm_count * LG_MAXM);
     e->gbar = dalloc<int>(2);
+    e->d_margin_thr = dalloc<float>(1);
+    { float thr = (float)atof(getenv("LG_DRAFT_MARGIN") ? getenv("LG_DRAFT_MARGIN") : "0"); if (thr != 0.0f) h2d_sync(e->d_margin_thr, &thr, 4); }
 
     const int ne = c->n_embd, H = c->n_head, ple = c->n_embd_per_layer;
     const struct gguf_tensor *emb = find_t(g, -1, "token_embd.weight");
@@ -957,7 +964,7 @@ void draft_free(DraftW *d) {
     }
     cudaFree(d->out_norm); cudaFree(d->cat); cudaFree(d->x); cudaFree(d->hbuf); cudaFree(d->qbuf); cudaFree(d->qrot);
     cudaFree(d->rope_local); cudaFree(d->rope_global); cudaFree(d->part_ml);
-    cudaFree(d->obuf); cudaFree(d->gu); cudaFree(d->part); cudaFree(d->amax_val); cudaFree(d->amax_idx); cudaFree(d->best);
+    cudaFree(d->obuf); cudaFree(d->gu); cudaFree(d->part); cudaFree(d->amax_val); cudaFree(d->amax_idx); cudaFree(d->best); cudaFree(d->amax_val2); cudaFree(d->margin);
     panel_free(d->p_cat); panel_free(d->p_ni); panel_free(d->p_attn); panel_free(d->p_ff);
     delete d;
 }
@@ -980,7 +987,7 @@ void engine_free(Engine *e) {
     cudaFree(e->hidden); cudaFree(e->h_prev); cudaFree(e->part); cudaFree(e->tokrow); cudaFree(e->pproj); cudaFree(e->ipl);
     cudaFree(e->pg); cudaFree(e->logits); cudaFree(e->amax_val); cudaFree(e->amax_idx);
     panel_free(e->p_ne); panel_free(e->p_attn); panel_free(e->p_ff); panel_free(e->p_ple);
-    cudaFree(e->st); cudaFreeHost(e->st_host); cudaFree(e->log); cudaFree(e->replay); cudaFree(e->d_n_replay); cudaFree(e->err); cudaFree(e->tickets);
+    cudaFree(e->st); cudaFreeHost(e->st_host); cudaFree(e->log); cudaFree(e->replay); cudaFree(e->d_n_replay); cudaFree(e->err); cudaFree(e->tickets); cudaFree(e->d_margin_thr);
     free(e->pick_rows);
     cudaStreamDestroy(e->stream);
     delete e;
@@ -1128,7 +1135,7 @@ void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags, int 
         int gx = 0;
         GemvExtra xh; xh.softcap = c->logit_softcap; xh.logits = lg; xh.amax_val = e->amax_val; xh.amax_idx = e->amax_idx; xh.gx_out = &gx;
         if (only & C_HEAD) launch_gemv(e, e->head, e->p_ne, M, nullptr, LG_EPI_HEAD, 1, xh); else gx = 1;
-        if (only & C_MISC) launch_k(e, lg_argmax_final, dim3(M), dim3(256), 0, e->amax_val, e->amax_idx, gx, e->st->out);
+        if (only & C_MISC) launch_k(e, lg_argmax_final, dim3(M), dim3(256), 0, (const float *)e->amax_val, (const int *)e->amax_idx, gx, e->st->out, (const float *)nullptr, (float *)nullptr);
         if (flags & F_ACCEPT) {
             if (only & C_MISC) launch_k(e, lg_accept_kernel, dim3(1), dim3(256), 0, e->st, M, e->hidden, ne, ne, e->h_prev, e->log, LOG_CAP, (flags & F_ADVANCE) ? 1 : 0);
         }
@@ -1407,6 +1414,7 @@ DraftW *draft_build(Engine *e, struct mtp *t, const struct kvcache *kv) {
     d->part_ml = dalloc<float2>((size_t)slots * d->n_head);
     d->amax_val = dalloc<float>((size_t)e->head_ctas * LG_MAXM); d->amax_idx = dalloc<int>((size_t)e->head_ctas * LG_MAXM);
     d->best = dalloc<int>(LG_MAXM);
+    d->amax_val2 = dalloc<float>((size_t)e->head_ctas * LG_MAXM); d->margin = dalloc<float>(LG_MAXM);
     if (!d->hd_local) d->hd_local = d->hd_global;
     if (!d->hd_global) d->hd_global = d->hd_local;
     d->rope_local = dalloc<float2>(d->hd_local / 2);
@@ -1421,25 +1429,29 @@ void enqueue_draft(Engine *e, DraftW *d, const struct kvcache *kv, int slot, boo
     const struct model *m = e->m;
     const struct config *c = &m->cfg;
     const int ni = d->ni, nb = d->nb;
+    // a chained draft does nothing when the round's drafting was called off (the previous draft's confidence margin fell
+    // below the threshold): its heavy kernels return at once on this word and lg_store_draft pads the slot
+    const int *skip = chained ? &e->st->stop : nullptr;
+    GemvExtra xs_; xs_.skip = skip;
     launch_k(e, lg_embed_rows, dim3(1), dim3(256), 0, e->head.wq, e->head.ws, e->head.wd, e->head.wm, e->head.fmt, e->head.nkp, e->head.m,
                                     e->st->toks + (slot - 1), sqrtf((float)nb), d->cat, 2 * nb);
     if (chained) {
         // h_prev = post(x): x still holds the previous draft's normed hidden, p_ni its panel
-        launch_gemv(e, d->post, d->p_ni, 1, d->obuf, LG_EPI_STORE, 1);
+        launch_gemv(e, d->post, d->p_ni, 1, d->obuf, LG_EPI_STORE, 1, xs_);
         launch_k(e, lg_copy_f32, dim3((nb + 255) / 256), dim3(256), 0, d->cat + nb, d->obuf, nb);
     } else {
         launch_k(e, lg_copy_f32, dim3((nb + 255) / 256), dim3(256), 0, d->cat + nb, e->h_prev, nb);
     }
     launch_k(e, lg_quant_rows, dim3((2 * nb / 32 + 7) / 8, 1), dim3(256), 0, d->cat, 2 * nb, 2 * nb, d->p_cat);
-    launch_gemv(e, d->pre, d->p_cat, 1, d->obuf, LG_EPI_STORE, 1);
+    launch_gemv(e, d->pre, d->p_cat, 1, d->obuf, LG_EPI_STORE, 1, xs_);
     launch_k(e, lg_copy_f32, dim3((ni + 255) / 256), dim3(256), 0, d->x, d->obuf, ni);
     launch_k(e, lg_rope_table_kernel, dim3(1), dim3(256), 0, (const int *)&e->st->dpos, 1, d->hd_local, d->base_swa, (const float *)nullptr, d->rope_local);
     launch_k(e, lg_rope_table_kernel, dim3(1), dim3(256), 0, (const int *)&e->st->dpos, 1, d->hd_global, d->base_full, (const float *)nullptr, d->rope_global);
-    launch_norm(e, 1, d->x, ni, ni, d->eps, nullptr, 0, 0, 0, nullptr, 1.0f, d->blk[0].attn_norm, &d->p_ni, nullptr, 0);
+    launch_norm(e, 1, d->x, ni, ni, d->eps, nullptr, 0, 0, 0, nullptr, 1.0f, d->blk[0].attn_norm, &d->p_ni, nullptr, 0, skip);
     for (size_t L = 0; L < d->blk.size(); L++) {
         DraftBlockW &b = d->blk[L];
         const int hd = b.hd, src = b.src, Hkv = m->n_head_kv[src];
-        launch_gemv(e, b.q, d->p_ni, 1, d->qbuf, LG_EPI_STORE, 1);
+        launch_gemv(e, b.q, d->p_ni, 1, d->qbuf, LG_EPI_STORE, 1, xs_);
         LgAttnArgs aa{};
         aa.qkv = d->qbuf; aa.ld = b.q.ldo; aa.q_ready = 0; aa.has_v = 0; aa.owns_kv = 0;
         aa.q_norm = b.q_norm; aa.k_norm = nullptr; aa.eps = d->eps;
@@ -1448,31 +1460,31 @@ void enqueue_draft(Engine *e, DraftW *d, const struct kvcache *kv, int slot, boo
         aa.H = d->n_head; aa.Hkv = Hkv; aa.hd = hd; aa.M = 1;
         aa.window = (b.local && c->sliding_window > 0) ? c->sliding_window : 0;
         aa.qpos_off = -1; aa.win_shrink = aa.window > 0 ? 1 : 0; aa.pos = &e->st->dpos;
-        aa.n_slots = d->n_slots_global; aa.part = d->part; aa.part_ml = d->part_ml; aa.err = e->err;
+        aa.n_slots = d->n_slots_global; aa.part = d->part; aa.part_ml = d->part_ml; aa.err = e->err; aa.skip = skip;
         LgPanel pa = d->p_attn; pa.nsb = d->n_head * hd / 32;
         aa.out = pa; aa.out_f32 = nullptr;
         const int cl = attn_cluster_size(e, aa.window, kv->max_seq, aa.seq, hd, d->n_head, Hkv);
         if (cl) launch_attn_cluster(e, aa, cl);
         else launch_attn(e, aa, tiles_for(aa.window, kv->max_seq, 1, hd));
         int ks_o = 1;
-        GemvExtra xo; xo.ks_out = &ks_o;
+        GemvExtra xo; xo.ks_out = &ks_o; xo.skip = skip;
         launch_gemv(e, b.o, pa, 1, d->obuf, LG_EPI_STORE, 0, xo);
         launch_norm(e, 1, d->x, ni, ni, d->eps, d->obuf, ks_o, (size_t)LG_MAXM * b.o.ldo, b.o.ldo, b.post_attn, 1.0f,
-                    b.ffn_norm, &d->p_ni, nullptr, 0);
-        GemvExtra xg; xg.outp = &d->p_ff;
+                    b.ffn_norm, &d->p_ni, nullptr, 0, skip);
+        GemvExtra xg; xg.outp = &d->p_ff; xg.skip = skip;
         launch_gemv(e, b.gateup, d->p_ni, 1, nullptr, LG_EPI_GEGLU, 1, xg);
         bool last = L + 1 == d->blk.size();
         int ks_d = 1;
-        GemvExtra xd; xd.ks_out = &ks_d;
+        GemvExtra xd; xd.ks_out = &ks_d; xd.skip = skip;
         launch_gemv(e, b.down, d->p_ff, 1, d->obuf, LG_EPI_STORE, 0, xd);
         launch_norm(e, 1, d->x, ni, ni, d->eps, d->obuf, ks_d, (size_t)LG_MAXM * b.down.ldo, b.down.ldo, b.post_ffw, b.out_scale,
-                    last ? d->out_norm : d->blk[L + 1].attn_norm, &d->p_ni, last ? d->hbuf : nullptr, ni);
+                    last ? d->out_norm : d->blk[L + 1].attn_norm, &d->p_ni, last ? d->hbuf : nullptr, ni, skip);
     }
     int gx = 0;
-    GemvExtra xh; xh.softcap = d->softcap; xh.amax_val = d->amax_val; xh.amax_idx = d->amax_idx; xh.gx_out = &gx;
+    GemvExtra xh; xh.softcap = d->softcap; xh.amax_val = d->amax_val; xh.amax_idx = d->amax_idx; xh.gx_out = &gx; xh.skip = skip; xh.amax_val2 = d->amax_val2;
     launch_gemv(e, d->head, d->p_ni, 1, nullptr, LG_EPI_HEAD, 1, xh);
-    launch_k(e, lg_argmax_final, dim3(1), dim3(256), 0, d->amax_val, d->amax_idx, gx, d->best);
-    launch_k(e, lg_store_draft, dim3(1), dim3(1), 0, e->st, slot, d->best);
+    launch_k(e, lg_argmax_final, dim3(1), dim3(256), 0, (const float *)d->amax_val, (const int *)d->amax_idx, gx, d->best, (const float *)d->amax_val2, d->margin);
+    launch_k(e, lg_store_draft, dim3(1), dim3(1), 0, e->st, slot, (const int *)d->best, (const float *)d->margin, (const float *)e->d_margin_thr);
 }
 
 DraftW *draft_for(Engine *e, struct mtp *t, const struct kvcache *kv) {
@@ -1801,9 +1813,10 @@ int mtp_draft_device(struct mtp *t, const struct model *m, const struct kvcache 
         h->pos = pos;                                    // what the chained-draft call derives its slot from
         return e->lazy.toks[1];
     }
-    h->pos = pos; h->toks[0] = token;
+    h->pos = pos; h->toks[0] = token; h->stop = 0;
     LG_CHECK(cudaMemcpyAsync(e->st, h, sizeof(int) * 2, cudaMemcpyHostToDevice, e->stream));
     LG_CHECK(cudaMemcpyAsync(&e->st->dpos, &h->pos, sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    LG_CHECK(cudaMemcpyAsync(&e->st->stop, &h->stop, sizeof(int), cudaMemcpyHostToDevice, e->stream));
     run_draft(e, d, kv, 1, false);
     LG_CHECK(cudaMemcpyAsync(&h->toks[1], &e->st->toks[1], sizeof(int), cudaMemcpyDeviceToHost, e->stream));
     LG_CHECK(cudaStreamSynchronize(e->stream));
@@ -1906,6 +1919,16 @@ void lg_set_replay_origin(struct model *m, int offset, int enable) {
     Engine *e = engine_for(m);
     e->replay_off = offset; e->lazy_replay = enable != 0; e->lazy.valid = false;
 }
+// Confidence early-exit of the draft head: a draft whose best logit leads the runner-up by less than `margin` calls off the
+// drafts after it in that round (their forwards are skipped, their slots repeat the previous token and the verify rejects
+// them).  0 = never (default; LG_DRAFT_MARGIN sets it at load).  Drafts never change the output, only the cost of a round.
+void lg_set_draft_margin(struct model *m, float margin) {
+    Engine *e = engine_for(m);
+    LG_CHECK(cudaStreamSynchronize(e->stream));
+    h2d_sync(e->d_margin_thr, &margin, 4);
+    e->lazy.valid = false;
+}
+long long lg_drafts_skipped(struct model *m) { return (long long)engine_for(m)->st_host->n_skipped; }   // as of the latest lg_rounds_collect
 // Blocking device-to-host waits the reference-shaped calls have made so far (the benchmark reports waits per round).
 long long lg_host_syncs(struct model *m) { return engine_for(m)->host_syncs; }
 

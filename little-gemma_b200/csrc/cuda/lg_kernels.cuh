@@ -395,6 +395,7 @@ struct LgNormArgs {
     int n; float eps;
     __half *yh; int ldyh;                // optional f16 copy (input of the wide prompt matmul; single-CTA kernel only)
     int tag;                             // launch index for LG_STAMP (profiling builds)
+    const int *skip;                     // optional: non-zero -> the launch does nothing (a draft that was called off)
 };
 
 struct LgGemvArgs {
@@ -415,6 +416,8 @@ struct LgGemvArgs {
     int n_valid_rows;          // rows >= this are padding
     float *amax_val;           // [gridDim.x][LG_MAXM] per-CTA best logit
     int *amax_idx;
+    float *amax_val2;          // optional [gridDim.x][LG_MAXM] per-CTA second-best logit (the draft head's confidence margin)
+    const int *skip;           // optional: non-zero -> the launch does nothing (a draft that was called off)
     int *err;
     // GeGLU epilogue: rows are interleaved (tile = 8 gate rows then the 8 matching up rows);
     // y = gelu_tanh(gate) * up goes straight into the next matmul's panel
@@ -557,6 +560,13 @@ lg_gemv_kernel(LgGemvArgs a) {
                     if (!panel_sent && ++issued == early) {
                         // a ring of weights is in flight; now the activations, which the previous kernel produced
                         pdl_wait();
+                        if (a.skip && *a.skip) {
+                            // called off: let the copies already in flight land (shared memory must not be released under
+                            // them), then leave; the consumers have left on the same word
+                            for (int i = 0; i < issued; i++) mbar_wait(full + (i % NS), 0);
+                            ok = false;
+                            break;
+                        }
                         uint32_t qb = (uint32_t)nsb_s * 256, sb = (uint32_t)nsb_s * 32;
                         mbar_expect_tx(pbar, NP * (qb + sb));
                         #pragma unroll
@@ -575,12 +585,13 @@ lg_gemv_kernel(LgGemvArgs a) {
     // ---------------- consumers ----------------
     constexpr int CT = LG_GEMV_CW * 32;
     constexpr int SLOTS = (R * NP * 64 + CT - 1) / CT;
-    float best_v[SLOTS]; int best_i[SLOTS];
+    float best_v[SLOTS], sec_v[SLOTS]; int best_i[SLOTS];
     #pragma unroll
-    for (int j = 0; j < SLOTS; j++) { best_v[j] = -INFINITY; best_i[j] = 0x7fffffff; }
+    for (int j = 0; j < SLOTS; j++) { best_v[j] = -INFINITY; sec_v[j] = -INFINITY; best_i[j] = 0x7fffffff; }
 
     pdl_wait();
     LG_STAMP(a.tag, 1);
+    if (a.skip && *a.skip) return;
     __shared__ float s_post[POST ? LG_MAXM : 1];
     // 1/rms of the deferred norm: a lane's partial sums of squares are all fetched here, before the first use (one memory
     // latency, hidden under the panel wait and the main loop); they are added in a fixed order just before the epilogue
@@ -815,7 +826,8 @@ lg_gemv_kernel(LgGemvArgs a) {
                         } else if (row < a.n_valid_rows) {
                             if (a.softcap > 0.0f) sum = a.softcap * tanhf(sum / a.softcap);
                             if (a.logits) a.logits[(size_t)tok * a.ldo + row] = sum;
-                            if (sum > best_v[j]) { best_v[j] = sum; best_i[j] = row; }   // rows ascend per slot: first max wins
+                            if (sum > best_v[j]) { sec_v[j] = best_v[j]; best_v[j] = sum; best_i[j] = row; }   // rows ascend per slot: first max wins
+                            else if (sum > sec_v[j]) sec_v[j] = sum;
                         }
                     }
                 }
@@ -827,54 +839,66 @@ lg_gemv_kernel(LgGemvArgs a) {
 
     if (EB == LG_EPI_HEAD) {
         // candidates of this CTA: one per (slot, thread); merge per token (larger value, lower index on ties)
-        float *cv = red; int *ci = (int *)(red + R * NP * 64);
+        float *cv = red; int *ci = (int *)(red + R * NP * 64); float *c2 = red + 2 * R * NP * 64;
         #pragma unroll
         for (int j = 0; j < SLOTS; j++) {
             int idx = threadIdx.x + j * CT;
-            if (idx < R * NP * 64) { cv[idx] = best_v[j]; ci[idx] = best_i[j]; }
+            if (idx < R * NP * 64) { cv[idx] = best_v[j]; ci[idx] = best_i[j]; c2[idx] = sec_v[j]; }
         }
         consumer_sync();
         if (threadIdx.x < a.M) {
             int tok = threadIdx.x, p = tok >> 2, tl = tok & 3;
-            float bv = -INFINITY; int bi = 0x7fffffff;
+            float bv = -INFINITY, s2 = -INFINITY; int bi = 0x7fffffff;
             for (int r = 0; r < R; r++)
                 for (int row = 0; row < 16; row++) {
                     int idx = ((r * NP + p) * 4 + tl) * 16 + row;
                     float v = cv[idx]; int i2 = ci[idx];
-                    if (v > bv || (v == bv && i2 < bi)) { bv = v; bi = i2; }
+                    if (v > bv || (v == bv && i2 < bi)) { s2 = fmaxf(s2, bv); bv = v; bi = i2; }
+                    else s2 = fmaxf(s2, v);
+                    s2 = fmaxf(s2, c2[idx]);
                 }
             a.amax_val[(size_t)blockIdx.x * LG_MAXM + tok] = bv;
             a.amax_idx[(size_t)blockIdx.x * LG_MAXM + tok] = bi;
+            if (a.amax_val2) a.amax_val2[(size_t)blockIdx.x * LG_MAXM + tok] = s2;
         }
     }
 }
 
 // Merge the per-CTA argmax candidates: out[tok] = index of the largest logit, lowest index on ties.
-__global__ void lg_argmax_final(const float *__restrict__ val, const int *__restrict__ idx, int n_parts, int *out) {
+// With val2 / margin: also the runner-up's value, margin[tok] = best - second best logit (the draft head's confidence).
+__device__ __forceinline__ void top2_merge(float &bv, int &bi, float &s2, float ov, int oi, float o2) {
+    if (ov > bv || (ov == bv && oi < bi)) { s2 = fmaxf(s2, bv); bv = ov; bi = oi; }
+    else s2 = fmaxf(s2, ov);
+    s2 = fmaxf(s2, o2);
+}
+__global__ void lg_argmax_final(const float *__restrict__ val, const int *__restrict__ idx, int n_parts, int *out,
+                                const float *__restrict__ val2, float *__restrict__ margin) {
     pdl_launch(); pdl_wait();
     int tok = blockIdx.x;
-    float bv = -INFINITY; int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < n_parts; i += blockDim.x) {
-        float v = val[(size_t)i * LG_MAXM + tok]; int x = idx[(size_t)i * LG_MAXM + tok];
-        if (v > bv || (v == bv && x < bi)) { bv = v; bi = x; }
-    }
-    __shared__ float sv[32]; __shared__ int si[32];
+    float bv = -INFINITY, s2 = -INFINITY; int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < n_parts; i += blockDim.x)
+        top2_merge(bv, bi, s2, val[(size_t)i * LG_MAXM + tok], idx[(size_t)i * LG_MAXM + tok], val2 ? val2[(size_t)i * LG_MAXM + tok] : -INFINITY);
+    __shared__ float sv[32], sv2[32]; __shared__ int si[32];
     #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
-        float ov = __shfl_xor_sync(0xffffffffu, bv, o); int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        float ov = __shfl_xor_sync(0xffffffffu, bv, o), o2 = __shfl_xor_sync(0xffffffffu, s2, o); int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        top2_merge(bv, bi, s2, ov, oi, o2);
     }
-    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; sv2[threadIdx.x >> 5] = s2; }
     __syncthreads();
     if (threadIdx.x < 32) {
         int nw = blockDim.x >> 5;
         bv = threadIdx.x < nw ? sv[threadIdx.x] : -INFINITY; bi = threadIdx.x < nw ? si[threadIdx.x] : 0x7fffffff;
+        s2 = threadIdx.x < nw ? sv2[threadIdx.x] : -INFINITY;
         #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
-            float ov = __shfl_xor_sync(0xffffffffu, bv, o); int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+            float ov = __shfl_xor_sync(0xffffffffu, bv, o), o2 = __shfl_xor_sync(0xffffffffu, s2, o); int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            top2_merge(bv, bi, s2, ov, oi, o2);
         }
-        if (threadIdx.x == 0) out[tok] = bi == 0x7fffffff ? 0 : bi;
+        if (threadIdx.x == 0) {
+            out[tok] = bi == 0x7fffffff ? 0 : bi;
+            if (margin) margin[tok] = bv - s2;
+        }
     }
 }
 
@@ -936,6 +960,7 @@ __global__ void lg_embed_rows(const uint4 *__restrict__ wq, const uint2 *__restr
 // ---------------------------------------------------------------------------------------------
 __global__ void lg_norm_kernel(LgNormArgs a) {
     pdl_launch(); pdl_wait();
+    if (a.skip && *a.skip) return;
     extern __shared__ float row[];       // 2n floats + 32
     float *rowx = row + a.n, *red = rowx + a.n;
     const int tok = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -1019,6 +1044,7 @@ __global__ void __launch_bounds__(LG_NORM_CL_THREADS) lg_norm_cluster_kernel(LgN
     LG_STAMP_KIND(a.tag, 7);
     pdl_wait();
     LG_STAMP(a.tag, 1);
+    if (a.skip && *a.skip) return;                       // the whole cluster leaves on the same word: nobody waits at a cluster barrier
     float *x = a.x + (size_t)tok * a.ldx;
     float ss2 = 0.0f;
     if (a.add_src && cnt <= LG_NORM_CL_EPT * LG_NORM_CL_THREADS && a.n_parts <= 4) {
@@ -1159,6 +1185,7 @@ struct LgAttnArgs {
     __half *out_h; int ld_h;       // and/or f16 rows [M][ld_h] (input of the wide prompt matmul)
     int tag;                       // launch index for LG_STAMP (profiling builds)
     int *err;                      // status word for bounded waits that gave up (may be null)
+    const int *skip;               // optional: non-zero -> the launch does nothing (a draft that was called off)
 };
 
 #define LG_ATTN_THREADS 256
@@ -1240,7 +1267,7 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_kernel(LgAttnArgs a) 
         for (int i = threadIdx.x; i < HD; i += LG_ATTN_THREADS) { s_qn[i] = a.q_norm[i]; s_kn[i] = a.k_norm ? a.k_norm[i] : 1.0f; }
     // early_kv: the position and the cached rows below the block were written by earlier graph launches (this layer
     // writes its own rows, and only here), so the tile may start streaming before the previous kernel has finished
-    if (!a.early_kv) pdl_wait();
+    if (!a.early_kv) { pdl_wait(); if (a.skip && *a.skip) return; }
     constexpr int S = lg_attn_tile(HD), LDH = HD + 8, LDP = S + 8, PER = HD / 64, HALF = HD / 2, NW = LG_ATTN_THREADS / 32;
     const int kvh = blockIdx.x, gqa = a.H / a.Hkv, nq = gqa * a.M, nq16 = (nq + 15) & ~15;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -1562,6 +1589,8 @@ struct LgRoundState {          // lives in device memory; one per session
     int n_emitted;             // tokens appended to the log so far
     int n_draft, n_accept;
     int dpos;                  // position the draft head is drafting for
+    int stop;                  // this round's remaining drafts are called off (a draft's confidence margin fell below the threshold)
+    int n_skipped;             // drafts called off so far
 };
 // After a verify of M rows: adv = 1 + run of out[j-1] == toks[j]; append toks[1..adv-1] and
 // out[adv-1] to the token log; next round starts at pos+adv with toks[0] = out[adv-1];
@@ -1606,7 +1635,15 @@ __global__ void lg_copy_f32(float *__restrict__ dst, const float *__restrict__ s
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) dst[i] = src[i];
 }
-__global__ void lg_set_draft_pos(LgRoundState *st, int j) { pdl_launch(); pdl_wait(); st->dpos = st->pos + j; }
+__global__ void lg_set_draft_pos(LgRoundState *st, int j) { pdl_launch(); pdl_wait(); st->dpos = st->pos + j; if (j == 0) st->stop = 0; }
 // slots a head cannot draft repeat the previous token, so the verify simply rejects them
 __global__ void lg_pad_drafts(LgRoundState *st, int from, int M) { pdl_launch(); pdl_wait(); for (int j = from; j < M; j++) st->toks[j] = st->toks[j - 1]; }
-__global__ void lg_store_draft(LgRoundState *st, int j, const int *best) { pdl_launch(); pdl_wait(); st->toks[j] = *best; }
+// Draft j is in: keep it -- or, when the round's drafting was called off before it ran, repeat the previous token (the
+// verify then rejects the slot, as for a head that cannot chain).  A draft whose confidence margin (best - second best
+// logit) is below *thr calls off the drafts after it: they would most likely be rejected, and their forwards are skipped.
+__global__ void lg_store_draft(LgRoundState *st, int j, const int *best, const float *margin, const float *thr) {
+    pdl_launch(); pdl_wait();
+    if (st->stop) { st->toks[j] = st->toks[j - 1]; st->n_skipped++; return; }
+    st->toks[j] = *best;
+    if (thr && margin && *margin < *thr) st->stop = 1;
+}

@@ -196,3 +196,32 @@ def test_a_wait_that_runs_out_reports_and_returns(lg):
         assert g.L.lg_debug_bounded_wait(g.model, 1024) == 1      # LG_ERR_MBAR_TIMEOUT: the wait ran out and said so
         assert g.L.lg_debug_bounded_wait(g.model, 0) == -1        # bad argument, no launch
         assert g.next(5, 0) == before                              # the engine and the context still work
+
+
+def test_low_confidence_drafts_are_called_off_and_the_output_does_not_change(lg):
+    """Variable draft length: with the margin threshold out of reach every round drafts once and skips the two chained
+    drafts; with the threshold off none is skipped.  The emitted stream is the plain greedy one in every case."""
+    s = synth_module()
+    tp, hp = model_files("mid")
+    with lg.Session(tp, hp, 1024, mtp_n=4) as g:
+        prompt = s.prompt_ids(20, g.n_vocab, seed=47)
+        plain, _ = g.generate(prompt, 48, 0)
+    with lg.Session(tp, hp, 1024, mtp_n=4) as g:
+        g.set_draft_margin(1e30)
+        dev, st = g.generate_device(prompt, 48, 1)
+        assert np.array_equal(dev[:48], plain)
+        rounds = st[0] // 3
+        assert rounds > 0 and g.drafts_skipped() == 2 * rounds
+    with lg.Session(tp, hp, 1024, mtp_n=4) as g:
+        g.set_draft_margin(0.0)
+        dev, st = g.generate_device(prompt, 48, 1)
+        assert np.array_equal(dev[:48], plain) and g.drafts_skipped() == 0
+    with lg.Session(tp, hp, 1024, mtp_n=4) as g:
+        g.set_draft_margin(1e30)
+        host, _ = g.generate(prompt, 48, 1)                     # the blocking calls see the padded slots and still agree
+        assert np.array_equal(host, plain)
+    with lg.Session(tp, hp, 1024, mtp_n=4) as g:
+        # a finite threshold: some rounds stop early, some do not -- the stream still does not move
+        g.set_draft_margin(0.05)
+        dev, st = g.generate_device(prompt, 48, 1)
+        assert np.array_equal(dev[:48], plain)
