@@ -107,12 +107,17 @@ lg_attn_cluster_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_con
     LG_STAMP(a.tag, 1);
 
     const int g = lane >> 2, t = lane & 3;
-    constexpr int PVW = HD / 16 < NW ? HD / 16 : NW, DW = HD / PVW, NT = DW / 8;
-    float o[2][NT][4];                                        // accumulators of up to 32 query rows, kept across this CTA's tiles
+    // Both products run "transposed": keys (QK^T) or head dims (PV) are the 16-row M side of the tensor-core tile and the
+    // queries its 8-column N side, so a block of up to 8 query rows -- the usual case: 4 tokens x 2 heads per KV head --
+    // costs one tile column instead of a 16-row tile that is half padding.
+    constexpr int KW = S / 16;                                 // warps that hold a 16-key row tile of the scores
+    constexpr int PVW = HD / 16 < NW ? HD / 16 : NW, MTW = HD / 16 / PVW;      // warps on PV; 16-dim row tiles per such warp
+    const int nq8 = (nq + 7) >> 3;                             // 8-query column tiles (at most 4)
+    float o[MTW][4][4];                                        // O^T accumulators [dim tile][query tile][frag], kept across this CTA's tiles
     #pragma unroll
-    for (int mt = 0; mt < 2; mt++)
+    for (int mt = 0; mt < MTW; mt++)
         #pragma unroll
-        for (int n = 0; n < NT; n++) o[mt][n][0] = o[mt][n][1] = o[mt][n][2] = o[mt][n][3] = 0.0f;
+        for (int n = 0; n < 4; n++) o[mt][n][0] = o[mt][n][1] = o[mt][n][2] = o[mt][n][3] = 0.0f;
 
     if (live) {
         // ---- queries: per-head RMSNorm + RoPE, split into f16 hi + lo (once per CTA) ----
@@ -175,46 +180,49 @@ lg_attn_cluster_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_con
             }
             if (T == T_first) LG_STAMP(a.tag, 3);
 
-            // ---- scores: warp w takes keys [w*S/8, (w+1)*S/8); keys past a query's position or before its window: -inf ----
-            constexpr int KPW = S / NW, NKT = KPW / 8;
-            for (int mt = 0; mt < nmt; mt++) {
-                float c0[NKT][4];
+            // ---- scores S^T = K Q^T: warp w < KW holds keys [16w, 16w + 16) as the tile's rows, 8 queries per column tile;
+            //      keys past a query's position or before its window: -inf ----
+            if (warp < KW) {
+                float c0[4][4];
                 #pragma unroll
-                for (int n = 0; n < NKT; n++) c0[n][0] = c0[n][1] = c0[n][2] = c0[n][3] = 0.0f;
-                const __half *qa_hi = qhi + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + (lane >> 4) * 8;
-                const __half *qa_lo = qlo + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + (lane >> 4) * 8;
+                for (int n = 0; n < 4; n++) c0[n][0] = c0[n][1] = c0[n][2] = c0[n][3] = 0.0f;
+                const int krow = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, kcol = (lane >> 4) * 8;
                 #pragma unroll 2
                 for (int k0 = 0; k0 < HD; k0 += 32) {
-                    uint32_t ah[4], al[4], ah2[4], al2[4];
-                    ldsm_x4(ah, qa_hi + k0); ldsm_x4(al, qa_lo + k0);
-                    ldsm_x4(ah2, qa_hi + k0 + 16); ldsm_x4(al2, qa_lo + k0 + 16);
+                    uint32_t ka[4], kb2[4];                    // A operands: 16 keys x dims k0..k0+15 and k0+16..k0+31
+                    ldsm_x4(ka, kv_at<S>(sk, krow, k0 + kcol));
+                    ldsm_x4(kb2, kv_at<S>(sk, krow, k0 + 16 + kcol));
                     #pragma unroll
-                    for (int n = 0; n < NKT; n++) {
-                        uint32_t b[4];                          // 4 matrices: key rows n*8.., dims k0, +8, +16, +24
-                        ldsm_x4(b, kv_at<S>(sk, warp * KPW + n * 8 + (lane & 7), k0 + (lane >> 3) * 8));
-                        mma_f16(c0[n], ah, b[0], b[1]); mma_f16(c0[n], al, b[0], b[1]);
-                        mma_f16(c0[n], ah2, b[2], b[3]); mma_f16(c0[n], al2, b[2], b[3]);
+                    for (int n = 0; n < 4; n++) {
+                        if (n >= nq8) break;
+                        uint32_t bh[4], bl[4];                  // B operands: 8 queries x dims k0, +8, +16, +24 (hi and lo halves of q)
+                        ldsm_x4(bh, qhi + (size_t)(n * 8 + (lane & 7)) * LDH + k0 + (lane >> 3) * 8);
+                        ldsm_x4(bl, qlo + (size_t)(n * 8 + (lane & 7)) * LDH + k0 + (lane >> 3) * 8);
+                        mma_f16(c0[n], ka, bh[0], bh[1]); mma_f16(c0[n], ka, bl[0], bl[1]);
+                        mma_f16(c0[n], kb2, bh[2], bh[3]); mma_f16(c0[n], kb2, bl[2], bl[3]);
                     }
                 }
                 #pragma unroll
-                for (int h2 = 0; h2 < 2; h2++) {
-                    const int qi = mt * 16 + g + h2 * 8;
-                    const int pj = pos0 + qi / gqa + a.qpos_off;
-                    const int lo = a.window > 0 ? max(0, pj + a.win_shrink - a.window + 1) : 0;
+                for (int n = 0; n < 4; n++) {
+                    if (n >= nq8) break;
                     #pragma unroll
-                    for (int n = 0; n < NKT; n++)
+                    for (int e = 0; e < 2; e++) {
+                        const int qi = n * 8 + t * 2 + e;
+                        const int pj = pos0 + qi / gqa + a.qpos_off;
+                        const int lo = a.window > 0 ? max(0, pj + a.win_shrink - a.window + 1) : 0;
                         #pragma unroll
-                        for (int e = 0; e < 2; e++) {
-                            const int key = warp * KPW + n * 8 + t * 2 + e, p = T * S + key;
+                        for (int h2 = 0; h2 < 2; h2++) {
+                            const int key = warp * 16 + g + h2 * 8, p = T * S + key;
                             sc[(size_t)qi * S + key] = (qi < nq && p >= lo && p <= pj) ? c0[n][h2 * 2 + e] : -INFINITY;
                         }
+                    }
                 }
             }
             __syncthreads();
 
             // ---- online softmax, one warp per query row: new running max, the tile's weights against it, the rescale of
             //      what was accumulated before (exactly 1 when the tile adds nothing for this row) ----
-            for (int qi = warp; qi < nq16; qi += NW) {
+            for (int qi = warp; qi < nq8 * 8; qi += NW) {
                 float sv_[S / 32], mx = -INFINITY;
                 #pragma unroll
                 for (int j = 0; j < S / 32; j++) { sv_[j] = sc[(size_t)qi * S + lane + 32 * j]; mx = fmaxf(mx, sv_[j]); }
@@ -239,26 +247,35 @@ lg_attn_cluster_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_con
             }
             __syncthreads();
 
-            // ---- O = alpha O + P V: PVW warps split the head dims ----
+            // ---- O^T = alpha O^T + V^T P^T: warp w < PVW holds MTW tiles of 16 head dims as rows, 8 queries per column tile ----
             if (warp < PVW) {
                 #pragma unroll
-                for (int mt = 0; mt < 2; mt++) {
-                    if (mt >= nmt) break;
-                    const float a0 = row_a[mt * 16 + g], a1 = row_a[mt * 16 + g + 8];
+                for (int n = 0; n < 4; n++) {
+                    if (n >= nq8) break;
+                    const float a0 = row_a[n * 8 + t * 2], a1 = row_a[n * 8 + t * 2 + 1];
                     #pragma unroll
-                    for (int n = 0; n < NT; n++) { o[mt][n][0] *= a0; o[mt][n][1] *= a0; o[mt][n][2] *= a1; o[mt][n][3] *= a1; }
-                    const __half *pa_hi = phi + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDP + (lane >> 4) * 8;
-                    const __half *pa_lo = plo + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDP + (lane >> 4) * 8;
+                    for (int mt = 0; mt < MTW; mt++) { o[mt][n][0] *= a0; o[mt][n][1] *= a1; o[mt][n][2] *= a0; o[mt][n][3] *= a1; }
+                }
+                #pragma unroll
+                for (int k0 = 0; k0 < S; k0 += 32) {
+                    uint32_t ph[4][4], pl[4][4];                // B operands: 8 queries x keys k0, +8, +16, +24 (hi and lo halves of P)
                     #pragma unroll
-                    for (int k0 = 0; k0 < S; k0 += 16) {
-                        uint32_t ah[4], al[4];
-                        ldsm_x4(ah, pa_hi + k0); ldsm_x4(al, pa_lo + k0);
+                    for (int n = 0; n < 4; n++) {
+                        if (n >= nq8) break;
+                        ldsm_x4(ph[n], phi + (size_t)(n * 8 + (lane & 7)) * LDP + k0 + (lane >> 3) * 8);
+                        ldsm_x4(pl[n], plo + (size_t)(n * 8 + (lane & 7)) * LDP + k0 + (lane >> 3) * 8);
+                    }
+                    #pragma unroll
+                    for (int mt = 0; mt < MTW; mt++) {
+                        const int d0 = (warp * MTW + mt) * 16;
+                        uint32_t va[4], vb[4];                  // A operands (transposed loads): 16 dims x keys k0..k0+15, k0+16..k0+31
+                        ldsm_x4_t(va, kv_at<S>(sv, k0 + (lane & 7) + (lane >> 4) * 8, d0 + ((lane >> 3) & 1) * 8));
+                        ldsm_x4_t(vb, kv_at<S>(sv, k0 + 16 + (lane & 7) + (lane >> 4) * 8, d0 + ((lane >> 3) & 1) * 8));
                         #pragma unroll
-                        for (int n = 0; n < NT; n += 2) {
-                            uint32_t b[4];                      // key rows k0.. (two halves of 8), dims warp*DW + n*8, +8
-                            ldsm_x4_t(b, kv_at<S>(sv, k0 + (lane & 7) + ((lane >> 3) & 1) * 8, warp * DW + n * 8 + (lane >> 4) * 8));
-                            mma_f16(o[mt][n], ah, b[0], b[1]); mma_f16(o[mt][n], al, b[0], b[1]);
-                            mma_f16(o[mt][n + 1], ah, b[2], b[3]); mma_f16(o[mt][n + 1], al, b[2], b[3]);
+                        for (int n = 0; n < 4; n++) {
+                            if (n >= nq8) break;
+                            mma_f16(o[mt][n], va, ph[n][0], ph[n][1]); mma_f16(o[mt][n], va, pl[n][0], pl[n][1]);
+                            mma_f16(o[mt][n], vb, ph[n][2], ph[n][3]); mma_f16(o[mt][n], vb, pl[n][2], pl[n][3]);
                         }
                     }
                 }
@@ -268,14 +285,17 @@ lg_attn_cluster_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_con
         __syncthreads();
         if (warp < PVW) {
             #pragma unroll
-            for (int mt = 0; mt < 2; mt++) {
-                if (mt >= nmt) break;
+            for (int mt = 0; mt < MTW; mt++) {
+                const int d0 = (warp * MTW + mt) * 16;
                 #pragma unroll
-                for (int h2 = 0; h2 < 2; h2++) {
-                    const int qi = mt * 16 + g + h2 * 8;
+                for (int n = 0; n < 4; n++) {
+                    if (n >= nq8) break;
                     #pragma unroll
-                    for (int n = 0; n < NT; n++)
-                        *(float2 *)(opart + (size_t)qi * HD + warp * DW + n * 8 + t * 2) = make_float2(o[mt][n][h2 * 2], o[mt][n][h2 * 2 + 1]);
+                    for (int e = 0; e < 2; e++) {
+                        const int qi = n * 8 + t * 2 + e;
+                        opart[(size_t)qi * HD + d0 + g] = o[mt][n][e];
+                        opart[(size_t)qi * HD + d0 + g + 8] = o[mt][n][2 + e];
+                    }
                 }
             }
         }

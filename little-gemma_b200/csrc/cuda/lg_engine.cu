@@ -26,6 +26,7 @@
     fprintf(stderr, "lg_b200: CUDA error %s at %s:%d\n", cudaGetErrorString(e_), __FILE__, __LINE__); exit(1); } } while (0)
 
 extern "C" const int model_kv_host = 0;      // cache rows live on the device: mtp.c must call the device hooks
+extern "C" int lg_set_replay(struct model *m, const int *replay, int n);
 
 namespace {
 
@@ -397,8 +398,12 @@ void set_kernel_attributes() {
 // Decomposition of one matmul into CTA work items: R row tiles x one of ks column slices, walked
 // by a persistent grid of about two CTAs per SM.  Few slices (each slice's partial costs an extra
 // pass in the consumer), and as many row tiles per item as still leave enough items to balance.
-GemvPlan plan_gemv(const Engine *e, const WMat &W, int np, int want_ks, bool head, bool geglu = false) {
+GemvPlan plan_gemv(const Engine *e, const WMat &W, int np_actual, int want_ks, bool head, bool geglu = false) {
     GemvPlan p;
+    // The decomposition (row tiles per item, k slices) fixes the order in which a row's products are added, so it must not
+    // depend on the block width: it is planned for two activation panels (5..8 rows) always; only the shared memory and the
+    // ring depth at the end follow the panels this launch really has.
+    const int np = 2;
     static const int cta_mult = env_int("LG_GEMV_CTAS_PER_SM", 2);
     const int ctas = e->sm_count * cta_mult;
     static const int force_r = env_int("LG_GEMV_R", 0), force_ks = env_int("LG_GEMV_KS", 0);
@@ -434,6 +439,7 @@ GemvPlan plan_gemv(const Engine *e, const WMat &W, int np, int want_ks, bool hea
         if (p.smem <= GEMV_SMEM_MAX || p.ks >= e->max_ks || p.ks * 2 > W.nkp || head || geglu) break;
         p.ks *= 2;                                   // the slice's panel does not fit: cut k finer
     }
+    gemv_pick_stages(p, np_actual, (W.nkp + p.ks - 1) / p.ks + 1, W.fmt, false);
     // items beyond one wave: spread them evenly -- every CTA walks the same number of items (or one fewer), so no CTA
     // is still on its second item while the others have left
     int groups = (W.n_row_tiles + p.r - 1) / p.r;
@@ -1071,7 +1077,7 @@ void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags, int 
         static const int early_kv = env_int("LG_ATTN_EARLY_KV", 1);
         aa.early_kv = early_kv && w.owns_kv;     // the target's position and this layer's older rows come from earlier graph launches
         static const int deep_local = env_int("LG_ATTN_DEEP_LOCAL", 0);
-        const int deepG = (w.local && !deep_local) ? 0 : deep_span_tiles(e, kv->max_seq, w.nkv, hd, (H / w.nkv) * M);
+        const int deepG = (w.local && !deep_local) ? 0 : deep_span_tiles(e, kv->max_seq, w.nkv, hd, (H / w.nkv) * LG_MAXM);
         if (only & C_ATTN) {
             const int cl = deepG ? 0 : attn_cluster_size(e, aa.window, kv->max_seq, aa.seq, hd, H, w.nkv);
             if (deepG) launch_attn_deep(e, aa, kv->max_seq, deepG);
@@ -1084,7 +1090,9 @@ void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags, int 
         GemvExtra xo; xo.ks_out = &ks_o;
         // (class-isolated timing passes keep the o-projection a pure matmul followed by the norm kernel unless C_FUSED asks
         // for the variants the full step runs)
-        const bool tail_o = ((only & C_ALL) == C_ALL || (only & C_FUSED)) && normtail_ok(e, w.o, M > 4 ? 2 : 1);
+            // (decided for the widest block, never for this block's width: a verify row must run the very kernels -- and so
+        // carry the very bits -- of the plain decode step at its position)
+        const bool tail_o = ((only & C_ALL) == C_ALL || (only & C_FUSED)) && normtail_ok(e, w.o, 2) && normtail_ok(e, w.o, 1);
         // gate/up with the GeGLU epilogue writing the down-projection's panel
         LgPanel pf = e->p_ff; pf.nsb = w.nff / 32;
         GemvExtra xg; xg.outp = &pf;
@@ -1571,6 +1579,9 @@ int spec_n(struct model *m, struct kvcache *kv, int n, const int *toks, int pos,
 // width n, greedy acceptance; `advance` also moves the device state on to the next round (device-resident rounds).
 cudaGraphExec_t round_graph(Engine *e, const struct kvcache *kv, DraftW *d, int n, bool replay, bool advance) {
     bind_kv(e, kv);
+    // a round that replays drafts needs the table's device addresses at capture time: with none set yet, make the empty one
+    // (its address stays valid when a table is set later; only growing past its capacity rebuilds the round graphs)
+    if (replay && !e->replay) lg_set_replay(const_cast<struct model *>(e->m), nullptr, 0);
     char key[48];
     snprintf(key, sizeof key, "r%d_%d_%d_%d", n, replay ? 1 : 0, d ? 1 : 0, advance ? 1 : 0);
     auto it = e->graphs.find(key);
@@ -1712,38 +1723,46 @@ static void prefill_impl(struct model *m, struct kvcache *kv, const float *rows,
     }
     int i = 0;
     if (prefill_wide_ok(e) && n >= 4 * LG_MAXM) {
-        // whole blocks of up to LG_PF_MAXN tokens (a multiple of the attention group) on the wide pass
+        // Blocks of up to LG_PF_MAXN tokens on the wide pass.  A ragged tail of more than one attention group is padded to
+        // a whole number of groups by repeating the last token (src/cuda/prefill-kernel.cuh:631-660 pads its tail the same
+        // way): the cache rows the pad positions write lie past the prompt, where the next step overwrites them before any
+        // query can see them.  Host staging of every block stays alive until the single synchronisation at the end.
         bind_kv(e, kv);
         prefill_alloc(e);
-        int gpos[LG_PF_MAXN / LG_MAXM];
-        std::vector<float> stage;
-        while (n - i >= 4 * LG_MAXM) {
-            const int b = std::min(LG_PF_MAXN, (n - i) / LG_MAXM * LG_MAXM);
-            for (int g = 0; g < LG_PF_MAXN / LG_MAXM; g++) gpos[g] = pos0 + i + g * LG_MAXM;
+        std::vector<std::vector<int>> gpos_all, toks_all, ridx_all;
+        std::vector<std::vector<float>> stage_all;
+        while (n - i > LG_MAXM) {                                    // a last group of <= 8 tokens is cheaper on the verify path
+            const int real = std::min(LG_PF_MAXN, n - i);
+            const int b = (real + LG_MAXM - 1) / LG_MAXM * LG_MAXM;
+            if ((long long)pos0 + i + b > kv->max_seq) break;          // pad rows would wrap onto the cache's first rows: narrow path
+            gpos_all.emplace_back(LG_PF_MAXN / LG_MAXM);
+            for (int g = 0; g < LG_PF_MAXN / LG_MAXM; g++) gpos_all.back()[g] = pos0 + i + g * LG_MAXM;
+            toks_all.emplace_back(b);
+            ridx_all.emplace_back(b, -1);
+            stage_all.emplace_back();
+            std::vector<int> &bt = toks_all.back(), &br = ridx_all.back();
+            std::vector<float> &stage = stage_all.back();
             bool blk_media = false;
-            if (media) {                                 // this block's media rows, packed
-                stage.clear();
-                for (int j = 0; j < b; j++) {
-                    ridx[i + j] = -1;
-                    if (ids[i + j] < 0) {
-                        ridx[i + j] = (int)(stage.size() / ne);
-                        const float *r = rows + (size_t)(-ids[i + j] - 1) * ne;
-                        stage.insert(stage.end(), r, r + ne);
-                        blk_media = true;
-                    }
-                }
-                if (blk_media) {
-                    LG_CHECK(cudaMemcpyAsync(e->pf.rows, stage.data(), stage.size() * sizeof(float), cudaMemcpyHostToDevice, e->stream));
-                    LG_CHECK(cudaMemcpyAsync(e->pf.ridx, ridx.data() + i, sizeof(int) * b, cudaMemcpyHostToDevice, e->stream));
+            for (int j = 0; j < b; j++) {
+                const int src = i + std::min(j, real - 1);          // pad: the block's last token again
+                bt[j] = toks[src];
+                if (j < real && ids[src] < 0) {                      // this block's media rows, packed
+                    br[j] = (int)(stage.size() / ne);
+                    const float *r = rows + (size_t)(-ids[src] - 1) * ne;
+                    stage.insert(stage.end(), r, r + ne);
+                    blk_media = true;
                 }
             }
-            LG_CHECK(cudaMemcpyAsync(e->pf.toks, toks.data() + i, sizeof(int) * b, cudaMemcpyHostToDevice, e->stream));
-            LG_CHECK(cudaMemcpyAsync(e->pf.pos, gpos, sizeof gpos, cudaMemcpyHostToDevice, e->stream));
+            if (blk_media) {
+                LG_CHECK(cudaMemcpyAsync(e->pf.rows, stage.data(), stage.size() * sizeof(float), cudaMemcpyHostToDevice, e->stream));
+                LG_CHECK(cudaMemcpyAsync(e->pf.ridx, br.data(), sizeof(int) * b, cudaMemcpyHostToDevice, e->stream));
+            }
+            LG_CHECK(cudaMemcpyAsync(e->pf.toks, bt.data(), sizeof(int) * b, cudaMemcpyHostToDevice, e->stream));
+            LG_CHECK(cudaMemcpyAsync(e->pf.pos, gpos_all.back().data(), sizeof(int) * (LG_PF_MAXN / LG_MAXM), cudaMemcpyHostToDevice, e->stream));
             enqueue_prefill_block(e, kv, b, C_ALL, blk_media);
-            LG_CHECK(cudaStreamSynchronize(e->stream));  // the host staging above is read by the copies
-            i += b;
+            i += real;
         }
-        check_err(e);
+        check_err(e);                                               // the one wait: every copy above has read its host buffer by now
     }
     for (; i < n; i += LG_MAXM) {
         int b = n - i < LG_MAXM ? n - i : LG_MAXM;

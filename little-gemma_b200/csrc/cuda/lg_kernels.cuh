@@ -1626,7 +1626,8 @@ __global__ void lg_accept_kernel(LgRoundState *st, int M, const float *__restric
 __global__ void lg_replay_drafts_kernel(LgRoundState *st, int M, const int *__restrict__ replay, const int *__restrict__ n_replay) {
     pdl_launch(); pdl_wait();
     int j = threadIdx.x + 1;
-    if (j < M) { int i = st->n_emitted + j - 1; st->toks[j] = (i >= 0 && i < *n_replay) ? replay[i] : 0; }
+    const int n = (replay && n_replay) ? *n_replay : 0;      // no table set: every draft is token 0
+    if (j < M) { int i = st->n_emitted + j - 1; st->toks[j] = (i >= 0 && i < n) ? replay[i] : 0; }
 }
 
 // draft-head input: cat = [ embed(tok)*sqrt(nb) , h_prev ] is assembled by lg_embed_rows + this copy

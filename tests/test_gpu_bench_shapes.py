@@ -137,3 +137,26 @@ def test_bench_head_drafts_match_oracle(lg, port_built):
     o.close()
     print(f"12B-class head: draft tokens equal to the oracle's {same}/{total}")
     assert same >= total * 0.8
+
+
+@pytest.mark.parametrize("name", ["b12_cut", "b12k_cut", "e4b_cut", "hd512"])
+def test_verify_rows_carry_the_bits_of_plain_steps(lg, name):
+    """The logits rows of verify blocks of width 4, 5 and 8 (the sampling hook receives them) are bit-identical to the
+    logits of plain decode steps at the same positions: no kernel choice, tiling or summation order may depend on the
+    block width -- on these norms = 1 files a last-bit difference is enough to send a greedy stream elsewhere."""
+    from tests.test_gpu_serving import _Hook
+    s = synth_module()
+    tp, _ = model_files(name)
+    with lg.Session(tp, None, 512, mtp_n=4) as g:
+        stream = s.prompt_ids(48, g.n_vocab, seed=36)
+        g.prefill(stream[:16], 0)
+        plain = [g.forward(int(stream[i]), i) for i in range(16, 48)]
+    for n in (4, 5, 8):
+        with lg.Session(tp, None, 512, mtp_n=n) as g:
+            g.prefill(stream[:16], 0)
+            with _Hook(g.L, lambda row: int(row.argmax())) as h:
+                for p in range(16, 48 - n + 1, n):
+                    g.spec(stream[p:p + n], p)
+            assert len(h.rows) >= n
+            for j, row in enumerate(h.rows):
+                assert np.array_equal(row.view(np.uint32), plain[j].view(np.uint32)), (name, n, j)
