@@ -567,8 +567,8 @@ def main():
                     clocks=clocks, gpu_launches=int(launches_per_round * a.steps),
                     e2e={"value": agg["e2e_tok_s"], "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                          "rounds": e2e_rounds, "host_syncs_per_round": syncs_per_round},
-                    roofline={"bound": "hbm", "kernel": "lg_gemv_kernel (the step's epilogue variants: store, residual+norm tail, "
-                                                        "GeGLU with deferred norm, head)",
+                    roofline={"bound": "hbm", "kernel": "lg_gemv_kernel (the step's epilogue variants: store, complete rows + norm sums, "
+                                                        "GeGLU, head)",
                               "achieved": mm_gbs, "peak": peak, "unit": "GB/s",
                               "frac": mm_gbs / peak, "traffic": int(W * DRAM_TRAFFIC_RATIO), "peak_source": peak_src,
                               "traffic_note": "dram read+write bytes of the matmul pass: ncu capture of the E4B-class gate/up "

@@ -52,6 +52,7 @@ __device__ __forceinline__ __half *kv_at(__half *tile, int row, int col) {
 // grid (Hkv, C), cluster (1, C, 1).
 // dynamic smem (1024-byte aligned): K tile | V tile [HD/64][S][64] f16 swizzled (K later: the CTA's accumulators [NQ16][HD] f32)
 //               | Qhi | Qlo [NQ16][HD+8] f16 | scores [NQ16][S] f32 | Phi | Plo [NQ16][S+8] f16 | ml [NQ16] float2 | alpha [NQ16]
+//               | new K / V rows [2 LG_MAXM][HD] f16
 template <int HD>
 __global__ void __launch_bounds__(LG_ATTN_THREADS)
 lg_attn_cluster_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_constant__ CUtensorMap tmv, LgAttnArgs a) {
@@ -75,6 +76,7 @@ lg_attn_cluster_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_con
     __half *phi = (__half *)(sc + (size_t)nq16 * S), *plo = phi + (size_t)nq16 * LDP;
     float2 *ml = (float2 *)(plo + (size_t)nq16 * LDP);        // running (max, sum) of this CTA's tiles, per query
     float *row_a = (float *)(ml + nq16);
+    __half *kvnew = (__half *)(row_a + nq16);                 // [2 LG_MAXM][HD]: the block's own K / V rows (row 2 tok + isv)
     float *opart = (float *)sk;                               // [nq16][HD] f32, written once the last K tile has been consumed
 
     if (threadIdx.x == 0) mbar_init(&kv_bar, 1);
@@ -114,28 +116,22 @@ lg_attn_cluster_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_con
     constexpr int PVW = HD / 16 < NW ? HD / 16 : NW, MTW = HD / 16 / PVW;      // warps on PV; 16-dim row tiles per such warp
     const int nq8 = (nq + 7) >> 3;                             // 8-query column tiles (at most 4)
     float o[MTW][4][4];                                        // O^T accumulators [dim tile][query tile][frag], kept across this CTA's tiles
+    constexpr bool SPLIT = HD <= 256;                          // the lo half of P accumulates into a second set: two shorter chains
+    float o2[SPLIT ? MTW : 1][4][4];
     #pragma unroll
     for (int mt = 0; mt < MTW; mt++)
         #pragma unroll
-        for (int n = 0; n < 4; n++) o[mt][n][0] = o[mt][n][1] = o[mt][n][2] = o[mt][n][3] = 0.0f;
+        for (int n = 0; n < 4; n++) {
+            o[mt][n][0] = o[mt][n][1] = o[mt][n][2] = o[mt][n][3] = 0.0f;
+            if (SPLIT) o2[mt][n][0] = o2[mt][n][1] = o2[mt][n][2] = o2[mt][n][3] = 0.0f;
+        }
 
+    __syncthreads();                                          // the norm weights, ml and the barrier are in place
     if (live) {
-        // ---- queries: per-head RMSNorm + RoPE, split into f16 hi + lo (once per CTA) ----
-        for (int qi = warp; qi < nq16; qi += NW) {
-            float v0[PER], v1[PER];
-            if (qi < nq) {
-                const int tok = qi / gqa, hq = kvh * gqa + qi % gqa;
-                if (a.q_ready) {
-                    const float *src = a.qkv + ((size_t)tok * a.H + hq) * HD;
-                    #pragma unroll
-                    for (int e = 0; e < PER; e++) { v0[e] = src[lane * PER + e]; v1[e] = src[lane * PER + e + HALF]; }
-                } else {
-                    head_norm_rope<HD>(a.qkv + (size_t)tok * a.ld + (size_t)hq * HD, s_qn, a.rope + (size_t)tok * HALF, a.eps, lane, v0, v1);
-                }
-            } else {
-                #pragma unroll
-                for (int e = 0; e < PER; e++) v0[e] = v1[e] = 0.0f;
-            }
+        // ---- queries (per-head RMSNorm + RoPE, split into f16 hi + lo) and the block's own K / V rows that fall into
+        //      this CTA's tiles.  Every global load of a warp's first query row and of its K / V rows is issued before
+        //      the first use, so the prologue holds one memory latency instead of one per row. ----
+        auto store_q = [&](int qi, const float (&v0)[PER], const float (&v1)[PER]) {
             #pragma unroll
             for (int e = 0; e < PER; e++) {
                 int i = lane * PER + e;
@@ -144,6 +140,56 @@ lg_attn_cluster_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_con
                 qlo[(size_t)qi * LDH + i] = __float2half_rn(v0[e] - __half2float(h0));
                 qlo[(size_t)qi * LDH + i + HALF] = __float2half_rn(v1[e] - __half2float(h1));
             }
+        };
+        auto q_src = [&](int qi) {
+            const int tok = qi / gqa, hq = kvh * gqa + qi % gqa;
+            return a.q_ready ? a.qkv + ((size_t)tok * a.H + hq) * HD : a.qkv + (size_t)tok * a.ld + (size_t)hq * HD;
+        };
+        float qv0[PER], qv1[PER]; float2 qcs[PER];
+        float kv0[2][PER], kv1[2][PER]; float2 kcs[2][PER];
+        bool hask[2];
+        const bool hasq = warp < nq;
+        if (hasq) head_load<HD>(q_src(warp), a.q_ready ? nullptr : a.rope + (size_t)(warp / gqa) * HALF, lane, qv0, qv1, qcs);
+        #pragma unroll
+        for (int u = 0; u < 2; u++) {
+            const int j = warp + u * NW, tok = j >> 1, isv = j & 1, TT = (pos0 + tok) / S;
+            hask[u] = writes_kv && j < 2 * a.M && TT >= T_first && TT <= t_hi && (TT - T_first) % C == 0;
+            if (hask[u])
+                head_load<HD>(a.qkv + (size_t)tok * a.ld + (size_t)(a.H + ((isv && a.has_v) ? a.Hkv : 0) + kvh) * HD,
+                              isv ? nullptr : a.rope + (size_t)tok * HALF, lane, kv0[u], kv1[u], kcs[u]);
+        }
+        if (hasq) {
+            if (!a.q_ready) head_finish<HD>(s_qn, true, a.eps, lane, qv0, qv1, qcs);
+            store_q(warp, qv0, qv1);
+        }
+        #pragma unroll
+        for (int u = 0; u < 2; u++) {
+            if (!hask[u]) continue;
+            const int j = warp + u * NW, tok = j >> 1, isv = j & 1, p = pos0 + tok;
+            head_finish<HD>(isv ? nullptr : s_kn, !isv, a.eps, lane, kv0[u], kv1[u], kcs[u]);
+            __half *dst = (isv ? a.vc : a.kc) + (size_t)(p % a.seq) * a.kv_dim + (size_t)kvh * HD;
+            #pragma unroll
+            for (int e = 0; e < PER; e++) {
+                const __half h0 = __float2half_rn(kv0[u][e]), h1 = __float2half_rn(kv1[u][e]);
+                dst[lane * PER + e] = h0; dst[lane * PER + e + HALF] = h1;
+                kvnew[(size_t)j * HD + lane * PER + e] = h0; kvnew[(size_t)j * HD + lane * PER + e + HALF] = h1;
+            }
+        }
+        for (int qi = warp + (hasq ? NW : 0); qi < nq16; qi += NW) {
+            float v0[PER], v1[PER];
+            if (qi < nq) {
+                if (a.q_ready) {
+                    const float *src = q_src(qi);
+                    #pragma unroll
+                    for (int e = 0; e < PER; e++) { v0[e] = src[lane * PER + e]; v1[e] = src[lane * PER + e + HALF]; }
+                } else {
+                    head_norm_rope<HD>(q_src(qi), s_qn, a.rope + (size_t)(qi / gqa) * HALF, a.eps, lane, v0, v1);
+                }
+            } else {
+                #pragma unroll
+                for (int e = 0; e < PER; e++) v0[e] = v1[e] = 0.0f;
+            }
+            store_q(qi, v0, v1);
         }
         LG_STAMP(a.tag, 2);
 
@@ -158,22 +204,17 @@ lg_attn_cluster_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_con
             if (!mbar_wait(&kv_bar, parity) && a.err && lane == 0) atomicOr(a.err, LG_ERR_MBAR_TIMEOUT);
             parity ^= 1;
             if (writes_kv) {
-                // rows of the new positions that fall into this tile: K (norm + rope) and V (plain norm), f16 RNE, to the
-                // cache and -- over whatever the copy brought for those rows -- into the tile
+                // rows of the new positions that fall into this tile go over whatever the copy brought for them (the cache
+                // itself was written in the prologue)
                 for (int j = warp; j < 2 * a.M; j += NW) {
                     const int tok = j >> 1, isv = j & 1, p = pos0 + tok;
                     if (p / S != T) continue;
-                    float v0[PER], v1[PER];
-                    const float *src = a.qkv + (size_t)tok * a.ld + (size_t)(a.H + ((isv && a.has_v) ? a.Hkv : 0) + kvh) * HD;
-                    head_norm_rope<HD>(src, isv ? nullptr : s_kn, isv ? nullptr : a.rope + (size_t)tok * HALF, a.eps, lane, v0, v1);
-                    __half *dst = (isv ? a.vc : a.kc) + (size_t)(p % a.seq) * a.kv_dim + (size_t)kvh * HD;
                     __half *tile = isv ? sv : sk;
                     const int row = p - T * S;
                     #pragma unroll
                     for (int e = 0; e < PER; e++) {
-                        const __half h0 = __float2half_rn(v0[e]), h1 = __float2half_rn(v1[e]);
-                        dst[lane * PER + e] = h0; dst[lane * PER + e + HALF] = h1;
-                        *kv_at<S>(tile, row, lane * PER + e) = h0; *kv_at<S>(tile, row, lane * PER + e + HALF) = h1;
+                        *kv_at<S>(tile, row, lane * PER + e) = kvnew[(size_t)j * HD + lane * PER + e];
+                        *kv_at<S>(tile, row, lane * PER + e + HALF) = kvnew[(size_t)j * HD + lane * PER + e + HALF];
                     }
                 }
                 __syncthreads();
@@ -183,9 +224,13 @@ lg_attn_cluster_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_con
             // ---- scores S^T = K Q^T: warp w < KW holds keys [16w, 16w + 16) as the tile's rows, 8 queries per column tile;
             //      keys past a query's position or before its window: -inf ----
             if (warp < KW) {
-                float c0[4][4];
+                // four independent chains per column tile (first / second 16 dims of a step x hi / lo half of q): a chain is
+                // HD/32 dependent tensor-core instructions instead of HD/8
+                float c0[4][4], c1[4][4], c2[4][4], c3[4][4];
                 #pragma unroll
-                for (int n = 0; n < 4; n++) c0[n][0] = c0[n][1] = c0[n][2] = c0[n][3] = 0.0f;
+                for (int n = 0; n < 4; n++)
+                    #pragma unroll
+                    for (int f = 0; f < 4; f++) c0[n][f] = c1[n][f] = c2[n][f] = c3[n][f] = 0.0f;
                 const int krow = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, kcol = (lane >> 4) * 8;
                 #pragma unroll 2
                 for (int k0 = 0; k0 < HD; k0 += 32) {
@@ -198,10 +243,14 @@ lg_attn_cluster_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_con
                         uint32_t bh[4], bl[4];                  // B operands: 8 queries x dims k0, +8, +16, +24 (hi and lo halves of q)
                         ldsm_x4(bh, qhi + (size_t)(n * 8 + (lane & 7)) * LDH + k0 + (lane >> 3) * 8);
                         ldsm_x4(bl, qlo + (size_t)(n * 8 + (lane & 7)) * LDH + k0 + (lane >> 3) * 8);
-                        mma_f16(c0[n], ka, bh[0], bh[1]); mma_f16(c0[n], ka, bl[0], bl[1]);
-                        mma_f16(c0[n], kb2, bh[2], bh[3]); mma_f16(c0[n], kb2, bl[2], bl[3]);
+                        mma_f16(c0[n], ka, bh[0], bh[1]); mma_f16(c1[n], ka, bl[0], bl[1]);
+                        mma_f16(c2[n], kb2, bh[2], bh[3]); mma_f16(c3[n], kb2, bl[2], bl[3]);
                     }
                 }
+                #pragma unroll
+                for (int n = 0; n < 4; n++)
+                    #pragma unroll
+                    for (int f = 0; f < 4; f++) c0[n][f] = (c0[n][f] + c2[n][f]) + (c1[n][f] + c3[n][f]);
                 #pragma unroll
                 for (int n = 0; n < 4; n++) {
                     if (n >= nq8) break;
@@ -219,6 +268,7 @@ lg_attn_cluster_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_con
                 }
             }
             __syncthreads();
+            if (T == T_first) LG_STAMP(a.tag, 8);
 
             // ---- online softmax, one warp per query row: new running max, the tile's weights against it, the rescale of
             //      what was accumulated before (exactly 1 when the tile adds nothing for this row) ----
@@ -246,6 +296,7 @@ lg_attn_cluster_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_con
                 }
             }
             __syncthreads();
+            if (T == T_first) LG_STAMP(a.tag, 9);
 
             // ---- O^T = alpha O^T + V^T P^T: warp w < PVW holds MTW tiles of 16 head dims as rows, 8 queries per column tile ----
             if (warp < PVW) {
@@ -254,7 +305,10 @@ lg_attn_cluster_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_con
                     if (n >= nq8) break;
                     const float a0 = row_a[n * 8 + t * 2], a1 = row_a[n * 8 + t * 2 + 1];
                     #pragma unroll
-                    for (int mt = 0; mt < MTW; mt++) { o[mt][n][0] *= a0; o[mt][n][1] *= a1; o[mt][n][2] *= a0; o[mt][n][3] *= a1; }
+                    for (int mt = 0; mt < MTW; mt++) {
+                        o[mt][n][0] *= a0; o[mt][n][1] *= a1; o[mt][n][2] *= a0; o[mt][n][3] *= a1;
+                        if (SPLIT) { o2[mt][n][0] *= a0; o2[mt][n][1] *= a1; o2[mt][n][2] *= a0; o2[mt][n][3] *= a1; }
+                    }
                 }
                 #pragma unroll
                 for (int k0 = 0; k0 < S; k0 += 32) {
@@ -274,8 +328,8 @@ lg_attn_cluster_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_con
                         #pragma unroll
                         for (int n = 0; n < 4; n++) {
                             if (n >= nq8) break;
-                            mma_f16(o[mt][n], va, ph[n][0], ph[n][1]); mma_f16(o[mt][n], va, pl[n][0], pl[n][1]);
-                            mma_f16(o[mt][n], vb, ph[n][2], ph[n][3]); mma_f16(o[mt][n], vb, pl[n][2], pl[n][3]);
+                            mma_f16(o[mt][n], va, ph[n][0], ph[n][1]); mma_f16(SPLIT ? o2[mt][n] : o[mt][n], va, pl[n][0], pl[n][1]);
+                            mma_f16(o[mt][n], vb, ph[n][2], ph[n][3]); mma_f16(SPLIT ? o2[mt][n] : o[mt][n], vb, pl[n][2], pl[n][3]);
                         }
                     }
                 }
@@ -283,6 +337,7 @@ lg_attn_cluster_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_con
         }
         // ---- this CTA's accumulators go where the K tile was (every warp is past its last use of K) ----
         __syncthreads();
+        LG_STAMP(a.tag, 10);
         if (warp < PVW) {
             #pragma unroll
             for (int mt = 0; mt < MTW; mt++) {
@@ -293,8 +348,8 @@ lg_attn_cluster_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_con
                     #pragma unroll
                     for (int e = 0; e < 2; e++) {
                         const int qi = n * 8 + t * 2 + e;
-                        opart[(size_t)qi * HD + d0 + g] = o[mt][n][e];
-                        opart[(size_t)qi * HD + d0 + g + 8] = o[mt][n][2 + e];
+                        opart[(size_t)qi * HD + d0 + g] = SPLIT ? o[mt][n][e] + o2[mt][n][e] : o[mt][n][e];
+                        opart[(size_t)qi * HD + d0 + g + 8] = SPLIT ? o[mt][n][2 + e] + o2[mt][n][2 + e] : o[mt][n][2 + e];
                     }
                 }
             }
@@ -316,16 +371,17 @@ lg_attn_cluster_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_con
         if (pj >= 0) {
             const int lo = a.window > 0 ? max(0, pj + a.win_shrink - a.window + 1) : 0;
             const int i0 = lo / S - t_lo, i1 = min(pj / S - t_lo, i0 + C - 1);      // ranks that hold tiles of this query
+            // every remote load of this item -- the ranks' (max, sum) pairs and their accumulators of this lane's dim --
+            // is issued before the first use; the sums then run in ascending rank order
             float2 v = make_float2(-INFINITY, 0.0f);
             if (lane < C && lane >= i0 && lane <= i1) v = dsmem_ld_f32x2(dsmem_addr(ml + qi, (uint32_t)lane));
-            const bool ok = v.y > 0.0f;
-            const float mx = warp_max(ok ? v.x : -INFINITY);
-            const float w = ok ? expf(v.x - mx) : 0.0f;
-            // the ranks' accumulators of this lane's dim: all loads first, then the sums in ascending rank order
             float ov[LG_ATTN_CL_MAX];
             #pragma unroll
             for (int i = 0; i < LG_ATTN_CL_MAX; i++)
                 ov[i] = (i < C && i >= i0 && i <= i1) ? dsmem_ld_f32(dsmem_addr(opart + (size_t)qi * HD + d, (uint32_t)i)) : 0.0f;
+            const bool ok = v.y > 0.0f;
+            const float mx = warp_max(ok ? v.x : -INFINITY);
+            const float w = ok ? expf(v.x - mx) : 0.0f;
             float acc = 0.0f, lsum = 0.0f;
             #pragma unroll
             for (int i = 0; i < LG_ATTN_CL_MAX; i++) {
@@ -347,5 +403,5 @@ lg_attn_cluster_kernel(const __grid_constant__ CUtensorMap tmk, const __grid_con
 
 inline size_t attn_cluster_smem(int nq, int hd) {
     size_t nq16 = (size_t)((nq + 15) & ~15), ldh = hd + 8, S = lg_attn_tile(hd);
-    return 1024 + 2 * S * hd * 2 + 2 * nq16 * ldh * 2 + nq16 * S * 4 + 2 * nq16 * (S + 8) * 2 + nq16 * 12 + 64;
+    return 1024 + 2 * S * hd * 2 + 2 * nq16 * ldh * 2 + nq16 * S * 4 + 2 * nq16 * (S + 8) * 2 + nq16 * 12 + 64 + (size_t)2 * LG_MAXM * hd * 2;
 }

@@ -123,7 +123,7 @@ struct Engine {
     int pdl = 1;                              // programmatic dependent launch (LG_PDL=0 turns it off)
     long long round_launches = 0;
     PrefillBuf pf;
-    float *ssq1 = nullptr, *ssq2 = nullptr; int *gbar = nullptr;     // NORMTAIL scratch: partial sums of squares, grid barrier
+    float4 *sums = nullptr;                   // SUMS epilogue: per work item and token the partial sums the next kernel builds the norms from
     int pos_hi = 0;                           // host-side upper bound of the device position (device-resident rounds)
     // One host synchronisation per round behind the blocking calls: mtp_draft_device runs the WHOLE round and keeps its
     // outcome here; the chained-draft and verify calls that follow are answered from it when they ask what was computed.
@@ -147,6 +147,20 @@ void launch_k(Engine *e, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = e->pdl ? 1 : 0;
+    LG_CHECK(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
+    e->launches++;
+}
+// The same with the CTAs of one blockIdx.x forming a thread-block cluster (1, grid.y, 1).
+template <typename... KArgs, typename... Args>
+void launch_k_cluster_y(Engine *e, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = e->stream;
+    cudaLaunchAttribute at[2];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 1; at[0].val.clusterDim.y = grid.y; at[0].val.clusterDim.z = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = e->pdl ? 2 : 1;
     LG_CHECK(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
     e->launches++;
 }
@@ -319,25 +333,26 @@ void free_wmat(WMat &W) { cudaFree(W.wq); cudaFree(W.ws); cudaFree(W.wd); cudaFr
 // ------------------------------------------------------------------------------------------
 int env_int(const char *name, int fb) { const char *v = getenv(name); return v && v[0] ? atoi(v) : fb; }
 
-struct GemvPlan { int r, ks, gx, ns; size_t smem; };
-// dynamic shared memory of the small-M matmul: panel slice | ring | warp partials (| norm-tail sums) | mbarriers
-size_t gemv_smem_bytes(int np, int nkp_slice, int r, int fmt, int ns, bool normtail) {
+struct GemvPlan { int r, ks, gx, ns, cl; size_t smem; };
+// dynamic shared memory of the small-M matmul: panel slice | ring | warp partials | item sums | peers' sums (cluster) | mbarriers
+size_t gemv_smem_bytes(int np, int nkp_slice, int r, int fmt, int ns, int cl_ks) {
     const int stage = fmt == LG_FMT_Q4_0 ? gemv_stage_bytes<LG_FMT_Q4_0>() : fmt == LG_FMT_Q4_K ? gemv_stage_bytes<LG_FMT_Q4_K>()
                     : fmt == LG_FMT_I8 ? gemv_stage_bytes<LG_FMT_I8>() : gemv_stage_bytes<LG_FMT_I8M>();
-    return (size_t)np * nkp_slice * 2 * (256 + 32) + 128 + (size_t)ns * stage + (size_t)LG_GEMV_CW * r * np * 64 * 4
-         + (normtail ? (size_t)np * 128 * 4 : 0) + (2 * LG_GEMV_STAGES_MAX + 1) * 8 + 16;
+    return (size_t)np * nkp_slice * 2 * (256 + 32) + 128 + (size_t)ns * stage + (size_t)(LG_GEMV_CW + 1) * r * np * 64 * 4
+         + (cl_ks > 1 ? (size_t)(cl_ks - 1) * r * np * 64 * 4 : 0) + (2 * LG_GEMV_STAGES_MAX + 2) * 8 + 16;
 }
 // most dynamic shared memory a CTA may take while two CTAs still share an SM (228 KB per SM, 1 KB reserved per CTA), less
 // the kernel's few static bytes
 constexpr size_t GEMV_SMEM_2CTA = (233472 - 2 * 1024) / 2 - 256;
 // One more ring stage where two CTAs per SM still fit: a short kernel (an item or two per CTA) then has its whole share of
 // the weights in flight before the activations arrive instead of refilling a stage behind a full memory latency.
-void gemv_pick_stages(GemvPlan &p, int np, int nkp_slice, int fmt, bool normtail) {
+void gemv_pick_stages(GemvPlan &p, int np, int nkp_slice, int fmt) {
     static const int max_ns = env_int("LG_GEMV_STAGES", LG_GEMV_STAGES_MAX);
+    const int cl_ks = p.cl ? p.ks : 0;
     p.ns = LG_GEMV_STAGES;
-    p.smem = gemv_smem_bytes(np, nkp_slice, p.r, fmt, p.ns, normtail);
+    p.smem = gemv_smem_bytes(np, nkp_slice, p.r, fmt, p.ns, cl_ks);
     if (max_ns >= 4 && p.smem <= GEMV_SMEM_2CTA) {
-        const size_t s4 = gemv_smem_bytes(np, nkp_slice, p.r, fmt, 4, normtail);
+        const size_t s4 = gemv_smem_bytes(np, nkp_slice, p.r, fmt, 4, cl_ks);
         if (s4 <= GEMV_SMEM_2CTA) { p.ns = 4; p.smem = s4; }
     }
 }
@@ -354,7 +369,10 @@ template <int FMT> void gemv_attr_f() {
     gemv_attr_rf<1, FMT>(); gemv_attr_rf<2, FMT>(); gemv_attr_rf<4, FMT>();
     gemv_attr<4, 1, FMT, LG_EPI_HEAD>(); gemv_attr<4, 2, FMT, LG_EPI_HEAD>();
     gemv_attr<4, 1, FMT, LG_EPI_GEGLU>(); gemv_attr<4, 2, FMT, LG_EPI_GEGLU>();
-    gemv_attr<4, 1, FMT, LG_EPI_GEGLU | LG_EPI_POST>(); gemv_attr<4, 2, FMT, LG_EPI_GEGLU | LG_EPI_POST>();
+    gemv_attr<1, 1, FMT, LG_EPI_SUMS>(); gemv_attr<1, 2, FMT, LG_EPI_SUMS>();
+    gemv_attr<2, 1, FMT, LG_EPI_SUMS>(); gemv_attr<2, 2, FMT, LG_EPI_SUMS>();
+    gemv_attr<4, 1, FMT, LG_EPI_SUMS>(); gemv_attr<4, 2, FMT, LG_EPI_SUMS>();
+    gemv_attr<2, 1, FMT, LG_EPI_GATE>(); gemv_attr<2, 2, FMT, LG_EPI_GATE>();
 }
 // Opt every kernel into large dynamic shared memory once, outside any stream capture.
 template <int NT, int FMT, int EPI> void pf_attr() {
@@ -377,8 +395,6 @@ void set_kernel_attributes() {
     if (done[dev]) return;
     done[dev] = true;
     gemv_attr_f<LG_FMT_Q4_0>(); gemv_attr_f<LG_FMT_Q4_K>(); gemv_attr_f<LG_FMT_I8>(); gemv_attr_f<LG_FMT_I8M>();
-    gemv_attr<2, 1, LG_FMT_Q4_0, LG_EPI_NORMTAIL>(); gemv_attr<2, 2, LG_FMT_Q4_0, LG_EPI_NORMTAIL>();
-    gemv_attr<2, 1, LG_FMT_Q4_K, LG_EPI_NORMTAIL>(); gemv_attr<2, 2, LG_FMT_Q4_K, LG_EPI_NORMTAIL>();
     LG_CHECK(cudaFuncSetAttribute(lg_attn_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
     LG_CHECK(cudaFuncSetAttribute(lg_attn_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
     LG_CHECK(cudaFuncSetAttribute(lg_attn_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATTN_SMEM_MAX));
@@ -398,8 +414,9 @@ void set_kernel_attributes() {
 // Decomposition of one matmul into CTA work items: R row tiles x one of ks column slices, walked
 // by a persistent grid of about two CTAs per SM.  Few slices (each slice's partial costs an extra
 // pass in the consumer), and as many row tiles per item as still leave enough items to balance.
-GemvPlan plan_gemv(const Engine *e, const WMat &W, int np_actual, int want_ks, bool head, bool geglu = false) {
+GemvPlan plan_gemv(const Engine *e, const WMat &W, int np_actual, int want_ks, bool head, bool geglu = false, bool complete = false) {
     GemvPlan p;
+    p.cl = 0;
     // The decomposition (row tiles per item, k slices) fixes the order in which a row's products are added, so it must not
     // depend on the block width: it is planned for two activation panels (5..8 rows) always; only the shared memory and the
     // ring depth at the end follow the panels this launch really has.
@@ -435,11 +452,10 @@ GemvPlan plan_gemv(const Engine *e, const WMat &W, int np_actual, int want_ks, b
     if (p.ks > W.nkp) p.ks = W.nkp;
     for (;;) {
         int nkp_s = (W.nkp + p.ks - 1) / p.ks + 1;
-        gemv_pick_stages(p, np, nkp_s, W.fmt, false);
+        gemv_pick_stages(p, np, nkp_s, W.fmt);
         if (p.smem <= GEMV_SMEM_MAX || p.ks >= e->max_ks || p.ks * 2 > W.nkp || head || geglu) break;
         p.ks *= 2;                                   // the slice's panel does not fit: cut k finer
     }
-    gemv_pick_stages(p, np_actual, (W.nkp + p.ks - 1) / p.ks + 1, W.fmt, false);
     // items beyond one wave: spread them evenly -- every CTA walks the same number of items (or one fewer), so no CTA
     // is still on its second item while the others have left
     int groups = (W.n_row_tiles + p.r - 1) / p.r;
@@ -448,6 +464,15 @@ GemvPlan plan_gemv(const Engine *e, const WMat &W, int np_actual, int want_ks, b
     const int waves = (groups + cap - 1) / cap;
     p.gx = (groups + waves - 1) / waves;
     if (p.gx < 1) p.gx = 1;
+    // The caller wants complete rows in one CTA (an epilogue that needs them): the k slices of a row group become one
+    // thread-block cluster that adds its partial sums in rank 0 -- possible with one item per CTA and a portable cluster size.
+    static const int cl_on = env_int("LG_GEMV_CLUSTER", 1);
+    if (complete && cl_on && p.ks > 1 && p.ks <= LG_GEMV_CL_MAX && waves == 1) p.cl = 1;
+    gemv_pick_stages(p, np_actual, (W.nkp + p.ks - 1) / p.ks + 1, W.fmt);
+    if (p.cl && (gemv_smem_bytes(2, (W.nkp + p.ks - 1) / p.ks + 1, p.r, W.fmt, LG_GEMV_STAGES, p.ks) > GEMV_SMEM_MAX)) {
+        p.cl = 0;
+        gemv_pick_stages(p, np_actual, (W.nkp + p.ks - 1) / p.ks + 1, W.fmt);
+    }
 
     return p;
 }
@@ -456,7 +481,8 @@ template <int R, int NP, int FMT, int EPI>
 void launch_gemv_t(Engine *e, const LgGemvArgs &a, const GemvPlan &p) {
     if (p.smem > GEMV_SMEM_MAX) { fprintf(stderr, "lg_b200: matmul slice needs %zu bytes of shared memory\n", p.smem); exit(1); }
     dim3 grid(p.gx, p.ks);
-    launch_k(e, (lg_gemv_kernel<R, NP, FMT, EPI>), dim3(grid), dim3(LG_GEMV_THREADS), p.smem, a);
+    if (p.cl) launch_k_cluster_y(e, (lg_gemv_kernel<R, NP, FMT, EPI>), dim3(grid), dim3(LG_GEMV_THREADS), p.smem, a);
+    else launch_k(e, (lg_gemv_kernel<R, NP, FMT, EPI>), dim3(grid), dim3(LG_GEMV_THREADS), p.smem, a);
 }
 // dispatch on the weight format (a template parameter of the kernel)
 template <int R, int NP, int EPI>
@@ -471,77 +497,67 @@ void launch_gemv_f(Engine *e, const LgGemvArgs &a, const GemvPlan &p, int fmt) {
 
 struct GemvExtra {
     float softcap = 0.0f; float *logits = nullptr; float *amax_val = nullptr; int *amax_idx = nullptr;
-    const LgPanel *outp = nullptr;            // GeGLU / NORMTAIL epilogue target
+    const LgPanel *outp = nullptr;            // GeGLU epilogue target
     int *ks_out = nullptr, *gx_out = nullptr;
     int ldo = 0;                              // row stride of the output when it is not the matrix's own padded row count
     const int *skip = nullptr;                // the launch does nothing when this device word is non-zero
     float *amax_val2 = nullptr;               // head epilogue: runner-up logits
-    // NORMTAIL epilogue
-    float *xres = nullptr; int ldx = 0, n_cols = 0; const float *add_w = nullptr, *norm_w = nullptr; float out_scale = 1.0f, eps = 0.0f;
-    float *ssq1 = nullptr, *ssq2 = nullptr; int *gbar = nullptr;
-    // consumer of a deferred-norm panel
-    const float *post_ss = nullptr; int n_post = 0; float post_n = 1.0f, post_eps = 0.0f;
+    // SUMS epilogue
+    const float *xres = nullptr; int ldx = 0, n_cols = 0; const float *add_w = nullptr; float4 *sums = nullptr;
+    int *groups_out = nullptr;                // items of the launch (= entries of sums written)
+    const float *mul = nullptr; int ld_mul = 0;   // GATE epilogue: the per-token vector the activation is multiplied by
 };
 
-// Whether the o-projection can carry the residual update and the next norm in its epilogue: one item of 32 rows per
-// CTA, all items resident at once (they meet at a grid-wide barrier), the whole panel in one slice.
-bool normtail_ok(const Engine *e, const WMat &W, int np) {
-    static const int on = env_int("LG_NORMTAIL", 1);
-    const int groups = W.n_row_tiles / 2;
-    size_t smem = gemv_smem_bytes(np, W.nkp + 1, 2, W.fmt, LG_GEMV_STAGES, true);
-    if (!on || W.fmt > LG_FMT_Q4_K || W.n_row_tiles % 2 || smem > 100 * 1024) return false;
-    // The epilogue's grid-wide barrier needs every CTA of the grid resident at once: ask the device how many CTAs of this
-    // kernel (with its registers and this much shared memory) an SM holds instead of trusting the shared-memory estimate.
-    static std::map<long long, int> per_sm;
-    const long long key = ((long long)np << 40) | ((long long)W.fmt << 32) | (long long)smem;
-    auto it = per_sm.find(key);
-    if (it == per_sm.end()) {
-        int n = 0;
-        cudaError_t rc;
-        if (np == 1) rc = W.fmt == LG_FMT_Q4_0 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, lg_gemv_kernel<2, 1, LG_FMT_Q4_0, LG_EPI_NORMTAIL>, LG_GEMV_THREADS, smem)
-                                                : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, lg_gemv_kernel<2, 1, LG_FMT_Q4_K, LG_EPI_NORMTAIL>, LG_GEMV_THREADS, smem);
-        else         rc = W.fmt == LG_FMT_Q4_0 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, lg_gemv_kernel<2, 2, LG_FMT_Q4_0, LG_EPI_NORMTAIL>, LG_GEMV_THREADS, smem)
-                                                : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, lg_gemv_kernel<2, 2, LG_FMT_Q4_K, LG_EPI_NORMTAIL>, LG_GEMV_THREADS, smem);
-        if (rc != cudaSuccess) { cudaGetLastError(); n = 0; }
-        it = per_sm.emplace(key, n).first;
-    }
-    return groups <= it->second * e->sm_count;
+// Whether a matmul can run with the SUMS epilogue: complete rows in one CTA (no k slices, or k slices reduced inside a
+// cluster) and few enough items for the consumer's one-round read of the partial sums.  Decided from the matrix alone,
+// never from the block's width.
+bool sums_ok(const Engine *e, const WMat &W) {
+    static const int on = env_int("LG_SUMS", 1);
+    if (!on) return false;
+    GemvPlan p = plan_gemv(e, W, 2, 0, false, false, true);
+    const int groups = (W.n_row_tiles + p.r - 1) / p.r;
+    return (p.ks == 1 || p.cl) && groups <= LG_SUMS_ITEMS;
 }
 
 // out[ks][tok][ldo] partial sums (EPI_STORE, optional tail), the GeGLU epilogue, or the head epilogue.
 void launch_gemv(Engine *e, const WMat &W, const LgPanel &X, int M, float *out, int epi, int force_ks,
                  const GemvExtra &x = GemvExtra()) {
     int np = M > 4 ? 2 : 1;
-    GemvPlan p = plan_gemv(e, W, np, epi == LG_EPI_STORE ? force_ks : 1, epi == LG_EPI_HEAD, epi == LG_EPI_GEGLU);
-    if (epi == LG_EPI_NORMTAIL) {
-        p.r = 2; p.ks = 1; p.gx = W.n_row_tiles / 2;
-        gemv_pick_stages(p, np, W.nkp + 1, W.fmt, true);
+    const bool sums = epi == LG_EPI_SUMS;
+    GemvPlan p = plan_gemv(e, W, np, (epi == LG_EPI_STORE || sums) ? force_ks : 1, epi == LG_EPI_HEAD, epi == LG_EPI_GEGLU, sums);
+    if (sums && p.ks > 1 && !p.cl) { fprintf(stderr, "lg_b200: the SUMS epilogue needs complete rows (see sums_ok)\n"); exit(1); }
+    if (epi == LG_EPI_GATE) {                    // one panel group (32 rows) per item, the whole k range in one CTA
+        p.r = 2; p.ks = 1; p.cl = 0; p.gx = std::max(1, std::min(W.n_row_tiles / 2, e->sm_count * 2));
+        gemv_pick_stages(p, np, W.nkp + 1, W.fmt);
     }
     LgGemvArgs a{};
     a.wq = W.wq; a.ws = W.ws; a.wd = W.wd; a.wm = W.wm; a.x = X; a.nkp = W.nkp; a.n_row_tiles = W.n_row_tiles; a.kslices = p.ks;
     a.out = out; a.ldo = x.ldo ? x.ldo : W.ldo; a.M = M; a.softcap = x.softcap; a.logits = x.logits; a.n_valid_rows = W.m;
     a.amax_val = x.amax_val; a.amax_idx = x.amax_idx; a.amax_val2 = x.amax_val2; a.skip = x.skip; a.err = e->err;
     if (x.outp) a.outp = *x.outp;
-    a.xres = x.xres; a.ldx = x.ldx; a.n_cols = x.n_cols; a.add_w = x.add_w; a.norm_w = x.norm_w; a.out_scale = x.out_scale; a.eps = x.eps;
-    a.ssq1 = x.ssq1; a.ssq2 = x.ssq2; a.gbar = x.gbar;
-    a.post_ss = x.post_ss; a.n_post = x.n_post; a.post_n = x.post_n; a.post_eps = x.post_eps;
+    a.cl_ks = p.cl;
+    a.xres = x.xres; a.ldx = x.ldx; a.n_cols = x.n_cols; a.add_w = x.add_w; a.sums = x.sums; a.mul = x.mul; a.ld_mul = x.ld_mul;
     a.tag = (int)e->launches; a.ns = p.ns;
     if (X.nsb * 32 != W.k) { fprintf(stderr, "lg_b200: panel width %d does not match matrix k %d\n", X.nsb * 32, W.k); exit(1); }
-    if (x.ks_out) *x.ks_out = p.ks;
+    if (x.ks_out) *x.ks_out = p.cl ? 1 : p.ks;
     if (x.gx_out) *x.gx_out = p.gx;
-    if (a.post_ss && epi != LG_EPI_GEGLU) { fprintf(stderr, "lg_b200: a deferred norm is only wired into the gate/up matmul\n"); exit(1); }
-    if (epi == LG_EPI_NORMTAIL) {
-        if (np == 1) { if (W.fmt == LG_FMT_Q4_0) launch_gemv_t<2, 1, LG_FMT_Q4_0, LG_EPI_NORMTAIL>(e, a, p); else launch_gemv_t<2, 1, LG_FMT_Q4_K, LG_EPI_NORMTAIL>(e, a, p); }
-        else         { if (W.fmt == LG_FMT_Q4_0) launch_gemv_t<2, 2, LG_FMT_Q4_0, LG_EPI_NORMTAIL>(e, a, p); else launch_gemv_t<2, 2, LG_FMT_Q4_K, LG_EPI_NORMTAIL>(e, a, p); }
+    if (x.groups_out) *x.groups_out = (W.n_row_tiles + p.r - 1) / p.r;
+    if (sums) {
+        if (np == 1) {
+            if (p.r == 4) launch_gemv_f<4, 1, LG_EPI_SUMS>(e, a, p, W.fmt); else if (p.r == 2) launch_gemv_f<2, 1, LG_EPI_SUMS>(e, a, p, W.fmt); else launch_gemv_f<1, 1, LG_EPI_SUMS>(e, a, p, W.fmt);
+        } else {
+            if (p.r == 4) launch_gemv_f<4, 2, LG_EPI_SUMS>(e, a, p, W.fmt); else if (p.r == 2) launch_gemv_f<2, 2, LG_EPI_SUMS>(e, a, p, W.fmt); else launch_gemv_f<1, 2, LG_EPI_SUMS>(e, a, p, W.fmt);
+        }
+        return;
+    }
+    if (epi == LG_EPI_GATE) {
+        // 32 rows per item, complete rows: the whole k range in one CTA, or k slices reduced inside a cluster
+        if (W.n_row_tiles % 2) { fprintf(stderr, "lg_b200: the gate matmul needs a multiple of 32 outputs\n"); exit(1); }
+        if (np == 1) launch_gemv_f<2, 1, LG_EPI_GATE>(e, a, p, W.fmt); else launch_gemv_f<2, 2, LG_EPI_GATE>(e, a, p, W.fmt);
         return;
     }
     if (epi == LG_EPI_GEGLU) {
         if (W.n_row_tiles % 4) { fprintf(stderr, "lg_b200: GeGLU matmul needs a multiple of 32 outputs\n"); exit(1); }
-        constexpr int GP = LG_EPI_GEGLU | LG_EPI_POST;
-        if (a.post_ss) {     // the panel's norm was deferred: the variant that rescales by 1/rms
-            if (np == 1) launch_gemv_f<4, 1, GP>(e, a, p, W.fmt); else launch_gemv_f<4, 2, GP>(e, a, p, W.fmt);
-            return;
-        }
         if (np == 1) launch_gemv_f<4, 1, LG_EPI_GEGLU>(e, a, p, W.fmt); else launch_gemv_f<4, 2, LG_EPI_GEGLU>(e, a, p, W.fmt);
         return;
     }
@@ -585,6 +601,17 @@ void launch_norm(Engine *e, int M, float *x, int ldx, int n, float eps,
     }
     int threads = n >= 2048 ? 1024 : (n >= 512 ? 512 : 256);
     launch_k(e, lg_norm_kernel, dim3(M), dim3(threads), (size_t)(2 * n + 32) * 4, a);
+}
+
+// x = (x + rmsnorm(o) add_w) * out_scale and the next panel / f32 row, from the SUMS epilogue's partial sums.
+void launch_elt(Engine *e, int M, float *x, int ldx, int n, float eps, const float *o, int ldo, int n_sums,
+                const float *add_w, float out_scale, const float *norm_w, const LgPanel *panel, float *y, int ldy, const int *skip = nullptr) {
+    LgEltArgs a{};
+    a.x = x; a.ldx = ldx; a.o = o; a.ldo = ldo; a.sums = e->sums; a.n_sums = n_sums;
+    a.add_w = add_w; a.norm_w = norm_w; a.out_scale = out_scale; a.eps = eps; a.n = n;
+    if (panel) { a.panel = *panel; a.want_panel = 1; }
+    a.y = y; a.ldy = ldy; a.skip = skip; a.tag = (int)e->launches;
+    launch_k(e, lg_elt_kernel, dim3((n / 32 + LG_ELT_WARPS - 1) / LG_ELT_WARPS, M), dim3(LG_ELT_WARPS * 32), 0, a);
 }
 
 size_t attn_smem(int nq, int hd) {
@@ -848,8 +875,7 @@ Engine *engine_for(const struct model *m) {
     e->pdl = env_int("LG_PDL", 1);
     e->err = dalloc<int>(1);
     e->tickets = dalloc<int>(MAX_KV_HEADS);
-    e->ssq1 = dalloc<float>((size_t)2 * e->sm_count * LG_MAXM); e->ssq2 = dalloc<float>((size_t)2 * e->sm_count * LG_MAXM);
-    e->gbar = dalloc<int>(2);
+    e->sums = dalloc<float4>((size_t)LG_SUMS_ITEMS * LG_MAXM);
     e->d_margin_thr = dalloc<float>(1);
     { float thr = (float)atof(getenv("LG_DRAFT_MARGIN") ? getenv("LG_DRAFT_MARGIN") : "0"); if (thr != 0.0f) h2d_sync(e->d_margin_thr, &thr, 4); }
 
@@ -1026,8 +1052,8 @@ void bind_kv(Engine *e, const struct kvcache *kv) {
 enum { F_HEAD = 1, F_LOGITS = 2, F_ACCEPT = 4, F_ADVANCE = 8, F_NOEMBED = 16 };   // NOEMBED: x rows are already in place
 
 // `only` selects kernel classes (the benchmark times them in isolation); the default runs everything.
-// C_FUSED: a class-restricted pass keeps the epilogue variants of the full step (the o-projection that carries the
-// residual update and the next norm, the gate/up matmul that applies the deferred 1/rms) instead of the plain ones.
+// C_FUSED: a class-restricted pass keeps the epilogue variants of the full step (the o / down / PLE projections that leave
+// complete rows and the partial sums of the norms that follow them) instead of the plain ones.
 enum { C_QKV = 1, C_O = 2, C_GATEUP = 4, C_DOWN = 8, C_HEAD = 16, C_PLE = 32, C_NORM = 64, C_ATTN = 256, C_MISC = 512,
        C_ALL = 1023, C_FUSED = 1024 };
 
@@ -1085,29 +1111,31 @@ void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags, int 
             else launch_attn(e, aa, tiles_for(aa.window, kv->max_seq, M, hd));
         }
 
-        // o-projection, then x += norm(o)*w_post_attn and the ffn_norm panel
-        int ks_o = 1;
-        GemvExtra xo; xo.ks_out = &ks_o;
-        // (class-isolated timing passes keep the o-projection a pure matmul followed by the norm kernel unless C_FUSED asks
-        // for the variants the full step runs)
-            // (decided for the widest block, never for this block's width: a verify row must run the very kernels -- and so
-        // carry the very bits -- of the plain decode step at its position)
-        const bool tail_o = ((only & C_ALL) == C_ALL || (only & C_FUSED)) && normtail_ok(e, w.o, 2) && normtail_ok(e, w.o, 1);
+        // o-projection, then x += norm(o)*w_post_attn and the ffn_norm panel.  Where the matmul can leave complete rows
+        // and their partial sums (decided from the matrix, never from the block's width: a verify row must run the very
+        // kernels -- and so carry the very bits -- of the plain decode step at its position), one elementwise kernel
+        // follows it; otherwise the norm kernel adds the k-slice partials and reduces the row itself.
+        const bool fused_pass = (only & C_ALL) == C_ALL || (only & C_FUSED);
+        // a matmul followed by the residual update (and the next norm): out -> x, panel, y
+        auto matmul_resid = [&](const WMat &W, const LgPanel &in, float *out, int cls, const float *add_w, float out_scale,
+                                const float *norm_w, const LgPanel *panel, float *y) {
+            if (fused_pass && sums_ok(e, W)) {
+                int groups = 0;
+                GemvExtra xs; xs.xres = e->x; xs.ldx = ne; xs.n_cols = ne; xs.add_w = add_w; xs.sums = e->sums; xs.groups_out = &groups;
+                if (only & cls) launch_gemv(e, W, in, M, out, LG_EPI_SUMS, 0, xs);
+                else { GemvPlan p = plan_gemv(e, W, M > 4 ? 2 : 1, 0, false, false, true); groups = (W.n_row_tiles + p.r - 1) / p.r; }
+                if (only & C_NORM) launch_elt(e, M, e->x, ne, ne, c->rms_eps, out, W.ldo, groups, add_w, out_scale, norm_w, panel, y, ne);
+            } else {
+                int ks = 1;
+                GemvExtra xs; xs.ks_out = &ks;
+                if (only & cls) launch_gemv(e, W, in, M, out, LG_EPI_STORE, 0, xs); else ks = plan_gemv(e, W, M > 4 ? 2 : 1, 0, false).ks;
+                if (only & C_NORM) launch_norm(e, M, e->x, ne, ne, c->rms_eps, out, ks, (size_t)LG_MAXM * W.ldo, W.ldo, add_w, out_scale, norm_w, panel, y, ne);
+            }
+        };
+        matmul_resid(w.o, pa, e->oout, C_O, w.post_attn, 1.0f, w.ffn_norm, &e->p_ne, nullptr);
         // gate/up with the GeGLU epilogue writing the down-projection's panel
         LgPanel pf = e->p_ff; pf.nsb = w.nff / 32;
         GemvExtra xg; xg.outp = &pf;
-        if (tail_o) {
-            // the o-projection's epilogue does the residual update and writes the ffn_norm panel; that norm's 1/rms
-            // is applied by the gate/up matmul's epilogue
-            xo.xres = e->x; xo.ldx = ne; xo.n_cols = ne; xo.add_w = w.post_attn; xo.norm_w = w.ffn_norm; xo.out_scale = 1.0f;
-            xo.eps = c->rms_eps; xo.outp = &e->p_ne; xo.ssq1 = e->ssq1; xo.ssq2 = e->ssq2; xo.gbar = e->gbar;
-            if (only & C_O) launch_gemv(e, w.o, pa, M, nullptr, LG_EPI_NORMTAIL, 1, xo);
-            xg.post_ss = e->ssq2; xg.n_post = w.o.n_row_tiles / 2; xg.post_n = (float)ne; xg.post_eps = c->rms_eps;
-        } else {
-            if (only & C_O) launch_gemv(e, w.o, pa, M, e->oout, LG_EPI_STORE, 0, xo); else ks_o = plan_gemv(e, w.o, M > 4 ? 2 : 1, 0, false).ks;
-            if (only & C_NORM) launch_norm(e, M, e->x, ne, ne, c->rms_eps, e->oout, ks_o, (size_t)LG_MAXM * w.o.ldo, w.o.ldo, w.post_attn, 1.0f,
-                        w.ffn_norm, &e->p_ne, nullptr, 0);
-        }
         if (only & C_GATEUP) launch_gemv(e, w.gateup, e->p_ne, M, nullptr, LG_EPI_GEGLU, 1, xg);
 
         const bool last = l == nl - 1;
@@ -1116,21 +1144,19 @@ void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags, int 
         const LgPanel *next_p = next_w ? &e->p_ne : nullptr;
         if (e->has_ple) {
             // down, then x += norm(down)*w_post_ffw and the panel of x itself for the PLE gate
-            int ks_d = 1;
-            GemvExtra xd; xd.ks_out = &ks_d;
-            if (only & C_DOWN) launch_gemv(e, w.down, pf, M, e->dout, LG_EPI_STORE, 0, xd); else ks_d = plan_gemv(e, w.down, M > 4 ? 2 : 1, 0, false).ks;
-            if (only & C_NORM) launch_norm(e, M, e->x, ne, ne, c->rms_eps, e->dout, ks_d, (size_t)LG_MAXM * w.down.ldo, w.down.ldo, w.post_ffw, 1.0f,
-                        nullptr, &e->p_ne, nullptr, 0);
-            if (only & C_PLE) launch_gemv(e, w.inp_gate, e->p_ne, M, e->pg, LG_EPI_STORE, 1);
-            if (only & C_MISC) launch_k(e, lg_geglu_kernel, dim3((ple / 32 + 7) / 8, M), dim3(256), 0, e->pg, e->ipl + (size_t)l * ple, w.inp_gate.ldo, total, ple, e->p_ple);
-            if (only & C_PLE) launch_gemv(e, w.proj, e->p_ple, M, e->oout, LG_EPI_STORE, 1);
-            if (only & C_NORM) launch_norm(e, M, e->x, ne, ne, c->rms_eps, e->oout, 1, 0, w.proj.ldo, w.post_norm, w.out_scale, next_w, next_p, y, ne);
+            matmul_resid(w.down, pf, e->dout, C_DOWN, w.post_ffw, 1.0f, nullptr, &e->p_ne, nullptr);
+            // the PLE gate: gelu(inp_gate x) * (this layer's per-layer input) straight into the projection's panel
+            static const int gate_epi = env_int("LG_GATE_EPILOGUE", 1);
+            if (gate_epi && fused_pass && w.inp_gate.n_row_tiles % 2 == 0 && w.inp_gate.nkp <= 160) {
+                GemvExtra xq; xq.outp = &e->p_ple; xq.mul = e->ipl + (size_t)l * ple; xq.ld_mul = total;
+                if (only & C_PLE) launch_gemv(e, w.inp_gate, e->p_ne, M, nullptr, LG_EPI_GATE, 1, xq);
+            } else {
+                if (only & C_PLE) launch_gemv(e, w.inp_gate, e->p_ne, M, e->pg, LG_EPI_STORE, 1);
+                if (only & C_MISC) launch_k(e, lg_geglu_kernel, dim3((ple / 32 + 7) / 8, M), dim3(256), 0, e->pg, e->ipl + (size_t)l * ple, w.inp_gate.ldo, total, ple, e->p_ple);
+            }
+            matmul_resid(w.proj, e->p_ple, e->oout, C_PLE, w.post_norm, w.out_scale, next_w, next_p, y);
         } else {
-            int ks_d = 1;
-            GemvExtra xd; xd.ks_out = &ks_d;
-            if (only & C_DOWN) launch_gemv(e, w.down, pf, M, e->dout, LG_EPI_STORE, 0, xd); else ks_d = plan_gemv(e, w.down, M > 4 ? 2 : 1, 0, false).ks;
-            if (only & C_NORM) launch_norm(e, M, e->x, ne, ne, c->rms_eps, e->dout, ks_d, (size_t)LG_MAXM * w.down.ldo, w.down.ldo, w.post_ffw, w.out_scale,
-                        next_w, next_p, y, ne);
+            matmul_resid(w.down, pf, e->dout, C_DOWN, w.post_ffw, w.out_scale, next_w, next_p, y);
         }
     }
     if (e->mid_event) LG_CHECK(cudaEventRecord(e->mid_event, e->stream));
@@ -2040,7 +2066,7 @@ int lg_bench_prefill_pass(struct model *m, int n, int classes) {
 void lg_set_attn_deep(int min_seq, int force_g) { g_deep_min = min_seq; g_deep_force = force_g; }
 
 // Profiling builds (-DLG_STAMPS): copy the phase time stamps of the most recent launches to the host;
-// out is [96 launches][320 CTAs][10 slots] of nanosecond timer values (0 = not written; slot 9 of CTA 0 = kernel kind).  -1 in the product build.
+// out is [96 launches][320 CTAs][12 slots] of nanosecond timer values (0 = not written; the last slot of CTA 0 = kernel kind).  -1 in the product build.
 int lg_debug_stamps(long long *out) {
 #ifdef LG_STAMPS
     LG_CHECK(cudaDeviceSynchronize());

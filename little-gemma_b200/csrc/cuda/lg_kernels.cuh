@@ -108,7 +108,7 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)_
 // layer on one time axis (lg_debug_stamps).  Compiled out of the product build.
 #define LG_STAMP_LAUNCHES 96
 #define LG_STAMP_CTAS 320
-#define LG_STAMP_SLOTS 10
+#define LG_STAMP_SLOTS 12
 #ifdef LG_STAMPS
 __device__ long long lg_stamps[LG_STAMP_LAUNCHES][LG_STAMP_CTAS][LG_STAMP_SLOTS];
 __device__ __forceinline__ void lg_stamp(int tag, int slot) {
@@ -122,8 +122,8 @@ __device__ __forceinline__ void lg_stamp(int tag, int slot) {
     }
 }
 #define LG_STAMP(tag, slot) lg_stamp(tag, slot)
-// slot 9 of CTA 0 names the kernel (1 matmul store, 2 head, 3 GeGLU, 4 norm tail, 5 attention/ticket, 6 attention/cluster, 7 norm)
-#define LG_STAMP_KIND(tag, kind) do { if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && (tag) >= 0 && (tag) < LG_STAMP_LAUNCHES) lg_stamps[tag][0][9] = (kind); } while (0)
+// the last slot of CTA 0 names the kernel (1 matmul store, 2 head, 3 GeGLU, 4 matmul with sums, 5 attention/ticket, 6 attention/cluster, 7 norm / residual update)
+#define LG_STAMP_KIND(tag, kind) do { if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && (tag) >= 0 && (tag) < LG_STAMP_LAUNCHES) lg_stamps[tag][0][LG_STAMP_SLOTS - 1] = (kind); } while (0)
 #else
 #define LG_STAMP(tag, slot) do { } while (0)
 #define LG_STAMP_KIND(tag, kind) do { } while (0)
@@ -167,6 +167,34 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
     for (int it = 0; it < LG_SPIN_LIMIT; ++it) {
         uint32_t ok;
         asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void dsmem_store(float *local_addr, uint32_t rank, float v) {
+    uint32_t la = smem_u32(local_addr), ra;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(la), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" :: "r"(ra), "f"(v) : "memory");
+}
+// One f32 into a peer CTA's shared memory, counted (4 bytes) on that peer's mbarrier: the receiver waits for the byte
+// count instead of a cluster-wide barrier, so threads that never join a barrier (a producer warp) are no obstacle.
+__device__ __forceinline__ void dsmem_st_async_f32(float *local_addr, uint64_t *local_bar, uint32_t rank, float v) {
+    uint32_t ra, rb;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(smem_u32(local_addr)), "r"(rank));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rb) : "r"(smem_u32(local_bar)), "r"(rank));
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.f32 [%0], %1, [%2];" :: "r"(ra), "f"(v), "r"(rb) : "memory");
+}
+// Bounded wait with cluster-scope acquire: the data counted on the barrier came from peer CTAs.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity) {
+    for (int it = 0; it < LG_SPIN_LIMIT; ++it) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
         if (ok) return true;
     }
@@ -422,15 +450,17 @@ struct LgGemvArgs {
     // GeGLU epilogue: rows are interleaved (tile = 8 gate rows then the 8 matching up rows);
     // y = gelu_tanh(gate) * up goes straight into the next matmul's panel
     LgPanel outp;
-    // NORMTAIL epilogue (R = 2: an item's 32 rows are one panel group; one item per CTA, no k slices):
-    // after a grid-wide barrier, x[tok][rows] = (x + rmsnorm(out) * add_w) * out_scale and the next
-    // panel gets x * norm_w -- the 1/rms of that second norm is left to the consumer (post_ss below)
-    float *xres; int ldx;
-    const float *add_w, *norm_w; float out_scale, eps; int n_cols;
-    float *ssq1, *ssq2;        // [groups][LG_MAXM] partial sums of squares: of out, of the new x
-    int *gbar;                 // {arrived, left}, zero between launches
-    // consumer of a panel whose norm was deferred: results are multiplied by 1/rms from these partials
-    const float *post_ss; int n_post; float post_n, post_eps;
+    // cl_ks: the kslices CTAs of a row group are one thread-block cluster (1, kslices, 1); ranks > 0 send their partial
+    // sums into rank 0's shared memory, so rank 0 holds the complete rows and runs the epilogue (one item per CTA)
+    int cl_ks;
+    // SUMS epilogue (complete rows only): besides out[tok][row], per item and token the four partial sums
+    //   A = sum o^2,  B = sum x (w o),  C = sum (w o)^2,  D = sum x^2      (x = xres, the residual row; w = add_w)
+    // from which the consumer forms 1/rms(o) and 1/rms(x + rmsnorm(o) w) without another pass over the row
+    const float *xres; int ldx;
+    const float *add_w; int n_cols;
+    // GATE epilogue (R = 2: an item's 32 rows are one panel group; complete rows): y = gelu_tanh(out) * mul[tok][row] -> outp
+    const float *mul; int ld_mul;
+    float4 *sums;              // [LG_MAXM][LG_SUMS_ITEMS]: a token's partials lie side by side (one coalesced read for the consumer)
     int tag;                   // launch index for LG_STAMP (profiling builds)
     int ns;                    // ring stages (LG_GEMV_STAGES .. LG_GEMV_STAGES_MAX)
 };
@@ -444,13 +474,12 @@ struct LgGemvArgs {
 enum { LG_FMT_Q4_0 = 0, LG_FMT_Q4_K = 1, LG_FMT_I8 = 2, LG_FMT_I8M = 3 };
 __host__ __device__ constexpr int lg_tile_bytes(int fmt) { return fmt >= LG_FMT_I8 ? 1024 : 512; }              // weights of one 16x64 tile
 __host__ __device__ constexpr int lg_tile_extra(int fmt) { return fmt == LG_FMT_Q4_0 ? 64 : fmt == LG_FMT_I8M ? 256 : 128; }   // its scale bytes
-// bit 2 (LG_EPI_POST): the input panel's norm was deferred -- results are multiplied by 1/rms from post_ss.
-// A separate instantiation, so the plain epilogues carry none of that code.
-enum { LG_EPI_STORE = 0, LG_EPI_HEAD = 1, LG_EPI_GEGLU = 2, LG_EPI_NORMTAIL = 3, LG_EPI_POST = 4 };
-#define LG_ERR_GRID_BARRIER 256
-// partial sums of squares one lane adds when a row's norm is assembled from per-CTA partials: 32 lanes x 10 cover the
-// 296 CTAs of a grid of two per SM (the planner keeps such grids at or below 320 CTAs)
+enum { LG_EPI_STORE = 0, LG_EPI_HEAD = 1, LG_EPI_GEGLU = 2, LG_EPI_SUMS = 3, LG_EPI_GATE = 4 };
+// partial sums one lane adds when a row's norms are assembled from per-item partials: 32 lanes x 10 cover 320 items
+// (the host uses the SUMS epilogue only for matrices of at most that many items)
 #define LG_SS_PER_LANE 10
+#define LG_SUMS_ITEMS (32 * LG_SS_PER_LANE)
+#define LG_GEMV_CL_MAX 8               // most k slices a cluster-reduced matmul may have (the portable cluster size)
 
 #define LG_GEMV_CW 8                    // consumer warps per CTA
 #define LG_GEMV_THREADS ((LG_GEMV_CW + 1) * 32)   // + one producer warp
@@ -489,7 +518,10 @@ __device__ __forceinline__ void mma_s8_k16(int (&c)[4], uint32_t a0, uint32_t a1
 //     shared load per lane, `mma.sync.m16n8k32.s8`, f32 scale-accumulate.  Partial sums of the
 //     warps are added in warp order.
 // Every wait is bounded; a timeout raises LG_ERR_MBAR_TIMEOUT and the kernel runs to its end.
-// Dynamic shared memory: panel q | panel s | ring | reduction (| NORMTAIL: final sums) | mbarriers
+//   * k slices (gridDim.y > 1) either leave one partial result per slice for the consumer to add, or -- cl_ks -- form
+//     a thread-block cluster whose ranks 1.. send their sums into rank 0's shared memory (st.async, counted on an
+//     mbarrier of rank 0), so that rank 0 runs the epilogue on complete rows.
+// Dynamic shared memory: panel q | panel s | ring | warp partials | item sums | peers' sums (cluster) | mbarriers
 template <int R, int NP, int FMT, int EPI>
 __global__ void __launch_bounds__(LG_GEMV_THREADS)
 lg_gemv_kernel(LgGemvArgs a) {
@@ -500,8 +532,8 @@ lg_gemv_kernel(LgGemvArgs a) {
     // fewer positions than consumer warps (i8 tiles with R = 4): the warps also split the row tiles of a position
     constexpr int PW = P < LG_GEMV_CW ? P : LG_GEMV_CW, RS = LG_GEMV_CW / PW;
     const int NS = a.ns;                                     // ring depth chosen by the host (3 or 4)
-    constexpr int EB = EPI & 3;                              // the epilogue proper
-    constexpr bool POST = (EPI & LG_EPI_POST) != 0;
+    constexpr int EB = EPI;
+    constexpr int RN = R * NP * 64;                          // outputs of one item: R row tiles x 16 rows x NP panels x 4 tokens
     constexpr int STAGE = gemv_stage_bytes<FMT>();
     constexpr int SC_OFF = ST * TB;                          // scales after the weights, {d,dmin} / integer scales after them, offsets last
     constexpr int DD_OFF = SC_OFF + ST * 64;
@@ -512,14 +544,17 @@ lg_gemv_kernel(LgGemvArgs a) {
     const int nkp_s = kp1 - kp0, nsb_s = nkp_s * 2;
     const int n_chunks = (nkp_s + P - 1) / P;
     const int n_groups = (a.n_row_tiles + R - 1) / R;
+    const bool cl = a.cl_ks != 0;                            // cluster (1, kslices, 1): cluster rank == blockIdx.y
 
     int8_t *sq = (int8_t *)smem;
     float2 *ss = (float2 *)(smem + (size_t)NP * nsb_s * 256);
     unsigned char *ring = (unsigned char *)(ss + (size_t)NP * nsb_s * 4);
     ring = (unsigned char *)(((uintptr_t)ring + 127) & ~(uintptr_t)127);
     float *red = (float *)(ring + (size_t)NS * STAGE);
-    uint64_t *full = (uint64_t *)(red + LG_GEMV_CW * R * NP * 64 + (EB == LG_EPI_NORMTAIL ? NP * 128 : 0));   // NORMTAIL: + fin[tok][32]
-    uint64_t *empty = full + NS, *pbar = empty + NS;
+    float *fin = red + LG_GEMV_CW * RN;                      // [RN] complete sums of the item (GeGLU, SUMS)
+    float *cred = fin + RN;                                  // cluster reduce: [kslices - 1][RN] partials of ranks 1.. (rank 0's copy is used)
+    uint64_t *full = (uint64_t *)(cred + (cl ? (a.kslices - 1) * RN : 0));
+    uint64_t *empty = full + NS, *pbar = empty + NS, *cbar = pbar + 1;
 
     pdl_launch();
     LG_STAMP(a.tag, 0);
@@ -527,8 +562,14 @@ lg_gemv_kernel(LgGemvArgs a) {
     if (threadIdx.x == 0) {
         for (int i = 0; i < NS; i++) { mbar_init(full + i, 1); mbar_init(empty + i, LG_GEMV_CW); }
         mbar_init(pbar, 1);
+        mbar_init(cbar, 1);
+        // rank 0 of a cluster expects every peer's RN partial sums (once: a cluster-reduced launch has one item per CTA)
+        if (cl && ks == 0) mbar_expect_tx(cbar, (uint32_t)(a.kslices - 1) * RN * 4);
     }
     __syncthreads();
+    // no peer may send before the receiving barrier exists: every thread arrives at the cluster barrier here; the consumer
+    // warps complete it (wait) only just before the exchange, microseconds later, so the start of the kernel does not stall
+    if (cl) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 
     if (warp == LG_GEMV_CW) {
         // ---------------- producer ----------------
@@ -584,7 +625,7 @@ lg_gemv_kernel(LgGemvArgs a) {
 
     // ---------------- consumers ----------------
     constexpr int CT = LG_GEMV_CW * 32;
-    constexpr int SLOTS = (R * NP * 64 + CT - 1) / CT;
+    constexpr int SLOTS = (RN + CT - 1) / CT;
     float best_v[SLOTS], sec_v[SLOTS]; int best_i[SLOTS];
     #pragma unroll
     for (int j = 0; j < SLOTS; j++) { best_v[j] = -INFINITY; sec_v[j] = -INFINITY; best_i[j] = 0x7fffffff; }
@@ -592,18 +633,6 @@ lg_gemv_kernel(LgGemvArgs a) {
     pdl_wait();
     LG_STAMP(a.tag, 1);
     if (a.skip && *a.skip) return;
-    __shared__ float s_post[POST ? LG_MAXM : 1];
-    // 1/rms of the deferred norm: a lane's partial sums of squares are all fetched here, before the first use (one memory
-    // latency, hidden under the panel wait and the main loop); they are added in a fixed order just before the epilogue
-    float post_pv[POST ? LG_SS_PER_LANE : 1];
-    if (POST && warp < a.M) {
-        #pragma unroll
-        for (int j = 0; j < LG_SS_PER_LANE; j++) {
-            const int i = lane + 32 * j;
-            post_pv[j] = i < a.n_post ? __ldcg(a.post_ss + (size_t)i * LG_MAXM + warp) : 0.0f;
-        }
-    }
-    bool post_done = false;
     bool ok = mbar_wait(pbar, 0);
     if (!ok && threadIdx.x == 0) atomicOr(a.err, LG_ERR_MBAR_TIMEOUT);
     LG_STAMP(a.tag, 2);
@@ -611,6 +640,18 @@ lg_gemv_kernel(LgGemvArgs a) {
 
     for (int grp = blockIdx.x; grp < n_groups; grp += gridDim.x) {
         const int rt0 = grp * R;
+        // SUMS: this thread's residual elements and norm weights, fetched now and used after the main loop
+        float x_v[SLOTS], w_v[SLOTS];
+        if (EB == LG_EPI_SUMS && ks == 0) {
+            #pragma unroll
+            for (int j = 0; j < SLOTS; j++) {
+                const int idx = threadIdx.x + j * CT;
+                const int rp = idx >> 6, r = rp / NP, p = rp % NP, tok = p * 4 + ((idx >> 4) & 3), row = (rt0 + r) * 16 + (idx & 15);
+                const bool live = idx < RN && tok < a.M && row < a.n_cols;
+                x_v[j] = live ? __ldcg(a.xres + (size_t)tok * a.ldx + row) : 0.0f;
+                w_v[j] = live ? a.add_w[row] : 0.0f;
+            }
+        }
         float acc[R][NP][2];
         #pragma unroll
         for (int r = 0; r < R; r++)
@@ -713,17 +754,7 @@ lg_gemv_kernel(LgGemvArgs a) {
         }
 
         LG_STAMP(a.tag, 3);
-        if (POST && !post_done) {
-            if (warp < a.M) {
-                float v = 0.0f;
-                #pragma unroll
-                for (int j = 0; j < LG_SS_PER_LANE; j++) v += post_pv[j];       // lane-strided, then the shuffle tree: a fixed order
-                v = warp_sum(v);
-                if (lane == 0) s_post[warp] = 1.0f / sqrtf(v / a.post_n + a.post_eps);
-            }
-            post_done = true;                                  // the consumer_sync below orders s_post before its readers
-        }
-        // fixed-order sum over the consumer warps
+        // the consumer warps' partial sums, added in warp order; output idx = ((r NP + p) 4 + token) 16 + row
         #pragma unroll
         for (int r = 0; r < R; r++)
             #pragma unroll
@@ -732,97 +763,90 @@ lg_gemv_kernel(LgGemvArgs a) {
                 red[(warp * R * NP + r * NP + p) * 64 + t * 16 + g + 8] = acc[r][p][1];
             }
         consumer_sync();
+        float fs[SLOTS];
+        #pragma unroll
+        for (int j = 0; j < SLOTS; j++) {
+            const int idx = threadIdx.x + j * CT;
+            float sum = 0.0f;
+            if (idx < RN) {
+                #pragma unroll
+                for (int w2 = 0; w2 < LG_GEMV_CW; w2++) sum += red[w2 * RN + idx];
+            }
+            fs[j] = sum;
+        }
+        if (cl) {
+            // k slices of one cluster: ranks 1.. send their sums to rank 0 and are done with the item; rank 0 adds them in
+            // rank order once every byte has arrived (bounded wait)
+            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+            if (ks != 0) {
+                #pragma unroll
+                for (int j = 0; j < SLOTS; j++) {
+                    const int idx = threadIdx.x + j * CT;
+                    if (idx < RN) dsmem_st_async_f32(cred + (size_t)(ks - 1) * RN + idx, cbar, 0, fs[j]);
+                }
+                consumer_sync();
+                continue;
+            }
+            // (waited for even after an earlier timeout: this CTA must not leave while peers still send into it)
+            if (!mbar_wait_cluster(cbar, 0)) { ok = false; if (lane == 0) atomicOr(a.err, LG_ERR_MBAR_TIMEOUT); }
+            LG_STAMP(a.tag, 4);
+            #pragma unroll
+            for (int j = 0; j < SLOTS; j++) {
+                const int idx = threadIdx.x + j * CT;
+                if (idx < RN)
+                    for (int r2 = 1; r2 < a.kslices; r2++) fs[j] += cred[(size_t)(r2 - 1) * RN + idx];
+            }
+        }
         if (EB == LG_EPI_GEGLU) {
+            #pragma unroll
+            for (int j = 0; j < SLOTS; j++) {
+                const int idx = threadIdx.x + j * CT;
+                if (idx < RN) fin[idx] = fs[j];
+            }
+            consumer_sync();
             // one warp per token: lane o = output (r, row8) of this item's 32 outputs
             for (int tok = warp; tok < NP * 4 && tok < a.M; tok += LG_GEMV_CW) {
                 const int p = tok >> 2, tl = tok & 3, row8 = lane & 7;
-                const float sc16 = POST ? 0.0625f * s_post[tok] : 0.0625f;
                 #pragma unroll
                 for (int rh = 0; rh < R / 4; rh++) {
                     const int r = rh * 4 + (lane >> 3);
                     const int ig = ((r * NP + p) * 4 + tl) * 16 + row8;
-                    float gate = 0.0f, up = 0.0f;
-                    #pragma unroll
-                    for (int w2 = 0; w2 < LG_GEMV_CW; w2++) { gate += red[w2 * R * NP * 64 + ig]; up += red[w2 * R * NP * 64 + ig + 8]; }
-                    float y = __fmul_rn(gelu_tanh(gate * sc16), up * sc16);
+                    const float gate = fin[ig], up = fin[ig + 8];
+                    float y = __fmul_rn(gelu_tanh(gate * 0.0625f), up * 0.0625f);
                     quant_group_store(y, lane, tok, rt0 / 4 + rh, a.outp);
                 }
             }
-        } else if (EB == LG_EPI_NORMTAIL) {
-            // (a) the item's final sums: fin[tok][32 rows]
-            float *fin = red + LG_GEMV_CW * R * NP * 64;
+        } else if (EB == LG_EPI_GATE) {
             #pragma unroll
             for (int j = 0; j < SLOTS; j++) {
-                int idx = threadIdx.x + j * CT;
-                if (idx < R * NP * 64) {
-                    int rp = idx >> 6, r = rp / NP, p = rp % NP, tok = p * 4 + ((idx >> 4) & 3);
-                    float sum = 0.0f;
-                    #pragma unroll
-                    for (int w2 = 0; w2 < LG_GEMV_CW; w2++) sum += red[w2 * R * NP * 64 + idx];
-                    fin[tok * 32 + r * 16 + (idx & 15)] = sum * 0.0625f;
-                }
+                const int idx = threadIdx.x + j * CT;
+                if (idx < RN) fin[idx] = fs[j];
             }
             consumer_sync();
-            // (b) warp tok: this item's sum of squares of token tok; its slice of x and of the two weight vectors
-            const int col = grp * 32 + lane;
-            const bool live = warp < a.M && col < a.n_cols;
-            float o_v = 0.0f, x_v = 0.0f, wa = 0.0f, wn = 0.0f;
-            if (warp < a.M) {
-                o_v = fin[warp * 32 + lane];
-                if (live) { x_v = a.xres[(size_t)warp * a.ldx + col]; wa = a.add_w[col]; wn = a.norm_w ? a.norm_w[col] : 1.0f; }
-                float ss = warp_sum(live ? o_v * o_v : 0.0f);
-                if (lane == 0) a.ssq1[(size_t)grp * LG_MAXM + warp] = ss;
+            // one warp per token: lane = row of the item's 32 rows (R = 2)
+            for (int tok = warp; tok < NP * 4 && tok < a.M; tok += LG_GEMV_CW) {
+                const int p = tok >> 2, tl = tok & 3, r = lane >> 4, row = (rt0 + r) * 16 + (lane & 15);
+                const float gv = fin[((r * NP + p) * 4 + tl) * 16 + (lane & 15)] * 0.0625f;
+                const float mv = row < a.n_valid_rows ? a.mul[(size_t)tok * a.ld_mul + row] : 0.0f;
+                quant_group_store(__fmul_rn(gelu_tanh(gv), mv), lane, tok, rt0 / 2, a.outp);
             }
-            // (c) grid-wide barrier: every item's partial is visible after it (bounded spin)
-            LG_STAMP(a.tag, 4);
-            __threadfence();
-            consumer_sync();
-            if (threadIdx.x == 0) {
-                atomicAdd(a.gbar, 1);
-                int it = 0;
-                while (*(volatile int *)a.gbar < n_groups && ++it < (LG_SPIN_LIMIT << 2)) { }
-                if (it >= (LG_SPIN_LIMIT << 2)) atomicOr(a.err, LG_ERR_GRID_BARRIER);
-                __threadfence();
-            }
-            consumer_sync();
-            LG_STAMP(a.tag, 5);
-            // (d) 1/rms of the whole row from all partials (fixed order), the residual update, the next panel
-            if (warp < a.M) {
-                float pv[LG_SS_PER_LANE];
-                #pragma unroll
-                for (int j = 0; j < LG_SS_PER_LANE; j++) {
-                    const int i = lane + 32 * j;
-                    pv[j] = i < n_groups ? __ldcg(a.ssq1 + (size_t)i * LG_MAXM + warp) : 0.0f;
-                }
-                float v = 0.0f;
-                #pragma unroll
-                for (int j = 0; j < LG_SS_PER_LANE; j++) v += pv[j];
-                v = warp_sum(v);
-                const float s1 = 1.0f / sqrtf(v / (float)a.n_cols + a.eps);
-                float xn = __fadd_rn(x_v, __fmul_rn(__fmul_rn(o_v, s1), wa));
-                xn = __fmul_rn(xn, a.out_scale);
-                if (!live) xn = 0.0f;
-                if (live) a.xres[(size_t)warp * a.ldx + col] = xn;
-                float ss2 = warp_sum(xn * xn);
-                if (lane == 0) a.ssq2[(size_t)grp * LG_MAXM + warp] = ss2;
-                if (grp < a.outp.nsb) quant_group_store(__fmul_rn(xn, wn), lane, warp, grp, a.outp);
-            }
-            // (e) the last CTA to leave re-arms the barrier for the next launch
-            if (threadIdx.x == 0 && atomicAdd(a.gbar + 1, 1) == n_groups - 1) { a.gbar[0] = 0; a.gbar[1] = 0; }
         } else {
+            float4 part[SLOTS];
             #pragma unroll
             for (int j = 0; j < SLOTS; j++) {
                 int idx = threadIdx.x + j * CT;
-                if (idx < R * NP * 64) {
+                part[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (idx < RN) {
                     int rp = idx >> 6, r = rp / NP, p = rp % NP, tok = p * 4 + ((idx >> 4) & 3);
-                    float sum = 0.0f;
-                    #pragma unroll
-                    for (int w2 = 0; w2 < LG_GEMV_CW; w2++) sum += red[w2 * R * NP * 64 + idx];
-                    sum *= POST ? 0.0625f * s_post[tok & (LG_MAXM - 1)] : 0.0625f;
+                    float sum = fs[j] * 0.0625f;
                     int row = (rt0 + r) * 16 + (idx & 15);
                     if (rt0 + r < a.n_row_tiles && tok < a.M) {
-                        if (EB == LG_EPI_STORE) {
+                        if (EB == LG_EPI_STORE || EB == LG_EPI_SUMS) {
                             a.out[((size_t)ks * LG_MAXM + tok) * a.ldo + row] = sum;
+                            if (EB == LG_EPI_SUMS && row < a.n_cols) {
+                                const float wo = __fmul_rn(w_v[j], sum);
+                                part[j] = make_float4(__fmul_rn(sum, sum), __fmul_rn(x_v[j], wo), __fmul_rn(wo, wo), __fmul_rn(x_v[j], x_v[j]));
+                            }
                         } else if (row < a.n_valid_rows) {
                             if (a.softcap > 0.0f) sum = a.softcap * tanhf(sum / a.softcap);
                             if (a.logits) a.logits[(size_t)tok * a.ldo + row] = sum;
@@ -832,6 +856,33 @@ lg_gemv_kernel(LgGemvArgs a) {
                     }
                 }
             }
+            if (EB == LG_EPI_SUMS) {
+                // the item's four sums per token: 16 rows of one (row tile, token) lie in one half warp (xor tree), then
+                // the row tiles in ascending order
+                float4 *hs = (float4 *)fin;                     // [R NP 4] one entry per (row tile, panel, token)
+                #pragma unroll
+                for (int j = 0; j < SLOTS; j++) {
+                    float4 v = part[j];
+                    #pragma unroll
+                    for (int o = 8; o > 0; o >>= 1) {
+                        v.x += __shfl_xor_sync(0xffffffffu, v.x, o); v.y += __shfl_xor_sync(0xffffffffu, v.y, o);
+                        v.z += __shfl_xor_sync(0xffffffffu, v.z, o); v.w += __shfl_xor_sync(0xffffffffu, v.w, o);
+                    }
+                    const int idx = threadIdx.x + j * CT;
+                    if (idx < RN && (idx & 15) == 0) hs[idx >> 4] = v;
+                }
+                consumer_sync();
+                if (threadIdx.x < a.M) {
+                    const int tok = threadIdx.x, p = tok >> 2, tl = tok & 3;
+                    float4 tot = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    #pragma unroll
+                    for (int r = 0; r < R; r++) {
+                        const float4 v = hs[(r * NP + p) * 4 + tl];
+                        tot.x += v.x; tot.y += v.y; tot.z += v.z; tot.w += v.w;
+                    }
+                    a.sums[(size_t)tok * LG_SUMS_ITEMS + grp] = tot;
+                }
+            }
         }
         consumer_sync();
         LG_STAMP(a.tag, 6);
@@ -839,11 +890,11 @@ lg_gemv_kernel(LgGemvArgs a) {
 
     if (EB == LG_EPI_HEAD) {
         // candidates of this CTA: one per (slot, thread); merge per token (larger value, lower index on ties)
-        float *cv = red; int *ci = (int *)(red + R * NP * 64); float *c2 = red + 2 * R * NP * 64;
+        float *cv = red; int *ci = (int *)(red + RN); float *c2 = red + 2 * RN;
         #pragma unroll
         for (int j = 0; j < SLOTS; j++) {
             int idx = threadIdx.x + j * CT;
-            if (idx < R * NP * 64) { cv[idx] = best_v[j]; ci[idx] = best_i[j]; c2[idx] = sec_v[j]; }
+            if (idx < RN) { cv[idx] = best_v[j]; ci[idx] = best_i[j]; c2[idx] = sec_v[j]; }
         }
         consumer_sync();
         if (threadIdx.x < a.M) {
@@ -1015,15 +1066,6 @@ __global__ void lg_norm_kernel(LgNormArgs a) {
 #define LG_NORM_CL_THREADS 128
 #define LG_NORM_CL_EPT 4               // row elements per thread the batched-load path holds in registers (rows up to 4096)
 
-__device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void dsmem_store(float *local_addr, uint32_t rank, float v) {
-    uint32_t la = smem_u32(local_addr), ra;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(la), "r"(rank));
-    asm volatile("st.shared::cluster.f32 [%0], %1;" :: "r"(ra), "f"(v) : "memory");
-}
 
 __global__ void __launch_bounds__(LG_NORM_CL_THREADS) lg_norm_cluster_kernel(LgNormArgs a) {
     extern __shared__ float row[];                       // this CTA's run of the row, then the two weight runs (3 * gpc*32 floats)
@@ -1136,6 +1178,67 @@ __global__ void __launch_bounds__(LG_NORM_CL_THREADS) lg_norm_cluster_kernel(LgN
     // every remote write into this CTA's slots precedes a cluster barrier this CTA has passed: safe to exit
 }
 
+// ---- residual update + next norm from the producer's partial sums ---------------------------------
+// The matmul before this kernel (SUMS epilogue) left the complete rows o and, per work item and token, the partial sums
+//   A = sum o^2,  B = sum x (w o),  C = sum (w o)^2,  D = sum x^2.
+// With s1 = 1/rms(o) the new residual row is x' = (x + (o s1) w) scale, and its own mean square follows from the same
+// sums without touching the row again:  sum x'^2 = scale^2 (D + 2 s1 B + s1^2 C).  So one warp per (token, 32 columns)
+// does the whole update with a single round of loads after the dependency wait -- no reduction across CTAs, no second
+// pass: x' goes back to the residual stream, y = (x' s2) norm_w (or x' itself without norm_w) to the next panel.
+// Every token's sums are added in a fixed order (lane-strided, then the shuffle tree), whatever the block's width.
+struct LgEltArgs {
+    float *x; int ldx;
+    const float *o; int ldo;                 // complete rows [M][ldo]
+    const float4 *sums; int n_sums;          // [LG_MAXM][LG_SUMS_ITEMS], n_sums entries per token
+    const float *add_w, *norm_w; float out_scale, eps; int n;
+    LgPanel panel; int want_panel;
+    float *y; int ldy;                       // optional f32 copy of y
+    const int *skip; int tag;
+};
+#define LG_ELT_WARPS 4
+__global__ void __launch_bounds__(LG_ELT_WARPS * 32) lg_elt_kernel(LgEltArgs a) {
+    const int lane = threadIdx.x & 31, tok = blockIdx.y, gq = blockIdx.x * LG_ELT_WARPS + (threadIdx.x >> 5);
+    const int i = gq * 32 + lane;
+    const bool live = i < a.n;
+    pdl_launch();
+    // the norm weights do not depend on the previous kernel
+    const float wa = live ? a.add_w[i] : 0.0f, wn = (live && a.norm_w) ? a.norm_w[i] : 1.0f;
+    LG_STAMP(a.tag, 0);
+    LG_STAMP_KIND(a.tag, 7);
+    pdl_wait();
+    LG_STAMP(a.tag, 1);
+    if (a.skip && *a.skip) return;
+    if (gq * 32 >= a.n) return;
+    float4 pv[LG_SS_PER_LANE];
+    #pragma unroll
+    for (int j = 0; j < LG_SS_PER_LANE; j++) {
+        const int k = lane + 32 * j;
+        pv[j] = k < a.n_sums ? __ldcg(a.sums + (size_t)tok * LG_SUMS_ITEMS + k) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    const float xv = live ? __ldcg(a.x + (size_t)tok * a.ldx + i) : 0.0f;
+    const float ov = live ? __ldcg(a.o + (size_t)tok * a.ldo + i) : 0.0f;
+    float4 tot = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    #pragma unroll
+    for (int j = 0; j < LG_SS_PER_LANE; j++) { tot.x += pv[j].x; tot.y += pv[j].y; tot.z += pv[j].z; tot.w += pv[j].w; }
+    tot.x = warp_sum(tot.x); tot.y = warp_sum(tot.y); tot.z = warp_sum(tot.z); tot.w = warp_sum(tot.w);
+    const float nf = (float)a.n;
+    const float s1 = 1.0f / sqrtf(tot.x / nf + a.eps);
+    float v = __fadd_rn(xv, __fmul_rn(__fmul_rn(ov, s1), wa));
+    v = __fmul_rn(v, a.out_scale);
+    if (live) a.x[(size_t)tok * a.ldx + i] = v;
+    float yv = v;
+    if (a.norm_w) {
+        const float ssq = __fmul_rn(__fmul_rn(a.out_scale, a.out_scale),
+                                    __fadd_rn(tot.w, __fadd_rn(__fmul_rn(__fmul_rn(2.0f, s1), tot.y), __fmul_rn(__fmul_rn(s1, s1), tot.z))));
+        const float s2 = 1.0f / sqrtf(fmaxf(ssq, 0.0f) / nf + a.eps);
+        yv = __fmul_rn(__fmul_rn(v, s2), wn);
+    }
+    if (!live) yv = 0.0f;
+    if (a.y && live) a.y[(size_t)tok * a.ldy + i] = yv;
+    if (a.want_panel) quant_group_store(yv, lane, tok, gq, a.panel);
+    LG_STAMP(a.tag, 6);
+}
+
 // Quantise f32 rows into a panel (used where the producer is not one of the fused kernels).
 __global__ void lg_quant_rows(const float *__restrict__ x, int ldx, int n, LgPanel P) {
     pdl_launch(); pdl_wait();
@@ -1225,17 +1328,25 @@ __global__ void lg_rope_table_kernel(const int *pos, int M, int hd, float base, 
 
 // RMSNorm (optional weight) + optional NeoX RoPE of one head vector by one warp.
 // lane owns pairs i = lane*PER + e (e < PER) and their partners i + hd/2;  out_lo[i], out_hi[i] returned in v0/v1.
+// In two halves (the loads; the arithmetic), for callers that put the loads of several rows in flight before the first use.
 template <int HD>
-__device__ __forceinline__ void head_norm_rope(const float *src, const float *w, const float2 *rope, float eps, int lane,
-                                               float (&v0)[HD / 64], float (&v1)[HD / 64]) {
+__device__ __forceinline__ void head_load(const float *src, const float2 *rope, int lane,
+                                          float (&v0)[HD / 64], float (&v1)[HD / 64], float2 (&cs)[HD / 64]) {
+    constexpr int PER = HD / 64, HALF = HD / 2;
+    #pragma unroll
+    for (int e = 0; e < PER; e++) {
+        const int i = lane * PER + e;
+        v0[e] = src[i]; v1[e] = src[i + HALF];               // plain loads: a caller may pass rows staged in shared memory
+        cs[e] = rope ? rope[i] : make_float2(1.0f, 0.0f);
+    }
+}
+template <int HD>
+__device__ __forceinline__ void head_finish(const float *w, bool rot, float eps, int lane,
+                                            float (&v0)[HD / 64], float (&v1)[HD / 64], const float2 (&cs)[HD / 64]) {
     constexpr int PER = HD / 64, HALF = HD / 2;
     float ss = 0.0f;
     #pragma unroll
-    for (int e = 0; e < PER; e++) {
-        int i = lane * PER + e;
-        v0[e] = src[i]; v1[e] = src[i + HALF];
-        ss += v0[e] * v0[e] + v1[e] * v1[e];
-    }
+    for (int e = 0; e < PER; e++) ss += v0[e] * v0[e] + v1[e] * v1[e];
     ss = warp_sum(ss);
     float s = 1.0f / sqrtf(ss / (float)HD + eps);
     #pragma unroll
@@ -1243,15 +1354,21 @@ __device__ __forceinline__ void head_norm_rope(const float *src, const float *w,
         int i = lane * PER + e;
         float a = __fmul_rn(v0[e], s), b = __fmul_rn(v1[e], s);
         if (w) { a = __fmul_rn(a, w[i]); b = __fmul_rn(b, w[i + HALF]); }
-        if (rope) {
-            const float2 cs = rope[i];
-            const float c = cs.x, sn = cs.y;
+        if (rot) {
+            const float c = cs[e].x, sn = cs[e].y;
             float r0 = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, sn));
             float r1 = __fadd_rn(__fmul_rn(a, sn), __fmul_rn(b, c));
             a = r0; b = r1;
         }
         v0[e] = a; v1[e] = b;
     }
+}
+template <int HD>
+__device__ __forceinline__ void head_norm_rope(const float *src, const float *w, const float2 *rope, float eps, int lane,
+                                               float (&v0)[HD / 64], float (&v1)[HD / 64]) {
+    float2 cs[HD / 64];
+    head_load<HD>(src, rope, lane, v0, v1, cs);
+    head_finish<HD>(w, rope != nullptr, eps, lane, v0, v1, cs);
 }
 
 // dynamic smem: Qhi | Qlo [NQ16][HD+8] f16 | K [S][HD+8] | V [S][HD+8] | scores [NQ16][S] f32 | Phi | Plo [NQ16][S+8] f16 | ml [NQ16][2]
