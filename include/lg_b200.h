@@ -159,7 +159,9 @@ int  lg_flash_decode_cluster_host(const float *q, const float *k, const float *v
  * reference.  The first call on a device looks up the array's device address; make that call
  * before any stream capture.  All calls share the array: two calls that overlap on the GPU
  * (different streams, no ordering) race.  Work is enqueued on `stream` (a cudaStream_t, or NULL)
- * and not waited for.  Returns 0, or a negative code with a message on stderr; -4 means
+ * and not waited for.  Alignment: k and v must be 16-byte aligned (their rows are fetched with 16-byte
+ * copies), q and out 4-byte aligned; a pointer into the middle of an element is turned away with -1, as
+ * are out-of-range arguments.  Returns 0, or a negative code with a message on stderr; -4 means
  * key tiles x M x H x (hd + 2) x 4 bytes exceed the array (e.g. M=4, H=16, hd=256: up to 63 tiles
  * of 128 keys, about 8,000 cached positions). */
 int  lg_flash_decode_noalloc(const float *d_q, const void *d_k_f16, const void *d_v_f16, int M, int H, int Hkv, int hd,
