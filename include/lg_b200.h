@@ -133,6 +133,13 @@ int  lg_dequant_host(int type, const void *blocks, int n_rows, int k, float *out
 /* y[tok][row] = W x[tok] for tok < M <= 8 through the tile-major repack, the 16-bit activation
  * panel and the tensor-core kernel; W is m rows of file-format blocks (q4_0, q4_K, q8_0, q6_K, q5_K, q3_K). */
 int  lg_gemv_host(int type, const void *blocks, int m, int k, const float *x, int M, int kslices, float *y);
+/* The decode step's "matmul + residual update + next norm" chain on caller data: o = W act (complete rows with the partial
+ * sums of the norms, k slices reduced inside a thread-block cluster where the plan has them), then
+ * xres = (xres + rmsnorm(o) add_w) * out_scale and y = rmsnorm(xres) norm_w (norm_w NULL: y = xres) by the residual kernel.
+ * The reference does this with separate norm kernels (src/cuda/model-cuda.cuh:119-190).  Returns 1 (cluster reduce used),
+ * 0 (whole k range in one CTA), -2 (matrix shape cannot leave complete rows), -1 (bad arguments). */
+int  lg_matmul_resid_host(int type, const void *blocks, int m, int k, const float *act, int M, float *xres,
+                          const float *add_w, float out_scale, const float *norm_w, float eps, float *y);
 /* The wide (prompt) matmul: out[tok][row] = W x[tok] for tok < n <= 256 at once, x rounded to f16,
  * weights expanded q4 -> f16 inside the kernel, tcgen05.mma with f32 accumulation.  With blocks_up
  * != NULL the two matrices are a gate/up pair and out[tok][row] = gelu_tanh(gate.x) * (up.x)

@@ -30,7 +30,7 @@ ABI_SYMBOLS = [
     "lg_forward_spec_n", "lg_set_replay", "lg_rounds_begin", "lg_rounds_enqueue", "lg_rounds_collect",
     "lg_set_round_width", "lg_set_replay_origin", "lg_host_syncs", "lg_set_draft_margin", "lg_drafts_skipped", "lg_weight_bytes", "lg_round_launches", "lg_last_hidden", "lg_kv_row", "lg_stream", "lg_engine_release",
     "lg_bench_matmul_pass", "lg_bench_prefill_pass", "lg_set_attn_deep", "lg_flash_decode_noalloc",
-    "lg_debug_bounded_wait", "lg_debug_stamps", "lg_debug_clear_stamps",
+    "lg_debug_bounded_wait", "lg_debug_stamps", "lg_debug_clear_stamps", "lg_matmul_resid_host",
     "lg_dequant_host", "lg_gemv_host", "lg_flash_decode_host", "lg_flash_decode_cluster_host", "lg_prefill_matmul_host",
 ]
 
@@ -71,6 +71,8 @@ def load() -> C.CDLL:
     L.lg_dequant_host.argtypes = [C.c_int, C.c_void_p, C.c_int, C.c_int, _f32p]; L.lg_dequant_host.restype = C.c_int
     L.lg_gemv_host.argtypes = [C.c_int, C.c_void_p, C.c_int, C.c_int, _f32p, C.c_int, C.c_int, _f32p]
     L.lg_gemv_host.restype = C.c_int
+    L.lg_matmul_resid_host.argtypes = [C.c_int, C.c_void_p, C.c_int, C.c_int, _f32p, C.c_int, _f32p, _f32p, C.c_float, C.c_void_p, C.c_float, _f32p]
+    L.lg_matmul_resid_host.restype = C.c_int
     L.lg_prefill_matmul_host.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, _f32p, C.c_int, _f32p]
     L.lg_prefill_matmul_host.restype = C.c_int
     L.lg_flash_decode_host.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
@@ -127,6 +129,25 @@ def gemv(ggml_type: int, raw: np.ndarray, m: int, k: int, x: np.ndarray, kslices
     if rc:
         raise ValueError(f"lg_gemv_host failed ({rc})")
     return y
+
+
+def matmul_resid(ggml_type: int, raw: np.ndarray, m: int, k: int, act: np.ndarray, xres: np.ndarray, add_w: np.ndarray,
+                 out_scale: float, norm_w, eps: float):
+    """The decode step's chain o = W act; x' = (x + rmsnorm(o) add_w) out_scale; y = rmsnorm(x') norm_w (norm_w None: y = x')
+    through the production kernels (matmul with complete rows + norm sums, residual kernel).  Returns (x', y, cluster_used)."""
+    L = load()
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    act = np.ascontiguousarray(act, dtype=np.float32)
+    x = np.array(xres, dtype=np.float32, order="C", copy=True)
+    aw = np.ascontiguousarray(add_w, dtype=np.float32)
+    nw = None if norm_w is None else np.ascontiguousarray(norm_w, dtype=np.float32)
+    M = act.shape[0]
+    y = np.empty((M, m), dtype=np.float32)
+    rc = L.lg_matmul_resid_host(ggml_type, raw.ctypes.data_as(C.c_void_p), m, k, act.reshape(-1), M, x.reshape(-1), aw, out_scale,
+                                None if nw is None else nw.ctypes.data_as(C.c_void_p), eps, y.reshape(-1))
+    if rc < 0:
+        raise ValueError(f"lg_matmul_resid_host failed ({rc})")
+    return x, y, bool(rc)
 
 
 def prefill_matmul(ggml_type: int, raw: np.ndarray, m: int, k: int, x: np.ndarray, raw_up: np.ndarray = None) -> np.ndarray:

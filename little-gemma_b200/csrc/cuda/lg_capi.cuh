@@ -69,6 +69,44 @@ extern "C" int lg_gemv_host(int type, const void *blocks, int m, int k, const fl
     return 0;
 }
 
+// The matmul with complete rows + norm sums followed by the residual kernel, as the decode step chains them:
+//   o = W act;  xres' = (xres + rmsnorm(o) add_w) * out_scale;  y = rmsnorm(xres') norm_w   (norm_w may be NULL: y = xres')
+// act [M][k], xres [M][m] (updated in place), y [M][m].  Returns 1 when the k slices were reduced inside a cluster, 0 when one
+// CTA held the whole k range, -2 when this matrix cannot leave complete rows (the engine then uses the norm kernel), -1 on bad arguments.
+extern "C" int lg_matmul_resid_host(int type, const void *blocks, int m, int k, const float *act, int M, float *xres,
+                                    const float *add_w, float out_scale, const float *norm_w, float eps, float *y) {
+    if (M < 1 || M > LG_MAXM || k % 64 || m % 32 || (type != GGML_TYPE_Q4_0 && type != GGML_TYPE_Q4_K && !lg_fmt_is_i8(type))) return -1;
+    if (ggml_blck_size((uint32_t)type) == 256 && k % 256) return -1;
+    Engine *e = scratch_engine();
+    if (!e->sums) e->sums = dalloc<float4>((size_t)LG_SUMS_ITEMS * LG_MAXM);
+    struct gguf_tensor t;
+    memset(&t, 0, sizeof t);
+    char name[] = "lg_matmul_resid_host";
+    t.name = name; t.n_dims = 2; t.dims[0] = k; t.dims[1] = m; t.dims[2] = t.dims[3] = 1; t.type = type; t.data = (void *)blocks;
+    WMat W = build_wmat(e, {&t});
+    if (!sums_ok(e, W)) { free_wmat(W); return -2; }
+    LgPanel P = panel_alloc(k), Py = panel_alloc(m);
+    float *d_act = dalloc<float>((size_t)M * k), *d_x = dalloc<float>((size_t)M * m), *d_y = dalloc<float>((size_t)M * m);
+    float *d_out = dalloc<float>((size_t)LG_MAXM * W.ldo), *d_aw = dalloc<float>(m), *d_nw = norm_w ? dalloc<float>(m) : nullptr;
+    LG_CHECK(cudaMemcpyAsync(d_act, act, (size_t)M * k * 4, cudaMemcpyHostToDevice, e->stream));
+    LG_CHECK(cudaMemcpyAsync(d_x, xres, (size_t)M * m * 4, cudaMemcpyHostToDevice, e->stream));
+    LG_CHECK(cudaMemcpyAsync(d_aw, add_w, (size_t)m * 4, cudaMemcpyHostToDevice, e->stream));
+    if (norm_w) LG_CHECK(cudaMemcpyAsync(d_nw, norm_w, (size_t)m * 4, cudaMemcpyHostToDevice, e->stream));
+    launch_k(e, lg_quant_rows, dim3((k / 32 + 7) / 8, M), dim3(256), 0, d_act, k, k, P);
+    int groups = 0;
+    GemvExtra xs; xs.xres = d_x; xs.ldx = m; xs.n_cols = m; xs.add_w = d_aw; xs.sums = e->sums; xs.groups_out = &groups;
+    const GemvPlan pl = plan_gemv(e, W, M > 4 ? 2 : 1, 0, false, false, true);
+    launch_gemv(e, W, P, M, d_out, LG_EPI_SUMS, 0, xs);
+    launch_elt(e, M, d_x, m, m, eps, d_out, W.ldo, groups, d_aw, out_scale, d_nw, &Py, d_y, m);
+    LG_CHECK(cudaGetLastError());
+    LG_CHECK(cudaMemcpyAsync(xres, d_x, (size_t)M * m * 4, cudaMemcpyDeviceToHost, e->stream));
+    LG_CHECK(cudaMemcpyAsync(y, d_y, (size_t)M * m * 4, cudaMemcpyDeviceToHost, e->stream));
+    check_err(e);
+    free_wmat(W); panel_free(P); panel_free(Py);
+    cudaFree(d_act); cudaFree(d_x); cudaFree(d_y); cudaFree(d_out); cudaFree(d_aw); if (d_nw) cudaFree(d_nw);
+    return pl.cl ? 1 : 0;
+}
+
 // out[tok][m] = W x[tok]  for n <= 256 rows at once through the wide (tcgen05) matmul; x is rounded to f16 first.
 // geglu != 0: `blocks`/`blocks_up` are the gate and up matrices [m x k]; out[tok][m] = gelu(gate . x) * (up . x), rounded to f16.
 extern "C" int lg_prefill_matmul_host(int type, const void *blocks, const void *blocks_up, int m, int k, const float *x, int n,

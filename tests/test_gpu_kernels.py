@@ -76,6 +76,50 @@ def test_gemv_matches_oracle(lg, port_built, wtype, m, k, M):
         assert np.abs(got2 - want).max() / scale < 2e-4
 
 
+def _resid_ref(w, act, x, add_w, out_scale, norm_w, eps):
+    """f64 statement of the chain: o = W act; x' = (x + rmsnorm(o) add_w) out_scale; y = rmsnorm(x') norm_w."""
+    o = act.astype(np.float64) @ w.astype(np.float64).T
+    s1 = 1.0 / np.sqrt((o * o).mean(axis=1, keepdims=True) + eps)
+    xn = (x.astype(np.float64) + o * s1 * add_w.astype(np.float64)) * out_scale
+    if norm_w is None:
+        return xn, xn
+    s2 = 1.0 / np.sqrt((xn * xn).mean(axis=1, keepdims=True) + eps)
+    return xn, xn * s2 * norm_w.astype(np.float64)
+
+
+@pytest.mark.parametrize("m,k,want_cluster", [(3840, 4096, False), (3840, 15360, True), (2048, 256, None), (2048, 16384, True), (256, 512, None)])
+@pytest.mark.parametrize("M", [1, 4, 5, 8])
+def test_matmul_with_sums_and_residual_kernel_match_f64(lg, port_built, m, k, want_cluster, M):
+    """The o / down / PLE projections of the benchmark shapes through the sums epilogue (k slices reduced inside a cluster
+    where the plan has them) and the residual kernel: the new residual row and the next norm's row against f64, with a
+    residual stream that carries outliers (the second norm's mean square comes from partial sums, not from a pass over the row)."""
+    s = synth_module()
+    rng = np.random.default_rng(m + k + M)
+    o = _oracle()
+    raw = s.quantize_q4_0(rng.standard_normal(m * k).astype(np.float32) * 0.02)
+    w = o.dequant(s.Q4_0, raw, m * k).reshape(m, k)
+    o.close()
+    act = (rng.standard_normal((M, k)) * np.exp(rng.standard_normal((M, k)))).astype(np.float32)
+    x = (rng.standard_normal((M, m)) * np.exp(1.5 * rng.standard_normal((M, m)))).astype(np.float32)
+    x[:, 7] *= 300.0                                        # one massive channel, as residual streams have
+    add_w = (1.0 + 0.3 * rng.standard_normal(m)).astype(np.float32)
+    norm_w = (1.0 + 0.3 * rng.standard_normal(m)).astype(np.float32)
+    eps = 1e-6
+    for out_scale, nw in ((1.0, norm_w), (0.37, norm_w), (1.0, None)):
+        xn, y, used_cluster = lg.matmul_resid(s.Q4_0, raw, m, k, act, x, add_w, out_scale, nw, eps)
+        want_x, want_y = _resid_ref(w, act, x, add_w, out_scale, nw, eps)
+        if want_cluster is not None:
+            assert used_cluster == want_cluster
+        ex = np.abs(xn - want_x).max() / np.abs(want_x).max()
+        ey = np.abs(y - want_y).max() / np.abs(want_y).max()
+        assert ex < 2e-4 and ey < 2e-4, (ex, ey)
+        # rows do not depend on the block's width: the row run alone carries the same bits
+        if M > 1:
+            xa, ya, _ = lg.matmul_resid(s.Q4_0, raw, m, k, act[M - 1:M], x[M - 1:M], add_w, out_scale, nw, eps)
+            assert np.array_equal(xa[0].view(np.uint32), xn[M - 1].view(np.uint32))
+            assert np.array_equal(ya[0].view(np.uint32), y[M - 1].view(np.uint32))
+
+
 def test_gemv_column_is_independent_of_block_width(lg):
     """Row j of an M-wide block is bit-identical to the same row run alone (MTP == plain)."""
     s = synth_module()
