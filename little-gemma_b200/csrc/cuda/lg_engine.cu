@@ -614,6 +614,24 @@ void launch_elt(Engine *e, int M, float *x, int ldx, int n, float eps, const flo
     launch_k(e, lg_elt_kernel, dim3((n / 32 + LG_ELT_WARPS - 1) / LG_ELT_WARPS, M), dim3(LG_ELT_WARPS * 32), 0, a);
 }
 
+// A projection followed by the residual update and the next norm: x = (x + rmsnorm(W in) add_w) out_scale, then the panel /
+// f32 row of rmsnorm(x) norm_w.  Where the matrix can leave complete rows (decided from the matrix alone), the matmul's
+// sums epilogue + one elementwise kernel; otherwise k-slice partials + the norm kernel.
+void launch_matmul_resid(Engine *e, const WMat &W, const LgPanel &in, int M, float *out, float *x, int n, float eps,
+                         const float *add_w, float out_scale, const float *norm_w, const LgPanel *panel, float *y, const int *skip = nullptr) {
+    if (sums_ok(e, W)) {
+        int groups = 0;
+        GemvExtra xs; xs.xres = x; xs.ldx = n; xs.n_cols = n; xs.add_w = add_w; xs.sums = e->sums; xs.groups_out = &groups; xs.skip = skip;
+        launch_gemv(e, W, in, M, out, LG_EPI_SUMS, 0, xs);
+        launch_elt(e, M, x, n, n, eps, out, W.ldo, groups, add_w, out_scale, norm_w, panel, y, n, skip);
+    } else {
+        int ks = 1;
+        GemvExtra xs; xs.ks_out = &ks; xs.skip = skip;
+        launch_gemv(e, W, in, M, out, LG_EPI_STORE, 0, xs);
+        launch_norm(e, M, x, n, n, eps, out, ks, (size_t)LG_MAXM * W.ldo, W.ldo, add_w, out_scale, norm_w, panel, y, n, skip);
+    }
+}
+
 size_t attn_smem(int nq, int hd) {
     size_t nq16 = (size_t)((nq + 15) & ~15), ldh = hd + 8, S = lg_attn_tile(hd);
     return 2 * nq16 * ldh * 2 + 2 * S * ldh * 2 + nq16 * S * 4 + 2 * nq16 * (S + 8) * 2 + nq16 * 8 + 64;
@@ -1076,8 +1094,8 @@ void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags, int 
     }
     // rotation tables of this block's positions, one per layer kind
     if (only & (C_ATTN | C_MISC)) {
-        launch_k(e, lg_rope_table_kernel, dim3(1), dim3(256), 0, d_pos, M, e->hd_local, c->rope_freq_base_swa, (const float *)nullptr, e->rope_local);
-        launch_k(e, lg_rope_table_kernel, dim3(1), dim3(256), 0, d_pos, M, e->hd_global, c->rope_freq_base, (const float *)e->rope_div, e->rope_global);
+        launch_k(e, lg_rope_tables_kernel, dim3(1, 2), dim3(256), 0, d_pos, M, e->hd_local, c->rope_freq_base_swa, (const float *)nullptr, e->rope_local,
+                 e->hd_global, c->rope_freq_base, (const float *)e->rope_div, e->rope_global);
     }
     if (only & C_NORM) launch_norm(e, M, e->x, ne, ne, c->rms_eps, nullptr, 0, 0, 0, nullptr, 1.0f, e->L[0].attn_norm, &e->p_ne, nullptr, 0);
 
@@ -1438,7 +1456,7 @@ DraftW *draft_build(Engine *e, struct mtp *t, const struct kvcache *kv) {
         draft_free(d);
         return nullptr;
     }
-    d->cat = dalloc<float>(2 * d->nb); d->x = dalloc<float>(d->ni); d->hbuf = dalloc<float>(d->ni);
+    d->cat = dalloc<float>(2 * d->nb + 64); d->x = dalloc<float>(d->ni + 64); d->hbuf = dalloc<float>(d->ni);     // + 64: matmuls write whole row tiles
     d->qbuf = dalloc<float>((size_t)LG_MAXM * (qmax + 64)); d->qrot = dalloc<float>(qmax);
     d->obuf = dalloc<float>((size_t)e->max_ks * LG_MAXM * (std::max(d->ni, d->nb) + 64));
     d->gu = dalloc<float>(32);
@@ -1464,23 +1482,32 @@ void enqueue_draft(Engine *e, DraftW *d, const struct kvcache *kv, int slot, boo
     const struct config *c = &m->cfg;
     const int ni = d->ni, nb = d->nb;
     // a chained draft does nothing when the round's drafting was called off (the previous draft's confidence margin fell
-    // below the threshold): its heavy kernels return at once on this word and lg_store_draft pads the slot
+    // below the threshold): its heavy kernels return at once on this word and lg_draft_pick_kernel pads the slot
     const int *skip = chained ? &e->st->stop : nullptr;
     GemvExtra xs_; xs_.skip = skip;
     launch_k(e, lg_embed_rows, dim3(1), dim3(256), 0, e->head.wq, e->head.ws, e->head.wd, e->head.wm, e->head.fmt, e->head.nkp, e->head.m,
                                     e->st->toks + (slot - 1), sqrtf((float)nb), d->cat, 2 * nb);
     if (chained) {
-        // h_prev = post(x): x still holds the previous draft's normed hidden, p_ni its panel
-        launch_gemv(e, d->post, d->p_ni, 1, d->obuf, LG_EPI_STORE, 1, xs_);
-        launch_k(e, lg_copy_f32, dim3((nb + 255) / 256), dim3(256), 0, d->cat + nb, d->obuf, nb);
+        // h_prev = post(x): x still holds the previous draft's normed hidden, p_ni its panel; the matmul writes its row
+        // straight into the second half of the concatenated input
+        if (plan_gemv(e, d->post, 1, 1, false).ks == 1) {
+            launch_gemv(e, d->post, d->p_ni, 1, d->cat + nb, LG_EPI_STORE, 1, xs_);
+        } else {                                             // (a k range too long for one slice: partial planes, then slice 0 .. added by the copy)
+            launch_gemv(e, d->post, d->p_ni, 1, d->obuf, LG_EPI_STORE, 1, xs_);
+            launch_k(e, lg_copy_f32, dim3((nb + 255) / 256), dim3(256), 0, d->cat + nb, d->obuf, nb);
+        }
     } else {
         launch_k(e, lg_copy_f32, dim3((nb + 255) / 256), dim3(256), 0, d->cat + nb, e->h_prev, nb);
     }
     launch_k(e, lg_quant_rows, dim3((2 * nb / 32 + 7) / 8, 1), dim3(256), 0, d->cat, 2 * nb, 2 * nb, d->p_cat);
-    launch_gemv(e, d->pre, d->p_cat, 1, d->obuf, LG_EPI_STORE, 1, xs_);
-    launch_k(e, lg_copy_f32, dim3((ni + 255) / 256), dim3(256), 0, d->x, d->obuf, ni);
-    launch_k(e, lg_rope_table_kernel, dim3(1), dim3(256), 0, (const int *)&e->st->dpos, 1, d->hd_local, d->base_swa, (const float *)nullptr, d->rope_local);
-    launch_k(e, lg_rope_table_kernel, dim3(1), dim3(256), 0, (const int *)&e->st->dpos, 1, d->hd_global, d->base_full, (const float *)nullptr, d->rope_global);
+    if (plan_gemv(e, d->pre, 1, 1, false).ks == 1) {
+        launch_gemv(e, d->pre, d->p_cat, 1, d->x, LG_EPI_STORE, 1, xs_);      // straight into the head's residual row
+    } else {
+        launch_gemv(e, d->pre, d->p_cat, 1, d->obuf, LG_EPI_STORE, 1, xs_);
+        launch_k(e, lg_copy_f32, dim3((ni + 255) / 256), dim3(256), 0, d->x, d->obuf, ni);
+    }
+    launch_k(e, lg_rope_tables_kernel, dim3(1, 2), dim3(256), 0, (const int *)&e->st->dpos, 1, d->hd_local, d->base_swa, (const float *)nullptr, d->rope_local,
+             d->hd_global, d->base_full, (const float *)nullptr, d->rope_global);
     launch_norm(e, 1, d->x, ni, ni, d->eps, nullptr, 0, 0, 0, nullptr, 1.0f, d->blk[0].attn_norm, &d->p_ni, nullptr, 0, skip);
     for (size_t L = 0; L < d->blk.size(); L++) {
         DraftBlockW &b = d->blk[L];
@@ -1500,25 +1527,18 @@ void enqueue_draft(Engine *e, DraftW *d, const struct kvcache *kv, int slot, boo
         const int cl = attn_cluster_size(e, aa.window, kv->max_seq, aa.seq, hd, d->n_head, Hkv);
         if (cl) launch_attn_cluster(e, aa, cl);
         else launch_attn(e, aa, tiles_for(aa.window, kv->max_seq, 1, hd));
-        int ks_o = 1;
-        GemvExtra xo; xo.ks_out = &ks_o; xo.skip = skip;
-        launch_gemv(e, b.o, pa, 1, d->obuf, LG_EPI_STORE, 0, xo);
-        launch_norm(e, 1, d->x, ni, ni, d->eps, d->obuf, ks_o, (size_t)LG_MAXM * b.o.ldo, b.o.ldo, b.post_attn, 1.0f,
-                    b.ffn_norm, &d->p_ni, nullptr, 0, skip);
+        launch_matmul_resid(e, b.o, pa, 1, d->obuf, d->x, ni, d->eps, b.post_attn, 1.0f, b.ffn_norm, &d->p_ni, nullptr, skip);
         GemvExtra xg; xg.outp = &d->p_ff; xg.skip = skip;
         launch_gemv(e, b.gateup, d->p_ni, 1, nullptr, LG_EPI_GEGLU, 1, xg);
         bool last = L + 1 == d->blk.size();
-        int ks_d = 1;
-        GemvExtra xd; xd.ks_out = &ks_d; xd.skip = skip;
-        launch_gemv(e, b.down, d->p_ff, 1, d->obuf, LG_EPI_STORE, 0, xd);
-        launch_norm(e, 1, d->x, ni, ni, d->eps, d->obuf, ks_d, (size_t)LG_MAXM * b.down.ldo, b.down.ldo, b.post_ffw, b.out_scale,
-                    last ? d->out_norm : d->blk[L + 1].attn_norm, &d->p_ni, last ? d->hbuf : nullptr, ni, skip);
+        launch_matmul_resid(e, b.down, d->p_ff, 1, d->obuf, d->x, ni, d->eps, b.post_ffw, b.out_scale,
+                            last ? d->out_norm : d->blk[L + 1].attn_norm, &d->p_ni, last ? d->hbuf : nullptr, skip);
     }
     int gx = 0;
     GemvExtra xh; xh.softcap = d->softcap; xh.amax_val = d->amax_val; xh.amax_idx = d->amax_idx; xh.gx_out = &gx; xh.skip = skip; xh.amax_val2 = d->amax_val2;
     launch_gemv(e, d->head, d->p_ni, 1, nullptr, LG_EPI_HEAD, 1, xh);
-    launch_k(e, lg_argmax_final, dim3(1), dim3(256), 0, (const float *)d->amax_val, (const int *)d->amax_idx, gx, d->best, (const float *)d->amax_val2, d->margin);
-    launch_k(e, lg_store_draft, dim3(1), dim3(1), 0, e->st, slot, (const int *)d->best, (const float *)d->margin, (const float *)e->d_margin_thr);
+    launch_k(e, lg_draft_pick_kernel, dim3(1), dim3(256), 0, (const float *)d->amax_val, (const int *)d->amax_idx, gx, (const float *)d->amax_val2,
+             e->st, slot, (const float *)e->d_margin_thr);
 }
 
 DraftW *draft_for(Engine *e, struct mtp *t, const struct kvcache *kv) {

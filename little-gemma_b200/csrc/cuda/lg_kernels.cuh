@@ -922,11 +922,10 @@ __device__ __forceinline__ void top2_merge(float &bv, int &bi, float &s2, float 
     else s2 = fmaxf(s2, ov);
     s2 = fmaxf(s2, o2);
 }
-__global__ void lg_argmax_final(const float *__restrict__ val, const int *__restrict__ idx, int n_parts, int *out,
-                                const float *__restrict__ val2, float *__restrict__ margin) {
-    pdl_launch(); pdl_wait();
-    int tok = blockIdx.x;
-    float bv = -INFINITY, s2 = -INFINITY; int bi = 0x7fffffff;
+// Block-wide merge of the per-CTA candidates of token `tok`; the result is valid in thread 0.
+__device__ __forceinline__ void argmax_block(const float *__restrict__ val, const int *__restrict__ idx, int n_parts, int tok,
+                                             const float *__restrict__ val2, float &bv, int &bi, float &s2) {
+    bv = -INFINITY; s2 = -INFINITY; bi = 0x7fffffff;
     for (int i = threadIdx.x; i < n_parts; i += blockDim.x)
         top2_merge(bv, bi, s2, val[(size_t)i * LG_MAXM + tok], idx[(size_t)i * LG_MAXM + tok], val2 ? val2[(size_t)i * LG_MAXM + tok] : -INFINITY);
     __shared__ float sv[32], sv2[32]; __shared__ int si[32];
@@ -946,10 +945,17 @@ __global__ void lg_argmax_final(const float *__restrict__ val, const int *__rest
             float ov = __shfl_xor_sync(0xffffffffu, bv, o), o2 = __shfl_xor_sync(0xffffffffu, s2, o); int oi = __shfl_xor_sync(0xffffffffu, bi, o);
             top2_merge(bv, bi, s2, ov, oi, o2);
         }
-        if (threadIdx.x == 0) {
-            out[tok] = bi == 0x7fffffff ? 0 : bi;
-            if (margin) margin[tok] = bv - s2;
-        }
+    }
+}
+__global__ void lg_argmax_final(const float *__restrict__ val, const int *__restrict__ idx, int n_parts, int *out,
+                                const float *__restrict__ val2, float *__restrict__ margin) {
+    pdl_launch(); pdl_wait();
+    int tok = blockIdx.x;
+    float bv, s2; int bi;
+    argmax_block(val, idx, n_parts, tok, val2, bv, bi, s2);
+    if (threadIdx.x == 0) {
+        out[tok] = bi == 0x7fffffff ? 0 : bi;
+        if (margin) margin[tok] = bv - s2;
     }
 }
 
@@ -1318,6 +1324,22 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 __global__ void lg_rope_table_kernel(const int *pos, int M, int hd, float base, const float *div, float2 *tab) {
     pdl_launch(); pdl_wait();
     const int half = hd >> 1;
+    for (int u = blockIdx.x * blockDim.x + threadIdx.x; u < M * half; u += gridDim.x * blockDim.x) {
+        const int tok = u / half, i = u % half;
+        float freq = powf(base, -2.0f * (float)i / (float)hd);
+        float ang = (float)(*pos + tok) * freq / (div ? div[i] : 1.0f);
+        tab[u] = make_float2(cosf(ang), sinf(ang));
+    }
+}
+// The tables of both layer kinds (sliding-window: blockIdx.y 0, full attention: 1) in one launch.
+__global__ void lg_rope_tables_kernel(const int *pos, int M, int hd_a, float base_a, const float *div_a, float2 *tab_a,
+                                      int hd_b, float base_b, const float *div_b, float2 *tab_b) {
+    pdl_launch(); pdl_wait();
+    const bool second = blockIdx.y != 0;
+    const int hd = second ? hd_b : hd_a, half = hd >> 1;
+    const float base = second ? base_b : base_a;
+    const float *div = second ? div_b : div_a;
+    float2 *tab = second ? tab_b : tab_a;
     for (int u = blockIdx.x * blockDim.x + threadIdx.x; u < M * half; u += gridDim.x * blockDim.x) {
         const int tok = u / half, i = u % half;
         float freq = powf(base, -2.0f * (float)i / (float)hd);
@@ -1756,12 +1778,18 @@ __global__ void lg_copy_f32(float *__restrict__ dst, const float *__restrict__ s
 __global__ void lg_set_draft_pos(LgRoundState *st, int j) { pdl_launch(); pdl_wait(); st->dpos = st->pos + j; if (j == 0) st->stop = 0; }
 // slots a head cannot draft repeat the previous token, so the verify simply rejects them
 __global__ void lg_pad_drafts(LgRoundState *st, int from, int M) { pdl_launch(); pdl_wait(); for (int j = from; j < M; j++) st->toks[j] = st->toks[j - 1]; }
-// Draft j is in: keep it -- or, when the round's drafting was called off before it ran, repeat the previous token (the
+// Draft j is in (lg_draft_pick_kernel): keep it -- or, when the round's drafting was called off before it ran, repeat the previous token (the
 // verify then rejects the slot, as for a head that cannot chain).  A draft whose confidence margin (best - second best
 // logit) is below *thr calls off the drafts after it: they would most likely be rejected, and their forwards are skipped.
-__global__ void lg_store_draft(LgRoundState *st, int j, const int *best, const float *margin, const float *thr) {
+// (Runs as the tail of the draft head's argmax merge: the winner of the per-CTA candidates becomes draft j.)
+__global__ void lg_draft_pick_kernel(const float *__restrict__ val, const int *__restrict__ idx, int n_parts,
+                                     const float *__restrict__ val2, LgRoundState *st, int j, const float *thr) {
     pdl_launch(); pdl_wait();
-    if (st->stop) { st->toks[j] = st->toks[j - 1]; st->n_skipped++; return; }
-    st->toks[j] = *best;
-    if (thr && margin && *margin < *thr) st->stop = 1;
+    float bv, s2; int bi;
+    argmax_block(val, idx, n_parts, 0, val2, bv, bi, s2);
+    if (threadIdx.x == 0) {
+        if (st->stop) { st->toks[j] = st->toks[j - 1]; st->n_skipped++; return; }
+        st->toks[j] = bi == 0x7fffffff ? 0 : bi;
+        if (thr && bv - s2 < *thr) st->stop = 1;
+    }
 }
