@@ -13,7 +13,8 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 REF = os.path.join(ROOT, "oracle", "_ref")
-HAVE_REFERENCE = os.path.isdir("/root/reference/src")
+_REF_TREE = subprocess.run(["make", "-s", "-C", os.path.join(ROOT, "oracle"), "print-ref"], capture_output=True, text=True).stdout.strip()
+HAVE_REFERENCE = bool(_REF_TREE) and os.path.isdir(os.path.join(_REF_TREE, "src"))
 
 BACKEND_SYMBOLS = ["model_kv_host", "kvcache_init", "kvcache_free", "kvcache_save_prefix", "kvcache_restore_prefix",
                    "model_forward", "model_forward_next", "model_prefill", "model_prefill_embd", "model_prefill_mixed",
