@@ -517,6 +517,12 @@ def main():
     n_mm, mm_ms = mm_pass(0)
     _, mm_plain_ms = mm_pass(63)
     W = matmul_weight_bytes(t_shape)
+    # ... and the ONE kernel with the largest share of the step: the gate/up matmul with its GeGLU epilogue, one launch per
+    # layer, replayed back to back (class 4, in the variant the step runs); bytes per launch = the layer's gate + up matrices
+    n_gu, gu_ms = mm_pass(1024 + 4)
+    gu_bytes = int(2 * t_shape.n_ff * t_shape.n_embd * 0.5625)
+    gu_us = gu_ms * 1e3 / max(n_gu, 1)
+    gu_gbs = gu_bytes / (gu_us * 1e-6) / 1e9
 
     peaks = load_peaks()
     prefill_rec = time_prefill(r, synth, torch, t_shape, peaks)
@@ -567,15 +573,19 @@ def main():
                     clocks=clocks, gpu_launches=int(launches_per_round * a.steps),
                     e2e={"value": agg["e2e_tok_s"], "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                          "rounds": e2e_rounds, "host_syncs_per_round": syncs_per_round},
-                    roofline={"bound": "hbm", "kernel": "lg_gemv_kernel (the step's epilogue variants: store, complete rows + norm sums, "
-                                                        "GeGLU, head)",
-                              "achieved": mm_gbs, "peak": peak, "unit": "GB/s",
-                              "frac": mm_gbs / peak, "traffic": int(W * DRAM_TRAFFIC_RATIO), "peak_source": peak_src,
-                              "traffic_note": "dram read+write bytes of the matmul pass: ncu capture of the E4B-class gate/up "
-                                              "launch (37.793 MB moved for 37.749 MB of q4_0) scaled by weight bytes; writes 0",
-                              "algorithmic_bytes": W, "launches": n_mm, "ms": mm_ms,
-                              "frac_of_8TBs": mm_gbs / 8000.0,
-                              "plain_store_variants_ms": mm_plain_ms,
+                    roofline={"bound": "hbm",
+                              "kernel": "lg_gemv_kernel<4, NP, q4, GeGLU>: the gate/up matmul, the step's dominant kernel (23 % of its "
+                                        "kernel time), one launch per layer timed back to back",
+                              "achieved": gu_gbs, "peak": peak, "unit": "GB/s", "frac": gu_gbs / peak,
+                              "traffic": int(gu_bytes * DRAM_TRAFFIC_RATIO), "peak_source": peak_src,
+                              "traffic_note": "dram read+write bytes per launch: ncu capture of the E4B-class gate/up launch "
+                                              "(37.793 MB moved for 37.749 MB of q4_0) scaled by the launch's weight bytes; writes 0",
+                              "algorithmic_bytes": gu_bytes, "launches": n_gu, "us_per_launch": gu_us,
+                              "frac_of_8TBs": gu_gbs / 8000.0,
+                              # every weight matmul of one verify step replayed alone, in the epilogue variants the step runs
+                              "all_matmuls": {"algorithmic_bytes": W, "launches": n_mm, "ms": mm_ms, "achieved": mm_gbs,
+                                              "frac": mm_gbs / peak, "plain_store_variants_ms": mm_plain_ms},
+                              # the whole verify step (weights + cache rows over its device time): the number the kernels add up to
                               "step_ms": verify_ms, "step_bytes": W + kvb, "step_achieved": step_gbs,
                               "step_frac": step_gbs / peak, "step_frac_of_8TBs": step_gbs / 8000.0},
                     cpu_baseline=cpu, prefill=prefill_rec)
