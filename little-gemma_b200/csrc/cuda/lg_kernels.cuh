@@ -504,104 +504,6 @@ __device__ __forceinline__ void mma_s8_k16(int (&c)[4], uint32_t a0, uint32_t a1
         : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(b0));
 }
 
-// One tile position of a ring stage: the B fragments of the position's two 32-column sub-blocks, then every row tile of
-// the position (or this warp's share of them) -- unpack, tensor-core product, integer hi/lo combine, f32 scale-accumulate.
-// `st` = the stage, `sbl0` = the position's first sub-block in the CTA's panel slice, `pp` = the position inside the stage.
-template <int R, int NP, int FMT>
-__device__ __forceinline__ void gemv_position(const unsigned char *st, const int8_t *sq, const float2 *ss, int nsb_s, int sbl0, int pp,
-                                              int warp, int lane, float (&acc)[R][NP][2]) {
-    constexpr int ST = gemv_stage_tiles<FMT>();
-    constexpr int P = ST / R;
-    constexpr int TB = lg_tile_bytes(FMT);
-    constexpr int PW = P < LG_GEMV_CW ? P : LG_GEMV_CW, RS = LG_GEMV_CW / PW;
-    constexpr int SC_OFF = ST * TB, DD_OFF = SC_OFF + ST * 64, MM_OFF = DD_OFF + ST * 64;
-    const int g = lane >> 2, t = lane & 3;
-    uint2 b[2][NP]; float2 xs[2][NP];
-    #pragma unroll
-    for (int s = 0; s < 2; s++)
-        #pragma unroll
-        for (int p = 0; p < NP; p++) {
-            const int sbl = sbl0 + s;
-            b[s][p] = *(const uint2 *)(sq + ((size_t)p * nsb_s + sbl) * 256 + lane * 8);
-            xs[s][p] = ss[((size_t)p * nsb_s + sbl) * 4 + t];
-        }
-    #pragma unroll
-    for (int r = 0; r < R; r++) {
-        if (RS > 1 && (r % RS) != warp / PW) continue;          // another warp's row tile
-        if (FMT >= LG_FMT_I8) {
-            // i8 tile: per sub-block this lane's 16 bytes are {row g, row g+8} x {columns 4t.., 16+4t..}; one
-            // k16 MMA per 16-column group, whose integer scale joins the block's f16 d (x16: the common
-            // epilogue divides by the 16 the q4 tiles carry)
-            const unsigned char *tp = st + (size_t)(r * P + pp) * TB;
-            const uint2 sw2 = *(const uint2 *)(st + SC_OFF + (size_t)(r * P + pp) * 64 + g * 8);
-            const uint2 is2 = *(const uint2 *)(st + DD_OFF + (size_t)(r * P + pp) * 64 + g * 8);
-            uint4 mm = make_uint4(0, 0, 0, 0);
-            if (FMT == LG_FMT_I8M) mm = *(const uint4 *)(st + MM_OFF + (size_t)(r * P + pp) * 128 + g * 16);
-            #pragma unroll
-            for (int s = 0; s < 2; s++) {
-                const uint4 w = *(const uint4 *)(tp + s * 512 + lane * 16);
-                const float2 fd = __half22float2(*(const __half2 *)(s ? &sw2.y : &sw2.x));
-                #pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    const int i0 = (int)(int8_t)((is2.x >> (8 * (2 * s + h))) & 0xff), i1 = (int)(int8_t)((is2.y >> (8 * (2 * s + h))) & 0xff);
-                    const float e0 = 16.0f * __fmul_rn(fd.x, (float)i0), e1 = 16.0f * __fmul_rn(fd.y, (float)i1);
-                    #pragma unroll
-                    for (int p = 0; p < NP; p++) {
-                        int cc[4] = {0, 0, 0, 0};
-                        mma_s8_k16(cc, h ? w.z : w.x, h ? w.w : w.y, h ? b[s][p].y : b[s][p].x);
-                        const float v0 = (float)((cc[0] << 8) + cc[1]) * xs[s][p].x;
-                        const float v1 = (float)((cc[2] << 8) + cc[3]) * xs[s][p].x;
-                        acc[r][p][0] = fmaf(v0, e0, acc[r][p][0]);
-                        acc[r][p][1] = fmaf(v1, e1, acc[r][p][1]);
-                    }
-                }
-                if (FMT == LG_FMT_I8M) {
-                    const float m0 = -16.0f * __uint_as_float(s ? mm.z : mm.x), m1 = -16.0f * __uint_as_float(s ? mm.w : mm.y);
-                    #pragma unroll
-                    for (int p = 0; p < NP; p++) {
-                        acc[r][p][0] = fmaf(m0, xs[s][p].y, acc[r][p][0]);
-                        acc[r][p][1] = fmaf(m1, xs[s][p].y, acc[r][p][1]);
-                    }
-                }
-            }
-            continue;
-        }
-        // this lane's 16 bytes: {row g, row g+8} words of sub-block 0, then of sub-block 1
-        const uint4 w = *(const uint4 *)(st + (size_t)(r * P + pp) * 512 + lane * 16);
-        const uint2 sw2 = *(const uint2 *)(st + SC_OFF + (size_t)(r * P + pp) * 64 + g * 8);
-        uint2 dd = make_uint2(0, 0);
-        if (FMT == LG_FMT_Q4_K) dd = *(const uint2 *)(st + DD_OFF + (size_t)(r * P + pp) * 64 + g * 8);
-        #pragma unroll
-        for (int s = 0; s < 2; s++) {
-            const uint32_t wg = s ? w.z : w.x, wh = s ? w.w : w.y, sw = s ? sw2.y : sw2.x;
-            uint32_t a0 = (wg << 4) & 0xF0F0F0F0u, a2 = wg & 0xF0F0F0F0u;
-            uint32_t a1 = (wh << 4) & 0xF0F0F0F0u, a3 = wh & 0xF0F0F0F0u;
-            float d0, d1, m0 = 0.0f, m1 = 0.0f;
-            if (FMT == LG_FMT_Q4_0) {
-                float2 fd = __half22float2(*(const __half2 *)&sw);
-                d0 = fd.x; d1 = fd.y;
-            } else {
-                float2 r0 = __half22float2(*(const __half2 *)&dd.x), r1 = __half22float2(*(const __half2 *)&dd.y);
-                d0 = r0.x * (float)(sw & 0xff); m0 = 16.0f * (8.0f * d0 - r0.y * (float)((sw >> 8) & 0xff));
-                d1 = r1.x * (float)((sw >> 16) & 0xff); m1 = 16.0f * (8.0f * d1 - r1.y * (float)(sw >> 24));
-            }
-            #pragma unroll
-            for (int p = 0; p < NP; p++) {
-                int cc[4] = {0, 0, 0, 0};
-                mma_s8(cc, a0, a1, a2, a3, b[s][p].x, b[s][p].y);
-                float v0 = (float)((cc[0] << 8) + cc[1]) * xs[s][p].x;      // row g,   token 4p+t
-                float v1 = (float)((cc[2] << 8) + cc[3]) * xs[s][p].x;      // row g+8
-                acc[r][p][0] = fmaf(v0, d0, acc[r][p][0]);
-                acc[r][p][1] = fmaf(v1, d1, acc[r][p][1]);
-                if (FMT == LG_FMT_Q4_K) {     // nibbles are stored as (q-8): add back (8 d sc - dmin m) * sum(x)
-                    acc[r][p][0] = fmaf(m0, xs[s][p].y, acc[r][p][0]);
-                    acc[r][p][1] = fmaf(m1, xs[s][p].y, acc[r][p][1]);
-                }
-            }
-        }
-    }
-}
-
 // The small-M matmul.  A CTA walks items = (group of R consecutive row tiles) x (its k slice,
 // blockIdx.y), item after item (blockIdx.x, +gridDim.x, ...).
 //   * One producer thread streams the items' weight tiles HBM -> shared memory with bulk copies
@@ -760,8 +662,92 @@ lg_gemv_kernel(LgGemvArgs a) {
             if (ok && !mbar_wait(full + stage, phase)) { ok = false; if (lane == 0) atomicOr(a.err, LG_ERR_MBAR_TIMEOUT); }
             const int np = min(P, nkp_s - c * P);
             const unsigned char *st = ring + (size_t)stage * STAGE;
-            for (int pp = warp % PW; pp < np; pp += PW)
-                gemv_position<R, NP, FMT>(st, sq, ss, nsb_s, (c * P + pp) * 2, pp, warp, lane, acc);
+            for (int pp = warp % PW; pp < np; pp += PW) {
+                uint2 b[2][NP]; float2 xs[2][NP];
+                #pragma unroll
+                for (int s = 0; s < 2; s++)
+                    #pragma unroll
+                    for (int p = 0; p < NP; p++) {
+                        const int sbl = (c * P + pp) * 2 + s;
+                        b[s][p] = *(const uint2 *)(sq + ((size_t)p * nsb_s + sbl) * 256 + lane * 8);
+                        xs[s][p] = ss[((size_t)p * nsb_s + sbl) * 4 + t];
+                    }
+                #pragma unroll
+                for (int r = 0; r < R; r++) {
+                    if (RS > 1 && (r % RS) != warp / PW) continue;          // another warp's row tile
+                    if (FMT >= LG_FMT_I8) {
+                        // i8 tile: per sub-block this lane's 16 bytes are {row g, row g+8} x {columns 4t.., 16+4t..}; one
+                        // k16 MMA per 16-column group, whose integer scale joins the block's f16 d (x16: the common
+                        // epilogue divides by the 16 the q4 tiles carry)
+                        const unsigned char *tp = st + (size_t)(r * P + pp) * TB;
+                        const uint2 sw2 = *(const uint2 *)(st + SC_OFF + (size_t)(r * P + pp) * 64 + g * 8);
+                        const uint2 is2 = *(const uint2 *)(st + DD_OFF + (size_t)(r * P + pp) * 64 + g * 8);
+                        uint4 mm = make_uint4(0, 0, 0, 0);
+                        if (FMT == LG_FMT_I8M) mm = *(const uint4 *)(st + MM_OFF + (size_t)(r * P + pp) * 128 + g * 16);
+                        #pragma unroll
+                        for (int s = 0; s < 2; s++) {
+                            const uint4 w = *(const uint4 *)(tp + s * 512 + lane * 16);
+                            const float2 fd = __half22float2(*(const __half2 *)(s ? &sw2.y : &sw2.x));
+                            #pragma unroll
+                            for (int h = 0; h < 2; h++) {
+                                const int i0 = (int)(int8_t)((is2.x >> (8 * (2 * s + h))) & 0xff), i1 = (int)(int8_t)((is2.y >> (8 * (2 * s + h))) & 0xff);
+                                const float e0 = 16.0f * __fmul_rn(fd.x, (float)i0), e1 = 16.0f * __fmul_rn(fd.y, (float)i1);
+                                #pragma unroll
+                                for (int p = 0; p < NP; p++) {
+                                    int cc[4] = {0, 0, 0, 0};
+                                    mma_s8_k16(cc, h ? w.z : w.x, h ? w.w : w.y, h ? b[s][p].y : b[s][p].x);
+                                    const float v0 = (float)((cc[0] << 8) + cc[1]) * xs[s][p].x;
+                                    const float v1 = (float)((cc[2] << 8) + cc[3]) * xs[s][p].x;
+                                    acc[r][p][0] = fmaf(v0, e0, acc[r][p][0]);
+                                    acc[r][p][1] = fmaf(v1, e1, acc[r][p][1]);
+                                }
+                            }
+                            if (FMT == LG_FMT_I8M) {
+                                const float m0 = -16.0f * __uint_as_float(s ? mm.z : mm.x), m1 = -16.0f * __uint_as_float(s ? mm.w : mm.y);
+                                #pragma unroll
+                                for (int p = 0; p < NP; p++) {
+                                    acc[r][p][0] = fmaf(m0, xs[s][p].y, acc[r][p][0]);
+                                    acc[r][p][1] = fmaf(m1, xs[s][p].y, acc[r][p][1]);
+                                }
+                            }
+                        }
+                        continue;
+                    }
+                    // this lane's 16 bytes: {row g, row g+8} words of sub-block 0, then of sub-block 1
+                    const uint4 w = *(const uint4 *)(st + (size_t)(r * P + pp) * 512 + lane * 16);
+                    const uint2 sw2 = *(const uint2 *)(st + SC_OFF + (size_t)(r * P + pp) * 64 + g * 8);
+                    uint2 dd = make_uint2(0, 0);
+                    if (FMT == LG_FMT_Q4_K) dd = *(const uint2 *)(st + DD_OFF + (size_t)(r * P + pp) * 64 + g * 8);
+                    #pragma unroll
+                    for (int s = 0; s < 2; s++) {
+                        const uint32_t wg = s ? w.z : w.x, wh = s ? w.w : w.y, sw = s ? sw2.y : sw2.x;
+                        uint32_t a0 = (wg << 4) & 0xF0F0F0F0u, a2 = wg & 0xF0F0F0F0u;
+                        uint32_t a1 = (wh << 4) & 0xF0F0F0F0u, a3 = wh & 0xF0F0F0F0u;
+                        float d0, d1, m0 = 0.0f, m1 = 0.0f;
+                        if (FMT == LG_FMT_Q4_0) {
+                            float2 fd = __half22float2(*(const __half2 *)&sw);
+                            d0 = fd.x; d1 = fd.y;
+                        } else {
+                            float2 r0 = __half22float2(*(const __half2 *)&dd.x), r1 = __half22float2(*(const __half2 *)&dd.y);
+                            d0 = r0.x * (float)(sw & 0xff); m0 = 16.0f * (8.0f * d0 - r0.y * (float)((sw >> 8) & 0xff));
+                            d1 = r1.x * (float)((sw >> 16) & 0xff); m1 = 16.0f * (8.0f * d1 - r1.y * (float)(sw >> 24));
+                        }
+                        #pragma unroll
+                        for (int p = 0; p < NP; p++) {
+                            int cc[4] = {0, 0, 0, 0};
+                            mma_s8(cc, a0, a1, a2, a3, b[s][p].x, b[s][p].y);
+                            float v0 = (float)((cc[0] << 8) + cc[1]) * xs[s][p].x;      // row g,   token 4p+t
+                            float v1 = (float)((cc[2] << 8) + cc[3]) * xs[s][p].x;      // row g+8
+                            acc[r][p][0] = fmaf(v0, d0, acc[r][p][0]);
+                            acc[r][p][1] = fmaf(v1, d1, acc[r][p][1]);
+                            if (FMT == LG_FMT_Q4_K) {     // nibbles are stored as (q-8): add back (8 d sc - dmin m) * sum(x)
+                                acc[r][p][0] = fmaf(m0, xs[s][p].y, acc[r][p][0]);
+                                acc[r][p][1] = fmaf(m1, xs[s][p].y, acc[r][p][1]);
+                            }
+                        }
+                    }
+                }
+            }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty + stage);
             if (++stage == NS) { stage = 0; phase ^= 1; }
