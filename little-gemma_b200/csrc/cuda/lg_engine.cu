@@ -1082,7 +1082,7 @@ void enqueue_forward(Engine *e, const struct kvcache *kv, int M, int flags, int 
     const int *d_toks = e->st->toks, *d_pos = &e->st->pos;
 
     if ((only & C_MISC) && !(flags & F_NOEMBED))
-        launch_k(e, lg_embed_rows, dim3(M), dim3(256), 0, e->head.wq, e->head.ws, e->head.wd, e->head.wm, e->head.fmt, e->head.nkp, e->head.m, d_toks,
+        launch_k(e, lg_embed_rows, dim3(M), dim3(1024), 0, e->head.wq, e->head.ws, e->head.wd, e->head.wm, e->head.fmt, e->head.nkp, e->head.m, d_toks,
                  sqrtf((float)ne), e->x, ne);
     const int total = ple * nl;
     if (e->has_ple) {
@@ -1485,7 +1485,7 @@ void enqueue_draft(Engine *e, DraftW *d, const struct kvcache *kv, int slot, boo
     // below the threshold): its heavy kernels return at once on this word and lg_draft_pick_kernel pads the slot
     const int *skip = chained ? &e->st->stop : nullptr;
     GemvExtra xs_; xs_.skip = skip;
-    launch_k(e, lg_embed_rows, dim3(1), dim3(256), 0, e->head.wq, e->head.ws, e->head.wd, e->head.wm, e->head.fmt, e->head.nkp, e->head.m,
+    launch_k(e, lg_embed_rows, dim3(1), dim3(1024), 0, e->head.wq, e->head.ws, e->head.wd, e->head.wm, e->head.fmt, e->head.nkp, e->head.m,
                                     e->st->toks + (slot - 1), sqrtf((float)nb), d->cat, 2 * nb);
     if (chained) {
         // h_prev = post(x): x still holds the previous draft's normed hidden, p_ni its panel; the matmul writes its row
