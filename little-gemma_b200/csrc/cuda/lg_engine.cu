@@ -1477,7 +1477,7 @@ DraftW *draft_build(Engine *e, struct mtp *t, const struct kvcache *kv) {
 
 // One draft: cat[0:nb] = embed(toks[slot-1]) * sqrt(nb); cat[nb:] = h_prev (first draft) or post(x) (chained);
 // the head's forward; argmax -> st->toks[slot].  Position = st->dpos.
-void enqueue_draft(Engine *e, DraftW *d, const struct kvcache *kv, int slot, bool chained) {
+void enqueue_draft(Engine *e, DraftW *d, const struct kvcache *kv, int slot, bool chained, int set_pos_j = -1) {
     const struct model *m = e->m;
     const struct config *c = &m->cfg;
     const int ni = d->ni, nb = d->nb;
@@ -1485,8 +1485,6 @@ void enqueue_draft(Engine *e, DraftW *d, const struct kvcache *kv, int slot, boo
     // below the threshold): its heavy kernels return at once on this word and lg_draft_pick_kernel pads the slot
     const int *skip = chained ? &e->st->stop : nullptr;
     GemvExtra xs_; xs_.skip = skip;
-    launch_k(e, lg_embed_rows, dim3(1), dim3(1024), 0, e->head.wq, e->head.ws, e->head.wd, e->head.wm, e->head.fmt, e->head.nkp, e->head.m,
-                                    e->st->toks + (slot - 1), sqrtf((float)nb), d->cat, 2 * nb);
     if (chained) {
         // h_prev = post(x): x still holds the previous draft's normed hidden, p_ni its panel; the matmul writes its row
         // straight into the second half of the concatenated input
@@ -1496,18 +1494,23 @@ void enqueue_draft(Engine *e, DraftW *d, const struct kvcache *kv, int slot, boo
             launch_gemv(e, d->post, d->p_ni, 1, d->obuf, LG_EPI_STORE, 1, xs_);
             launch_k(e, lg_copy_f32, dim3((nb + 255) / 256), dim3(256), 0, d->cat + nb, d->obuf, nb);
         }
-    } else {
-        launch_k(e, lg_copy_f32, dim3((nb + 255) / 256), dim3(256), 0, d->cat + nb, e->h_prev, nb);
     }
-    launch_k(e, lg_quant_rows, dim3((2 * nb / 32 + 7) / 8, 1), dim3(256), 0, d->cat, 2 * nb, 2 * nb, d->p_cat);
+    // position, embedding + hidden row -> the pre-projection's panel, rotation tables: one launch
+    {
+        LgDraftBeginArgs b{};
+        b.st = e->st; b.slot = slot; b.set_pos_j = set_pos_j;
+        b.wq = e->head.wq; b.ws = e->head.ws; b.wd = e->head.wd; b.wm = e->head.wm; b.fmt = e->head.fmt; b.nkp = e->head.nkp; b.n_rows = e->head.m;
+        b.scale = sqrtf((float)nb); b.h_src = chained ? nullptr : e->h_prev; b.cat = d->cat; b.nb = nb; b.p_cat = d->p_cat;
+        b.hd_a = d->hd_local; b.base_a = d->base_swa; b.tab_a = d->rope_local; b.hd_b = d->hd_global; b.base_b = d->base_full; b.tab_b = d->rope_global;
+        const int groups = 2 * nb / 32;
+        launch_k(e, lg_draft_begin_kernel, dim3((groups + 7) / 8 + 1), dim3(256), 0, b);
+    }
     if (plan_gemv(e, d->pre, 1, 1, false).ks == 1) {
         launch_gemv(e, d->pre, d->p_cat, 1, d->x, LG_EPI_STORE, 1, xs_);      // straight into the head's residual row
     } else {
         launch_gemv(e, d->pre, d->p_cat, 1, d->obuf, LG_EPI_STORE, 1, xs_);
         launch_k(e, lg_copy_f32, dim3((ni + 255) / 256), dim3(256), 0, d->x, d->obuf, ni);
     }
-    launch_k(e, lg_rope_tables_kernel, dim3(1, 2), dim3(256), 0, (const int *)&e->st->dpos, 1, d->hd_local, d->base_swa, (const float *)nullptr, d->rope_local,
-             d->hd_global, d->base_full, (const float *)nullptr, d->rope_global);
     launch_norm(e, 1, d->x, ni, ni, d->eps, nullptr, 0, 0, 0, nullptr, 1.0f, d->blk[0].attn_norm, &d->p_ni, nullptr, 0, skip);
     for (size_t L = 0; L < d->blk.size(); L++) {
         DraftBlockW &b = d->blk[L];
@@ -1641,8 +1644,7 @@ cudaGraphExec_t round_graph(Engine *e, const struct kvcache *kv, DraftW *d, int 
                     launch_k(e, lg_pad_drafts, dim3(1), dim3(1), 0, e->st, j, n);
                     break;
                 }
-                launch_k(e, lg_set_draft_pos, dim3(1), dim3(1), 0, e->st, j - 1);
-                enqueue_draft(e, d, kv, j, j >= 2);
+                enqueue_draft(e, d, kv, j, j >= 2, j - 1);
             }
         }
         if (replay && n > 1) launch_k(e, lg_replay_drafts_kernel, dim3(1), dim3(32), 0, e->st, n, (const int *)e->replay, (const int *)e->d_n_replay);

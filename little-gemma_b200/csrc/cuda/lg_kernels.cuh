@@ -964,52 +964,47 @@ __global__ void lg_argmax_final(const float *__restrict__ val, const int *__rest
 // ---------------------------------------------------------------------------------------------
 // x[tok][0..ne) = decode(token_embd row toks[tok]) * sqrt(ne) from the TILE-MAJOR copy (the same
 // matrix is the output head).  Bit-identical to decoding the file row: value = d * (nibble-8).
+// Element e of matrix row `row` from the tile-major copy: the file's decode, bit for bit.
+__device__ __forceinline__ float lg_tile_value(const uint4 *__restrict__ wq, const uint2 *__restrict__ ws, const uint2 *__restrict__ wd,
+                                               const uint4 *__restrict__ wm, int fmt, int nkp, int row, int e) {
+    const int rt = row >> 4, r = row & 15, g = r & 7, hi8 = r >> 3;
+    const int kp = e >> 6, s = (e >> 5) & 1, kk = e & 31;
+    const size_t tile = (size_t)rt * nkp + kp;
+    if (fmt >= LG_FMT_I8) {
+        // i8 tiles: value = (d * s) * q - m
+        const int half = kk >> 4, t = (kk & 15) >> 2, i = kk & 3;
+        const int q = ((const int8_t *)wq)[tile * 1024 + (size_t)s * 512 + (g * 4 + t) * 16 + (half * 2 + hi8) * 4 + i];
+        const uint16_t db = ((const uint16_t *)(ws + tile * 8 + g))[s * 2 + hi8];
+        const int sc = ((const int8_t *)(wd + tile * 8 + g))[hi8 * 4 + s * 2 + half];
+        float v = __fmul_rn(__fmul_rn(__half2float(__ushort_as_half(db)), (float)sc), (float)q);
+        if (fmt == LG_FMT_I8M) v = __fsub_rn(v, ((const float *)(wm + tile * 8 + g))[s * 2 + hi8]);
+        return v;
+    }
+    const int t = (kk & 15) >> 2, i = kk & 3;
+    const uint32_t word = ((const uint32_t *)wq)[(tile * 32 + g * 4 + t) * 4 + s * 2 + hi8];
+    const int nib = (word >> (8 * i + (kk >> 4) * 4)) & 15;
+    const int qv = (nib ^ 8) - 8;                               // stored two's complement of (q-8)
+    const uint2 sc = ws[tile * 8 + g];
+    const uint32_t sw = s ? sc.y : sc.x;
+    if (fmt == LG_FMT_Q4_0) {
+        const float d = __half2float(__ushort_as_half((unsigned short)(hi8 ? (sw >> 16) : (sw & 0xffff))));
+        return __fmul_rn(d, (float)qv);
+    }
+    const uint2 dd = wd[tile * 8 + g];
+    const uint32_t dw = hi8 ? dd.y : dd.x;
+    const float d = __half2float(__ushort_as_half((unsigned short)(dw & 0xffff)));
+    const float dmin = __half2float(__ushort_as_half((unsigned short)(dw >> 16)));
+    const uint32_t sm = hi8 ? (sw >> 16) : (sw & 0xffff);
+    return __fsub_rn(__fmul_rn(__fmul_rn(d, (float)(sm & 0xff)), (float)(qv + 8)), __fmul_rn(dmin, (float)(sm >> 8)));
+}
 __global__ void lg_embed_rows(const uint4 *__restrict__ wq, const uint2 *__restrict__ ws, const uint2 *__restrict__ wd,
                               const uint4 *__restrict__ wm, int fmt, int nkp, int n_rows, const int *__restrict__ toks, float scale,
                               float *__restrict__ out, int ldo) {
     pdl_launch(); pdl_wait();
-    int tok = blockIdx.x;
-    int row = min(max(toks[tok], 0), n_rows - 1);               // an out-of-range id must not read outside the table
-    int rt = row >> 4, r = row & 15, g = r & 7, hi8 = r >> 3;
-    const uint32_t *wq32 = (const uint32_t *)wq;
-    if (fmt >= LG_FMT_I8) {
-        // i8 tiles: value = (d * s) * q - m, the file's decode
-        const int8_t *wq8 = (const int8_t *)wq;
-        for (int e = threadIdx.x; e < nkp * 64; e += blockDim.x) {
-            const int kp = e >> 6, s = (e >> 5) & 1, kk = e & 31, half = kk >> 4, t = (kk & 15) >> 2, i = kk & 3;
-            const size_t tile = (size_t)rt * nkp + kp;
-            const int q = wq8[tile * 1024 + (size_t)s * 512 + (g * 4 + t) * 16 + (half * 2 + hi8) * 4 + i];
-            const uint16_t db = ((const uint16_t *)(ws + tile * 8 + g))[s * 2 + hi8];
-            const int sc = ((const int8_t *)(wd + tile * 8 + g))[hi8 * 4 + s * 2 + half];
-            float v = __fmul_rn(__fmul_rn(__half2float(__ushort_as_half(db)), (float)sc), (float)q);
-            if (fmt == LG_FMT_I8M) v = __fsub_rn(v, ((const float *)(wm + tile * 8 + g))[s * 2 + hi8]);
-            out[(size_t)tok * ldo + e] = __fmul_rn(v, scale);
-        }
-        return;
-    }
-    for (int e = threadIdx.x; e < nkp * 64; e += blockDim.x) {
-        int kp = e >> 6, s = (e >> 5) & 1, kk = e & 31;
-        int t = (kk & 15) >> 2, i = kk & 3;
-        size_t tile = (size_t)rt * nkp + kp;
-        uint32_t word = wq32[(tile * 32 + g * 4 + t) * 4 + s * 2 + hi8];
-        int nib = (word >> (8 * i + (kk >> 4) * 4)) & 15;
-        int qv = (nib ^ 8) - 8;                               // stored two's complement of (q-8)
-        uint2 sc = ws[tile * 8 + g];
-        uint32_t sw = s ? sc.y : sc.x;
-        float v;
-        if (fmt == LG_FMT_Q4_0) {
-            float d = __half2float(__ushort_as_half((unsigned short)(hi8 ? (sw >> 16) : (sw & 0xffff))));
-            v = __fmul_rn(d, (float)qv);
-        } else {
-            uint2 dd = wd[tile * 8 + g];
-            uint32_t dw = hi8 ? dd.y : dd.x;
-            float d = __half2float(__ushort_as_half((unsigned short)(dw & 0xffff)));
-            float dmin = __half2float(__ushort_as_half((unsigned short)(dw >> 16)));
-            uint32_t sm = hi8 ? (sw >> 16) : (sw & 0xffff);
-            v = __fsub_rn(__fmul_rn(__fmul_rn(d, (float)(sm & 0xff)), (float)(qv + 8)), __fmul_rn(dmin, (float)(sm >> 8)));
-        }
-        out[(size_t)tok * ldo + e] = __fmul_rn(v, scale);
-    }
+    const int tok = blockIdx.x;
+    const int row = min(max(toks[tok], 0), n_rows - 1);         // an out-of-range id must not read outside the table
+    for (int e = threadIdx.x; e < nkp * 64; e += blockDim.x)
+        out[(size_t)tok * ldo + e] = __fmul_rn(lg_tile_value(wq, ws, wd, wm, fmt, nkp, row, e), scale);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1774,6 +1769,44 @@ __global__ void lg_copy_f32(float *__restrict__ dst, const float *__restrict__ s
     pdl_launch(); pdl_wait();
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) dst[i] = src[i];
+}
+// The start of a draft-head forward in one launch: the position (set_pos_j >= 0: dpos = pos + set_pos_j, the round's stop
+// flag cleared before its first draft), the concatenated input [ embed(toks[slot-1]) * scale , h ] quantised group by group
+// into the pre-projection's panel (h = h_src, or -- h_src null -- what the previous kernel left in cat[nb ..]), and the
+// rotation tables of both layer kinds at the draft's position.  One warp per 32-element group; the last block does the
+// tables.  cat keeps the f32 rows (the chained draft's post-projection writes its half there).
+struct LgDraftBeginArgs {
+    LgRoundState *st; int slot, set_pos_j;
+    const uint4 *wq; const uint2 *ws, *wd; const uint4 *wm; int fmt, nkp, n_rows; float scale;
+    const float *h_src; float *cat; int nb; LgPanel p_cat;
+    int hd_a; float base_a; float2 *tab_a; int hd_b; float base_b; float2 *tab_b;
+};
+__global__ void lg_draft_begin_kernel(LgDraftBeginArgs a) {
+    pdl_launch(); pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int dpos = a.set_pos_j >= 0 ? a.st->pos + a.set_pos_j : a.st->dpos;
+    if (blockIdx.x == gridDim.x - 1) {
+        if (threadIdx.x == 0 && a.set_pos_j >= 0) { a.st->dpos = dpos; if (a.set_pos_j == 0) a.st->stop = 0; }
+        for (int k = 0; k < 2; k++) {
+            const int hd = k ? a.hd_b : a.hd_a, half = hd >> 1;
+            const float base = k ? a.base_b : a.base_a;
+            float2 *tab = k ? a.tab_b : a.tab_a;
+            for (int i = threadIdx.x; i < half; i += blockDim.x) {
+                const float ang = (float)dpos * powf(base, -2.0f * (float)i / (float)hd);
+                tab[i] = make_float2(cosf(ang), sinf(ang));
+            }
+        }
+        return;
+    }
+    const int row = min(max(a.st->toks[a.slot - 1], 0), a.n_rows - 1);
+    for (int gq = blockIdx.x * nw + warp; gq < 2 * a.nb / 32; gq += (gridDim.x - 1) * nw) {
+        const int i = gq * 32 + lane;
+        float v;
+        if (i < a.nb) v = __fmul_rn(lg_tile_value(a.wq, a.ws, a.wd, a.wm, a.fmt, a.nkp, row, i), a.scale);
+        else v = a.h_src ? a.h_src[i - a.nb] : a.cat[i];
+        if (i < a.nb || a.h_src) a.cat[i] = v;
+        quant_group_store(v, lane, 0, gq, a.p_cat);
+    }
 }
 __global__ void lg_set_draft_pos(LgRoundState *st, int j) { pdl_launch(); pdl_wait(); st->dpos = st->pos + j; if (j == 0) st->stop = 0; }
 // slots a head cannot draft repeat the previous token, so the verify simply rejects them
