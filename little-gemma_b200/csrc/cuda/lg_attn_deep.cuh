@@ -91,7 +91,11 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_deep_kernel(LgAttnArg
             qlo[(size_t)qi * LDH + i + HALF] = __float2half_rn(v1[e] - __half2float(h1));
         }
     }
-    for (int r = threadIdx.x; r < nq16; r += LG_ATTN_THREADS) { row_m[r] = -INFINITY; row_l[r] = 0.0f; }
+    for (int r = threadIdx.x; r < nq16; r += LG_ATTN_THREADS) { row_m[r] = -INFINITY; row_l[r] = 0.0f; row_a[r] = 1.0f; }
+    // rows past the last query only pad the 16-row tiles: their probabilities stay zero, the softmax skips them
+    for (int i = threadIdx.x; i < (nq16 - nq) * LDP; i += LG_ATTN_THREADS) {
+        phi[(size_t)nq * LDP + i] = __float2half_rn(0.0f); plo[(size_t)nq * LDP + i] = __float2half_rn(0.0f);
+    }
 
     const int g = lane >> 2, t = lane & 3;
     constexpr int KPW = S / NW;                                  // 8 keys per warp: one 8-key n tile
@@ -132,7 +136,8 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_deep_kernel(LgAttnArg
         #pragma unroll
         for (int mt = 0; mt < MTM; mt++) {
             if (mt >= nmt) break;
-            float c0[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            // four independent chains (first / second 16 dims of a step x hi / lo half of q) instead of one of HD/8 products
+            float c0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, c1[4] = {0.0f, 0.0f, 0.0f, 0.0f}, c2[4] = {0.0f, 0.0f, 0.0f, 0.0f}, c3[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             const __half *qa_hi = qhi + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + (lane >> 4) * 8;
             const __half *qa_lo = qlo + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + (lane >> 4) * 8;
             const __half *kb = sk + (size_t)(warp * KPW + (lane & 7)) * LDH + (lane >> 3) * 8;
@@ -142,9 +147,11 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_deep_kernel(LgAttnArg
                 ldsm_x4(ah, qa_hi + k0); ldsm_x4(al, qa_lo + k0);
                 ldsm_x4(ah2, qa_hi + k0 + 16); ldsm_x4(al2, qa_lo + k0 + 16);
                 ldsm_x4(b, kb + k0);
-                mma_f16(c0, ah, b[0], b[1]); mma_f16(c0, al, b[0], b[1]);
-                mma_f16(c0, ah2, b[2], b[3]); mma_f16(c0, al2, b[2], b[3]);
+                mma_f16(c0, ah, b[0], b[1]); mma_f16(c1, al, b[0], b[1]);
+                mma_f16(c2, ah2, b[2], b[3]); mma_f16(c3, al2, b[2], b[3]);
             }
+            #pragma unroll
+            for (int f = 0; f < 4; f++) c0[f] = (c0[f] + c2[f]) + (c1[f] + c3[f]);
             #pragma unroll
             for (int h2 = 0; h2 < 2; h2++) {
                 const int qi = mt * 16 + g + h2 * 8;
@@ -161,7 +168,7 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_deep_kernel(LgAttnArg
 
         // online softmax, one warp per query row: new running max, the tile's weights against it, the rescale
         // of what was accumulated before (exactly 1 when the tile adds nothing for this row)
-        for (int qi = warp; qi < nq16; qi += NW) {
+        for (int qi = warp; qi < nq; qi += NW) {
             const float s0 = sc[(size_t)qi * S + lane], s1 = sc[(size_t)qi * S + lane + 32];
             const float m_old = row_m[qi];
             const float m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
