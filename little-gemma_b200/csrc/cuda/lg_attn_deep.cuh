@@ -17,7 +17,7 @@
 
 #define LG_DEEP_S 64
 
-// dynamic smem: Qhi | Qlo [NQ16][HD+8] f16 | K [64][HD+8] | V [64][HD+8] | scores [NQ16][64] f32 | Phi | Plo [NQ16][72] f16 | m, l, alpha [NQ16][3]
+// dynamic smem: Qhi | Qlo [NQ16][HD+8] f16 | K [64][HD+8] | V [64][HD+8] | scores 2 x [NQ16][64] f32 | Phi | Plo [NQ16][72] f16 | m, l, alpha [NQ16][3]
 template <int HD, int MTM>      // MTM = 16-row query blocks the CTA carries accumulators for (>= nq16 / 16)
 __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_deep_kernel(LgAttnArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
@@ -44,8 +44,8 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_deep_kernel(LgAttnArg
 
     __half *qhi = (__half *)smem, *qlo = qhi + (size_t)nq16 * LDH;
     __half *sk = qlo + (size_t)nq16 * LDH, *sv = sk + (size_t)S * LDH;
-    float *sc = (float *)(sv + (size_t)S * LDH);
-    __half *phi = (__half *)(sc + (size_t)nq16 * S), *plo = phi + (size_t)nq16 * LDP;
+    float *sc = (float *)(sv + (size_t)S * LDH), *sc2 = sc + (size_t)nq16 * S;    // scores: lower / upper half of the head dims
+    __half *phi = (__half *)(sc2 + (size_t)nq16 * S), *plo = phi + (size_t)nq16 * LDP;
     float *row_m = (float *)(plo + (size_t)nq16 * LDP), *row_l = row_m + nq16, *row_a = row_l + nq16;
 
     constexpr int CH = HD / 8;
@@ -98,13 +98,16 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_deep_kernel(LgAttnArg
     }
 
     const int g = lane >> 2, t = lane & 3;
-    constexpr int KPW = S / NW;                                  // 8 keys per warp: one 8-key n tile
-    constexpr int PVW = HD / 16 < NW ? HD / 16 : NW, DW = HD / PVW, NT = DW / 8;
-    float o[MTM][NT][4];
+    // Both products run "transposed": keys (scores) or head dims (P V) are the 16-row side of the tensor-core tile and
+    // the queries its 8-column side, so a block of up to 8 query rows costs one column tile, not a half-empty 16-row tile.
+    constexpr int MTW = HD / 16 / NW;                            // 16-dim row tiles of O^T per warp
+    static_assert(S == 64 && NW == 8 && HD % (16 * NW) == 0, "four 16-key row tiles x two halves of the head dims over eight warps");
+    const int nq8 = (nq + 7) >> 3;                               // 8-query column tiles (at most 4)
+    float o[MTW][4][4];                                          // O^T accumulators [dim tile][query tile][frag], kept across the span's tiles
     #pragma unroll
-    for (int mt = 0; mt < MTM; mt++)
+    for (int mt = 0; mt < MTW; mt++)
         #pragma unroll
-        for (int n = 0; n < NT; n++) o[mt][n][0] = o[mt][n][1] = o[mt][n][2] = o[mt][n][3] = 0.0f;
+        for (int n = 0; n < 4; n++) o[mt][n][0] = o[mt][n][1] = o[mt][n][2] = o[mt][n][3] = 0.0f;
 
     for (int T = T0; T <= T1; T++) {
         if (T > T0) {
@@ -132,35 +135,44 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_deep_kernel(LgAttnArg
         cp_async_wait_all();
         __syncthreads();
 
-        // scores: warp w takes keys [8w, 8w + 8)
-        #pragma unroll
-        for (int mt = 0; mt < MTM; mt++) {
-            if (mt >= nmt) break;
-            // four independent chains (first / second 16 dims of a step x hi / lo half of q) instead of one of HD/8 products
-            float c0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, c1[4] = {0.0f, 0.0f, 0.0f, 0.0f}, c2[4] = {0.0f, 0.0f, 0.0f, 0.0f}, c3[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            const __half *qa_hi = qhi + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + (lane >> 4) * 8;
-            const __half *qa_lo = qlo + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + (lane >> 4) * 8;
-            const __half *kb = sk + (size_t)(warp * KPW + (lane & 7)) * LDH + (lane >> 3) * 8;
+        // scores S^T = K Q^T: warp w holds keys [16 (w & 3), +16) as the tile's rows and half (w >> 2) of the head dims,
+        // 8 queries per column tile; the two halves land in two buffers the softmax adds
+        {
+            float c0[4][4], c1[4][4];
+            #pragma unroll
+            for (int n = 0; n < 4; n++)
+                #pragma unroll
+                for (int f = 0; f < 4; f++) c0[n][f] = c1[n][f] = 0.0f;
+            const int kt = warp & 3, dh = warp >> 2;
+            const __half *ka_p = sk + (size_t)(kt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + dh * (HD / 2) + (lane >> 4) * 8;
             #pragma unroll 2
-            for (int k0 = 0; k0 < HD; k0 += 32) {
-                uint32_t ah[4], al[4], ah2[4], al2[4], b[4];
-                ldsm_x4(ah, qa_hi + k0); ldsm_x4(al, qa_lo + k0);
-                ldsm_x4(ah2, qa_hi + k0 + 16); ldsm_x4(al2, qa_lo + k0 + 16);
-                ldsm_x4(b, kb + k0);
-                mma_f16(c0, ah, b[0], b[1]); mma_f16(c1, al, b[0], b[1]);
-                mma_f16(c2, ah2, b[2], b[3]); mma_f16(c3, al2, b[2], b[3]);
+            for (int k0 = 0; k0 < HD / 2; k0 += 16) {
+                uint32_t ka[4];                                  // A operand: 16 keys x 16 dims
+                ldsm_x4(ka, ka_p + k0);
+                #pragma unroll
+                for (int n = 0; n < 4; n++) {
+                    if (n >= nq8) break;
+                    uint32_t bq[4];                              // B operands: 8 queries x 16 dims, hi (bq[0..1]) and lo (bq[2..3])
+                    const __half *qp = ((lane >> 4) ? qlo : qhi) + (size_t)(n * 8 + (lane & 7)) * LDH + dh * (HD / 2) + k0 + ((lane >> 3) & 1) * 8;
+                    ldsm_x4(bq, qp);
+                    mma_f16(c0[n], ka, bq[0], bq[1]); mma_f16(c1[n], ka, bq[2], bq[3]);
+                }
             }
+            float *dst = dh ? sc2 : sc;
             #pragma unroll
-            for (int f = 0; f < 4; f++) c0[f] = (c0[f] + c2[f]) + (c1[f] + c3[f]);
-            #pragma unroll
-            for (int h2 = 0; h2 < 2; h2++) {
-                const int qi = mt * 16 + g + h2 * 8;
-                const int pj = pos0 + qi / gqa + a.qpos_off;
-                const int lo = a.window > 0 ? max(0, pj + a.win_shrink - a.window + 1) : 0;
+            for (int n = 0; n < 4; n++) {
+                if (n >= nq8) break;
                 #pragma unroll
                 for (int e = 0; e < 2; e++) {
-                    const int key = warp * KPW + t * 2 + e, p = T * S + key;
-                    sc[(size_t)qi * S + key] = (qi < nq && p >= lo && p <= pj) ? c0[h2 * 2 + e] : -INFINITY;
+                    const int qi = n * 8 + t * 2 + e;
+                    const int pj = pos0 + qi / gqa + a.qpos_off;
+                    const int lo = a.window > 0 ? max(0, pj + a.win_shrink - a.window + 1) : 0;
+                    #pragma unroll
+                    for (int h2 = 0; h2 < 2; h2++) {
+                        const int key = kt * 16 + g + h2 * 8, p = T * S + key;
+                        const float v = c0[n][h2 * 2 + e] + c1[n][h2 * 2 + e];
+                        dst[(size_t)qi * S + key] = (dh || (qi < nq && p >= lo && p <= pj)) ? v : -INFINITY;
+                    }
                 }
             }
         }
@@ -169,7 +181,7 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_deep_kernel(LgAttnArg
         // online softmax, one warp per query row: new running max, the tile's weights against it, the rescale
         // of what was accumulated before (exactly 1 when the tile adds nothing for this row)
         for (int qi = warp; qi < nq; qi += NW) {
-            const float s0 = sc[(size_t)qi * S + lane], s1 = sc[(size_t)qi * S + lane + 32];
+            const float s0 = sc[(size_t)qi * S + lane] + sc2[(size_t)qi * S + lane], s1 = sc[(size_t)qi * S + lane + 32] + sc2[(size_t)qi * S + lane + 32];
             const float m_old = row_m[qi];
             const float m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
             const float e0 = s0 == -INFINITY ? 0.0f : expf(s0 - m_new), e1 = s1 == -INFINITY ? 0.0f : expf(s1 - m_new);
@@ -187,27 +199,35 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_deep_kernel(LgAttnArg
         }
         __syncthreads();
 
-        // O = alpha O + P V: PVW warps split the head dims
-        if (warp < PVW) {
+        // O^T = alpha O^T + V^T P^T: warp w holds MTW tiles of 16 head dims as rows, 8 queries per column tile
+        {
             #pragma unroll
-            for (int mt = 0; mt < MTM; mt++) {
-                if (mt >= nmt) break;
-                const float a0 = row_a[mt * 16 + g], a1 = row_a[mt * 16 + g + 8];
+            for (int n = 0; n < 4; n++) {
+                if (n >= nq8) break;
+                const float a0 = row_a[n * 8 + t * 2], a1 = row_a[n * 8 + t * 2 + 1];
                 #pragma unroll
-                for (int n = 0; n < NT; n++) { o[mt][n][0] *= a0; o[mt][n][1] *= a0; o[mt][n][2] *= a1; o[mt][n][3] *= a1; }
-                const __half *pa_hi = phi + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDP + (lane >> 4) * 8;
-                const __half *pa_lo = plo + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDP + (lane >> 4) * 8;
+                for (int mt = 0; mt < MTW; mt++) { o[mt][n][0] *= a0; o[mt][n][1] *= a1; o[mt][n][2] *= a0; o[mt][n][3] *= a1; }
+            }
+            #pragma unroll
+            for (int k0 = 0; k0 < S; k0 += 32) {
+                uint32_t ph[4][4], pl[4][4];                    // B operands: 8 queries x keys k0, +8, +16, +24 (hi and lo halves of P)
                 #pragma unroll
-                for (int k0 = 0; k0 < S; k0 += 16) {
-                    uint32_t ah[4], al[4];
-                    ldsm_x4(ah, pa_hi + k0); ldsm_x4(al, pa_lo + k0);
-                    const __half *vb = sv + (size_t)(k0 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDH + warp * DW + (lane >> 4) * 8;
+                for (int n = 0; n < 4; n++) {
+                    if (n >= nq8) break;
+                    ldsm_x4(ph[n], phi + (size_t)(n * 8 + (lane & 7)) * LDP + k0 + (lane >> 3) * 8);
+                    ldsm_x4(pl[n], plo + (size_t)(n * 8 + (lane & 7)) * LDP + k0 + (lane >> 3) * 8);
+                }
+                #pragma unroll
+                for (int mt = 0; mt < MTW; mt++) {
+                    const int d0 = (warp * MTW + mt) * 16;
+                    uint32_t va[4], vb[4];                      // A operands (transposed loads): 16 dims x keys k0..k0+15, k0+16..k0+31
+                    ldsm_x4_t(va, sv + (size_t)(k0 + (lane & 7) + (lane >> 4) * 8) * LDH + d0 + ((lane >> 3) & 1) * 8);
+                    ldsm_x4_t(vb, sv + (size_t)(k0 + 16 + (lane & 7) + (lane >> 4) * 8) * LDH + d0 + ((lane >> 3) & 1) * 8);
                     #pragma unroll
-                    for (int n = 0; n < NT; n += 2) {
-                        uint32_t b[4];
-                        ldsm_x4_t(b, vb + n * 8);
-                        mma_f16(o[mt][n], ah, b[0], b[1]); mma_f16(o[mt][n], al, b[0], b[1]);
-                        mma_f16(o[mt][n + 1], ah, b[2], b[3]); mma_f16(o[mt][n + 1], al, b[2], b[3]);
+                    for (int n = 0; n < 4; n++) {
+                        if (n >= nq8) break;
+                        mma_f16(o[mt][n], va, ph[n][0], ph[n][1]); mma_f16(o[mt][n], va, pl[n][0], pl[n][1]);
+                        mma_f16(o[mt][n], vb, ph[n][2], ph[n][3]); mma_f16(o[mt][n], vb, pl[n][2], pl[n][3]);
                     }
                 }
             }
@@ -215,23 +235,22 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_deep_kernel(LgAttnArg
     }
 
     // the span's partial (max, sum, accumulators) of every query row
-    if (warp < PVW) {
+    #pragma unroll
+    for (int n = 0; n < 4; n++) {
+        if (n >= nq8) break;
         #pragma unroll
-        for (int mt = 0; mt < MTM; mt++) {
-            if (mt >= nmt) break;
+        for (int e = 0; e < 2; e++) {
+            const int qi = n * 8 + t * 2 + e;
+            if (qi >= nq) continue;
+            const int tok = qi / gqa, hq = kvh * gqa + qi % gqa;
+            float *pp = a.part + (((size_t)slot * a.M + tok) * a.H + hq) * HD;
             #pragma unroll
-            for (int h2 = 0; h2 < 2; h2++) {
-                const int qi = mt * 16 + g + h2 * 8;
-                if (qi < nq) {
-                    const int tok = qi / gqa, hq = kvh * gqa + qi % gqa;
-                    float *pp = a.part + (((size_t)slot * a.M + tok) * a.H + hq) * HD;
-                    #pragma unroll
-                    for (int n = 0; n < NT; n++)
-                        *(float2 *)(pp + warp * DW + n * 8 + t * 2) = make_float2(o[mt][n][h2 * 2], o[mt][n][h2 * 2 + 1]);
-                    if (warp == 0 && t == 0)
-                        a.part_ml[((size_t)slot * a.M + tok) * a.H + hq] = make_float2(row_m[qi], row_l[qi]);
-                }
+            for (int mt = 0; mt < MTW; mt++) {
+                const int d0 = (warp * MTW + mt) * 16;
+                pp[d0 + g] = o[mt][n][e];
+                pp[d0 + g + 8] = o[mt][n][2 + e];
             }
+            if (warp == 0 && g == 0) a.part_ml[((size_t)slot * a.M + tok) * a.H + hq] = make_float2(row_m[qi], row_l[qi]);
         }
     }
 
@@ -313,5 +332,5 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_deep_kernel(LgAttnArg
 
 inline size_t attn_deep_smem(int nq, int hd) {
     size_t nq16 = (size_t)((nq + 15) & ~15), ldh = hd + 8, S = LG_DEEP_S;
-    return 2 * nq16 * ldh * 2 + 2 * S * ldh * 2 + nq16 * S * 4 + 2 * nq16 * (S + 8) * 2 + nq16 * 12 + 64;
+    return 2 * nq16 * ldh * 2 + 2 * S * ldh * 2 + 2 * nq16 * S * 4 + 2 * nq16 * (S + 8) * 2 + nq16 * 12 + 64;
 }
