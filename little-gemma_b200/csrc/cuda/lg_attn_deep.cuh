@@ -23,6 +23,7 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_deep_kernel(LgAttnArg
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ float s_qn[HD], s_kn[HD];
     pdl_launch();
+    LG_STAMP_KIND(a.tag, 5);
     if (!a.q_ready)
         for (int i = threadIdx.x; i < HD; i += LG_ATTN_THREADS) { s_qn[i] = a.q_norm[i]; s_kn[i] = a.k_norm ? a.k_norm[i] : 1.0f; }
     if (!a.early_kv) pdl_wait();
@@ -112,6 +113,7 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_deep_kernel(LgAttnArg
     for (int T = T0; T <= T1; T++) {
         if (T > T0) {
             __syncthreads();                                     // the previous tile's K, V and P are no longer read
+            if (T == T0 + 2) LG_STAMP(a.tag, 0);
             load_tile(T);
         }
         if (writes_kv) {
@@ -134,6 +136,7 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_deep_kernel(LgAttnArg
         }
         cp_async_wait_all();
         __syncthreads();
+        if (T == T0 + 2) LG_STAMP(a.tag, 1);
 
         // scores S^T = K Q^T: warp w holds keys [16 (w & 3), +16) as the tile's rows and half (w >> 2) of the head dims,
         // 8 queries per column tile; the two halves land in two buffers the softmax adds
@@ -177,6 +180,7 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_deep_kernel(LgAttnArg
             }
         }
         __syncthreads();
+        if (T == T0 + 2) LG_STAMP(a.tag, 2);
 
         // online softmax, one warp per query row: new running max, the tile's weights against it, the rescale
         // of what was accumulated before (exactly 1 when the tile adds nothing for this row)
@@ -198,6 +202,7 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_deep_kernel(LgAttnArg
             }
         }
         __syncthreads();
+        if (T == T0 + 2) LG_STAMP(a.tag, 3);
 
         // O^T = alpha O^T + V^T P^T: warp w holds MTW tiles of 16 head dims as rows, 8 queries per column tile
         {
@@ -232,6 +237,7 @@ __global__ void __launch_bounds__(LG_ATTN_THREADS) lg_attn_deep_kernel(LgAttnArg
                 }
             }
         }
+        if (T == T0 + 2) LG_STAMP(a.tag, 4);
     }
 
     // the span's partial (max, sum, accumulators) of every query row

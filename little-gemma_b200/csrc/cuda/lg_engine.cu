@@ -759,7 +759,7 @@ void launch_attn_deep(Engine *e, LgAttnArgs a, int max_seq, int G) {
     if (n_spans > a.n_slots || (size_t)nq * n_spans * 8 > 2 * (size_t)LG_DEEP_S * (a.hd + 8) * 2 || sm > ATTN_SMEM_MAX || a.Hkv > MAX_KV_HEADS) {
         fprintf(stderr, "lg_b200: %d key spans x %d queries do not fit the span attention kernel\n", n_spans, nq); exit(1);
     }
-    a.tickets = e->tickets; a.G = G;
+    a.tickets = e->tickets; a.G = G; a.tag = (int)e->launches;
     dim3 grid(a.Hkv, n_spans), block(LG_ATTN_THREADS);
     if (a.hd == 256) { if (nmt <= 1) launch_k(e, lg_attn_deep_kernel<256, 1>, grid, block, sm, a); else launch_k(e, lg_attn_deep_kernel<256, 2>, grid, block, sm, a); }
     else             { if (nmt <= 1) launch_k(e, lg_attn_deep_kernel<128, 1>, grid, block, sm, a); else launch_k(e, lg_attn_deep_kernel<128, 2>, grid, block, sm, a); }
